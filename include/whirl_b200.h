@@ -1,0 +1,165 @@
+/*
+ * whirl_b200: the token-sampling hot path of WHIRL for NVIDIA B200 (sm_100a), behind a C ABI.
+ *
+ * Every entry point is stream-ordered and asynchronous unless it says otherwise, never allocates, never throws and
+ * never aborts: it returns a WHIRL_* status, and whirl_last_error() gives a message for the calling thread.  The
+ * caller owns all buffers (device pointers unless a name says host) and passes a workspace sized by
+ * whirl_workspace_bytes().  One CUDA context per GPU; calls on different streams may overlap when their workspaces
+ * differ.  `stream` is a cudaStream_t.  Logits rows are dense: row r starts at x + r * n elements.
+ *
+ * Each declaration names the reference interface it stands in for (paths relative to the reference project).
+ */
+#ifndef WHIRL_B200_H
+#define WHIRL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes (the reference throws hip::Error / std::invalid_argument instead, include/whirl/hip.h:31-40) */
+enum {
+    WHIRL_OK = 0,
+    WHIRL_ERR_INVALID = 1,     /* a bad argument: null pointer, negative size, K out of range ... */
+    WHIRL_ERR_CUDA = 2,        /* a CUDA call failed; whirl_last_error() has its text */
+    WHIRL_ERR_WORKSPACE = 3,   /* workspace missing or too small */
+    WHIRL_ERR_UNSUPPORTED = 4, /* a documented limit was exceeded */
+    WHIRL_ERR_TIMEOUT = 5      /* a bounded device-side wait ran out (reported through the error word) */
+};
+
+/* element type of the logits */
+enum { WHIRL_F32 = 0, WHIRL_BF16 = 1 };
+
+/* per-row outcome written by whirl_sample_rows */
+enum {
+    WHIRL_ROW_DONE = 0,      /* token drawn */
+    WHIRL_ROW_ESCALATE = 1,  /* the kept set may reach past every candidate level this library has (see limits) */
+    WHIRL_ROW_OPEN_TAIL = 2  /* open set whose draw fell past the candidates and the row walk is not available */
+};
+
+/* indices into the counters array of whirl_sample_rows */
+enum {
+    WHIRL_CNT_ESCALATED = 0, /* rows that needed the second candidate level (the reference's Sampler::big_used) */
+    WHIRL_CNT_OPEN_TAIL = 1, /* rows whose draw walked the row in id order (Sampler::full_used) */
+    WHIRL_CNT_UNRESOLVED = 2,/* rows left with a status other than WHIRL_ROW_DONE */
+    WHIRL_CNT_WORDS = 8
+};
+
+/* limits */
+#define WHIRL_MAX_K 16384        /* candidates per row of whirl_topk_rows (the reference's k_big) */
+#define WHIRL_STREAM_MAX_K 1024  /* top_k served by the single-pass kernel; larger values take the multi-pass one */
+#define WHIRL_MAX_HIST 4096      /* history ids per row for the penalties */
+#define WHIRL_Q_WORDS 72         /* i32 words of one draft-distribution entry (include/whirl/spec_sample.h:43) */
+#define WHIRL_Q_MAX 32           /* support of a draft distribution (include/whirl/spec_sample.h:40) */
+#define WHIRL_CTL_WORDS 64       /* i32 words of one sequence's control area (include/whirl/model_types.h:55-61) */
+
+const char* whirl_status_string(int status);
+const char* whirl_last_error(void);
+int whirl_version(void);
+
+/* Bytes of workspace that cover every entry point below for batches of up to `rows` rows of `n` logits. */
+size_t whirl_workspace_bytes(int rows, int n);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Greedy picks.  Same results as the reference kernels: the first index of the maximum.
+ * ---------------------------------------------------------------------------------------------------------------- */
+
+/* argmax(x, n, out, ids, pos, advance): kernels/shared/misc_kv_argmax_kv_store.h:32-42 (launch: src/model/qwen35/
+ * forward/run.cpp:59,66).  out[0] = ids[0] = first max of x[0..n); pos[0] += advance.  ids / pos may be null. */
+int whirl_argmax(const void* x, int dtype, int n, int* out, int* ids, int* pos, int advance, void* ws, size_t ws_bytes,
+                 void* stream);
+
+/* argmax_rows(x, n, out), grid = rows: kernels/shared/sample_pick_set_tokens.h:15-21. */
+int whirl_argmax_rows(const void* x, int dtype, int rows, int n, int* out, void* ws, size_t ws_bytes, void* stream);
+
+/* argmax_rows_to(x, n, out, RowIdx dst): kernels/shared/sample_pick_set_tokens.h:47-53.  out[dst[row]] = first max.
+ * dst is a device array of `rows` ints (the reference passes 32 of them by value). */
+int whirl_argmax_rows_to(const void* x, int dtype, int rows, int n, int* out, const int* dst, void* ws, size_t ws_bytes,
+                         void* stream);
+
+/* argmax_prob(x, n, out_tok, out_prob): kernels/shared/sample_pick_set_tokens.h:96-105; here for `rows` rows:
+ * out_tok[row] = first max, out_prob[row] = 1 / sum exp(x - max). */
+int whirl_argmax_prob(const void* x, int dtype, int rows, int n, int* out_tok, float* out_prob, void* ws, size_t ws_bytes,
+                      void* stream);
+
+/* draft_pick(x, n, tok, prob, ctl, r, n_min, p_min, map): kernels/shared/sample_pick_set_tokens.h:60-86.  Greedy draft r
+ * (through map when given), its probability, and the p-min chain cut-off in ctl[0] (drafts kept) / ctl[1] (stopped). */
+int whirl_draft_pick(const void* x, int dtype, int n, int* tok, float* prob, int* ctl, int r, int n_min, float p_min,
+                     const int* map, void* ws, size_t ws_bytes, void* stream);
+
+/* draft_pick_rows(x, n, ctl_all, RowIdx area, r, n_min, p_min, map): kernels/shared/sample_pick_set_tokens.h:88-92.  Row b
+ * writes into the control area at ctl_all + area[b]: words [16,32) tokens, [32,48) probabilities, 48 / 49 the cut-off.
+ * area is a device array of `rows` ints. */
+int whirl_draft_pick_rows(const void* x, int dtype, int rows, int n, int* ctl_all, const int* area, int r, int n_min,
+                          float p_min, const int* map, void* ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * Candidates.
+ * ---------------------------------------------------------------------------------------------------------------- */
+
+/* topk_rows(x, n, K, inv_t, ids, vals, stats), grid = rows: kernels/shared/sample_cand_topk_rows.h:11-98; the device
+ * seam ServerModel::topkRows (src/server/backend.h:96-99).  ids / vals [rows][K], stats [rows][2] = {max,
+ * sum exp((x - max) * inv_t)}.  The K candidates are exactly the K best by (logit desc, id asc), the order of the
+ * host comparators, and come out in that order (the reference leaves them unordered and fills ties at the K-th logit
+ * in arrival order).  K <= min(n, WHIRL_MAX_K) entries per row are written when K > n.  inv_t_rows (device, may be
+ * null) overrides inv_t per row. */
+int whirl_topk_rows(const void* x, int dtype, int rows, int n, int K, float inv_t, const float* inv_t_rows, int* ids,
+                    float* vals, float* stats, void* ws, size_t ws_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------------
+ * The fused sampler: penalties -> candidates -> top-k / top-p / min-p -> draw, one token per row, all on the device.
+ * It replaces the round trip topk_rows -> download -> sampling::filterCands -> sampling::sampleRow
+ * (src/server/engine_decode.cpp:383-406, src/server/engine_sampling.cpp:51-84, src/sampling/sampler.cpp:15-147).
+ * ---------------------------------------------------------------------------------------------------------------- */
+
+/* Per-row parameters, device arrays of `rows` entries; a null pointer means the default in brackets.  These are the
+ * fields of sampling::Sampler (src/sampling/sampler.h:26-53) that the arithmetic reads. */
+typedef struct whirl_sample_params {
+    const float* inv_t;         /* [1] 1 / temperature */
+    const int32_t* top_k;       /* [0 = off] */
+    const double* top_p;        /* [1] */
+    const double* min_p;        /* [0] */
+    const uint8_t* greedy;      /* [0] non-zero: the token is the row's first maximum (Sampler.greedy requests) */
+    const double* u;            /* [0] uniform in [0,1) of the inverse-CDF draw: Sampler::uniform() of the row's
+                                   (seed, output index), or any host stream such as Philox */
+    const uint64_t* race_key;   /* [null: inverse CDF] spec::raceBase(seed, index): draw by the exponential race */
+    /* penalties (no counterpart in the reference, which ignores them: src/server/engine_start.cpp:70-73) */
+    const int32_t* hist;        /* [null] [rows][hist_stride] token ids, hist_len[row] valid; hist_stride <= WHIRL_MAX_HIST */
+    const int32_t* hist_len;
+    int64_t hist_stride;
+    const float* rep;           /* [1] repetition: l > 0 ? l / rep : l * rep */
+    const float* pres;          /* [0] presence: l -= pres */
+    const float* freq;          /* [0] frequency: l -= freq * count */
+} whirl_sample_params;
+
+/* Outputs, device arrays; only token is required. */
+typedef struct whirl_sample_out {
+    int32_t* token;     /* [rows] */
+    int32_t* status;    /* [rows] WHIRL_ROW_* (may be null) */
+    int32_t* n_kept;    /* [rows] size of the kept set, Sampler.n */
+    int32_t* closed;    /* [rows] Sampler.closed */
+    float* stats;       /* [rows][2] max, sum exp((x - max) * inv_t) of the penalised row */
+    int32_t* kept_ids;  /* [rows][kept_cap] the kept candidates in order, first min(n, kept_cap) */
+    double* kept_p;     /* [rows][kept_cap] their probabilities (renormalised when closed) */
+    int32_t kept_cap;
+    uint32_t* counters; /* [WHIRL_CNT_WORDS] added to, never cleared */
+} whirl_sample_out;
+
+int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sample_params* params,
+                      const whirl_sample_out* out, void* ws, size_t ws_bytes, void* stream);
+
+/* The same call on HOST buffers: logits, parameters and outputs are host pointers; the call copies them to the device
+ * (workspace + staging it allocates on first use and keeps), runs whirl_sample_rows in row chunks that overlap the
+ * copies, copies the outputs back and synchronises.  For callers that hold logits in host memory and for end-to-end
+ * measurement; a serving engine whose logits are already on the device calls whirl_sample_rows. */
+int whirl_sample_rows_host(const void* x_host, int dtype, int rows, int n, const whirl_sample_params* params_host,
+                           const whirl_sample_out* out_host, int device);
+/* Releases what whirl_sample_rows_host keeps. */
+void whirl_host_release(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WHIRL_B200_H */

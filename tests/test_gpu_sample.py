@@ -1,0 +1,154 @@
+"""The fused sampler on the GPU against the oracle and against the fixtures generated from the reference's own code.
+Tokens, kept-set sizes and kept ids must match exactly (a draw within 1e-6 of a cumulative boundary may pick the
+neighbour; such rows are counted); probabilities within 1e-5 relative; the row maximum exactly; the softmax normaliser
+within 1e-5 relative."""
+import numpy as np
+import pytest
+import torch
+
+import synth
+from golden import make_golden as mg
+from gpu_util import bf16_tensor, compare_rows, dev, row_params
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def api():
+    from whirl_llm_b200 import api
+    return api
+
+
+def uniforms(oracle, prm):
+    return np.array([oracle.uniform(int(s), int(p), 0) for s, p in zip(prm["seed"], prm["pos_idx"])])
+
+
+def race_keys(oracle, prm):
+    return np.array([oracle.race_base(int(s), int(p)) for s, p in zip(prm["seed"], prm["pos_idx"])], dtype=np.uint64)
+
+
+def run_split(api, oracle, x, prm, kept_cap, **pen):
+    """GPU sample_rows takes one draw rule per call (race key array or not): run race and non-race rows separately."""
+    u = uniforms(oracle, prm)
+    rk = race_keys(oracle, prm)
+    race = prm.get("race")
+    race = np.zeros(len(u), dtype=np.uint8) if race is None else race
+    out = []
+    for flag in (0, 1):
+        sel = np.nonzero(race == flag)[0]
+        if len(sel) == 0:
+            continue
+        sub = {k: (None if v is None else np.asarray(v)[sel]) for k, v in prm.items()}
+        pp = {k: (None if v is None else np.asarray(v)[sel]) for k, v in pen.items()}
+        res = api.sample_rows(dev(np.ascontiguousarray(x[sel])), row_params(sub, u=u[sel], race_key=rk[sel] if flag else None, **pp),
+                              kept_cap=kept_cap)
+        out.append((sel, res))
+    return out, u
+
+
+def subset(want, sel):
+    return {k: (None if v is None else v[sel]) for k, v in want.items()}
+
+
+def test_small_vocab_mix(api, oracle):
+    R, V = 300, 777
+    x = np.where(np.arange(R)[:, None] % 3 == 0, synth.grid_logits(31, (R, V), 2.0), synth.normalish(32, (R, V), 1.5)).astype(np.float32)
+    prm = mg.row_params(R, 33, 64)
+    # rows with no filter at all are open sets whose draw may walk the row: exercised in test_open_rows
+    open_rows = (prm["top_k"] == 0) & (prm["top_p"] >= 1.0) & (prm["min_p"] <= 0.0) & (prm["greedy"] == 0)
+    prm["top_k"] = np.where(open_rows, 7, prm["top_k"]).astype(np.uint32)
+    want = oracle.sample_rows(x, kept_cap=V, **prm)
+    assert want["full_used"].sum() == 0
+    runs, u = run_split(api, oracle, x, prm, V)
+    for sel, res in runs:
+        compare_rows(res, subset(want, sel), u=u[sel])
+
+
+def test_golden_engine_rows(api, oracle, golden):
+    """The fixture made by the reference's real SampleBuffers / filterCands / sampleRow (V = 20000)."""
+    R, V = mg.ENGINE_ROWS["rows"], mg.ENGINE_ROWS["V"]
+    x = synth.normalish(80, (R, V), 3.0)
+    x[::5] = synth.grid_logits(81, (R, V), 3.0)[::5]
+    x[3] = 0.0
+    prm = mg.row_params(R, 82, 600)
+    g = golden.npz("rows_engine")
+    want = {k: g[k] for k in g.files}
+    # rows the reference resolved on the full row (third escalation level) or by walking the row are outside what the
+    # device path resolves today; they must be REPORTED as unresolved, never answered wrongly
+    runs, u = run_split(api, oracle, x, prm, 1024)
+    seen_unresolved = 0
+    for sel, res in runs:
+        torch.cuda.synchronize()
+        st = res.status.cpu().numpy()
+        hard = want["full_used"][sel] > 0
+        assert ((st != 0) <= hard).all(), "a row the candidate levels can resolve came back unresolved"
+        seen_unresolved += int((st != 0).sum())
+        ok = np.nonzero(st == 0)[0]
+        sub = subset(want, sel[ok])
+        r2 = api.SampleResult(token=res.token[ok], status=res.status[ok], n_kept=res.n_kept[ok], closed=res.closed[ok],
+                              stats=res.stats[ok], kept_ids=res.kept_ids[ok], kept_p=res.kept_p[ok], counters=res.counters)
+        compare_rows(r2, sub, u=u[sel][ok])
+    assert seen_unresolved <= int((want["full_used"] > 0).sum())
+
+
+def test_config2_penalised(api, oracle):
+    """BASELINE config 2 (reduced batch): V 151936, N(0, 2.5^2), 4096-id Zipf history, rep 1.1 / pres 0.5 / freq 0.3,
+    T 0.8, top-k 50, top-p 0.9, min-p 0.05."""
+    R, V, H = 16, 151936, 4096
+    x = synth.normalish(21, (R, V), 2.5)
+    hist = synth.zipf_history(22, R, H, V)
+    hist_len = np.full(R, H, dtype=np.int32)
+    hist_len[1] = 100
+    hist_len[2] = 0
+    f = lambda v, dt=np.float32: np.full(R, v, dtype=dt)
+    prm = dict(inv_t=f(1 / 0.8), top_k=f(50, np.uint32), top_p=f(0.9, np.float64), min_p=f(0.05, np.float64))
+    u = np.array([oracle.philox_uniform(1234, 0, r) for r in range(R)])
+    pen = dict(hist=hist, hist_len=hist_len, rep=f(1.1), pres=f(0.5), freq=f(0.3))
+    want = oracle.sample_rows(x, kept_cap=50, u=u, threads=4, **prm, **{k: (v.astype(np.uint32) if k == "hist_len" else v) for k, v in pen.items()})
+    res = api.sample_rows(dev(x), row_params(prm, u=u, **pen), kept_cap=50)
+    compare_rows(res, want, u=u)
+    # the penalties changed something: the unpenalised run differs in at least one kept set
+    plain = oracle.sample_rows(x, kept_cap=50, u=u, threads=4, **prm)
+    assert any(not np.array_equal(plain["kept_ids"][r], want["kept_ids"][r]) for r in range(R))
+
+
+def test_config1_draws(api, oracle):
+    """BASELINE config 1: one row, V 151936, 20 boosted ids, greedy + T 0.7 / top-k 40 / top-p 0.95, successive draws."""
+    V, draws = 151936, 200
+    x = synth.normalish(1234, (1, V), 3.0)
+    x[0, (np.arange(20) * 7573 + 11) % V] += 15.0
+    xs = np.repeat(x, draws, axis=0)
+    f = lambda v, dt=np.float32: np.full(draws, v, dtype=dt)
+    prm = dict(inv_t=f(1 / 0.7), top_k=f(40, np.uint32), top_p=f(0.95, np.float64))
+    for src in ("splitmix", "philox"):
+        u = np.array([oracle.uniform(1234, i, 0) if src == "splitmix" else oracle.philox_uniform(1234, i, 0) for i in range(draws)])
+        want = oracle.sample_rows(xs, kept_cap=40, u=u, threads=4, **prm)
+        res = api.sample_rows(dev(xs), row_params(prm, u=u), kept_cap=40)
+        compare_rows(res, want, u=u)
+    g = api.sample_rows(dev(x), row_params(dict(greedy=np.ones(1, dtype=np.uint8))))
+    assert g.token.item() == oracle.first_max(x[0])
+
+
+def test_config4_bf16_mix(api, oracle):
+    """BASELINE config 4 (reduced batch): bf16, V 262144, 1% of entries +10, 25% greedy, T U[0.5,1.2], top-k U{1..1024},
+    top-p U[0.8,1]."""
+    R, V = 24, 262144
+    x = synth.normalish(41, (R, V), 3.0)
+    x[synth.hash_u01(42, R * V, 1).reshape(R, V) < 0.01] += 10.0
+    bits = synth.to_bf16_bits(x)
+    u8 = synth.hash_u01(43, R * 4, 2).reshape(R, 4)
+    prm = dict(inv_t=(1.0 / (0.5 + 0.7 * u8[:, 0])).astype(np.float32), top_k=(1 + (u8[:, 1] * 1024).astype(np.uint32)).astype(np.uint32),
+               top_p=0.8 + 0.2 * u8[:, 2], greedy=(u8[:, 3] < 0.25).astype(np.uint8))
+    u = synth.hash_u01(44, R, 3)
+    want = oracle.sample_rows(bits, kept_cap=1024, u=u, threads=4, **prm)
+    res = api.sample_rows(bf16_tensor(bits), row_params(prm, u=u), kept_cap=1024)
+    compare_rows(res, want, u=u)
+
+
+def test_argument_errors(api):
+    x = torch.zeros((2, 64), device="cuda")
+    with pytest.raises(api.WhirlError) as e:
+        api.sample_rows(x, api.RowParams(), ws=torch.zeros(16, dtype=torch.uint8, device="cuda"))
+    assert e.value.status == 3
+    with pytest.raises(ValueError):
+        api.sample_rows(torch.zeros((2, 64)), api.RowParams())

@@ -1,0 +1,254 @@
+"""ctypes bindings of libwhirl_b200.so over torch tensors (device memory and streams only; all arithmetic is in the
+library).  Function names and argument meaning follow include/whirl_b200.h, which follows the reference's kernel and
+ServerModel interfaces."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libwhirl_b200.so")
+
+F32, BF16 = 0, 1
+ROW_DONE, ROW_ESCALATE, ROW_OPEN_TAIL = 0, 1, 2
+CNT_ESCALATED, CNT_OPEN_TAIL, CNT_UNRESOLVED, CNT_WORDS = 0, 1, 2, 8
+MAX_K, STREAM_MAX_K, MAX_HIST, Q_WORDS, Q_MAX, CTL_WORDS = 16384, 1024, 4096, 72, 32, 64
+
+
+class WhirlError(RuntimeError):
+    def __init__(self, status: int, msg: str):
+        super().__init__(f"whirl_b200 status {status}: {msg}")
+        self.status = status
+
+
+class SampleParams(C.Structure):
+    _fields_ = [("inv_t", C.c_void_p), ("top_k", C.c_void_p), ("top_p", C.c_void_p), ("min_p", C.c_void_p),
+                ("greedy", C.c_void_p), ("u", C.c_void_p), ("race_key", C.c_void_p), ("hist", C.c_void_p),
+                ("hist_len", C.c_void_p), ("hist_stride", C.c_int64), ("rep", C.c_void_p), ("pres", C.c_void_p),
+                ("freq", C.c_void_p)]
+
+
+class SampleOut(C.Structure):
+    _fields_ = [("token", C.c_void_p), ("status", C.c_void_p), ("n_kept", C.c_void_p), ("closed", C.c_void_p),
+                ("stats", C.c_void_p), ("kept_ids", C.c_void_p), ("kept_p", C.c_void_p), ("kept_cap", C.c_int32),
+                ("counters", C.c_void_p)]
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(f"{LIB_PATH} is missing: build it with `python -m whirl_llm_b200.build` "
+                          "(there is no fallback implementation)")
+    lib = C.CDLL(LIB_PATH)
+    vp, i, f, sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+    sigs = {
+        "whirl_status_string": (C.c_char_p, [i]),
+        "whirl_last_error": (C.c_char_p, []),
+        "whirl_version": (i, []),
+        "whirl_workspace_bytes": (sz, [i, i]),
+        "whirl_argmax": (i, [vp, i, i, vp, vp, vp, i, vp, sz, vp]),
+        "whirl_argmax_rows": (i, [vp, i, i, i, vp, vp, sz, vp]),
+        "whirl_argmax_rows_to": (i, [vp, i, i, i, vp, vp, vp, sz, vp]),
+        "whirl_argmax_prob": (i, [vp, i, i, i, vp, vp, vp, sz, vp]),
+        "whirl_draft_pick": (i, [vp, i, i, vp, vp, vp, i, i, f, vp, vp, sz, vp]),
+        "whirl_draft_pick_rows": (i, [vp, i, i, i, vp, vp, i, i, f, vp, vp, sz, vp]),
+        "whirl_topk_rows": (i, [vp, i, i, i, i, f, vp, vp, vp, vp, vp, sz, vp]),
+        "whirl_sample_rows": (i, [vp, i, i, i, C.POINTER(SampleParams), C.POINTER(SampleOut), vp, sz, vp]),
+        "whirl_sample_rows_host": (i, [vp, i, i, i, C.POINTER(SampleParams), C.POINTER(SampleOut), i]),
+        "whirl_host_release": (None, []),
+    }
+    for name, (res, args) in sigs.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    return lib
+
+
+lib = _load()
+DECLARED = ["whirl_status_string", "whirl_last_error", "whirl_version", "whirl_workspace_bytes", "whirl_argmax",
+            "whirl_argmax_rows", "whirl_argmax_rows_to", "whirl_argmax_prob", "whirl_draft_pick", "whirl_draft_pick_rows",
+            "whirl_topk_rows", "whirl_sample_rows", "whirl_sample_rows_host", "whirl_host_release"]
+
+
+def _check(status: int):
+    if status != 0:
+        raise WhirlError(status, (lib.whirl_last_error() or b"").decode())
+
+
+def _dtype(x: torch.Tensor) -> int:
+    if x.dtype == torch.float32:
+        return F32
+    if x.dtype == torch.bfloat16:
+        return BF16
+    raise TypeError(f"logits must be float32 or bfloat16, got {x.dtype}")
+
+
+def _rows(x: torch.Tensor):
+    if not x.is_cuda:
+        raise ValueError("logits must be on a CUDA device (this library has no CPU path)")
+    if x.dim() == 1:
+        x = x.unsqueeze(0)
+    if x.dim() != 2 or x.stride(1) != 1 or (x.shape[0] > 1 and x.stride(0) != x.shape[1]):
+        raise ValueError("logits must be dense rows [rows, n]")
+    return x, x.shape[0], x.shape[1]
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(x: torch.Tensor):
+    return torch.cuda.current_stream(x.device).cuda_stream
+
+
+def workspace_bytes(rows: int, n: int) -> int:
+    return lib.whirl_workspace_bytes(rows, n)
+
+
+_ws_cache: dict = {}
+
+
+def workspace(rows: int, n: int, device) -> torch.Tensor:
+    """A cached workspace tensor for (rows, n) on `device` (callers that manage memory pass their own)."""
+    device = torch.device(device)
+    need = workspace_bytes(rows, n)
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    ws = _ws_cache.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=device)
+        _ws_cache[key] = ws
+    return ws
+
+
+def argmax(x, out=None, ids=None, pos=None, advance=0, ws=None):
+    x, rows, n = _rows(x)
+    assert rows == 1
+    out = torch.empty(1, dtype=torch.int32, device=x.device) if out is None else out
+    ws = workspace(1, n, x.device) if ws is None else ws
+    _check(lib.whirl_argmax(x.data_ptr(), _dtype(x), n, out.data_ptr(), _p(ids), _p(pos), advance, ws.data_ptr(), ws.numel(),
+                            _stream(x)))
+    return out
+
+
+def argmax_rows(x, out=None, ws=None):
+    x, rows, n = _rows(x)
+    out = torch.empty(rows, dtype=torch.int32, device=x.device) if out is None else out
+    ws = workspace(rows, n, x.device) if ws is None else ws
+    _check(lib.whirl_argmax_rows(x.data_ptr(), _dtype(x), rows, n, out.data_ptr(), ws.data_ptr(), ws.numel(), _stream(x)))
+    return out
+
+
+def argmax_rows_to(x, out, dst, ws=None):
+    x, rows, n = _rows(x)
+    ws = workspace(rows, n, x.device) if ws is None else ws
+    _check(lib.whirl_argmax_rows_to(x.data_ptr(), _dtype(x), rows, n, out.data_ptr(), dst.data_ptr(), ws.data_ptr(), ws.numel(),
+                                    _stream(x)))
+    return out
+
+
+def argmax_prob(x, ws=None):
+    x, rows, n = _rows(x)
+    tok = torch.empty(rows, dtype=torch.int32, device=x.device)
+    prob = torch.empty(rows, dtype=torch.float32, device=x.device)
+    ws = workspace(rows, n, x.device) if ws is None else ws
+    _check(lib.whirl_argmax_prob(x.data_ptr(), _dtype(x), rows, n, tok.data_ptr(), prob.data_ptr(), ws.data_ptr(), ws.numel(),
+                                 _stream(x)))
+    return tok, prob
+
+
+def draft_pick(x, tok, prob, ctl, r, n_min, p_min, vmap=None, ws=None):
+    x, rows, n = _rows(x)
+    assert rows == 1
+    ws = workspace(1, n, x.device) if ws is None else ws
+    _check(lib.whirl_draft_pick(x.data_ptr(), _dtype(x), n, tok.data_ptr(), prob.data_ptr(), ctl.data_ptr(), r, n_min, p_min,
+                                _p(vmap), ws.data_ptr(), ws.numel(), _stream(x)))
+
+
+def draft_pick_rows(x, ctl_all, area, r, n_min, p_min, vmap=None, ws=None):
+    x, rows, n = _rows(x)
+    ws = workspace(rows, n, x.device) if ws is None else ws
+    _check(lib.whirl_draft_pick_rows(x.data_ptr(), _dtype(x), rows, n, ctl_all.data_ptr(), area.data_ptr(), r, n_min, p_min,
+                                     _p(vmap), ws.data_ptr(), ws.numel(), _stream(x)))
+
+
+def topk_rows(x, K, inv_t=1.0, inv_t_rows=None, ws=None):
+    """ids [rows, K] i32, vals [rows, K] f32, stats [rows, 2] f32 (ServerModel::topkRows)."""
+    x, rows, n = _rows(x)
+    ids = torch.full((rows, K), -1, dtype=torch.int32, device=x.device)
+    vals = torch.zeros((rows, K), dtype=torch.float32, device=x.device)
+    stats = torch.zeros((rows, 2), dtype=torch.float32, device=x.device)
+    ws = workspace(rows, n, x.device) if ws is None else ws
+    _check(lib.whirl_topk_rows(x.data_ptr(), _dtype(x), rows, n, K, float(inv_t), _p(inv_t_rows), ids.data_ptr(), vals.data_ptr(),
+                               stats.data_ptr(), ws.data_ptr(), ws.numel(), _stream(x)))
+    return ids, vals, stats
+
+
+@dataclass
+class RowParams:
+    """Device tensors of per-row sampler settings (None = the library default)."""
+    inv_t: Optional[torch.Tensor] = None      # float32
+    top_k: Optional[torch.Tensor] = None      # int32
+    top_p: Optional[torch.Tensor] = None      # float64
+    min_p: Optional[torch.Tensor] = None      # float64
+    greedy: Optional[torch.Tensor] = None     # uint8
+    u: Optional[torch.Tensor] = None          # float64
+    race_key: Optional[torch.Tensor] = None   # int64 holding the uint64 bit pattern
+    hist: Optional[torch.Tensor] = None       # int32 [rows, H]
+    hist_len: Optional[torch.Tensor] = None   # int32
+    rep: Optional[torch.Tensor] = None        # float32
+    pres: Optional[torch.Tensor] = None       # float32
+    freq: Optional[torch.Tensor] = None       # float32
+
+    _DT = dict(inv_t=torch.float32, top_k=torch.int32, top_p=torch.float64, min_p=torch.float64, greedy=torch.uint8,
+               u=torch.float64, race_key=torch.int64, hist=torch.int32, hist_len=torch.int32, rep=torch.float32,
+               pres=torch.float32, freq=torch.float32)
+
+    def struct(self, rows: int) -> SampleParams:
+        s = SampleParams()
+        for k, dt in self._DT.items():
+            t = getattr(self, k)
+            if t is not None:
+                if t.dtype != dt or not t.is_cuda or not t.is_contiguous():
+                    raise TypeError(f"{k}: want a contiguous CUDA tensor of {dt}, got {t.dtype} on {t.device}")
+                if k != "hist" and t.shape != (rows,):
+                    raise ValueError(f"{k}: want shape ({rows},), got {tuple(t.shape)}")
+                if k == "hist" and (t.dim() != 2 or t.shape[0] != rows):
+                    raise ValueError(f"hist: want [rows, H], got {tuple(t.shape)}")
+            setattr(s, k, _p(t))
+        s.hist_stride = 0 if self.hist is None else self.hist.shape[1]
+        return s
+
+
+@dataclass
+class SampleResult:
+    token: torch.Tensor
+    status: torch.Tensor
+    n_kept: torch.Tensor
+    closed: torch.Tensor
+    stats: torch.Tensor
+    kept_ids: Optional[torch.Tensor]
+    kept_p: Optional[torch.Tensor]
+    counters: torch.Tensor
+
+
+def sample_rows(x, params: RowParams, kept_cap: int = 0, ws=None, result: Optional[SampleResult] = None) -> SampleResult:
+    """One token per row: penalties -> candidates -> top-k / top-p / min-p -> draw (whirl_sample_rows)."""
+    x, rows, n = _rows(x)
+    dev = x.device
+    if result is None:
+        result = SampleResult(
+            token=torch.empty(rows, dtype=torch.int32, device=dev), status=torch.empty(rows, dtype=torch.int32, device=dev),
+            n_kept=torch.empty(rows, dtype=torch.int32, device=dev), closed=torch.empty(rows, dtype=torch.int32, device=dev),
+            stats=torch.empty((rows, 2), dtype=torch.float32, device=dev),
+            kept_ids=torch.full((rows, kept_cap), -1, dtype=torch.int32, device=dev) if kept_cap else None,
+            kept_p=torch.zeros((rows, kept_cap), dtype=torch.float64, device=dev) if kept_cap else None,
+            counters=torch.zeros(CNT_WORDS, dtype=torch.int32, device=dev))
+    o = SampleOut(token=_p(result.token), status=_p(result.status), n_kept=_p(result.n_kept), closed=_p(result.closed),
+                  stats=_p(result.stats), kept_ids=_p(result.kept_ids), kept_p=_p(result.kept_p),
+                  kept_cap=0 if result.kept_ids is None else result.kept_ids.shape[1], counters=_p(result.counters))
+    ws = workspace(rows, n, dev) if ws is None else ws
+    ps = params.struct(rows)
+    _check(lib.whirl_sample_rows(x.data_ptr(), _dtype(x), rows, n, C.byref(ps), C.byref(o), ws.data_ptr(), ws.numel(), _stream(x)))
+    return result

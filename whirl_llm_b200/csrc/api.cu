@@ -1,0 +1,247 @@
+// The C ABI of the library (include/whirl_b200.h): argument checks, workspace carving, launches.  No allocation and no
+// synchronisation here, except in whirl_sample_rows_host, which owns its staging.
+#include "../../include/whirl_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "kernels.h"
+#include "tail.cuh"
+
+namespace {
+
+thread_local std::string g_err;
+
+int fail(int code, const char* msg) {
+    g_err = msg;
+    return code;
+}
+int fail_cuda(cudaError_t e, const char* where) {
+    g_err = std::string(where) + ": " + cudaGetErrorString(e);
+    return WHIRL_ERR_CUDA;
+}
+
+int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        cached[dev] = v;
+    }
+    return cached[dev];
+}
+
+constexpr int kMaxSplits = 64;
+constexpr int kSmBound = 256;  // upper bound on SMs used when sizing the workspace
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// workspace layout (all offsets 256-byte aligned)
+struct Ws {
+    size_t off_scan, off_status, off_list, off_count, off_err, off_p, total;
+};
+Ws ws_layout(int rows) {
+    Ws w;
+    size_t o = 0;
+    w.off_scan = o;
+    o = align_up(o + wb::rowscan_ws_bytes(rows, kMaxSplits), 256);
+    w.off_status = o;
+    o = align_up(o + size_t(rows) * 4, 256);
+    w.off_list = o;
+    o = align_up(o + size_t(rows) * 4, 256);
+    w.off_count = o;
+    o = align_up(o + 16, 256);
+    w.off_err = o;
+    o = align_up(o + 16, 256);
+    w.off_p = o;
+    o = align_up(o + wb::select_generic_ws_bytes(std::min(rows, 2 * kSmBound), wb::kGenericMaxK), 256);
+    w.total = o;
+    return w;
+}
+
+bool bad_dtype(int d) { return d != WHIRL_F32 && d != WHIRL_BF16; }
+
+// rows flagged with `want` -> list, count (one CTA; rows is at most a few thousand)
+__global__ void gather_rows_kernel(const int32_t* status, int rows, int want, int32_t* list, int32_t* count) {
+    __shared__ int s_n;
+    if (threadIdx.x == 0) s_n = 0;
+    __syncthreads();
+    for (int base = 0; base < rows; base += blockDim.x) {
+        const int r = base + threadIdx.x;
+        const bool f = r < rows && status[r] == want;
+        // order inside the list does not matter: rows are independent
+        if (f) list[atomicAdd(&s_n, 1)] = r;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *count = s_n;
+}
+
+__global__ void count_unresolved_kernel(const int32_t* status, int rows, uint32_t* counters) {
+    int c = 0;
+    for (int r = threadIdx.x; r < rows; r += blockDim.x) c += status[r] != wb::ROW_DONE;
+    c = int(wb::warp_sum(uint32_t(c)));
+    if ((threadIdx.x & 31) == 0 && c) atomicAdd(&counters[WHIRL_CNT_UNRESOLVED], uint32_t(c));
+}
+
+int scan_call(int mode, const void* x, int dtype, int rows, int n, wb::RowScanArgs a, void* ws, size_t ws_bytes, void* stream) {
+    if (!x || rows < 0 || n <= 0 || bad_dtype(dtype)) return fail(WHIRL_ERR_INVALID, "rowscan: bad x / rows / n / dtype");
+    if (rows == 0) return WHIRL_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int splits = wb::rowscan_splits(rows, n, sm_count());
+    if (splits > kMaxSplits) splits = kMaxSplits;
+    if (splits > 1) {
+        const size_t need = wb::rowscan_ws_bytes(rows, splits);
+        if (!ws || ws_bytes < need) return fail(WHIRL_ERR_WORKSPACE, "rowscan: workspace missing or too small");
+        // the tickets start at zero; the last CTA of each row puts them back, this covers a first use
+        const cudaError_t e = cudaMemsetAsync(ws, 0, size_t((rows + 3) & ~3) * sizeof(int), st);
+        if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync");
+    }
+    a.x = x, a.n = n, a.ws = ws;
+    const cudaError_t e = wb::rowscan_launch(a, dtype, mode, rows, splits, st);
+    return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "rowscan launch");
+}
+
+}  // namespace
+
+#pragma GCC visibility push(default)
+extern "C" {
+
+const char* whirl_status_string(int s) {
+    switch (s) {
+    case WHIRL_OK: return "ok";
+    case WHIRL_ERR_INVALID: return "invalid argument";
+    case WHIRL_ERR_CUDA: return "CUDA error";
+    case WHIRL_ERR_WORKSPACE: return "workspace missing or too small";
+    case WHIRL_ERR_UNSUPPORTED: return "outside a documented limit";
+    case WHIRL_ERR_TIMEOUT: return "device-side wait ran out";
+    }
+    return "?";
+}
+const char* whirl_last_error(void) { return g_err.c_str(); }
+int whirl_version(void) { return 100; }
+
+size_t whirl_workspace_bytes(int rows, int n) {
+    (void)n;
+    return ws_layout(rows < 1 ? 1 : rows).total;
+}
+
+int whirl_argmax(const void* x, int dtype, int n, int* out, int* ids, int* pos, int advance, void* ws, size_t ws_bytes,
+                 void* stream) {
+    if (!out) return fail(WHIRL_ERR_INVALID, "argmax: out is null");
+    wb::RowScanArgs a{};
+    a.out = out, a.ids = ids, a.pos = pos, a.advance = advance;
+    return scan_call(wb::RS_ARGMAX, x, dtype, 1, n, a, ws, ws_bytes, stream);
+}
+int whirl_argmax_rows(const void* x, int dtype, int rows, int n, int* out, void* ws, size_t ws_bytes, void* stream) {
+    if (!out) return fail(WHIRL_ERR_INVALID, "argmax_rows: out is null");
+    wb::RowScanArgs a{};
+    a.out = out;
+    return scan_call(wb::RS_ARGMAX, x, dtype, rows, n, a, ws, ws_bytes, stream);
+}
+int whirl_argmax_rows_to(const void* x, int dtype, int rows, int n, int* out, const int* dst, void* ws, size_t ws_bytes,
+                         void* stream) {
+    if (!out || !dst) return fail(WHIRL_ERR_INVALID, "argmax_rows_to: out / dst is null");
+    wb::RowScanArgs a{};
+    a.out = out, a.dst = dst;
+    return scan_call(wb::RS_ARGMAX, x, dtype, rows, n, a, ws, ws_bytes, stream);
+}
+int whirl_argmax_prob(const void* x, int dtype, int rows, int n, int* out_tok, float* out_prob, void* ws, size_t ws_bytes,
+                      void* stream) {
+    if (!out_tok || !out_prob) return fail(WHIRL_ERR_INVALID, "argmax_prob: out is null");
+    wb::RowScanArgs a{};
+    a.out = out_tok, a.prob = out_prob;
+    return scan_call(wb::RS_ARGMAX_PROB, x, dtype, rows, n, a, ws, ws_bytes, stream);
+}
+int whirl_draft_pick(const void* x, int dtype, int n, int* tok, float* prob, int* ctl, int r, int n_min, float p_min,
+                     const int* map, void* ws, size_t ws_bytes, void* stream) {
+    if (!tok || !prob || !ctl || r < 0) return fail(WHIRL_ERR_INVALID, "draft_pick: tok / prob / ctl is null or r < 0");
+    wb::RowScanArgs a{};
+    a.tok = tok, a.prob = prob, a.ctl = ctl, a.r = r, a.n_min = n_min, a.p_min = p_min, a.map = map;
+    return scan_call(wb::RS_DRAFT_PICK, x, dtype, 1, n, a, ws, ws_bytes, stream);
+}
+int whirl_draft_pick_rows(const void* x, int dtype, int rows, int n, int* ctl_all, const int* area, int r, int n_min,
+                          float p_min, const int* map, void* ws, size_t ws_bytes, void* stream) {
+    if (!ctl_all || !area || r < 0 || r >= 16) return fail(WHIRL_ERR_INVALID, "draft_pick_rows: ctl_all / area is null or r outside [0,16)");
+    wb::RowScanArgs a{};
+    a.ctl_all = ctl_all, a.area = area, a.r = r, a.n_min = n_min, a.p_min = p_min, a.map = map;
+    return scan_call(wb::RS_DRAFT_PICK, x, dtype, rows, n, a, ws, ws_bytes, stream);
+}
+
+int whirl_topk_rows(const void* x, int dtype, int rows, int n, int K, float inv_t, const float* inv_t_rows, int* ids,
+                    float* vals, float* stats, void* ws, size_t ws_bytes, void* stream) {
+    if (!x || !ids || !vals || !stats || rows < 0 || n <= 0 || bad_dtype(dtype)) return fail(WHIRL_ERR_INVALID, "topk_rows: bad pointer / rows / n / dtype");
+    if (K < 1) return fail(WHIRL_ERR_INVALID, "topk_rows: K < 1");
+    if (K > WHIRL_MAX_K) return fail(WHIRL_ERR_UNSUPPORTED, "topk_rows: K above WHIRL_MAX_K");
+    if (rows == 0) return WHIRL_OK;
+    (void)ws, (void)ws_bytes;
+    wb::SelectArgs a{};
+    a.x = x, a.rows = rows, a.n = n, a.mode = wb::MODE_TOPK, a.K = K, a.ids = ids, a.vals = vals, a.stats = stats;
+    a.prm.inv_t = inv_t_rows, a.prm.inv_t_scalar = inv_t;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (wb::sample_stream_supported(a, dtype)) e = wb::sample_stream_launch(a, dtype, sm_count(), st);
+    else e = wb::select_generic_launch(a, dtype, sm_count(), st);
+    return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "topk_rows launch");
+}
+
+int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sample_params* prm, const whirl_sample_out* out,
+                      void* ws, size_t ws_bytes, void* stream) {
+    if (!x || !prm || !out || !out->token || rows < 0 || n <= 0 || bad_dtype(dtype)) return fail(WHIRL_ERR_INVALID, "sample_rows: bad pointer / rows / n / dtype");
+    if (rows == 0) return WHIRL_OK;
+    const Ws w = ws_layout(rows);
+    if (!ws || ws_bytes < w.total) return fail(WHIRL_ERR_WORKSPACE, "sample_rows: workspace missing or too small (whirl_workspace_bytes)");
+    if (prm->hist) {
+        if (!prm->hist_len) return fail(WHIRL_ERR_INVALID, "sample_rows: hist without hist_len");
+        if (prm->hist_stride < 0 || prm->hist_stride > WHIRL_MAX_HIST) return fail(WHIRL_ERR_UNSUPPORTED, "sample_rows: hist_stride above WHIRL_MAX_HIST");
+        if (uint32_t(n) > (1u << 19) - 1) return fail(WHIRL_ERR_UNSUPPORTED, "sample_rows: penalties need n < 2^19");
+    }
+    if (out->kept_cap < 0) return fail(WHIRL_ERR_INVALID, "sample_rows: kept_cap < 0");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    wb::SelectArgs a{};
+    a.x = x, a.rows = rows, a.n = n, a.mode = wb::MODE_SAMPLE;
+    a.prm.inv_t = prm->inv_t, a.prm.inv_t_scalar = 1.f, a.prm.top_k = prm->top_k, a.prm.top_p = prm->top_p, a.prm.min_p = prm->min_p;
+    a.prm.greedy = prm->greedy, a.prm.u = prm->u, a.prm.race_key = prm->race_key;
+    a.prm.hist = prm->hist, a.prm.hist_len = prm->hist_len, a.prm.hist_stride = prm->hist_stride;
+    a.prm.rep = prm->rep, a.prm.pres = prm->pres, a.prm.freq = prm->freq;
+    a.out.token = out->token, a.out.n_kept = out->n_kept, a.out.closed = out->closed, a.out.stats = out->stats;
+    a.out.kept_ids = out->kept_ids, a.out.kept_p = out->kept_p, a.out.kept_cap = out->kept_cap, a.out.counters = out->counters;
+    a.out.status = out->status ? out->status : reinterpret_cast<int32_t*>(base + w.off_status);
+    a.ws = base + w.off_p;
+    a.err = reinterpret_cast<uint32_t*>(base + w.off_err);
+    // level 1: top_k candidates (the set closes there), or 256 of them as the reference's first launch does
+    // (k_small, src/server/engine_sampling.h:20)
+    a.level_k = 256;
+    cudaError_t e;
+    if (wb::sample_stream_supported(a, dtype)) e = wb::sample_stream_launch(a, dtype, sm_count(), st);
+    else e = wb::select_generic_launch(a, dtype, sm_count(), st);
+    if (e != cudaSuccess) return fail_cuda(e, "sample_rows level 1");
+    // level 2: the rows whose kept set may reach past those candidates, with up to 16384 (k_big, :21)
+    int32_t* list = reinterpret_cast<int32_t*>(base + w.off_list);
+    int32_t* count = reinterpret_cast<int32_t*>(base + w.off_count);
+    gather_rows_kernel<<<1, 1024, 0, st>>>(a.out.status, rows, wb::ROW_ESCALATE, list, count);
+    wb::SelectArgs b = a;
+    b.level_k = wb::kGenericMaxK, b.row_list = list, b.row_count = count;
+    // counters[0] counts level-1 escalations; level 2 must not count again
+    b.out.counters = nullptr;
+    e = wb::select_generic_launch(b, dtype, sm_count(), st);
+    if (e != cudaSuccess) return fail_cuda(e, "sample_rows level 2");
+    if (out->counters) count_unresolved_kernel<<<1, 256, 0, st>>>(a.out.status, rows, out->counters);
+    e = cudaGetLastError();
+    return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "sample_rows");
+}
+
+int whirl_sample_rows_host(const void*, int, int, int, const whirl_sample_params*, const whirl_sample_out*, int) {
+    return fail(WHIRL_ERR_UNSUPPORTED, "sample_rows_host: not built yet");
+}
+void whirl_host_release(void) {}
+
+}  // extern "C"
+#pragma GCC visibility pop

@@ -1,0 +1,103 @@
+// Host-visible declarations of the kernel launchers (internal to the library; the public surface is
+// include/whirl_b200.h).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace wb {
+
+// ---- greedy picks (rowscan.cu)
+enum { RS_ARGMAX = 0, RS_ARGMAX_PROB = 1, RS_DRAFT_PICK = 2 };
+
+struct RowScanArgs {
+    const void* x;  // [rows][n] f32 or bf16
+    int n;
+    // RS_ARGMAX: out[dst ? dst[row] : row] = first max; ids / pos / advance as the reference's argmax()
+    int* out;
+    const int* dst;
+    int* ids;
+    int* pos;
+    int advance;
+    // RS_ARGMAX_PROB: out[row], prob[row].  RS_DRAFT_PICK with ctl_all == null: tok / prob / ctl of one sequence
+    float* prob;
+    // RS_DRAFT_PICK
+    int* tok;
+    int* ctl;
+    int* ctl_all;     // per-sequence control areas; row b's area starts at ctl_all + area[b]
+    const int* area;  // device [rows]
+    int r, n_min;
+    float p_min;
+    const int* map;
+    void* ws;
+};
+
+size_t rowscan_ws_bytes(int rows, int splits);
+int rowscan_splits(int rows, int n, int sm_count);
+cudaError_t rowscan_launch(const RowScanArgs& a, int dtype, int mode, int rows, int splits, cudaStream_t st);
+
+// ---- selection + sampling (select_generic.cu, sample_stream.cu)
+
+// Per-row parameters as device arrays (null = the default in brackets); the fields of the reference's
+// sampling::Sampler (src/sampling/sampler.h:26-53) plus this build's penalties.
+struct RowParams {
+    const float* inv_t;        // [inv_t_scalar]
+    float inv_t_scalar;
+    const int32_t* top_k;      // [0 = off]
+    const double* top_p;       // [1]
+    const double* min_p;       // [0]
+    const uint8_t* greedy;     // [0] non-zero: the row's token is its first maximum
+    const double* u;           // [0] uniform of the inverse-CDF draw (and of the race's open-target choice)
+    const uint64_t* race_key;  // [null = inverse CDF] spec::raceBase(seed, pos) per row; the race draw
+    // penalties over each row's token history
+    const int32_t* hist;       // [rows][hist_stride]
+    const int32_t* hist_len;   // [rows]
+    int64_t hist_stride;
+    const float* rep;          // [1]
+    const float* pres;         // [0]
+    const float* freq;         // [0]
+};
+
+struct RowOutputs {
+    int32_t* token;     // [rows]
+    int32_t* status;    // [rows] RowStatus
+    int32_t* n_kept;    // [rows] (may be null)
+    int32_t* closed;    // [rows] (may be null)
+    float* stats;       // [rows][2] max, sum (may be null)
+    int32_t* kept_ids;  // [rows][kept_cap] (may be null)
+    double* kept_p;     // [rows][kept_cap] (may be null)
+    int32_t kept_cap;
+    uint32_t* counters;  // [8] batch counters (may be null), see WHIRL_CNT_*
+};
+
+enum { MODE_TOPK = 0, MODE_SAMPLE = 1 };
+
+struct SelectArgs {
+    const void* x;  // [rows][n]
+    int rows, n;
+    int mode;
+    // MODE_TOPK: K candidates per row into ids / vals ([rows][K], sorted logit desc, id asc), stats [rows][2]
+    int K;
+    int32_t* ids;
+    float* vals;
+    float* stats;
+    // MODE_SAMPLE
+    RowParams prm;
+    RowOutputs out;
+    const int32_t* row_list;  // optional: process rows row_list[0..rows) of the batch (the escalated ones)
+    const int32_t* row_count; // optional device count overriding `rows` (with row_list)
+    int level_k;              // candidates for rows without a usable top_k (256 first level, 16384 second)
+    void* ws;                 // generic: [rows][level cap] doubles of probability scratch
+    uint32_t* err;            // device error word (bounded waits that ran out)
+};
+
+constexpr int kGenericMaxK = 16384;
+size_t select_generic_ws_bytes(int ctas, int K);  // ctas = min(rows, 2 * SMs)
+cudaError_t select_generic_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
+
+constexpr int kStreamMaxK = 1024;
+cudaError_t sample_stream_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
+bool sample_stream_supported(const SelectArgs& a, int dtype);
+
+}  // namespace wb

@@ -1,0 +1,312 @@
+// General candidate selection: the K best of each row for any K up to 16384 and any row width / alignment, one CTA
+// per row, several passes over the row (which stays in L2).  This is the path for what the single-pass kernel
+// (sample_stream.cu) does not take: K above its limit (the reference's 16384-candidate escalation launch,
+// src/server/engine_sampling.cpp:65-78), rows that are not 16-byte aligned, and the second escalation level of the
+// fused sampler.
+//
+// Replaces topk_rows (kernels/shared/sample_cand_topk_rows.h:11-98) with two differences in results: ties at the K-th
+// logit are broken by the lower token id (the rule of every host comparator of the path,
+// src/sampling/sampler.cpp:18-21) instead of by atomic arrival order, and the candidates come out sorted
+// (logit desc, id asc) instead of unordered.  The softmax normaliser is accumulated in f32 per thread against a
+// running maximum and combined in f64.
+#include "kernels.h"
+#include "penalty.cuh"
+#include "tail.cuh"
+
+namespace wb {
+
+constexpr int GT = 1024;      // threads per CTA
+constexpr int GBINS = 2048;   // histogram bins (11-bit digits)
+
+template <typename T>
+__device__ __forceinline__ float raw_elem(const T* row, uint32_t i) {
+    if (sizeof(T) == 4) return reinterpret_cast<const float*>(row)[i];
+    return bf16_to_f32(reinterpret_cast<const uint16_t*>(row)[i]);
+}
+template <typename T>
+__device__ __forceinline__ float elem(const T* row, uint32_t i, const PenaltyTable& pt) {
+    float x = raw_elem(row, i);
+    if (pt.on && pt.hit(i)) x = pt.apply(x, i);
+    return x;
+}
+
+struct GShared {
+    uint32_t prefix, remain, cnt, eq;
+    float m;
+    float sum;
+    TailOut res;
+    float red_m[32];
+    double red_s[32];
+    uint64_t red_c[32];
+};
+
+// One digit pass of a radix select over values v(i) of the elements that pass `keep(i)`: finds, going from the top bin
+// down (DESC) or from the bottom bin up, the bin where the running count reaches sh->remain; updates prefix / remain.
+// hist must be zero on entry and is zero again on exit.
+template <bool DESC>
+__device__ void pick_bin(uint32_t* hist, GShared* sh, int shift, int bits) {
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        const int nb = 1 << bits, per = nb / 32;
+        const int l = lane_id();
+        // lane l owns `per` consecutive bins, in scan order
+        uint32_t s = 0;
+        for (int j = 0; j < per; ++j) {
+            const int b = DESC ? nb - 1 - (l * per + j) : l * per + j;
+            s += hist[b];
+        }
+        const uint32_t incl = warp_scan_incl(s), excl = incl - s;
+        const uint32_t rem = sh->remain;
+        const bool mine = excl < rem && incl >= rem;
+        if (mine) {
+            uint32_t r = rem - excl;
+            for (int j = 0; j < per; ++j) {
+                const int b = DESC ? nb - 1 - (l * per + j) : l * per + j;
+                const uint32_t c = hist[b];
+                if (c >= r) {
+                    sh->prefix |= uint32_t(b) << shift;
+                    sh->remain = r;
+                    sh->eq = c;
+                    break;
+                }
+                r -= c;
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < GBINS; i += GT) hist[i] = 0;
+    __syncthreads();
+}
+
+template <typename T>
+__device__ void select_row(const SelectArgs& a, int row, int cap_max, int pen_words, uint64_t* cand, uint32_t* hist,
+                           GShared* sh, uint32_t* pen_mem);
+
+// grid-strided over the rows (or over the entries of row_list); one row at a time per CTA
+template <typename T>
+__global__ void __launch_bounds__(GT) select_generic_kernel(SelectArgs a, int cap_max, int pen_words) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint64_t* cand = reinterpret_cast<uint64_t*>(smem);
+    uint32_t* hist = reinterpret_cast<uint32_t*>(smem + size_t(cap_max) * 8);
+    GShared* sh = reinterpret_cast<GShared*>(hist + GBINS);
+    uint32_t* pen_mem = reinterpret_cast<uint32_t*>(sh + 1);
+
+    const int n_rows = a.row_count ? min(*a.row_count, a.rows) : a.rows;
+    for (int li = blockIdx.x; li < n_rows; li += gridDim.x) {
+        __syncthreads();  // the previous row's shared state is dead
+        const int row = a.row_list ? a.row_list[li] : li;
+        select_row<T>(a, row, cap_max, pen_words, cand, hist, sh, pen_mem);
+    }
+}
+
+template <typename T>
+__device__ void select_row(const SelectArgs& a, int row, int cap_max, int pen_words, uint64_t* cand, uint32_t* hist,
+                           GShared* sh, uint32_t* pen_mem) {
+    const uint32_t n = uint32_t(a.n);
+    const T* x = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
+    const int tid = threadIdx.x;
+    const bool sample = a.mode == MODE_SAMPLE;
+    const RowParams& P = a.prm;
+    const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
+
+    // ---- penalties table
+    PenaltyTable pt;
+    pt.on = false;
+    if (sample && P.hist && P.hist_len && P.hist_len[row] > 0) {
+        pt.rep = P.rep ? P.rep[row] : 1.f, pt.pres = P.pres ? P.pres[row] : 0.f, pt.freq = P.freq ? P.freq[row] : 0.f;
+        pt.on = pt.rep != 1.f || pt.pres != 0.f || pt.freq != 0.f;
+    }
+    if (pt.on) {
+        pt.bitmap = pen_mem;
+        pt.slots = pen_mem + pen_words;
+        pt.clear(tid, GT, n);
+        __syncthreads();
+        const int32_t* h = P.hist + size_t(row) * P.hist_stride;
+        const int hl = min(P.hist_len[row], kMaxHist);
+        for (int i = tid; i < hl; i += GT) pt.insert(h[i], n);
+    }
+    for (int i = tid; i < GBINS; i += GT) hist[i] = 0;
+    if (tid == 0) sh->prefix = 0, sh->cnt = 0, sh->eq = 0;
+    __syncthreads();
+
+    // ---- greedy rows: the first maximum
+    if (sample && P.greedy && P.greedy[row]) {
+        uint64_t best = 0;  // composite of the best element; 0 = none
+        for (uint32_t i = tid; i < n; i += GT) {
+            const float v = elem(x, i, pt);
+            if (v == v) {
+                const uint64_t c = make_cand(key_of(v), i);
+                best = c > best ? c : best;
+            }
+        }
+        best = warp_max(best);
+        if (lane_id() == 0) sh->red_c[tid >> 5] = best;
+        __syncthreads();
+        if (tid < 32) {
+            best = warp_max(sh->red_c[tid]);
+            if (tid == 0) {
+                const uint32_t tok = best ? cand_id(best) : 0;
+                a.out.token[row] = int32_t(tok);
+                a.out.status[row] = ROW_DONE;
+                if (a.out.n_kept) a.out.n_kept[row] = 1;
+                if (a.out.closed) a.out.closed[row] = 1;
+                if (a.out.stats) a.out.stats[2 * row] = best ? float_of_key(cand_key(best)) : -INFINITY, a.out.stats[2 * row + 1] = 0.f;
+                if (a.out.kept_ids && a.out.kept_cap > 0) a.out.kept_ids[size_t(row) * a.out.kept_cap] = int32_t(tok);
+                if (a.out.kept_p && a.out.kept_cap > 0) a.out.kept_p[size_t(row) * a.out.kept_cap] = 1.0;
+            }
+        }
+        return;
+    }
+
+    // ---- candidates wanted for this row
+    uint32_t top_k = 0, K;
+    if (sample) {
+        top_k = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
+        K = (top_k > 0 && top_k <= uint32_t(a.level_k)) ? top_k : uint32_t(a.level_k);
+    } else {
+        K = uint32_t(a.K);
+    }
+    if (K > n) K = n;
+
+    // ---- pass 0: max and sum exp((x - max) * inv_t)
+    {
+        const float c = inv_t * kLog2e;
+        float m = -INFINITY, s = 0.f;
+        for (uint32_t i = tid; i < n; i += GT) {
+            const float v = elem(x, i, pt);
+            if (v > m) {
+                s = (m == -INFINITY) ? 0.f : s * ex2_approx((m - v) * c);
+                m = v;
+            }
+            if (v == v && m != -INFINITY) s += ex2_approx((v - m) * c);
+        }
+        const float wm = warp_max(m);
+        double ds = (m == -INFINITY) ? 0.0 : double(s) * double(ex2_approx((m - wm) * c));
+        ds = warp_sum(ds);
+        if (lane_id() == 0) sh->red_m[tid >> 5] = wm, sh->red_s[tid >> 5] = ds;
+        __syncthreads();
+        if (tid < 32) {
+            const float pm = sh->red_m[tid];
+            const float M = warp_max(pm);
+            double t = (pm == -INFINITY) ? 0.0 : sh->red_s[tid] * double(ex2_approx((pm - M) * c));
+            t = warp_sum(t);
+            if (tid == 0) sh->m = M, sh->sum = float(t);
+        }
+        __syncthreads();
+    }
+
+    // ---- the K-th largest key by three digit passes (11 + 11 + 10 bits)
+    if (tid == 0) sh->remain = K;
+    uint32_t mask = 0;
+    const int shifts[3] = {21, 10, 0}, widths[3] = {11, 11, 10};
+    for (int ps = 0; ps < 3 && K > 0; ++ps) {
+        const uint32_t prefix = sh->prefix;
+        const uint32_t bm = (1u << widths[ps]) - 1;
+        for (uint32_t i = tid; i < n; i += GT) {
+            const uint32_t k = key_of(elem(x, i, pt));
+            if ((k & mask) == prefix) atomicAdd(&hist[(k >> shifts[ps]) & bm], 1u);
+        }
+        pick_bin<true>(hist, sh, shifts[ps], widths[ps]);
+        mask |= bm << shifts[ps];
+    }
+    const uint32_t thr = sh->prefix, need = sh->remain, n_eq = sh->eq;
+    // ---- more ties at the K-th key than wanted: the `need` lowest ids among them, by three digit passes on the id
+    uint32_t id_thr = 0xffffffffu;
+    if (K > 0 && n_eq > need) {
+        __syncthreads();
+        if (tid == 0) sh->prefix = 0;
+        __syncthreads();
+        uint32_t imask = 0;
+        for (int ps = 0; ps < 3; ++ps) {
+            const uint32_t prefix = sh->prefix;
+            const uint32_t bm = (1u << widths[ps]) - 1;
+            for (uint32_t i = tid; i < n; i += GT) {
+                if ((i & imask) != prefix) continue;
+                if (key_of(elem(x, i, pt)) == thr) atomicAdd(&hist[(i >> shifts[ps]) & bm], 1u);
+            }
+            pick_bin<false>(hist, sh, shifts[ps], widths[ps]);
+            imask |= bm << shifts[ps];
+        }
+        id_thr = sh->prefix;
+    }
+    // ---- collect
+    uint32_t cap = 1;
+    while (cap < K) cap <<= 1;
+    for (uint32_t i = tid; i < n && K > 0; i += GT) {
+        const uint32_t k = key_of(elem(x, i, pt));
+        if (k > thr || (k == thr && i <= id_thr)) {
+            const uint32_t pos = atomicAdd(&sh->cnt, 1u);
+            if (pos < cap) cand[pos] = make_cand(k, i);
+        }
+    }
+    for (uint32_t i = K + tid; i < cap; i += GT) cand[i] = 0;
+    __syncthreads();
+    const Group<GT> g{tid, 0};
+    if (!sample) {
+        sort_desc<GT>(g, cand, cap);
+        for (uint32_t j = tid; j < K; j += GT) {
+            const uint32_t id = cand_id(cand[j]);
+            a.ids[size_t(row) * a.K + j] = int32_t(id);
+            a.vals[size_t(row) * a.K + j] = raw_elem(x, id);
+        }
+        if (tid == 0) a.stats[2 * row] = sh->m, a.stats[2 * row + 1] = sh->sum;
+        return;
+    }
+    // ---- filter and draw
+    TailIn in;
+    in.inv_t = inv_t, in.top_k = top_k, in.top_p = P.top_p ? P.top_p[row] : 1.0, in.min_p = P.min_p ? P.min_p[row] : 0.0;
+    in.u = P.u ? P.u[row] : 0.0, in.m = sh->m, in.sum = sh->sum, in.cnt = K, in.cap = cap, in.V = n;
+    in.race = P.race_key != nullptr, in.race_key = P.race_key ? P.race_key[row] : 0;
+    double* p = reinterpret_cast<double*>(a.ws) + size_t(blockIdx.x) * (size_t(cap_max) + 2 * GT / 32);
+    // the tail's race scratch sits at p + in.cap; keep it inside this row's slice
+    sample_tail<GT>(g, in, cand, p, &sh->res);
+    const TailOut r = sh->res;
+    if (tid == 0) {
+        a.out.token[row] = int32_t(r.token);
+        a.out.status[row] = r.status;
+        if (a.out.n_kept) a.out.n_kept[row] = int32_t(r.n);
+        if (a.out.closed) a.out.closed[row] = r.closed;
+        if (a.out.stats) a.out.stats[2 * row] = sh->m, a.out.stats[2 * row + 1] = sh->sum;
+        if (a.out.counters && r.status == ROW_ESCALATE) atomicAdd(&a.out.counters[0], 1u);
+        if (a.out.counters && r.status == ROW_OPEN_TAIL) atomicAdd(&a.out.counters[1], 1u);
+    }
+    if (r.status != ROW_ESCALATE) {
+        const uint32_t nk = min(r.n, uint32_t(max(a.out.kept_cap, 0)));
+        for (uint32_t j = tid; j < nk; j += GT) {
+            if (a.out.kept_ids) a.out.kept_ids[size_t(row) * a.out.kept_cap + j] = int32_t(cand_id(cand[j]));
+            if (a.out.kept_p) a.out.kept_p[size_t(row) * a.out.kept_cap + j] = p[j];
+        }
+    }
+}
+
+static int pow2_at_least(int k) {
+    int c = 1;
+    while (c < k) c <<= 1;
+    return c;
+}
+
+size_t select_generic_ws_bytes(int ctas, int K) {
+    return size_t(ctas) * (size_t(pow2_at_least(K < 1 ? 1 : K)) + 2 * GT / 32) * sizeof(double);
+}
+
+cudaError_t select_generic_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st) {
+    const int grid = a.rows < 2 * sm_count ? a.rows : 2 * sm_count;
+    const int kmax = a.mode == MODE_TOPK ? a.K : a.level_k;
+    const int cap = pow2_at_least(kmax < 1 ? 1 : (kmax > a.n ? a.n : kmax));
+    const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
+    const int pen_words = pen ? ((a.n + 31) / 32 + 3) & ~3 : 0;
+    const size_t smem = size_t(cap) * 8 + GBINS * 4 + sizeof(GShared) + (pen ? size_t(pen_words) * 4 + kPenSlots * 4 : 0) + 16;
+    cudaError_t e;
+    if (dtype == 0) {
+        e = cudaFuncSetAttribute(select_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+        select_generic_kernel<float><<<grid, GT, smem, st>>>(a, cap, pen_words);
+    } else {
+        e = cudaFuncSetAttribute(select_generic_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+        select_generic_kernel<uint16_t><<<grid, GT, smem, st>>>(a, cap, pen_words);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace wb

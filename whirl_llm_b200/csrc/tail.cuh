@@ -1,0 +1,202 @@
+// The per-row tail of the sampling path: sort the selected candidates, probabilities in f64, top-k / top-p / min-p on
+// the sorted prefix, then the draw.  It restates, for a group of GPU threads, what the reference does on the host in
+// sampling::filterCands (src/sampling/sampler.cpp:15-78), sampleRow (:118-131, the candidate part) and sampleRace
+// (:82-106, the race part).  Sums that the host accumulates sequentially are accumulated sequentially here too (one
+// thread walks them in candidate order), so the kept set and the cumulative sums follow the same order of operations.
+#pragma once
+
+#include "common.cuh"
+
+namespace wb {
+
+enum RowStatus : int32_t {
+    ROW_DONE = 0,       // token drawn from a closed (or reached) candidate set
+    ROW_ESCALATE = 1,   // the kept set may reach past the candidates: needs a larger candidate set
+    ROW_OPEN_TAIL = 2,  // open set and the draw fell past the candidates: needs the id-order walk of the row
+};
+
+struct TailIn {
+    float inv_t;
+    uint32_t top_k;
+    double top_p, min_p, u;
+    float m, sum;
+    uint32_t cnt;       // valid candidates in cand[]
+    uint32_t cap;       // power of two >= cnt; cand[cnt..cap) must be 0
+    uint32_t V;         // row width (cnt == V means the candidates are the whole row)
+    uint64_t race_key;  // spec::raceBase(seed, pos) when race != 0
+    int32_t race;
+};
+struct TailOut {
+    int32_t status;
+    uint32_t token, n;
+    int32_t closed;
+    double cum;  // cumulative mass of the walked candidates (ROW_OPEN_TAIL: where the id-order walk continues)
+};
+
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {  // include/whirl/spec_sample.h:53-57
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+// E(v) = -ln(1 - U(base, v)), src/common/spec_sample.cpp:83-87
+__device__ __forceinline__ double race_e(uint64_t base, uint32_t token) {
+    const uint64_t z = mix64(base + (uint64_t(token) + 1ull) * 0xE7037ED1A0B428DBull);
+    const double u = double(z >> 11) * (1.0 / 9007199254740992.0);
+    return -log(1.0 - u);
+}
+
+// Bitonic sort of cand[0..cap) in descending composite order (= logit desc, id asc).
+template <int NT>
+__device__ void sort_desc(const Group<NT>& g, uint64_t* cand, uint32_t cap) {
+    for (uint32_t k = 2; k <= cap; k <<= 1) {
+        for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+            for (uint32_t t = g.tid; t < (cap >> 1); t += NT) {
+                // t enumerates the pairs (i, i ^ j) with i's bit j clear
+                const uint32_t i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+                const uint32_t q = i | j;
+                const uint64_t a = cand[i], b = cand[q];
+                const bool desc = (i & k) == 0;
+                if (desc ? (a < b) : (a > b)) {
+                    cand[i] = b;
+                    cand[q] = a;
+                }
+            }
+            g.sync();
+        }
+    }
+}
+
+// cand: shared, the exact candidate set (any order, padded with zeros up to cap); p: shared scratch of cap doubles;
+// res: one shared TailOut.  On return (after the group's barrier) cand is sorted, p[0..n) holds the kept
+// probabilities (renormalised when closed) and *res the outcome.
+template <int NT>
+__device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand, double* p, TailOut* res) {
+    sort_desc<NT>(g, cand, in.cap);
+    const double inv_t = double(in.inv_t), sum = double(in.sum);
+    for (uint32_t i = g.tid; i < in.cnt; i += NT) {
+        const float l = float_of_key(cand_key(cand[i]));
+        p[i] = exp(double(__fsub_rn(l, in.m)) * inv_t) / sum;
+    }
+    g.sync();
+    if (g.tid == 0) {
+        uint32_t n = in.cnt;
+        bool closed = in.cnt == in.V, esc = false;
+        if (in.top_k > 0) {
+            if (in.top_k <= in.cnt) n = in.top_k, closed = true;
+            else if (!closed) esc = true;
+        }
+        if (!esc && in.top_p < 1.0) {
+            double z = 1.0;
+            if (closed) {
+                z = 0;
+                for (uint32_t i = 0; i < n; ++i) z += p[i];
+            }
+            double cum = 0;
+            bool found = false;
+            for (uint32_t j = 0; j < n; ++j) {
+                cum += p[j] / z;
+                if (cum >= in.top_p) {
+                    n = j + 1;
+                    found = true;
+                    break;
+                }
+            }
+            if (found) closed = true;
+            else if (!closed) esc = true;
+        }
+        if (!esc && in.min_p > 0) {
+            const double thr = in.min_p * p[0];
+            uint32_t j = 0;
+            while (j < n && p[j] >= thr) ++j;
+            if (j == n && !closed) esc = true;
+            else n = j > 1 ? j : 1, closed = true;
+        }
+        double z = 1.0;
+        if (!esc && closed) {
+            z = 0;
+            for (uint32_t i = 0; i < n; ++i) z += p[i];
+        }
+        res->status = esc ? ROW_ESCALATE : ROW_DONE;
+        res->n = n;
+        res->closed = closed;
+        res->cum = z;  // the normaliser, read back below
+        res->token = 0;
+    }
+    g.sync();
+    if (res->status == ROW_ESCALATE) return;
+    const uint32_t n = res->n;
+    const bool closed = res->closed != 0;
+    if (closed) {
+        const double z = res->cum;
+        for (uint32_t i = g.tid; i < n; i += NT) p[i] /= z;
+    }
+    g.sync();
+    bool do_race = in.race != 0;
+    if (do_race && !closed) {
+        // open target: candidates vs tail by the stream-0 uniform (u < their mass S), src/sampling/sampler.cpp:84-93
+        if (g.tid == 0) {
+            double S = 0;
+            for (uint32_t i = 0; i < n; ++i) S += p[i];
+            res->cum = S;
+        }
+        g.sync();
+        do_race = in.u < res->cum;
+        g.sync();
+    }
+    if (do_race) {
+        // argmin over the kept candidates of E(id) / p, the first on ties
+        double bk = __longlong_as_double(0x7FF0000000000000ll);
+        uint32_t bi = 0xffffffffu;
+        for (uint32_t i = g.tid; i < n; i += NT) {
+            if (!(p[i] > 0)) continue;
+            const double k = race_e(in.race_key, cand_id(cand[i])) / p[i];
+            if (k < bk) bk = k, bi = i;  // i ascends per thread: strict < keeps the first
+        }
+        // group argmin through shared scratch above the kept set is not available here; reduce with warp shuffles and
+        // let thread 0 combine the warps through p[] beyond cap (callers give p at least cap + NT/32*2 doubles)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const double ok = __shfl_xor_sync(0xffffffffu, bk, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ok < bk || (ok == bk && oi < bi)) bk = ok, bi = oi;
+        }
+        double* wk = p + in.cap;
+        if ((g.tid & 31) == 0) {
+            wk[(g.tid >> 5) * 2] = bk;
+            wk[(g.tid >> 5) * 2 + 1] = __longlong_as_double((long long)bi);
+        }
+        g.sync();
+        if (g.tid == 0) {
+            for (int w = 1; w < NT / 32; ++w) {
+                const double ok = wk[w * 2];
+                const uint32_t oi = (uint32_t)__double_as_longlong(wk[w * 2 + 1]);
+                if (ok < bk || (ok == bk && oi < bi)) bk = ok, bi = oi;
+            }
+            res->token = cand_id(cand[bi == 0xffffffffu ? 0 : bi]);
+            res->status = ROW_DONE;
+        }
+        g.sync();
+        return;
+    }
+    if (g.tid == 0) {
+        // inverse CDF over the kept candidates (sampleRow with no excluded token)
+        const double target = in.u;
+        double cum = 0;
+        uint32_t tok = cand_id(cand[0]);
+        bool hit = false;
+        for (uint32_t i = 0; i < n; ++i) {
+            cum += p[i];
+            tok = cand_id(cand[i]);
+            if (cum > target) {
+                hit = true;
+                break;
+            }
+        }
+        res->token = tok;  // closed and not hit: the last candidate is the fallback
+        res->cum = cum;
+        res->status = (hit || closed) ? ROW_DONE : ROW_OPEN_TAIL;
+    }
+    g.sync();
+}
+
+}  // namespace wb
