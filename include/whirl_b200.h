@@ -59,6 +59,11 @@ const char* whirl_status_string(int status);
 const char* whirl_last_error(void);
 int whirl_version(void);
 
+/* Kernel launches this process has made through the library so far, per family: [0] greedy picks, [1] multi-pass
+ * selection, [2] single-pass sampler, [3] small helper kernels.  Fills min(n, 4) entries.  (The reference logs launches
+ * with WHIRL_LAUNCH_LOG, src/hip/launch_log.h.) */
+void whirl_launch_counts(uint64_t* out, int n);
+
 /* Bytes of workspace that cover every entry point below for batches of up to `rows` rows of `n` logits. */
 size_t whirl_workspace_bytes(int rows, int n);
 
@@ -158,6 +163,8 @@ int whirl_sample_rows_host(const void* x_host, int dtype, int rows, int n, const
                            const whirl_sample_out* out_host, int device);
 /* Releases what whirl_sample_rows_host keeps. */
 void whirl_host_release(void);
+/* Message of the last failing whirl_sample_rows_host call on this thread. */
+const char* whirl_host_last_error(void);
 
 #ifdef __cplusplus
 }

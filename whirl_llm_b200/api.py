@@ -59,6 +59,8 @@ def _load() -> C.CDLL:
         "whirl_sample_rows": (i, [vp, i, i, i, C.POINTER(SampleParams), C.POINTER(SampleOut), vp, sz, vp]),
         "whirl_sample_rows_host": (i, [vp, i, i, i, C.POINTER(SampleParams), C.POINTER(SampleOut), i]),
         "whirl_host_release": (None, []),
+        "whirl_host_last_error": (C.c_char_p, []),
+        "whirl_launch_counts": (None, [vp, i]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -69,7 +71,8 @@ def _load() -> C.CDLL:
 lib = _load()
 DECLARED = ["whirl_status_string", "whirl_last_error", "whirl_version", "whirl_workspace_bytes", "whirl_argmax",
             "whirl_argmax_rows", "whirl_argmax_rows_to", "whirl_argmax_prob", "whirl_draft_pick", "whirl_draft_pick_rows",
-            "whirl_topk_rows", "whirl_sample_rows", "whirl_sample_rows_host", "whirl_host_release"]
+            "whirl_topk_rows", "whirl_sample_rows", "whirl_sample_rows_host", "whirl_host_release", "whirl_host_last_error",
+            "whirl_launch_counts"]
 
 
 def _check(status: int):
@@ -252,3 +255,31 @@ def sample_rows(x, params: RowParams, kept_cap: int = 0, ws=None, result: Option
     ps = params.struct(rows)
     _check(lib.whirl_sample_rows(x.data_ptr(), _dtype(x), rows, n, C.byref(ps), C.byref(o), ws.data_ptr(), ws.numel(), _stream(x)))
     return result
+
+
+def launch_counts() -> dict:
+    """Kernel launches made through the library by this process so far, per family."""
+    a = (C.c_uint64 * 4)()
+    lib.whirl_launch_counts(a, 4)
+    return dict(rowscan=a[0], select_generic=a[1], sample_stream=a[2], aux=a[3])
+
+
+def sample_rows_host(x_host, params: dict, rows: int, n: int, dtype: int, out: dict, kept_cap: int = 0, device: int = 0):
+    """whirl_sample_rows_host on host buffers: `x_host`, the values of `params` and of `out` are CPU tensors (pinned for
+    full copy speed) or None.  Blocks until the tokens are in out['token']."""
+    ps = SampleParams()
+    for k, _ in SampleParams._fields_:
+        if k == "hist_stride":
+            continue
+        t = params.get(k)
+        setattr(ps, k, None if t is None else t.data_ptr())
+    ps.hist_stride = 0 if params.get("hist") is None else params["hist"].shape[1]
+    o = SampleOut(kept_cap=kept_cap)
+    for k, _ in SampleOut._fields_:
+        if k == "kept_cap":
+            continue
+        t = out.get(k)
+        setattr(o, k, None if t is None else t.data_ptr())
+    st = lib.whirl_sample_rows_host(x_host.data_ptr(), dtype, rows, n, C.byref(ps), C.byref(o), device)
+    if st != 0:
+        raise WhirlError(st, (lib.whirl_host_last_error() or b"").decode())

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -16,6 +17,11 @@
 namespace {
 
 thread_local std::string g_err;
+
+// host-side launch counters per kernel family (whirl_launch_counts)
+std::atomic<uint64_t> g_launch[4];
+enum { LC_ROWSCAN = 0, LC_GENERIC = 1, LC_STREAM = 2, LC_AUX = 3 };
+void bump(int which, uint64_t n = 1) { g_launch[which].fetch_add(n, std::memory_order_relaxed); }
 
 int fail(int code, const char* msg) {
     g_err = msg;
@@ -105,6 +111,7 @@ int scan_call(int mode, const void* x, int dtype, int rows, int n, wb::RowScanAr
     }
     a.x = x, a.n = n, a.ws = ws;
     const cudaError_t e = wb::rowscan_launch(a, dtype, mode, rows, splits, st);
+    bump(LC_ROWSCAN);
     return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "rowscan launch");
 }
 
@@ -180,14 +187,17 @@ int whirl_topk_rows(const void* x, int dtype, int rows, int n, int K, float inv_
     if (K < 1) return fail(WHIRL_ERR_INVALID, "topk_rows: K < 1");
     if (K > WHIRL_MAX_K) return fail(WHIRL_ERR_UNSUPPORTED, "topk_rows: K above WHIRL_MAX_K");
     if (rows == 0) return WHIRL_OK;
-    (void)ws, (void)ws_bytes;
     wb::SelectArgs a{};
     a.x = x, a.rows = rows, a.n = n, a.mode = wb::MODE_TOPK, a.K = K, a.ids = ids, a.vals = vals, a.stats = stats;
     a.prm.inv_t = inv_t_rows, a.prm.inv_t_scalar = inv_t;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
-    if (wb::sample_stream_supported(a, dtype)) e = wb::sample_stream_launch(a, dtype, sm_count(), st);
-    else e = wb::select_generic_launch(a, dtype, sm_count(), st);
+    // the single-pass kernel reports bounded waits that ran out through an error word in the workspace
+    const Ws w = ws_layout(rows);
+    const bool have_ws = ws && ws_bytes >= w.total;
+    if (have_ws) a.err = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ws) + w.off_err);
+    if (have_ws && wb::sample_stream_supported(a, dtype)) { e = wb::sample_stream_launch(a, dtype, sm_count(), st); bump(LC_STREAM); }
+    else { e = wb::select_generic_launch(a, dtype, sm_count(), st); bump(LC_GENERIC); }
     return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "topk_rows launch");
 }
 
@@ -220,8 +230,8 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
     // (k_small, src/server/engine_sampling.h:20)
     a.level_k = 256;
     cudaError_t e;
-    if (wb::sample_stream_supported(a, dtype)) e = wb::sample_stream_launch(a, dtype, sm_count(), st);
-    else e = wb::select_generic_launch(a, dtype, sm_count(), st);
+    if (wb::sample_stream_supported(a, dtype)) { e = wb::sample_stream_launch(a, dtype, sm_count(), st); bump(LC_STREAM); }
+    else { e = wb::select_generic_launch(a, dtype, sm_count(), st); bump(LC_GENERIC); }
     if (e != cudaSuccess) return fail_cuda(e, "sample_rows level 1");
     // level 2: the rows whose kept set may reach past those candidates, with up to 16384 (k_big, :21)
     int32_t* list = reinterpret_cast<int32_t*>(base + w.off_list);
@@ -232,16 +242,17 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
     // counters[0] counts level-1 escalations; level 2 must not count again
     b.out.counters = nullptr;
     e = wb::select_generic_launch(b, dtype, sm_count(), st);
+    bump(LC_GENERIC);
+    bump(LC_AUX);
     if (e != cudaSuccess) return fail_cuda(e, "sample_rows level 2");
-    if (out->counters) count_unresolved_kernel<<<1, 256, 0, st>>>(a.out.status, rows, out->counters);
+    if (out->counters) { count_unresolved_kernel<<<1, 256, 0, st>>>(a.out.status, rows, out->counters); bump(LC_AUX); }
     e = cudaGetLastError();
     return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "sample_rows");
 }
 
-int whirl_sample_rows_host(const void*, int, int, int, const whirl_sample_params*, const whirl_sample_out*, int) {
-    return fail(WHIRL_ERR_UNSUPPORTED, "sample_rows_host: not built yet");
+void whirl_launch_counts(uint64_t* out, int n) {
+    for (int i = 0; i < n && i < 4; ++i) out[i] = g_launch[i].load(std::memory_order_relaxed);
 }
-void whirl_host_release(void) {}
 
 }  // extern "C"
 #pragma GCC visibility pop
