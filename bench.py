@@ -140,6 +140,12 @@ def run_ours(args):
                 min_p=torch.full((rows,), SETTINGS["min_p"], dtype=torch.float64, device=dev),
                 hist=hist, hist_len=torch.full((rows,), HIST, dtype=torch.int32, device=dev),
                 rep=f32(SETTINGS["rep"]), pres=f32(SETTINGS["pres"]), freq=f32(SETTINGS["freq"]))
+    base["top_k"].fill_(args.top_k)
+    if args.no_penalties:
+        for k in ("hist", "hist_len", "rep", "pres", "freq"):
+            base[k] = None
+    if args.greedy:
+        base["greedy"] = torch.ones(rows, dtype=torch.uint8, device=dev)
     params = [api.RowParams(u=us[b], **base) for b in range(nbuf)]
     ws = torch.zeros(api.workspace_bytes(rows, vocab), dtype=torch.uint8, device=dev)
     res = api.sample_rows(xs[0], params[0], ws=ws)
@@ -178,6 +184,10 @@ def run_ours(args):
     launches = sum(lc1.values()) - sum(lc0.values())
 
     # ---- end to end: pinned host logits through whirl_sample_rows_host, copies inside the timed region
+    if args.no_e2e:
+        print(json.dumps({"variant": vars(args), "ms_per_step": ms_per_step, "rows_per_s": value,
+                          "frac": rows * algorithmic_bytes_per_row(vocab, esize, 0 if args.no_penalties else HIST) / (ms_per_step * 1e-3) / 1e9 / measured_peak_gbs()[0]}))
+        return
     x_host = torch.empty((rows, vocab), dtype=xs[0].dtype).pin_memory()
     x_host.copy_(xs[0])
     hp = {k: (v.cpu().pin_memory() if v is not None else None) for k, v in dict(u=us[0], **base).items()}
@@ -327,6 +337,10 @@ def main():
     ap.add_argument("--vocab", type=int, default=262144)
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-penalties", action="store_true", help="variant: no token history (not the headline workload)")
+    ap.add_argument("--greedy", action="store_true", help="variant: greedy rows (not the headline workload)")
+    ap.add_argument("--top-k", type=int, default=SETTINGS["top_k"], help="variant: another top-k (not the headline workload)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (variants only)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

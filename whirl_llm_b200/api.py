@@ -11,7 +11,7 @@ from typing import Optional
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libwhirl_b200.so")
+LIB_PATH = os.environ.get("WHIRL_B200_LIB") or os.path.join(_HERE, "libwhirl_b200.so")
 
 F32, BF16 = 0, 1
 ROW_DONE, ROW_ESCALATE, ROW_OPEN_TAIL = 0, 1, 2

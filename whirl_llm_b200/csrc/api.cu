@@ -51,7 +51,7 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // workspace layout (all offsets 256-byte aligned)
 struct Ws {
-    size_t off_scan, off_status, off_list, off_count, off_err, off_p, total;
+    size_t off_scan, off_status, off_list, off_list2, off_count, off_err, off_p, total;
 };
 Ws ws_layout(int rows) {
     Ws w;
@@ -61,6 +61,8 @@ Ws ws_layout(int rows) {
     w.off_status = o;
     o = align_up(o + size_t(rows) * 4, 256);
     w.off_list = o;
+    o = align_up(o + size_t(rows) * 4, 256);
+    w.off_list2 = o;
     o = align_up(o + size_t(rows) * 4, 256);
     w.off_count = o;
     o = align_up(o + 16, 256);
@@ -87,6 +89,25 @@ __global__ void gather_rows_kernel(const int32_t* status, int rows, int want, in
     }
     __syncthreads();
     if (threadIdx.x == 0) *count = s_n;
+}
+
+// After the small-K single-pass kernel: rows left to the large-K kernel -> list_a; rows for the multi-pass kernel ->
+// list_b (a row whose candidate log overflowed is redone at the first level: bit 30; a row whose kept set may reach past
+// its candidates goes to the second level).  counts[0], counts[1].
+__global__ void gather_two_kernel(const int32_t* status, int rows, int32_t* list_a, int32_t* list_b, int32_t* counts) {
+    __shared__ int s_a, s_b;
+    if (threadIdx.x == 0) s_a = 0, s_b = 0;
+    __syncthreads();
+    for (int base = 0; base < rows; base += blockDim.x) {
+        const int r = base + threadIdx.x;
+        if (r >= rows) continue;
+        const int st = status[r];
+        if (st == wb::ROW_LARGE_K) list_a[atomicAdd(&s_a, 1)] = r;
+        else if (st == wb::ROW_ESCALATE) list_b[atomicAdd(&s_b, 1)] = r;
+        else if (st == wb::ROW_RETRY) list_b[atomicAdd(&s_b, 1)] = r | (1 << 30);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) counts[0] = s_a, counts[1] = s_b;
 }
 
 __global__ void count_unresolved_kernel(const int32_t* status, int rows, uint32_t* counters) {
@@ -192,12 +213,36 @@ int whirl_topk_rows(const void* x, int dtype, int rows, int n, int K, float inv_
     a.prm.inv_t = inv_t_rows, a.prm.inv_t_scalar = inv_t;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
-    // the single-pass kernel reports bounded waits that ran out through an error word in the workspace
+    // the single-pass kernels report through an error word and a per-row status in the workspace
     const Ws w = ws_layout(rows);
     const bool have_ws = ws && ws_bytes >= w.total;
-    if (have_ws) a.err = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ws) + w.off_err);
-    if (have_ws && wb::sample_stream_supported(a, dtype)) { e = wb::sample_stream_launch(a, dtype, sm_count(), st); bump(LC_STREAM); }
-    else { e = wb::select_generic_launch(a, dtype, sm_count(), st); bump(LC_GENERIC); }
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    if (have_ws) {
+        a.err = reinterpret_cast<uint32_t*>(base + w.off_err);
+        a.out.status = reinterpret_cast<int32_t*>(base + w.off_status);
+    }
+    if (have_ws && wb::sample_async_supported(a, dtype)) {
+        e = wb::sample_async_launch(a, dtype, sm_count(), st);
+        bump(LC_STREAM);
+        if (e == cudaSuccess) {
+            // rows whose candidate log overflowed (adversarial element order) are redone by the multi-pass kernel
+            int32_t* list = reinterpret_cast<int32_t*>(base + w.off_list);
+            int32_t* count = reinterpret_cast<int32_t*>(base + w.off_count);
+            gather_rows_kernel<<<1, 1024, 0, st>>>(a.out.status, rows, wb::ROW_RETRY, list, count);
+            wb::SelectArgs b = a;
+            b.row_list = list, b.row_count = count;
+            e = wb::select_generic_launch(b, dtype, sm_count(), st);
+            bump(LC_AUX);
+            bump(LC_GENERIC);
+        }
+    } else if (have_ws && wb::sample_stream_supported(a, dtype)) {
+        e = wb::sample_stream_launch(a, dtype, sm_count(), st);
+        bump(LC_STREAM);
+    } else {
+        a.out.status = nullptr;
+        e = wb::select_generic_launch(a, dtype, sm_count(), st);
+        bump(LC_GENERIC);
+    }
     return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "topk_rows launch");
 }
 
@@ -229,26 +274,47 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
     // level 1: top_k candidates (the set closes there), or 256 of them as the reference's first launch does
     // (k_small, src/server/engine_sampling.h:20)
     a.level_k = 256;
+    int32_t* list_a = reinterpret_cast<int32_t*>(base + w.off_list);
+    int32_t* list_b = reinterpret_cast<int32_t*>(base + w.off_list2);
+    int32_t* counts = reinterpret_cast<int32_t*>(base + w.off_count);
     cudaError_t e;
-    if (wb::sample_stream_supported(a, dtype)) { e = wb::sample_stream_launch(a, dtype, sm_count(), st); bump(LC_STREAM); }
-    else { e = wb::select_generic_launch(a, dtype, sm_count(), st); bump(LC_GENERIC); }
-    if (e != cudaSuccess) return fail_cuda(e, "sample_rows level 1");
-    // level 2: the rows whose kept set may reach past those candidates, with up to 16384 (k_big, :21)
-    int32_t* list = reinterpret_cast<int32_t*>(base + w.off_list);
-    int32_t* count = reinterpret_cast<int32_t*>(base + w.off_count);
-    gather_rows_kernel<<<1, 1024, 0, st>>>(a.out.status, rows, wb::ROW_ESCALATE, list, count);
+    if (wb::sample_async_supported(a, dtype)) {
+        // small-K rows in one pass; rows with top_k in (256, 1024] are marked for the large-K single-pass kernel
+        e = wb::sample_async_launch(a, dtype, sm_count(), st);
+        bump(LC_STREAM);
+        if (e != cudaSuccess) return fail_cuda(e, "sample_rows small-K kernel");
+        gather_two_kernel<<<1, 1024, 0, st>>>(a.out.status, rows, list_a, list_b, counts);
+        bump(LC_AUX);
+        if (prm->top_k && wb::sample_stream_supported(a, dtype)) {
+            wb::SelectArgs c = a;
+            c.row_list = list_a, c.row_count = counts;
+            e = wb::sample_stream_launch(c, dtype, sm_count(), st);
+            bump(LC_STREAM);
+            if (e != cudaSuccess) return fail_cuda(e, "sample_rows large-K kernel");
+        }
+    } else {
+        e = wb::select_generic_launch(a, dtype, sm_count(), st);
+        bump(LC_GENERIC);
+        if (e != cudaSuccess) return fail_cuda(e, "sample_rows level 1");
+        gather_two_kernel<<<1, 1024, 0, st>>>(a.out.status, rows, list_a, list_b, counts);
+        bump(LC_AUX);
+    }
+    // level 2: the rows whose kept set may reach past those candidates, with up to 16384 (k_big, :21); and the rows the
+    // single-pass kernel gave up, at level 1
     wb::SelectArgs b = a;
-    b.level_k = wb::kGenericMaxK, b.row_list = list, b.row_count = count;
-    // counters[0] counts level-1 escalations; level 2 must not count again
-    b.out.counters = nullptr;
+    b.level_k = wb::kGenericMaxK, b.row_list = list_b, b.row_count = counts + 1;
+    b.out.counters = nullptr;  // counters[0] counted the level-1 escalations already
     e = wb::select_generic_launch(b, dtype, sm_count(), st);
     bump(LC_GENERIC);
-    bump(LC_AUX);
     if (e != cudaSuccess) return fail_cuda(e, "sample_rows level 2");
     if (out->counters) { count_unresolved_kernel<<<1, 256, 0, st>>>(a.out.status, rows, out->counters); bump(LC_AUX); }
     e = cudaGetLastError();
     return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "sample_rows");
 }
+
+#ifdef WB_PHASE_TIMERS
+size_t whirl_debug_err_offset(int rows) { return ws_layout(rows).off_err; }
+#endif
 
 void whirl_launch_counts(uint64_t* out, int n) {
     for (int i = 0; i < n && i < 4; ++i) out[i] = g_launch[i].load(std::memory_order_relaxed);

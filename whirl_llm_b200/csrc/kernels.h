@@ -85,17 +85,25 @@ struct SelectArgs {
     // MODE_SAMPLE
     RowParams prm;
     RowOutputs out;
-    const int32_t* row_list;  // optional: process rows row_list[0..rows) of the batch (the escalated ones)
+    const int32_t* row_list;  // optional: process rows row_list[0..rows) of the batch (the escalated ones); bit 30 of an
+                              // entry marks a row to redo at the first candidate level
     const int32_t* row_count; // optional device count overriding `rows` (with row_list)
     int level_k;              // candidates for rows without a usable top_k (256 first level, 16384 second)
     void* ws;                 // generic: [rows][level cap] doubles of probability scratch
     uint32_t* err;            // device error word (bounded waits that ran out)
+    int only_large_k;         // large-K kernel: 0 = every row, 1 = only rows whose top_k is above kAsyncMaxK
 };
 
 constexpr int kGenericMaxK = 16384;
 size_t select_generic_ws_bytes(int ctas, int K);  // ctas = min(rows, 2 * SMs)
 cudaError_t select_generic_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
 
+// small-K single-pass kernel (sample_async.cu)
+constexpr int kAsyncMaxK = 256;
+cudaError_t sample_async_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
+bool sample_async_supported(const SelectArgs& a, int dtype);
+
+// large-K single-pass kernel (sample_stream.cu)
 constexpr int kStreamMaxK = 1024;
 cudaError_t sample_stream_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
 bool sample_stream_supported(const SelectArgs& a, int dtype);

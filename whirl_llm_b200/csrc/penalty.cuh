@@ -28,10 +28,12 @@ struct PenaltyTable {
     __device__ __forceinline__ static uint32_t hash(uint32_t t) { return (t * 2654435761u) >> (32 - 13); }
 
     // all threads of the group: clear, then insert the history (call sync between and after)
+    // (bitmap and slots are 16-byte aligned and padded to multiples of four words)
     __device__ __forceinline__ void clear(int tid, int nt, uint32_t V) {
-        const uint32_t words = (V + 31) >> 5;
-        for (uint32_t i = tid; i < words; i += nt) bitmap[i] = 0;
-        for (uint32_t i = tid; i < kPenSlots; i += nt) slots[i] = 0;
+        const uint32_t quads = (((V + 31) >> 5) + 3) >> 2;
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        for (uint32_t i = tid; i < quads; i += nt) reinterpret_cast<uint4*>(bitmap)[i] = z;
+        for (uint32_t i = tid; i < kPenSlots / 4; i += nt) reinterpret_cast<uint4*>(slots)[i] = z;
     }
     __device__ __forceinline__ void insert(int32_t t, uint32_t V) {
         if (t < 0 || uint32_t(t) >= V) return;
@@ -43,6 +45,22 @@ struct PenaltyTable {
             if (old == 0) return;
             if ((old & kPenMaxV) == tag) {
                 atomicAdd(&slots[h], 1u << kPenIdBits);
+                return;
+            }
+            h = (h + 1) & (kPenSlots - 1);
+        }
+    }
+    // the same for c occurrences at once
+    __device__ __forceinline__ void insert_n(int32_t t, uint32_t V, uint32_t c) {
+        if (t < 0 || uint32_t(t) >= V) return;
+        atomicOr(&bitmap[uint32_t(t) >> 5], 1u << (t & 31));
+        const uint32_t tag = uint32_t(t) + 1;
+        uint32_t h = hash(uint32_t(t));
+        for (int probe = 0; probe < kPenSlots; ++probe) {
+            const uint32_t old = atomicCAS(&slots[h], 0u, tag | (c << kPenIdBits));
+            if (old == 0) return;
+            if ((old & kPenMaxV) == tag) {
+                atomicAdd(&slots[h], c << kPenIdBits);
                 return;
             }
             h = (h + 1) & (kPenSlots - 1);

@@ -1,0 +1,571 @@
+// The single-pass fused sampler for rows that keep at most 256 candidates: every logits row is read from HBM once and
+// the warps that read it never wait for one another.
+//
+// One persistent CTA per SM, three roles:
+//   producer (1 warp)   bulk async copies (TMA, cp.async.bulk + mbarrier) of the CTA's rows into a ring of shared
+//                       memory stages, running ahead across row boundaries; it also fetches the first stage of the NEXT
+//                       row into a side buffer, from which the tail group derives that row's first threshold.
+//   stream (16 warps)   consume the stages: penalties from a shared bit map, running max / sum exp for the softmax
+//                       normaliser, and a threshold test; the few elements above the threshold are appended to the
+//                       row's candidate log.  No barrier between stream warps while a row streams.
+//   tail   (4 warps)    concurrently: raise the row's threshold (the K-th largest of the log so far is a valid lower
+//                       bound of the row's K-th largest), bootstrap the next row's threshold, and when a row is through:
+//                       exact K best of its log, sort, top-k / top-p / min-p in f64, the draw, the outputs.
+//
+// Why a threshold from partial data is exact: an element is dropped only when it is below a value that at least K
+// elements of the same row reach, so the K best are always in the log; the final select over the log is exact.
+//
+// It replaces the reference's topk_rows kernel (seven passes over the row, kernels/shared/sample_cand_topk_rows.h:11-98),
+// the candidate download, and the host filter and draw (src/sampling/sampler.cpp:15-147).
+#include "kernels.h"
+#include "penalty.cuh"
+#include "select_smem.cuh"
+#include "tail.cuh"
+
+namespace wb {
+
+constexpr int A_SW = 16;                      // stream warps
+constexpr int A_ST = A_SW * 32;
+constexpr int A_TW = 4;                       // tail warps
+constexpr int A_TT = A_TW * 32;
+constexpr int A_THREADS = 32 + A_ST + A_TT;
+constexpr int A_CH = 4096;                    // logits per ring stage
+constexpr int A_L = 4096;                     // candidate log entries per row slot
+constexpr int A_MAXSTAGES = 16;
+
+struct ASlot {
+    unsigned long long tau;  // current threshold candidate; elements must beat it to be logged
+    uint32_t cnt;            // log entries reserved so far (may exceed A_L: overflow)
+    int32_t row;
+    float red_m[A_SW];       // per stream warp: max, reference exponent, scaled sum
+    float red_e[A_SW];
+    double red_s[A_SW];
+};
+
+struct AShared {
+    ASlot slot[2];
+    SelScratch sel;
+    TailOut res;
+    uint32_t flag[4];
+};
+
+__device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned long long* p) {
+    return *reinterpret_cast<const volatile unsigned long long*>(p);
+}
+__device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) { return *reinterpret_cast<const volatile uint32_t*>(p); }
+
+template <typename T>
+__global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* ring = smem;                                                          // stages * ch_bytes
+    uint8_t* boot = ring + size_t(stages) * ch_bytes;                              // ch_bytes: first stage of the next row
+    unsigned long long* logs = reinterpret_cast<unsigned long long*>(boot + ch_bytes);  // 2 * A_L
+    uint32_t* hist = reinterpret_cast<uint32_t*>(logs + 2 * A_L);                 // SEL_BINS
+    unsigned long long* hand = reinterpret_cast<unsigned long long*>(hist + SEL_BINS);   // kAsyncMaxK
+    double* tail_p = reinterpret_cast<double*>(hand + kAsyncMaxK);                 // kAsyncMaxK + 2 * A_TW
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail_p + kAsyncMaxK + 2 * A_TW);  // 2 * 16 + 6
+    AShared* sh = reinterpret_cast<AShared*>(bars + 2 * A_MAXSTAGES + 8);
+    uint32_t* pen_mem = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));
+    uint64_t *full = bars, *empty = bars + A_MAXSTAGES;
+    uint64_t *closed = bars + 2 * A_MAXSTAGES, *boot_done = closed + 2, *boot_full = closed + 4, *boot_empty = closed + 5;
+    uint64_t* tbl = closed + 6;  // rendezvous of the stream threads around the rebuild of the penalty table
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const uint32_t n = uint32_t(a.n);
+    const int n_rows = a.row_count ? min(*a.row_count, a.rows) : a.rows;
+    const int my_rows = n_rows > int(blockIdx.x) ? (n_rows - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
+    const uint32_t n_chunks = (n + A_CH - 1) / A_CH;
+    const size_t row_bytes = size_t(n) * sizeof(T);
+    auto row_of = [&](int k) -> int {
+        const int li = int(blockIdx.x) + k * int(gridDim.x);
+        return a.row_list ? a.row_list[li] : li;
+    };
+    // rows whose top_k is above this kernel's limit are left to the large-K kernel (every role skips them alike)
+    auto is_large = [&](int row) -> bool {
+        if (a.mode != MODE_SAMPLE || !a.prm.top_k) return false;
+        if (a.prm.greedy && a.prm.greedy[row]) return false;
+        const int tk = a.prm.top_k[row];
+        return tk > kAsyncMaxK && tk <= kStreamMaxK;
+    };
+    auto next_row = [&](int k) -> int {
+        for (++k; k < my_rows && is_large(row_of(k)); ++k) {}
+        return k;
+    };
+
+    if (tid == 0) {
+        for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], A_SW);
+        for (int p = 0; p < 2; ++p) mbar_init(&closed[p], A_SW), mbar_init(&boot_done[p], 1);
+        mbar_init(boot_full, 1), mbar_init(boot_empty, 1), mbar_init(tbl, A_ST);
+        mbar_fence_init();
+    }
+    for (int i = tid; i < 2 * A_L; i += A_THREADS) logs[i] = 0ull;
+    __syncthreads();
+    if (my_rows == 0 || next_row(-1) >= my_rows) {
+        if (tid < my_rows && a.out.status && a.mode == MODE_SAMPLE)
+            for (int k = tid; k < my_rows; k += A_THREADS) a.out.status[row_of(k)] = ROW_LARGE_K;
+        return;
+    }
+
+    // =========================================================== producer
+    if (warp == 0) {
+        if (lane_id() != 0) return;
+        const uint32_t boot_bytes = uint32_t(row_bytes < size_t(ch_bytes) ? row_bytes : size_t(ch_bytes));
+        uint32_t it = 0;
+        int ord = 0;  // ordinal of the row among this CTA's rows that are not skipped
+        for (int k = -1; k < my_rows;) {
+            const int kn = next_row(k);
+            if (kn < my_rows) {
+                // the first stage of the next row for the tail group's bootstrap
+                const int o = k < 0 ? 0 : ord + 1;
+                if (!mbar_wait(boot_empty, (o & 1) ^ 1)) {
+                    atomicExch(a.err, 1u);
+                    return;
+                }
+                mbar_expect_tx(boot_full, boot_bytes);
+                bulk_g2s(boot, reinterpret_cast<const uint8_t*>(a.x) + size_t(row_of(kn)) * row_bytes, boot_bytes, boot_full);
+            }
+            if (k >= 0) {
+                const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x) + size_t(row_of(k)) * row_bytes;
+                for (uint32_t c = 0; c < n_chunks; ++c, ++it) {
+                    const uint32_t s = it % stages, use = it / stages;
+                    if (!mbar_wait(&empty[s], (use & 1) ^ 1)) {
+                        atomicExch(a.err, 1u);
+                        return;
+                    }
+                    const size_t off = size_t(c) * ch_bytes;
+                    const uint32_t bytes = uint32_t(row_bytes - off < size_t(ch_bytes) ? row_bytes - off : size_t(ch_bytes));
+                    mbar_expect_tx(&full[s], bytes);
+                    bulk_g2s(ring + size_t(s) * ch_bytes, src + off, bytes, &full[s]);
+                }
+                ++ord;
+            }
+            k = kn;
+        }
+        return;
+    }
+
+    const bool sample = a.mode == MODE_SAMPLE;
+    const RowParams& P = a.prm;
+    // candidates wanted for a row (the stream and the tail group must agree)
+    auto k_of = [&](int row) -> uint32_t {
+        uint32_t K;
+        if (sample) {
+            const bool greedy = P.greedy && P.greedy[row];
+            const uint32_t tk = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
+            K = greedy ? 1u : ((tk > 0 && tk <= uint32_t(kAsyncMaxK)) ? tk : uint32_t(min(a.level_k, kAsyncMaxK)));
+        } else {
+            K = uint32_t(a.K);
+        }
+        return K > n ? n : K;
+    };
+
+    // =========================================================== tail
+    if (warp > A_SW) {
+        const Group<A_TT> g{tid - 32 - A_ST, 2};
+
+        // first threshold of row k (slot k & 1) from its first stage: the (K + h)-th largest raw logit there, h = history
+        // tokens inside the stage (at most h of the best can be pushed down by the penalties, so K stay at or above it)
+        auto bootstrap = [&](int k, int o) -> bool {  // row ordinal o (slot o & 1) is the CTA's k-th row
+            const int p = o & 1;
+            bool ok = true;
+            if (g.tid == 0) ok = mbar_wait(boot_full, o & 1);
+            if (g.sync_or(!ok)) return false;
+            if (g.tid != 0) mbar_wait(boot_full, o & 1);
+            const int row = row_of(k);
+            const uint32_t ne = n < uint32_t(A_CH) ? n : uint32_t(A_CH);
+            uint32_t K = k_of(row);
+            if (sample && P.hist && P.hist_len[row] > 0) {
+                const int32_t* h = P.hist + size_t(row) * P.hist_stride;
+                const int hl = min(P.hist_len[row], kMaxHist);
+                // distinct history tokens inside the stage: mark them in a small bit map (the select scratch), count bits
+                for (int i = g.tid; i < A_CH / 32; i += A_TT) hist[i] = 0;
+                g.sync();
+                for (int i = g.tid; i < hl; i += A_TT) {
+                    const uint32_t t = uint32_t(h[i]);
+                    if (t < ne) atomicOr(&hist[t >> 5], 1u << (t & 31));
+                }
+                if (g.tid == 0) sh->flag[0] = 0;
+                g.sync();
+                uint32_t c = g.tid < A_CH / 32 ? uint32_t(__popc(hist[g.tid])) : 0u;
+                c = warp_sum(c);
+                if ((g.tid & 31) == 0) atomicAdd(&sh->flag[0], c);
+                g.sync();
+                K += sh->flag[0];
+            }
+            unsigned long long tau = 0ull;
+            if (K <= ne) tau = (unsigned long long)select_key_kth<A_TT, T>(g, reinterpret_cast<const T*>(boot), ne, K, hist, &sh->sel) << 32;
+            g.sync();
+            if (g.tid == 0) {
+                sh->slot[p].tau = tau;
+                sh->slot[p].cnt = 0;
+                sh->slot[p].row = row;
+                mbar_arrive(boot_empty);
+                mbar_arrive(&boot_done[p]);
+            }
+            return true;
+        };
+
+        if (sample && a.out.status)
+            for (int k = g.tid; k < my_rows; k += A_TT)
+                if (is_large(row_of(k))) a.out.status[row_of(k)] = ROW_LARGE_K;
+        if (!bootstrap(next_row(-1), 0)) {
+            if (g.tid == 0) atomicExch(a.err, 2u);
+            return;
+        }
+        int ord = 0;
+        for (int k = next_row(-1); k < my_rows; ++ord) {
+            const int kn = next_row(k);
+            const int p = ord & 1;
+            ASlot* sl = &sh->slot[p];
+            unsigned long long* log = logs + size_t(p) * A_L;
+            const int row = row_of(k);
+            const uint32_t K = k_of(row);
+            bool booted = kn >= my_rows;
+            uint32_t n_last = 0;
+#ifdef WB_PHASE_TIMERS
+            uint32_t n_refine = 0;
+#endif
+            const uint32_t step = K / 2 > 48 ? K / 2 : 48;
+            // ---- while the row streams: raise its threshold, prepare the next row
+            for (uint32_t spin = 0;; ++spin) {
+                if (g.tid == 0) {
+                    sh->flag[1] = mbar_try_wait(&closed[p], (ord >> 1) & 1) ? 1u : 0u;
+                    const uint32_t c = ld_volatile_u32(&sl->cnt);
+                    sh->flag[2] = c < uint32_t(A_L) ? c : uint32_t(A_L);
+                }
+                g.sync();
+                const bool done = sh->flag[1] != 0;
+                const uint32_t nlog = sh->flag[2];
+                g.sync();
+                if (done) break;
+                if (spin > (1u << 22)) {
+                    if (g.tid == 0) atomicExch(a.err, 3u);
+                    return;
+                }
+                if (nlog >= K && nlog >= n_last + step) {
+                    // entries reserved but not written yet read as zero and rank last: the bound stays valid
+                    const unsigned long long kth = select_kth<A_TT>(g, log, nlog, K, hist, &sh->sel);
+                    if (g.tid == 0 && kth > sl->tau) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = kth;
+                    n_last = nlog;
+#ifdef WB_PHASE_TIMERS
+                    ++n_refine;
+#endif
+                    g.sync();
+                } else if (!booted) {
+                    if (!bootstrap(kn, ord + 1)) {
+                        if (g.tid == 0) atomicExch(a.err, 2u);
+                        return;
+                    }
+                    booted = true;
+                } else {
+                    __nanosleep(200);
+                }
+            }
+            if (!booted && !bootstrap(kn, ord + 1)) {
+                if (g.tid == 0) atomicExch(a.err, 2u);
+                return;
+            }
+            // acquire the stream warps' writes
+            mbar_wait(&closed[p], (ord >> 1) & 1);
+            // ---- the row is through
+            const uint32_t total = sl->cnt;
+            const bool overflow = total > uint32_t(A_L);
+#ifdef WB_PHASE_TIMERS
+            if (g.tid == 0) {
+                if (overflow) atomicAdd(&a.err[1], 1u);
+                atomicMax(&a.err[2], total);
+                atomicAdd(&a.err[3], n_refine);
+            }
+#endif
+            const uint32_t nlog = overflow ? uint32_t(A_L) : total;
+            // row max and normaliser: combine the stream warps' partials
+            const bool greedy = sample && P.greedy && P.greedy[row];
+            const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
+            float M = -INFINITY;
+            double S = 0;
+            {
+                const double cexp = double(inv_t * kLog2e);
+                for (int w = 0; w < A_SW; ++w) M = fmaxf(M, sl->red_m[w]);
+                for (int w = 0; w < A_SW; ++w)
+                    if (sl->red_m[w] != -INFINITY) S += sl->red_s[w] * exp2(double(sl->red_e[w]) - double(M) * cexp);
+            }
+            const float sum = greedy ? 0.f : float(S);
+            uint32_t kept = 0;
+            if (!overflow) {
+                if (nlog > K) {
+                    const unsigned long long kth = select_kth<A_TT>(g, log, nlog, K, hist, &sh->sel);
+                    write_survivors<A_TT>(g, log, nlog, kth, hand, kAsyncMaxK, &sh->sel);
+                    kept = sh->sel.wcnt < uint32_t(kAsyncMaxK) ? sh->sel.wcnt : uint32_t(kAsyncMaxK);
+                } else {
+                    for (uint32_t i = g.tid; i < nlog; i += A_TT) hand[i] = log[i];
+                    kept = nlog;
+                }
+            }
+            uint32_t cap = 1;
+            while (cap < kept) cap <<= 1;
+            g.sync();
+            for (uint32_t i = kept + g.tid; i < cap; i += A_TT) hand[i] = 0ull;
+            // the log is free for row k + 2 once it is zero again
+            for (uint32_t i = g.tid; i < nlog; i += A_TT) log[i] = 0ull;
+            g.sync();
+            if (overflow) {
+                // more candidates than the log holds (rows in adversarial order): the multi-pass kernel takes the row
+                if (g.tid == 0) a.out.status[row] = ROW_RETRY;
+            } else if (!sample) {
+                if (g.tid == 0) a.out.status[row] = ROW_DONE;
+                sort_desc<A_TT>(g, reinterpret_cast<uint64_t*>(hand), cap);
+                const T* xr = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
+                for (uint32_t j = g.tid; j < kept; j += A_TT) {
+                    const uint32_t id = cand_id(hand[j]);
+                    a.ids[size_t(row) * a.K + j] = int32_t(id);
+                    a.vals[size_t(row) * a.K + j] = sizeof(T) == 4 ? reinterpret_cast<const float*>(xr)[id] : bf16_to_f32(reinterpret_cast<const uint16_t*>(xr)[id]);
+                }
+                if (g.tid == 0) a.stats[2 * row] = M, a.stats[2 * row + 1] = sum;
+            } else if (greedy) {
+                if (g.tid == 0) {
+                    const uint32_t tok = kept ? cand_id(hand[0]) : 0;
+                    a.out.token[row] = int32_t(tok);
+                    a.out.status[row] = ROW_DONE;
+                    if (a.out.n_kept) a.out.n_kept[row] = 1;
+                    if (a.out.closed) a.out.closed[row] = 1;
+                    if (a.out.stats) a.out.stats[2 * row] = kept ? float_of_key(cand_key(hand[0])) : -INFINITY, a.out.stats[2 * row + 1] = 0.f;
+                    if (a.out.kept_ids && a.out.kept_cap > 0) a.out.kept_ids[size_t(row) * a.out.kept_cap] = int32_t(tok);
+                    if (a.out.kept_p && a.out.kept_cap > 0) a.out.kept_p[size_t(row) * a.out.kept_cap] = 1.0;
+                }
+            } else {
+                TailIn in;
+                in.inv_t = inv_t;
+                in.top_k = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
+                in.top_p = P.top_p ? P.top_p[row] : 1.0, in.min_p = P.min_p ? P.min_p[row] : 0.0, in.u = P.u ? P.u[row] : 0.0;
+                in.m = M, in.sum = sum, in.cnt = kept, in.cap = cap, in.V = n;
+                in.race = P.race_key != nullptr, in.race_key = P.race_key ? P.race_key[row] : 0;
+                sample_tail<A_TT>(g, in, reinterpret_cast<uint64_t*>(hand), tail_p, &sh->res);
+                const TailOut r = sh->res;
+                if (g.tid == 0) {
+                    a.out.token[row] = int32_t(r.token);
+                    a.out.status[row] = r.status;
+                    if (a.out.n_kept) a.out.n_kept[row] = int32_t(r.n);
+                    if (a.out.closed) a.out.closed[row] = r.closed;
+                    if (a.out.stats) a.out.stats[2 * row] = M, a.out.stats[2 * row + 1] = sum;
+                    if (a.out.counters && r.status == ROW_ESCALATE) atomicAdd(&a.out.counters[0], 1u);
+                    if (a.out.counters && r.status == ROW_OPEN_TAIL) atomicAdd(&a.out.counters[1], 1u);
+                }
+                if (r.status != ROW_ESCALATE) {
+                    const uint32_t nk = min(r.n, uint32_t(max(a.out.kept_cap, 0)));
+                    for (uint32_t j = g.tid; j < nk; j += A_TT) {
+                        if (a.out.kept_ids) a.out.kept_ids[size_t(row) * a.out.kept_cap + j] = int32_t(cand_id(hand[j]));
+                        if (a.out.kept_p) a.out.kept_p[size_t(row) * a.out.kept_cap + j] = tail_p[j];
+                    }
+                }
+            }
+            g.sync();
+            k = kn;
+        }
+        return;
+    }
+
+    // =========================================================== stream
+    const Group<A_ST> g{tid - 32, 1};
+    (void)g.bar;
+    const int lane = lane_id(), sw = (tid - 32) >> 5;
+    constexpr int EPV = 16 / sizeof(T);
+    static_assert(A_CH / EPV / A_ST * EPV == 8, "eight elements per thread per stage");
+    uint32_t it = 0;
+    PenaltyTable pt;
+    pt.bitmap = pen_mem, pt.slots = pen_mem + pen_words;
+
+    uint32_t tbl_use = 0;
+    // all stream threads meet (bounded wait): false when the wait ran out
+    auto rendezvous = [&]() -> bool {
+        mbar_arrive(tbl);
+        return mbar_wait(tbl, (tbl_use++) & 1);
+    };
+    int ord = 0;
+    for (int k = next_row(-1); k < my_rows; k = next_row(k), ++ord) {
+        const int p = ord & 1;
+        const int row = row_of(k);
+        ASlot* sl = &sh->slot[p];
+        unsigned long long* log = logs + size_t(p) * A_L;
+        const bool greedy = sample && P.greedy && P.greedy[row];
+        const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
+        const float cexp = inv_t * kLog2e;
+        pt.on = false;
+        if (sample && P.hist && P.hist_len[row] > 0) {
+            pt.rep = P.rep ? P.rep[row] : 1.f, pt.pres = P.pres ? P.pres[row] : 0.f, pt.freq = P.freq ? P.freq[row] : 0.f;
+            pt.on = pt.rep != 1.f || pt.pres != 0.f || pt.freq != 0.f;
+        }
+        if (sample && P.hist) {
+            // one table for the CTA: every stream warp must be done with the previous row before it is rebuilt
+            bool ok = rendezvous();
+            if (pt.on && ok) {
+                const int32_t* hrow = P.hist + size_t(row) * P.hist_stride;
+                const int hl = min(P.hist_len[row], kMaxHist);
+                int32_t hv[kMaxHist / A_ST];
+#pragma unroll
+                for (int j = 0; j < kMaxHist / A_ST; ++j) hv[j] = (g.tid + j * A_ST) < hl ? hrow[g.tid + j * A_ST] : -1;
+                pt.clear(g.tid, A_ST, n);
+                ok = rendezvous();
+#pragma unroll
+                for (int j = 0; j < kMaxHist / A_ST; ++j) {
+                    // equal ids inside a warp insert once, with their multiplicity
+                    const uint32_t peers = __match_any_sync(0xffffffffu, hv[j]);
+                    if ((__ffs(peers) - 1) == lane) pt.insert_n(hv[j], n, uint32_t(__popc(peers)));
+                }
+                ok = rendezvous() && ok;
+            }
+            if (!ok) {
+                if (lane == 0) atomicExch(a.err, 6u);
+                return;
+            }
+        }
+        // the row's first threshold (and the slot being free again) come from the tail group
+        if (!mbar_wait(&boot_done[p], (ord >> 1) & 1)) {
+            if (lane == 0) atomicExch(a.err, 4u);
+            return;
+        }
+        float m_t = -INFINITY, e_t = 0.f, s_t = 0.f;  // running max, reference exponent ceil(m_t * cexp), sum 2^(x * cexp - e_t)
+
+        for (uint32_t c = 0; c < n_chunks; ++c, ++it) {
+            const uint32_t s = it % stages, use = it / stages;
+            if (!mbar_wait(&full[s], use & 1)) {
+                if (lane == 0) atomicExch(a.err, 5u);
+                return;
+            }
+            const uint4* vec = reinterpret_cast<const uint4*>(ring + size_t(s) * ch_bytes);
+            float xv[8];
+            uint32_t qid[2];
+            bool qvalid[2];
+            if (sizeof(T) == 4) {
+                qid[0] = c * A_CH + 4 * g.tid, qid[1] = qid[0] + 4 * A_ST;
+                qvalid[0] = qid[0] < n, qvalid[1] = qid[1] < n;
+                const uint4 ninf = make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u);
+                const uint4 q0 = qvalid[0] ? vec[g.tid] : ninf;
+                const uint4 q1 = qvalid[1] ? vec[g.tid + A_ST] : ninf;
+                xv[0] = __uint_as_float(q0.x), xv[1] = __uint_as_float(q0.y), xv[2] = __uint_as_float(q0.z), xv[3] = __uint_as_float(q0.w);
+                xv[4] = __uint_as_float(q1.x), xv[5] = __uint_as_float(q1.y), xv[6] = __uint_as_float(q1.z), xv[7] = __uint_as_float(q1.w);
+            } else {
+                qid[0] = c * A_CH + 8 * g.tid, qid[1] = qid[0] + 4;
+                qvalid[0] = qvalid[1] = qid[0] < n;
+                const uint4 q = qvalid[0] ? vec[g.tid] : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
+                xv[0] = __uint_as_float(q.x << 16), xv[1] = __uint_as_float(q.x & 0xffff0000u);
+                xv[2] = __uint_as_float(q.y << 16), xv[3] = __uint_as_float(q.y & 0xffff0000u);
+                xv[4] = __uint_as_float(q.z << 16), xv[5] = __uint_as_float(q.z & 0xffff0000u);
+                xv[6] = __uint_as_float(q.w << 16), xv[7] = __uint_as_float(q.w & 0xffff0000u);
+            }
+            const unsigned long long tau = ld_volatile_u64(&sl->tau);
+            const float tau_f = tau ? float_of_key(cand_key(tau)) : -INFINITY;
+            // NaN counts as -inf (as the reference's draft kernel does, kernels/spec_sample.hip:61,118)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) xv[j] = fmaxf(xv[j], -INFINITY);
+            // Every loaded register has been consumed above, so the shared-memory reads have completed (instructions issue
+            // in order and the fmaxf had to wait for the data): only now may the producer overwrite the stage.
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+            if (pt.on) {
+                // history tokens among this thread's 8 elements: a lane loops over its own hits only
+                uint32_t bits = (qvalid[0] ? pt.bits(qid[0], 4) : 0u) | ((qvalid[1] ? pt.bits(qid[1], 4) : 0u) << 4);
+                while (bits) {
+                    const int j = __ffs(bits) - 1;
+                    bits &= bits - 1;
+                    float x = xv[0];
+#pragma unroll
+                    for (int e = 1; e < 8; ++e) x = j == e ? xv[e] : x;
+                    x = fmaxf(pt.apply(x, qid[j >> 2] + (j & 3)), -INFINITY);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) xv[e] = j == e ? x : xv[e];
+                }
+            }
+            const float vm0 = fmaxf(fmaxf(xv[0], xv[1]), fmaxf(xv[2], xv[3])), vm1 = fmaxf(fmaxf(xv[4], xv[5]), fmaxf(xv[6], xv[7]));
+            const float vm = fmaxf(vm0, vm1);
+            if (!greedy) {
+                if (vm > m_t) {
+                    // new reference exponent: an integer at or above m * cexp, so every term is at most 1 and x * cexp - e
+                    // is one fused operation with a single rounding
+                    const float ne = ceilf(vm * cexp);
+                    s_t = (m_t == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
+                    e_t = ne, m_t = vm;
+                }
+                if (m_t != -INFINITY) {
+                    float e[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) e[j] = ex2_approx(fmaf(xv[j], cexp, -e_t));
+                    s_t += ((e[0] + e[1]) + (e[2] + e[3])) + ((e[4] + e[5]) + (e[6] + e[7]));
+                }
+            } else {
+                m_t = fmaxf(m_t, vm);
+            }
+            if (__ballot_sync(0xffffffffu, vm >= tau_f)) {
+                // rare: some lane holds an element that may beat the threshold; each such lane logs its own
+                uint32_t mask = 0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) mask |= uint32_t(qvalid[j >> 2] && xv[j] >= tau_f) << j;
+                while (mask) {
+                    const int j = __ffs(mask) - 1;
+                    mask &= mask - 1;
+                    float x = xv[0];
+#pragma unroll
+                    for (int e = 1; e < 8; ++e) x = j == e ? xv[e] : x;
+                    const unsigned long long cnd = make_cand(key_of(x), qid[j >> 2] + (j & 3));
+                    if (cnd > tau) {
+                        const uint32_t pos = atomicAdd(&sl->cnt, 1u);
+                        if (pos < uint32_t(A_L)) log[pos] = cnd;
+                    }
+                }
+            }
+        }
+        // ---- the row is through for this warp: partials, then close
+        {
+            const float wm = warp_max(m_t);
+            float we = e_t;
+            if (m_t == -INFINITY) we = -INFINITY;
+            we = warp_max(we);
+            double ds = (m_t == -INFINITY) ? 0.0 : double(s_t) * double(ex2_approx(e_t - we));
+            ds = warp_sum(ds);
+            if (lane == 0) sl->red_m[sw] = wm, sl->red_e[sw] = we, sl->red_s[sw] = ds;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&closed[p]);
+    }
+}
+
+static size_t async_fixed_smem(bool pen, int pen_words, int ch_bytes) {
+    return size_t(ch_bytes) + size_t(2) * A_L * 8 + SEL_BINS * 4 + size_t(kAsyncMaxK) * 8 + (kAsyncMaxK + 2 * A_TW) * 8 +
+           (2 * A_MAXSTAGES + 8) * 8 + sizeof(AShared) + (pen ? size_t(pen_words) * 4 + kPenSlots * 4 : 0) + 128;
+}
+
+bool sample_async_supported(const SelectArgs& a, int dtype) {
+    const size_t es = dtype == 0 ? 4 : 2;
+    if (reinterpret_cast<uintptr_t>(a.x) % 16 != 0 || (size_t(a.n) * es) % 16 != 0) return false;  // bulk copies need 16-byte rows
+    if (a.mode == MODE_TOPK && a.K > kAsyncMaxK) return false;
+    const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
+    const int pen_words = pen ? ((a.n + 31) / 32 + 3) & ~3 : 0;
+    const int ch_bytes = int(A_CH * es);
+    return async_fixed_smem(pen, pen_words, ch_bytes) + 3 * size_t(ch_bytes) <= 232448;
+}
+
+cudaError_t sample_async_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st) {
+    const size_t es = dtype == 0 ? 4 : 2;
+    const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
+    const int pen_words = pen ? ((a.n + 31) / 32 + 3) & ~3 : 0;
+    const int ch_bytes = int(A_CH * es);
+    const size_t fixed = async_fixed_smem(pen, pen_words, ch_bytes);
+    int stages = int((232448 - fixed) / ch_bytes);
+    if (stages > A_MAXSTAGES) stages = A_MAXSTAGES;
+    if (stages < 3) return cudaErrorInvalidConfiguration;
+    const size_t smem = fixed + size_t(stages) * ch_bytes;
+    const int grid = a.rows < sm_count ? a.rows : sm_count;
+    const cudaError_t em = cudaMemsetAsync(a.err, 0, 16, st);
+    if (em != cudaSuccess) return em;
+    if (dtype == 0) {
+        const cudaError_t e = cudaFuncSetAttribute(sample_async_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+        sample_async_kernel<float><<<grid, A_THREADS, smem, st>>>(a, stages, pen_words, ch_bytes);
+    } else {
+        const cudaError_t e = cudaFuncSetAttribute(sample_async_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return e;
+        sample_async_kernel<uint16_t><<<grid, A_THREADS, smem, st>>>(a, stages, pen_words, ch_bytes);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace wb

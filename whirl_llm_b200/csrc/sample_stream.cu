@@ -15,6 +15,7 @@
 // image of the logit, so "larger candidate" is "logit desc, id asc", the order of the host comparators.
 #include "kernels.h"
 #include "penalty.cuh"
+#include "select_smem.cuh"
 #include "tail.cuh"
 
 namespace wb {
@@ -27,8 +28,7 @@ constexpr int NTHREADS = 32 + ST + ET;  // + the producer warp
 constexpr int CH_ELEMS = 4096;         // logits per ring stage
 constexpr int BUF_CAP = 8192;          // candidate buffer entries
 constexpr int BUF_TRIG = 4096;         // select when the buffer holds more than this after a stage
-constexpr int NBINS = 2048;
-constexpr int LIST_MAX = 512;
+constexpr int NBINS = SEL_BINS;
 constexpr int HAND = 2;                // hand-over buffers between stream and epilogue
 
 struct Hand {
@@ -38,8 +38,9 @@ struct Hand {
 };
 
 struct StreamShared {
-    unsigned long long lo, hi, kth, tau;
-    uint32_t cnt, bin, need, eq, lcnt, wcnt, abort_flag;
+    SelScratch sel;
+    unsigned long long tau;
+    uint32_t cnt, abort_flag;
     float tau_f;
     float red_m[SW];
     double red_s[SW];
@@ -47,112 +48,15 @@ struct StreamShared {
     TailOut res;
 };
 
+#ifdef WB_PHASE_TIMERS
+#define WB_T(var) const long long var = clock64()
+#define WB_ACC(i, t0, t1) do { if (g.tid == 0) tacc[i] += (t1) - (t0); } while (0)
+#else
+#define WB_T(var)
+#define WB_ACC(i, t0, t1)
+#endif
+
 __device__ __forceinline__ uint32_t ld_volatile(const uint32_t* p) { return *reinterpret_cast<const volatile uint32_t*>(p); }
-
-// The K-th largest of buf[0..cnt) (1 <= K <= cnt), entries distinct.  All ST stream threads call it.
-// hist: NBINS words, also used as the list of the entries of one bin.
-__device__ unsigned long long select_kth(const Group<ST>& g, const unsigned long long* buf, uint32_t cnt, uint32_t K,
-                                         uint32_t* hist, StreamShared* sh) {
-    if (g.tid == 0) sh->lo = ~0ull, sh->hi = 0ull;
-    g.sync();
-    {
-        unsigned long long lo = ~0ull, hi = 0ull;
-        for (uint32_t i = g.tid; i < cnt; i += ST) {
-            const unsigned long long c = buf[i];
-            lo = c < lo ? c : lo, hi = c > hi ? c : hi;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const unsigned long long l2 = __shfl_xor_sync(0xffffffffu, lo, o), h2 = __shfl_xor_sync(0xffffffffu, hi, o);
-            lo = l2 < lo ? l2 : lo, hi = h2 > hi ? h2 : hi;
-        }
-        if ((g.tid & 31) == 0) atomicMin(&sh->lo, lo), atomicMax(&sh->hi, hi);
-    }
-    g.sync();
-    unsigned long long lo = sh->lo, hi = sh->hi;
-    uint32_t need = K;
-    for (int pass = 0; pass < 8; ++pass) {
-        const unsigned long long range = hi - lo;
-        if (range == 0) return lo;
-        const int bits = 64 - __clzll((long long)range);
-        const int sa = bits > 11 ? bits - 11 : 0;  // (range >> sa) < NBINS
-        for (int i = g.tid; i < NBINS; i += ST) hist[i] = 0;
-        g.sync();
-        for (uint32_t i = g.tid; i < cnt; i += ST) {
-            const unsigned long long c = buf[i];
-            if (c >= lo && c <= hi) atomicAdd(&hist[uint32_t((c - lo) >> sa)], 1u);
-        }
-        g.sync();
-        if (g.tid < 32) {
-            // bins from the top down; lane l owns 64 consecutive bins in that order
-            constexpr int per = NBINS / 32;
-            uint32_t s = 0;
-            for (int j = 0; j < per; ++j) s += hist[NBINS - 1 - (g.tid * per + j)];
-            const uint32_t incl = warp_scan_incl(s), excl = incl - s;
-            if (excl < need && incl >= need) {
-                uint32_t r = need - excl;
-                for (int j = 0; j < per; ++j) {
-                    const int b = NBINS - 1 - (g.tid * per + j);
-                    const uint32_t c = hist[b];
-                    if (c >= r) {
-                        sh->bin = b, sh->need = r, sh->eq = c;
-                        break;
-                    }
-                    r -= c;
-                }
-            }
-            if (g.tid == 0) sh->lcnt = 0;
-        }
-        g.sync();
-        const uint32_t b = sh->bin, cb = sh->eq;
-        need = sh->need;
-        const unsigned long long nlo = lo + ((unsigned long long)b << sa);
-        if (sa == 0) return nlo;
-        unsigned long long nhi = nlo + ((1ull << sa) - 1);
-        nhi = nhi > hi ? hi : nhi;
-        if (cb <= LIST_MAX) {
-            // few entries left in the bin: rank them against each other
-            unsigned long long* list = reinterpret_cast<unsigned long long*>(hist);
-            for (uint32_t i = g.tid; i < cnt; i += ST) {
-                const unsigned long long c = buf[i];
-                if (c >= nlo && c <= nhi) list[atomicAdd(&sh->lcnt, 1u)] = c;
-            }
-            g.sync();
-            if (g.tid < cb) {
-                const unsigned long long mine = list[g.tid];
-                uint32_t rank = 0;
-                for (uint32_t j = 0; j < cb; ++j) rank += list[j] > mine;
-                if (rank == need - 1) sh->kth = mine;
-            }
-            g.sync();
-            return sh->kth;
-        }
-        lo = nlo, hi = nhi;
-        g.sync();
-    }
-    return lo;
-}
-
-// survivors (>= kth) of buf[0..cnt) -> dst[0..); returns nothing, sh->wcnt holds the count after the barrier
-__device__ void write_survivors(const Group<ST>& g, const unsigned long long* buf, uint32_t cnt, unsigned long long kth,
-                                unsigned long long* dst, StreamShared* sh) {
-    if (g.tid == 0) sh->wcnt = 0;
-    g.sync();
-    const uint32_t rounds = (cnt + ST - 1) / ST;
-    for (uint32_t r = 0; r < rounds; ++r) {
-        const uint32_t i = r * ST + g.tid;
-        const unsigned long long c = i < cnt ? buf[i] : 0ull;
-        const bool take = i < cnt && c >= kth;
-        const uint32_t bal = __ballot_sync(0xffffffffu, take);
-        if (bal) {
-            uint32_t base = 0;
-            if (lane_id() == 0) base = atomicAdd(&sh->wcnt, uint32_t(__popc(bal)));
-            base = __shfl_sync(0xffffffffu, base, 0);
-            if (take) dst[base + __popc(bal & ((1u << lane_id()) - 1))] = c;
-        }
-    }
-    g.sync();
-}
 
 template <typename T>
 __global__ void __launch_bounds__(NTHREADS, 1)
@@ -166,13 +70,17 @@ sample_stream_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
     double* tail_p = reinterpret_cast<double*>(hand_c + HAND * kStreamMaxK);       // kStreamMaxK + 2 * EW
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail_p + kStreamMaxK + 2 * EW);   // 2 * stages + 2 * HAND
     StreamShared* sh = reinterpret_cast<StreamShared*>(bars + 2 * 32 + 2 * HAND);
-    uint32_t* pen_mem = reinterpret_cast<uint32_t*>(sh + 1);
+    uint32_t* pen_mem = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));
     uint64_t *full = bars, *empty = bars + 32, *hfull = bars + 64, *hempty = bars + 64 + HAND;
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const uint32_t n = uint32_t(a.n);
-    const int rows = a.rows;
-    const int my_rows = (rows - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
+    const int rows = a.row_count ? min(*a.row_count, a.rows) : a.rows;
+    const int my_rows = rows > int(blockIdx.x) ? (rows - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
+    auto row_of = [&](int k) -> int {
+        const int li = int(blockIdx.x) + k * int(gridDim.x);
+        return a.row_list ? (a.row_list[li] & 0x3fffffff) : li;
+    };
     const uint32_t n_chunks = (n + CH_ELEMS - 1) / CH_ELEMS;
     const size_t row_bytes = size_t(n) * sizeof(T);
 
@@ -183,13 +91,14 @@ sample_stream_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
         mbar_fence_init();
     }
     __syncthreads();
+    if (my_rows == 0) return;
 
     // =========================================================== producer
     if (warp == 0) {
         if (lane_id() != 0) return;
         uint32_t it = 0;
         for (int k = 0; k < my_rows; ++k) {
-            const int row = int(blockIdx.x) + k * int(gridDim.x);
+            const int row = row_of(k);
             const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x) + size_t(row) * row_bytes;
             for (uint32_t c = 0; c < n_chunks; ++c, ++it) {
                 const uint32_t s = it % stages, use = it / stages;
@@ -290,9 +199,14 @@ sample_stream_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
     uint32_t it = 0;
     PenaltyTable pt;
     pt.bitmap = pen_mem, pt.slots = pen_mem + pen_words;
+#ifdef WB_PHASE_TIMERS
+    long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // setup, wait full, process, barrier, select, final, hand wait, total
+    const long long t_begin = clock64();
+#endif
 
     for (int k = 0; k < my_rows; ++k) {
-        const int row = int(blockIdx.x) + k * int(gridDim.x);
+        const int row = row_of(k);
+        WB_T(t_s0);
         // ---- the row's settings
         bool greedy = false;
         uint32_t K;
@@ -328,10 +242,15 @@ sample_stream_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
         unsigned long long tau = 0ull;
         float tau_f = -INFINITY;
         float m_t = -INFINITY, s_t = 0.f;
+        WB_T(t_s1);
+        WB_ACC(0, t_s0, t_s1);
 
         for (uint32_t c = 0; c < n_chunks; ++c, ++it) {
             const uint32_t s = it % stages, use = it / stages;
+            WB_T(t_w0);
             const bool ok = mbar_wait(&full[s], use & 1);
+            WB_T(t_w1);
+            WB_ACC(1, t_w0, t_w1);
             if (!ok) sh->abort_flag = 1;
             const uint4* vec = reinterpret_cast<const uint4*>(ring + size_t(s) * ch_bytes);
             float xv[8];
@@ -353,22 +272,26 @@ sample_stream_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
                 xv[4] = __uint_as_float(q.z << 16), xv[5] = __uint_as_float(q.z & 0xffff0000u);
                 xv[6] = __uint_as_float(q.w << 16), xv[7] = __uint_as_float(q.w & 0xffff0000u);
             }
-            // the stage's data is in registers: hand the stage back to the producer
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
             // NaN counts as -inf (as the reference's draft kernel does, kernels/spec_sample.hip:61,118)
 #pragma unroll
             for (int j = 0; j < 8; ++j) xv[j] = fmaxf(xv[j], -INFINITY);
+            // Every loaded register has been consumed above, so the shared-memory reads have completed (instructions issue
+            // in order and the fmaxf had to wait for the data): only now may the producer overwrite the stage.
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
             if (pt.on) {
+                // history tokens among this thread's 8 elements: one bit each.  A lane loops over its own hits only, so
+                // the warp pays for the most hits any lane has (one or two), not for all eight positions.
+                uint32_t bits = (qvalid[0] ? pt.bits(qid[0], 4) : 0u) | ((qvalid[1] ? pt.bits(qid[1], 4) : 0u) << 4);
+                while (bits) {
+                    const int j = __ffs(bits) - 1;
+                    bits &= bits - 1;
+                    float x = xv[0];
 #pragma unroll
-                for (int q = 0; q < QPT; ++q) {
-                    if (!qvalid[q]) continue;
-                    const uint32_t bits = pt.bits(qid[q], 4);
-                    if (bits) {
+                    for (int e = 1; e < 8; ++e) x = j == e ? xv[e] : x;
+                    x = fmaxf(pt.apply(x, qid[j >> 2] + (j & 3)), -INFINITY);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            if ((bits >> j) & 1u) xv[q * 4 + j] = fmaxf(pt.apply(xv[q * 4 + j], qid[q] + j), -INFINITY);
-                    }
+                    for (int e = 0; e < 8; ++e) xv[e] = j == e ? x : xv[e];
                 }
             }
             float vmax[QPT];
@@ -414,7 +337,11 @@ sample_stream_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
             }
             // every stream thread is past the stage: does the buffer need a select?
             const bool last = c + 1 == n_chunks;
+            WB_T(t_p1);
+            WB_ACC(2, t_w1, t_p1);
             const bool flag = g.sync_or(ld_volatile(&sh->cnt) > BUF_TRIG || ld_volatile(&sh->abort_flag) != 0);
+            WB_T(t_b1);
+            WB_ACC(3, t_p1, t_b1);
             if (flag) {
                 if (ld_volatile(&sh->abort_flag)) {
                     if (g.tid == 0) atomicExch(a.err, 3u);
@@ -422,18 +349,21 @@ sample_stream_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
                 }
                 if (!last) {
                     const uint32_t cnt = sh->cnt;
-                    const unsigned long long kth = select_kth(g, buf, cnt, K, hist, sh);
+                    const unsigned long long kth = select_kth<ST>(g, buf, cnt, K, hist, &sh->sel);
                     unsigned long long* stage = reinterpret_cast<unsigned long long*>(hist);
-                    write_survivors(g, buf, cnt, kth, stage, sh);
-                    const uint32_t kept = sh->wcnt;
+                    write_survivors<ST>(g, buf, cnt, kth, stage, kStreamMaxK, &sh->sel);
+                    const uint32_t kept = sh->sel.wcnt;
                     for (uint32_t i = g.tid; i < kept; i += ST) buf[i] = stage[i];
                     if (g.tid == 0) sh->cnt = kept, sh->tau = kth, sh->tau_f = float_of_key(cand_key(kth));
                     g.sync();
                     tau = kth;
                     tau_f = float_of_key(cand_key(kth));
                 }
+                WB_T(t_c1);
+                WB_ACC(4, t_b1, t_c1);
             }
         }
+        WB_T(t_f0);
         // ---- the row is through: exact K candidates to the epilogue, with the row's max and normaliser
         {
             float wm = warp_max(m_t);
@@ -443,18 +373,21 @@ sample_stream_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
         }
         const int h = k % HAND;
         bool ok = true;
+        WB_T(t_h0);
         if (g.tid == 0) ok = mbar_wait(&hempty[h], ((k / HAND) & 1) ^ 1);
         if (g.sync_or(!ok)) {
             if (g.tid == 0) atomicExch(a.err, 4u);
             return;
         }
+        WB_T(t_h1);
+        WB_ACC(6, t_h0, t_h1);
         const uint32_t cnt = sh->cnt;
         unsigned long long* dst = hand_c + size_t(h) * kStreamMaxK;
         uint32_t kept;
         if (cnt > K) {
-            const unsigned long long kth = select_kth(g, buf, cnt, K, hist, sh);
-            write_survivors(g, buf, cnt, kth, dst, sh);
-            kept = sh->wcnt;
+            const unsigned long long kth = select_kth<ST>(g, buf, cnt, K, hist, &sh->sel);
+            write_survivors<ST>(g, buf, cnt, kth, dst, kStreamMaxK, &sh->sel);
+            kept = sh->sel.wcnt;
         } else {
             for (uint32_t i = g.tid; i < cnt; i += ST) dst[i] = buf[i];
             kept = cnt;
@@ -473,7 +406,16 @@ sample_stream_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
         }
         g.sync();
         if (g.tid == 0) mbar_arrive(&hfull[h]);
+        WB_T(t_f1);
+        WB_ACC(5, t_f0, t_f1);
     }
+#ifdef WB_PHASE_TIMERS
+    if (g.tid == 0) {
+        tacc[7] = clock64() - t_begin;
+        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 4);
+        for (int i = 0; i < 8; ++i) atomicAdd(&dbg[i], (unsigned long long)tacc[i]);
+    }
+#endif
 }
 
 static size_t stream_fixed_smem(bool pen, int pen_words) {
@@ -485,7 +427,6 @@ bool sample_stream_supported(const SelectArgs& a, int dtype) {
     const size_t es = dtype == 0 ? 4 : 2;
     if (reinterpret_cast<uintptr_t>(a.x) % 16 != 0 || (size_t(a.n) * es) % 16 != 0) return false;  // bulk copies need 16-byte rows
     if (a.mode == MODE_TOPK && a.K > kStreamMaxK) return false;
-    if (a.row_list) return false;
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
     const int pen_words = pen ? ((a.n + 31) / 32 + 3) & ~3 : 0;
     const size_t ch_bytes = CH_ELEMS * es;

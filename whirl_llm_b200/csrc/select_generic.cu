@@ -79,8 +79,8 @@ __device__ void pick_bin(uint32_t* hist, GShared* sh, int shift, int bits) {
 }
 
 template <typename T>
-__device__ void select_row(const SelectArgs& a, int row, int cap_max, int pen_words, uint64_t* cand, uint32_t* hist,
-                           GShared* sh, uint32_t* pen_mem);
+__device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_max, int pen_words, uint64_t* cand,
+                           uint32_t* hist, GShared* sh, uint32_t* pen_mem);
 
 // grid-strided over the rows (or over the entries of row_list); one row at a time per CTA
 template <typename T>
@@ -89,19 +89,20 @@ __global__ void __launch_bounds__(GT) select_generic_kernel(SelectArgs a, int ca
     uint64_t* cand = reinterpret_cast<uint64_t*>(smem);
     uint32_t* hist = reinterpret_cast<uint32_t*>(smem + size_t(cap_max) * 8);
     GShared* sh = reinterpret_cast<GShared*>(hist + GBINS);
-    uint32_t* pen_mem = reinterpret_cast<uint32_t*>(sh + 1);
+    uint32_t* pen_mem = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));
 
     const int n_rows = a.row_count ? min(*a.row_count, a.rows) : a.rows;
     for (int li = blockIdx.x; li < n_rows; li += gridDim.x) {
         __syncthreads();  // the previous row's shared state is dead
-        const int row = a.row_list ? a.row_list[li] : li;
-        select_row<T>(a, row, cap_max, pen_words, cand, hist, sh, pen_mem);
+        const int entry = a.row_list ? a.row_list[li] : li;
+        // bit 30 of a list entry: redo the row at the first candidate level (the single-pass kernel gave it up)
+        select_row<T>(a, entry & 0x3fffffff, (entry >> 30) & 1 ? min(a.level_k, kAsyncMaxK) : a.level_k, cap_max, pen_words, cand, hist, sh, pen_mem);
     }
 }
 
 template <typename T>
-__device__ void select_row(const SelectArgs& a, int row, int cap_max, int pen_words, uint64_t* cand, uint32_t* hist,
-                           GShared* sh, uint32_t* pen_mem) {
+__device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_max, int pen_words, uint64_t* cand,
+                           uint32_t* hist, GShared* sh, uint32_t* pen_mem) {
     const uint32_t n = uint32_t(a.n);
     const T* x = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
     const int tid = threadIdx.x;
@@ -162,7 +163,7 @@ __device__ void select_row(const SelectArgs& a, int row, int cap_max, int pen_wo
     uint32_t top_k = 0, K;
     if (sample) {
         top_k = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
-        K = (top_k > 0 && top_k <= uint32_t(a.level_k)) ? top_k : uint32_t(a.level_k);
+        K = (top_k > 0 && top_k <= uint32_t(level_k)) ? top_k : uint32_t(level_k);
     } else {
         K = uint32_t(a.K);
     }
@@ -249,7 +250,10 @@ __device__ void select_row(const SelectArgs& a, int row, int cap_max, int pen_wo
             a.ids[size_t(row) * a.K + j] = int32_t(id);
             a.vals[size_t(row) * a.K + j] = raw_elem(x, id);
         }
-        if (tid == 0) a.stats[2 * row] = sh->m, a.stats[2 * row + 1] = sh->sum;
+        if (tid == 0) {
+            a.stats[2 * row] = sh->m, a.stats[2 * row + 1] = sh->sum;
+            if (a.out.status) a.out.status[row] = ROW_DONE;
+        }
         return;
     }
     // ---- filter and draw
@@ -295,7 +299,7 @@ cudaError_t select_generic_launch(const SelectArgs& a, int dtype, int sm_count, 
     const int cap = pow2_at_least(kmax < 1 ? 1 : (kmax > a.n ? a.n : kmax));
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
     const int pen_words = pen ? ((a.n + 31) / 32 + 3) & ~3 : 0;
-    const size_t smem = size_t(cap) * 8 + GBINS * 4 + sizeof(GShared) + (pen ? size_t(pen_words) * 4 + kPenSlots * 4 : 0) + 16;
+    const size_t smem = size_t(cap) * 8 + GBINS * 4 + sizeof(GShared) + (pen ? size_t(pen_words) * 4 + kPenSlots * 4 : 0) + 48;
     cudaError_t e;
     if (dtype == 0) {
         e = cudaFuncSetAttribute(select_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));

@@ -1,0 +1,169 @@
+// Exact selection inside shared memory by a group of NT threads: the K-th largest of a set of distinct 64-bit
+// candidates by adaptive-range histogram passes (2048 bins over [lo, hi] of what is left), finishing by direct
+// ranking once the bin that holds the answer has few entries.
+#pragma once
+
+#include "common.cuh"
+
+namespace wb {
+
+constexpr int SEL_BINS = 2048;
+constexpr int SEL_LIST = 256;  // rank directly when the target bin holds at most this many entries
+
+struct SelScratch {
+    unsigned long long lo, hi, kth;
+    uint32_t bin, need, eq, lcnt, wcnt;
+};
+
+// The K-th largest of buf[0..cnt) (1 <= K <= cnt; entries distinct; zeros allowed as "empty", they rank last).
+// hist: SEL_BINS words of shared scratch (also used as a list of up to SEL_LIST candidates).  Every thread of the
+// group calls it and gets the same answer.
+template <int NT>
+__device__ unsigned long long select_kth(const Group<NT>& g, const unsigned long long* buf, uint32_t cnt, uint32_t K,
+                                         uint32_t* hist, SelScratch* sc) {
+    if (g.tid == 0) sc->lo = ~0ull, sc->hi = 0ull;
+    g.sync();
+    {
+        unsigned long long lo = ~0ull, hi = 0ull;
+        for (uint32_t i = g.tid; i < cnt; i += NT) {
+            const unsigned long long c = buf[i];
+            lo = c < lo ? c : lo, hi = c > hi ? c : hi;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long l2 = __shfl_xor_sync(0xffffffffu, lo, o), h2 = __shfl_xor_sync(0xffffffffu, hi, o);
+            lo = l2 < lo ? l2 : lo, hi = h2 > hi ? h2 : hi;
+        }
+        if ((g.tid & 31) == 0) atomicMin(&sc->lo, lo), atomicMax(&sc->hi, hi);
+    }
+    g.sync();
+    unsigned long long lo = sc->lo, hi = sc->hi;
+    uint32_t need = K;
+    for (int pass = 0; pass < 8; ++pass) {
+        const unsigned long long range = hi - lo;
+        if (range == 0) return lo;
+        const int bits = 64 - __clzll((long long)range);
+        const int sa = bits > 11 ? bits - 11 : 0;  // (range >> sa) < SEL_BINS
+        for (int i = g.tid; i < SEL_BINS; i += NT) hist[i] = 0;
+        g.sync();
+        for (uint32_t i = g.tid; i < cnt; i += NT) {
+            const unsigned long long c = buf[i];
+            if (c >= lo && c <= hi) atomicAdd(&hist[uint32_t((c - lo) >> sa)], 1u);
+        }
+        g.sync();
+        if (g.tid < 32) {
+            // bins from the top down; lane l owns 64 consecutive bins in that order
+            constexpr int per = SEL_BINS / 32;
+            uint32_t s = 0;
+            for (int j = 0; j < per; ++j) s += hist[SEL_BINS - 1 - (g.tid * per + j)];
+            const uint32_t incl = warp_scan_incl(s), excl = incl - s;
+            if (excl < need && incl >= need) {
+                uint32_t r = need - excl;
+                for (int j = 0; j < per; ++j) {
+                    const int b = SEL_BINS - 1 - (g.tid * per + j);
+                    const uint32_t c = hist[b];
+                    if (c >= r) {
+                        sc->bin = b, sc->need = r, sc->eq = c;
+                        break;
+                    }
+                    r -= c;
+                }
+            }
+            if (g.tid == 0) sc->lcnt = 0;
+        }
+        g.sync();
+        const uint32_t b = sc->bin, cb = sc->eq;
+        need = sc->need;
+        const unsigned long long nlo = lo + ((unsigned long long)b << sa);
+        if (sa == 0) return nlo;
+        unsigned long long nhi = nlo + ((1ull << sa) - 1);
+        nhi = nhi > hi ? hi : nhi;
+        if (cb <= SEL_LIST) {
+            unsigned long long* list = reinterpret_cast<unsigned long long*>(hist);
+            for (uint32_t i = g.tid; i < cnt; i += NT) {
+                const unsigned long long c = buf[i];
+                if (c >= nlo && c <= nhi) list[atomicAdd(&sc->lcnt, 1u)] = c;
+            }
+            g.sync();
+            for (uint32_t t = g.tid; t < cb; t += NT) {
+                const unsigned long long mine = list[t];
+                uint32_t rank = 0;
+                for (uint32_t j = 0; j < cb; ++j) rank += list[j] > mine;
+                if (rank == need - 1) sc->kth = mine;
+            }
+            g.sync();
+            return sc->kth;
+        }
+        lo = nlo, hi = nhi;
+        g.sync();
+    }
+    return lo;
+}
+
+// Entries >= kth of buf[0..cnt) -> dst[0..), any order; after the call sc->wcnt holds how many.
+template <int NT>
+__device__ void write_survivors(const Group<NT>& g, const unsigned long long* buf, uint32_t cnt, unsigned long long kth,
+                                unsigned long long* dst, uint32_t dst_cap, SelScratch* sc) {
+    if (g.tid == 0) sc->wcnt = 0;
+    g.sync();
+    const uint32_t rounds = (cnt + NT - 1) / NT;
+    for (uint32_t r = 0; r < rounds; ++r) {
+        const uint32_t i = r * NT + g.tid;
+        const unsigned long long c = i < cnt ? buf[i] : 0ull;
+        const bool take = i < cnt && c >= kth && c != 0ull;
+        const uint32_t bal = __ballot_sync(0xffffffffu, take);
+        if (bal) {
+            uint32_t base = 0;
+            if (lane_id() == 0) base = atomicAdd(&sc->wcnt, uint32_t(__popc(bal)));
+            base = __shfl_sync(0xffffffffu, base, 0);
+            const uint32_t pos = base + __popc(bal & ((1u << lane_id()) - 1));
+            if (take && pos < dst_cap) dst[pos] = c;
+        }
+    }
+    g.sync();
+}
+
+// The K-th largest ordering key among n floats in shared memory (1 <= K <= n), by three digit passes (11 + 11 + 10).
+// NaN ranks lowest.  hist: SEL_BINS words.
+template <int NT, typename T>
+__device__ uint32_t select_key_kth(const Group<NT>& g, const T* x, uint32_t n, uint32_t K, uint32_t* hist, SelScratch* sc) {
+    uint32_t prefix = 0, mask = 0, need = K;
+    const int shifts[3] = {21, 10, 0}, widths[3] = {11, 11, 10};
+    for (int ps = 0; ps < 3; ++ps) {
+        const uint32_t bm = (1u << widths[ps]) - 1;
+        for (int i = g.tid; i < SEL_BINS; i += NT) hist[i] = 0;
+        g.sync();
+        for (uint32_t i = g.tid; i < n; i += NT) {
+            const float v = sizeof(T) == 4 ? reinterpret_cast<const float*>(x)[i] : bf16_to_f32(reinterpret_cast<const uint16_t*>(x)[i]);
+            const uint32_t k = key_of(v);
+            if ((k & mask) == prefix) atomicAdd(&hist[(k >> shifts[ps]) & bm], 1u);
+        }
+        g.sync();
+        if (g.tid < 32) {
+            const int nb = 1 << widths[ps], per = nb / 32;
+            uint32_t s = 0;
+            for (int j = 0; j < per; ++j) s += hist[nb - 1 - (g.tid * per + j)];
+            const uint32_t incl = warp_scan_incl(s), excl = incl - s;
+            if (excl < need && incl >= need) {
+                uint32_t r = need - excl;
+                for (int j = 0; j < per; ++j) {
+                    const int b = nb - 1 - (g.tid * per + j);
+                    const uint32_t c = hist[b];
+                    if (c >= r) {
+                        sc->bin = b, sc->need = r;
+                        break;
+                    }
+                    r -= c;
+                }
+            }
+        }
+        g.sync();
+        prefix |= sc->bin << shifts[ps];
+        need = sc->need;
+        mask |= bm << shifts[ps];
+        g.sync();
+    }
+    return prefix;
+}
+
+}  // namespace wb
