@@ -17,6 +17,8 @@
 //
 // It replaces the reference's topk_rows kernel (seven passes over the row, kernels/shared/sample_cand_topk_rows.h:11-98),
 // the candidate download, and the host filter and draw (src/sampling/sampler.cpp:15-147).
+#include <type_traits>
+
 #include "kernels.h"
 #include "penalty.cuh"
 #include "select_smem.cuh"
@@ -62,8 +64,9 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     unsigned long long* logs = reinterpret_cast<unsigned long long*>(boot + ch_bytes);  // 2 * A_L
     uint32_t* hist = reinterpret_cast<uint32_t*>(logs + 2 * A_L);                 // SEL_BINS
     unsigned long long* hand = reinterpret_cast<unsigned long long*>(hist + SEL_BINS);   // kAsyncMaxK
-    double* tail_p = reinterpret_cast<double*>(hand + kAsyncMaxK);                 // kAsyncMaxK + 2 * A_TW
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tail_p + kAsyncMaxK + 2 * A_TW);  // 2 * 16 + 6
+    double* tail_p = reinterpret_cast<double*>(hand + kAsyncMaxK);                 // 2 * (kAsyncMaxK + 2 * A_TW)
+    double* tail_q = tail_p + kAsyncMaxK + 2 * A_TW;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail_q + kAsyncMaxK + 2 * A_TW);  // 2 * 16 + 8
     AShared* sh = reinterpret_cast<AShared*>(bars + 2 * A_MAXSTAGES + 8);
     uint32_t* pen_mem = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));
     uint64_t *full = bars, *empty = bars + A_MAXSTAGES;
@@ -112,6 +115,9 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         const uint32_t boot_bytes = uint32_t(row_bytes < size_t(ch_bytes) ? row_bytes : size_t(ch_bytes));
         uint32_t it = 0;
         int ord = 0;  // ordinal of the row among this CTA's rows that are not skipped
+#ifdef WB_PHASE_TIMERS
+        long long tp_wait = 0;
+#endif
         for (int k = -1; k < my_rows;) {
             const int kn = next_row(k);
             if (kn < my_rows) {
@@ -128,10 +134,16 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x) + size_t(row_of(k)) * row_bytes;
                 for (uint32_t c = 0; c < n_chunks; ++c, ++it) {
                     const uint32_t s = it % stages, use = it / stages;
+#ifdef WB_PHASE_TIMERS
+                    const long long tw0 = clock64();
+#endif
                     if (!mbar_wait(&empty[s], (use & 1) ^ 1)) {
                         atomicExch(a.err, 1u);
                         return;
                     }
+#ifdef WB_PHASE_TIMERS
+                    tp_wait += clock64() - tw0;
+#endif
                     const size_t off = size_t(c) * ch_bytes;
                     const uint32_t bytes = uint32_t(row_bytes - off < size_t(ch_bytes) ? row_bytes - off : size_t(ch_bytes));
                     mbar_expect_tx(&full[s], bytes);
@@ -141,6 +153,9 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             }
             k = kn;
         }
+#ifdef WB_PHASE_TIMERS
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 4) + 7, (unsigned long long)tp_wait);
+#endif
         return;
     }
 
@@ -192,8 +207,33 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 g.sync();
                 K += sh->flag[0];
             }
+            // A valid bound without looking at every order statistic: split the stage into G interleaved groups, take each
+            // group's maximum; the K-th largest of the G maxima has K distinct elements at or above it.
             unsigned long long tau = 0ull;
-            if (K <= ne) tau = (unsigned long long)select_key_kth<A_TT, T>(g, reinterpret_cast<const T*>(boot), ne, K, hist, &sh->sel) << 32;
+            const uint32_t G = K <= 96 ? 128u : (K <= 384 ? 512u : 0u);
+            if (K <= ne && G != 0 && ne >= 4 * G) {
+                unsigned long long* gm = reinterpret_cast<unsigned long long*>(hist);  // G group maxima as (key, group)
+                const T* bx = reinterpret_cast<const T*>(boot);
+                for (uint32_t grp = g.tid; grp < G; grp += A_TT) {
+                    float m = -INFINITY;
+                    for (uint32_t i = grp; i < ne; i += G) {
+                        const float v = sizeof(T) == 4 ? reinterpret_cast<const float*>(bx)[i] : bf16_to_f32(reinterpret_cast<const uint16_t*>(bx)[i]);
+                        m = fmaxf(m, v);  // NaN is ignored
+                    }
+                    gm[grp] = (unsigned long long)key_of(m) << 32 | grp;
+                }
+                g.sync();
+                for (uint32_t t = g.tid; t < G; t += A_TT) {
+                    const unsigned long long mine = gm[t];
+                    uint32_t rank = 0;
+                    for (uint32_t j = 0; j < G; ++j) rank += gm[j] > mine;
+                    if (rank == K - 1) sh->sel.kth = mine;
+                }
+                g.sync();
+                tau = sh->sel.kth & 0xffffffff00000000ull;
+            } else if (K <= ne) {
+                tau = (unsigned long long)select_key_bound<A_TT, T>(g, reinterpret_cast<const T*>(boot), ne, K, hist, &sh->sel) << 32;
+            }
             g.sync();
             if (g.tid == 0) {
                 sh->slot[p].tau = tau;
@@ -205,6 +245,13 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             return true;
         };
 
+#ifdef WB_PHASE_TIMERS
+        long long tt[4] = {0, 0, 0, 0};  // bootstrap, refine, final, total
+        const long long tt0 = clock64();
+#define TT_ADD(i, t0) do { if (g.tid == 0) tt[i] += clock64() - (t0); } while (0)
+#else
+#define TT_ADD(i, t0)
+#endif
         if (sample && a.out.status)
             for (int k = g.tid; k < my_rows; k += A_TT)
                 if (is_large(row_of(k))) a.out.status[row_of(k)] = ROW_LARGE_K;
@@ -225,7 +272,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
 #ifdef WB_PHASE_TIMERS
             uint32_t n_refine = 0;
 #endif
-            const uint32_t step = K / 2 > 48 ? K / 2 : 48;
+            // the first refinement as soon as the log holds K entries, later ones when it has grown by a few K
+            uint32_t step = 0;
             // ---- while the row streams: raise its threshold, prepare the next row
             for (uint32_t spin = 0;; ++spin) {
                 if (g.tid == 0) {
@@ -243,22 +291,31 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                     return;
                 }
                 if (nlog >= K && nlog >= n_last + step) {
+#ifdef WB_PHASE_TIMERS
+                    const long long tr0 = clock64();
+#endif
                     // entries reserved but not written yet read as zero and rank last: the bound stays valid
                     const unsigned long long kth = select_kth<A_TT>(g, log, nlog, K, hist, &sh->sel);
                     if (g.tid == 0 && kth > sl->tau) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = kth;
                     n_last = nlog;
+                    step = 2 * K > 128 ? 2 * K : 128;
 #ifdef WB_PHASE_TIMERS
                     ++n_refine;
+                    TT_ADD(1, tr0);
 #endif
                     g.sync();
                 } else if (!booted) {
+#ifdef WB_PHASE_TIMERS
+                    const long long tb0 = clock64();
+#endif
                     if (!bootstrap(kn, ord + 1)) {
                         if (g.tid == 0) atomicExch(a.err, 2u);
                         return;
                     }
+                    TT_ADD(0, tb0);
                     booted = true;
                 } else {
-                    __nanosleep(200);
+                    __nanosleep(1000);
                 }
             }
             if (!booted && !bootstrap(kn, ord + 1)) {
@@ -267,8 +324,11 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             }
             // acquire the stream warps' writes
             mbar_wait(&closed[p], (ord >> 1) & 1);
+#ifdef WB_PHASE_TIMERS
+            const long long tf0 = clock64();
+#endif
             // ---- the row is through
-            const uint32_t total = sl->cnt;
+            const uint32_t total = sl->cnt;  // bit 31: a stream warp met a NaN logit
             const bool overflow = total > uint32_t(A_L);
 #ifdef WB_PHASE_TIMERS
             if (g.tid == 0) {
@@ -291,8 +351,24 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             }
             const float sum = greedy ? 0.f : float(S);
             uint32_t kept = 0;
+            bool presorted = false;
             if (!overflow) {
-                if (nlog > K) {
+                // Most of the log was appended under an earlier, looser threshold: only entries at or above the current one
+                // can be among the K best (at least K of them are).  Few survive, so rank them against each other: the
+                // rank is the position in the sorted order.
+                unsigned long long* list = reinterpret_cast<unsigned long long*>(hist);  // up to SEL_BINS / 2 entries
+                write_survivors<A_TT>(g, log, nlog, sl->tau, list, SEL_BINS / 2, &sh->sel);
+                const uint32_t m = sh->sel.wcnt;
+                if (m <= uint32_t(kAsyncMaxK)) {
+                    for (uint32_t t = g.tid; t < m; t += A_TT) {
+                        const unsigned long long mine = list[t];
+                        uint32_t rank = 0;
+                        for (uint32_t j = 0; j < m; ++j) rank += list[j] > mine;
+                        if (rank < K) hand[rank] = mine;
+                    }
+                    kept = m < K ? m : K;
+                    presorted = true;
+                } else if (nlog > K) {
                     const unsigned long long kth = select_kth<A_TT>(g, log, nlog, K, hist, &sh->sel);
                     write_survivors<A_TT>(g, log, nlog, kth, hand, kAsyncMaxK, &sh->sel);
                     kept = sh->sel.wcnt < uint32_t(kAsyncMaxK) ? sh->sel.wcnt : uint32_t(kAsyncMaxK);
@@ -313,7 +389,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 if (g.tid == 0) a.out.status[row] = ROW_RETRY;
             } else if (!sample) {
                 if (g.tid == 0) a.out.status[row] = ROW_DONE;
-                sort_desc<A_TT>(g, reinterpret_cast<uint64_t*>(hand), cap);
+                if (!presorted) sort_desc<A_TT>(g, reinterpret_cast<uint64_t*>(hand), cap);
                 const T* xr = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
                 for (uint32_t j = g.tid; j < kept; j += A_TT) {
                     const uint32_t id = cand_id(hand[j]);
@@ -339,7 +415,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 in.top_p = P.top_p ? P.top_p[row] : 1.0, in.min_p = P.min_p ? P.min_p[row] : 0.0, in.u = P.u ? P.u[row] : 0.0;
                 in.m = M, in.sum = sum, in.cnt = kept, in.cap = cap, in.V = n;
                 in.race = P.race_key != nullptr, in.race_key = P.race_key ? P.race_key[row] : 0;
-                sample_tail<A_TT>(g, in, reinterpret_cast<uint64_t*>(hand), tail_p, &sh->res);
+                in.presorted = presorted;
+                sample_tail<A_TT>(g, in, reinterpret_cast<uint64_t*>(hand), tail_p, tail_q, &sh->res);
                 const TailOut r = sh->res;
                 if (g.tid == 0) {
                     a.out.token[row] = int32_t(r.token);
@@ -359,8 +436,16 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 }
             }
             g.sync();
+            TT_ADD(2, tf0);
             k = kn;
         }
+#ifdef WB_PHASE_TIMERS
+        if (g.tid == 0) {
+            tt[3] = clock64() - tt0;
+            unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 4);
+            for (int i = 0; i < 4; ++i) atomicAdd(&dbg[i], (unsigned long long)tt[i]);
+        }
+#endif
         return;
     }
 
@@ -370,7 +455,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     const int lane = lane_id(), sw = (tid - 32) >> 5;
     constexpr int EPV = 16 / sizeof(T);
     static_assert(A_CH / EPV / A_ST * EPV == 8, "eight elements per thread per stage");
-    uint32_t it = 0;
+    uint32_t st_slot = 0, st_phase = 0;  // ring position of this warp and the parity it waits for
+    uint32_t st_ring[2] = {0, 0};
     PenaltyTable pt;
     pt.bitmap = pen_mem, pt.slots = pen_mem + pen_words;
 
@@ -380,8 +466,14 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         mbar_arrive(tbl);
         return mbar_wait(tbl, (tbl_use++) & 1);
     };
+#ifdef WB_PHASE_TIMERS
+    long long ts_wait = 0, ts_proc = 0, ts_setup = 0;
+#endif
     int ord = 0;
     for (int k = next_row(-1); k < my_rows; k = next_row(k), ++ord) {
+#ifdef WB_PHASE_TIMERS
+        const long long tsu0 = clock64();
+#endif
         const int p = ord & 1;
         const int row = row_of(k);
         ASlot* sl = &sh->slot[p];
@@ -424,59 +516,99 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             return;
         }
         float m_t = -INFINITY, e_t = 0.f, s_t = 0.f;  // running max, reference exponent ceil(m_t * cexp), sum 2^(x * cexp - e_t)
+#ifdef WB_PHASE_TIMERS
+        ts_setup += clock64() - tsu0;
+#endif
 
-        for (uint32_t c = 0; c < n_chunks; ++c, ++it) {
-            const uint32_t s = it % stages, use = it / stages;
-            if (!mbar_wait(&full[s], use & 1)) {
-                if (lane == 0) atomicExch(a.err, 5u);
-                return;
+        bool saw_nan = false, st_fail = false;
+        unsigned long long tau_seen = 0ull;
+        float tau_f = -INFINITY;
+        // NS consecutive stages at once (more independent work per warp, fixed costs paid once); PARTIAL: the last of them is
+        // the row's final, shorter stage (vectors past the row's end read as -inf).
+        auto stage = [&](uint32_t c, auto ns_tag, auto partial) {
+            constexpr int NS = decltype(ns_tag)::value;
+            constexpr bool PARTIAL = decltype(partial)::value;
+            constexpr int NE = 8 * NS;   // elements per thread
+            constexpr int NQ = 2 * NS;   // quads of 4 consecutive elements
+#ifdef WB_PHASE_TIMERS
+            const long long tw0 = clock64();
+#endif
+            float xv[NE];
+            uint32_t qid[NQ];
+            bool qv[NQ];
+#pragma unroll
+            for (int h = 0; h < NS; ++h) {
+                if (!mbar_wait(&full[st_slot], st_phase)) {
+                    if (lane == 0) atomicExch(a.err, 5u);
+                    st_fail = true;
+                    return;
+                }
+                const uint4* vec = reinterpret_cast<const uint4*>(ring + size_t(st_slot) * ch_bytes);
+                const bool part = PARTIAL && h == NS - 1;
+                float* x = xv + 8 * h;
+                if (sizeof(T) == 4) {
+                    qid[2 * h] = (c + h) * A_CH + 4 * g.tid, qid[2 * h + 1] = qid[2 * h] + 4 * A_ST;
+                    qv[2 * h] = !part || qid[2 * h] < n, qv[2 * h + 1] = !part || qid[2 * h + 1] < n;
+                    const uint4 ninf = make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u);
+                    const uint4 q0 = qv[2 * h] ? vec[g.tid] : ninf;
+                    const uint4 q1 = qv[2 * h + 1] ? vec[g.tid + A_ST] : ninf;
+                    x[0] = __uint_as_float(q0.x), x[1] = __uint_as_float(q0.y), x[2] = __uint_as_float(q0.z), x[3] = __uint_as_float(q0.w);
+                    x[4] = __uint_as_float(q1.x), x[5] = __uint_as_float(q1.y), x[6] = __uint_as_float(q1.z), x[7] = __uint_as_float(q1.w);
+                } else {
+                    qid[2 * h] = (c + h) * A_CH + 8 * g.tid, qid[2 * h + 1] = qid[2 * h] + 4;
+                    qv[2 * h] = qv[2 * h + 1] = !part || qid[2 * h] < n;
+                    const uint4 q = qv[2 * h] ? vec[g.tid] : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
+                    x[0] = __uint_as_float(q.x << 16), x[1] = __uint_as_float(q.x & 0xffff0000u);
+                    x[2] = __uint_as_float(q.y << 16), x[3] = __uint_as_float(q.y & 0xffff0000u);
+                    x[4] = __uint_as_float(q.z << 16), x[5] = __uint_as_float(q.z & 0xffff0000u);
+                    x[6] = __uint_as_float(q.w << 16), x[7] = __uint_as_float(q.w & 0xffff0000u);
+                }
+                st_ring[h] = st_slot;
+                if (++st_slot == uint32_t(stages)) st_slot = 0, st_phase ^= 1u;
             }
-            const uint4* vec = reinterpret_cast<const uint4*>(ring + size_t(s) * ch_bytes);
-            float xv[8];
-            uint32_t qid[2];
-            bool qvalid[2];
-            if (sizeof(T) == 4) {
-                qid[0] = c * A_CH + 4 * g.tid, qid[1] = qid[0] + 4 * A_ST;
-                qvalid[0] = qid[0] < n, qvalid[1] = qid[1] < n;
-                const uint4 ninf = make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u);
-                const uint4 q0 = qvalid[0] ? vec[g.tid] : ninf;
-                const uint4 q1 = qvalid[1] ? vec[g.tid + A_ST] : ninf;
-                xv[0] = __uint_as_float(q0.x), xv[1] = __uint_as_float(q0.y), xv[2] = __uint_as_float(q0.z), xv[3] = __uint_as_float(q0.w);
-                xv[4] = __uint_as_float(q1.x), xv[5] = __uint_as_float(q1.y), xv[6] = __uint_as_float(q1.z), xv[7] = __uint_as_float(q1.w);
-            } else {
-                qid[0] = c * A_CH + 8 * g.tid, qid[1] = qid[0] + 4;
-                qvalid[0] = qvalid[1] = qid[0] < n;
-                const uint4 q = qvalid[0] ? vec[g.tid] : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
-                xv[0] = __uint_as_float(q.x << 16), xv[1] = __uint_as_float(q.x & 0xffff0000u);
-                xv[2] = __uint_as_float(q.y << 16), xv[3] = __uint_as_float(q.y & 0xffff0000u);
-                xv[4] = __uint_as_float(q.z << 16), xv[5] = __uint_as_float(q.z & 0xffff0000u);
-                xv[6] = __uint_as_float(q.w << 16), xv[7] = __uint_as_float(q.w & 0xffff0000u);
+#ifdef WB_PHASE_TIMERS
+            const long long tw1 = clock64();
+            ts_wait += tw1 - tw0;
+#endif
+            // maxima of the quads; fmaxf skips NaN, so a NaN logit never raises a maximum
+            float qm[NQ];
+#pragma unroll
+            for (int q = 0; q < NQ; ++q) qm[q] = fmaxf(fmaxf(xv[4 * q], xv[4 * q + 1]), fmaxf(xv[4 * q + 2], xv[4 * q + 3]));
+            // Every loaded register has been consumed, so the shared-memory reads have completed (instructions issue in
+            // order and the fmaxf had to wait for the data): only now may the producer overwrite the stages.
+            __syncwarp();
+            if (lane == 0) {
+#pragma unroll
+                for (int h = 0; h < NS; ++h) mbar_arrive(&empty[st_ring[h]]);
             }
             const unsigned long long tau = ld_volatile_u64(&sl->tau);
-            const float tau_f = tau ? float_of_key(cand_key(tau)) : -INFINITY;
-            // NaN counts as -inf (as the reference's draft kernel does, kernels/spec_sample.hip:61,118)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) xv[j] = fmaxf(xv[j], -INFINITY);
-            // Every loaded register has been consumed above, so the shared-memory reads have completed (instructions issue
-            // in order and the fmaxf had to wait for the data): only now may the producer overwrite the stage.
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
+            if (tau != tau_seen) tau_seen = tau, tau_f = float_of_key(cand_key(tau));
             if (pt.on) {
-                // history tokens among this thread's 8 elements: a lane loops over its own hits only
-                uint32_t bits = (qvalid[0] ? pt.bits(qid[0], 4) : 0u) | ((qvalid[1] ? pt.bits(qid[1], 4) : 0u) << 4);
-                while (bits) {
-                    const int j = __ffs(bits) - 1;
-                    bits &= bits - 1;
-                    float x = xv[0];
+                // history tokens among this thread's elements: a lane loops over its own hits only
+                uint32_t bits = 0;
 #pragma unroll
-                    for (int e = 1; e < 8; ++e) x = j == e ? xv[e] : x;
-                    x = fmaxf(pt.apply(x, qid[j >> 2] + (j & 3)), -INFINITY);
+                for (int q = 0; q < NQ; ++q) bits |= (qv[q] ? pt.bits(qid[q], 4) : 0u) << (4 * q);
+                if (bits) {
+                    do {
+                        const int j = __ffs(bits) - 1;
+                        bits &= bits - 1;
+                        float x = xv[0];
+                        uint32_t id = qid[0];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) xv[e] = j == e ? x : xv[e];
+                        for (int e = 1; e < NE; ++e) x = j == e ? xv[e] : x;
+#pragma unroll
+                        for (int q = 1; q < NQ; ++q) id = (j >> 2) == q ? qid[q] : id;
+                        x = pt.apply(x, id + (j & 3));
+#pragma unroll
+                        for (int e = 0; e < NE; ++e) xv[e] = j == e ? x : xv[e];
+                    } while (bits);
+#pragma unroll
+                    for (int q = 0; q < NQ; ++q) qm[q] = fmaxf(fmaxf(xv[4 * q], xv[4 * q + 1]), fmaxf(xv[4 * q + 2], xv[4 * q + 3]));
                 }
             }
-            const float vm0 = fmaxf(fmaxf(xv[0], xv[1]), fmaxf(xv[2], xv[3])), vm1 = fmaxf(fmaxf(xv[4], xv[5]), fmaxf(xv[6], xv[7]));
-            const float vm = fmaxf(vm0, vm1);
+            float vm = qm[0];
+#pragma unroll
+            for (int q = 1; q < NQ; ++q) vm = fmaxf(vm, qm[q]);
             if (!greedy) {
                 if (vm > m_t) {
                     // new reference exponent: an integer at or above m * cexp, so every term is at most 1 and x * cexp - e
@@ -486,33 +618,55 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                     e_t = ne, m_t = vm;
                 }
                 if (m_t != -INFINITY) {
-                    float e[8];
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) e[j] = ex2_approx(fmaf(xv[j], cexp, -e_t));
-                    s_t += ((e[0] + e[1]) + (e[2] + e[3])) + ((e[4] + e[5]) + (e[6] + e[7]));
+                    for (int j = 0; j < NE; ++j) acc[j & 3] += ex2_approx(fmaf(xv[j], cexp, -e_t));
+                    s_t += (acc[0] + acc[1]) + (acc[2] + acc[3]);
                 }
             } else {
                 m_t = fmaxf(m_t, vm);
             }
-            if (__ballot_sync(0xffffffffu, vm >= tau_f)) {
-                // rare: some lane holds an element that may beat the threshold; each such lane logs its own
-                uint32_t mask = 0;
+            if (vm >= tau_f) {
+                // rare: this lane holds an element that may beat the threshold
 #pragma unroll
-                for (int j = 0; j < 8; ++j) mask |= uint32_t(qvalid[j >> 2] && xv[j] >= tau_f) << j;
-                while (mask) {
-                    const int j = __ffs(mask) - 1;
-                    mask &= mask - 1;
-                    float x = xv[0];
+                for (int q = 0; q < NQ; ++q) {
+                    if (qm[q] >= tau_f && qv[q]) {
 #pragma unroll
-                    for (int e = 1; e < 8; ++e) x = j == e ? xv[e] : x;
-                    const unsigned long long cnd = make_cand(key_of(x), qid[j >> 2] + (j & 3));
-                    if (cnd > tau) {
-                        const uint32_t pos = atomicAdd(&sl->cnt, 1u);
-                        if (pos < uint32_t(A_L)) log[pos] = cnd;
+                        for (int j = 0; j < 4; ++j) {
+                            const float x = xv[4 * q + j];
+                            if (x >= tau_f) {
+                                const unsigned long long cnd = make_cand(key_of(x), qid[q] + j);
+                                if (cnd > tau) {
+                                    const uint32_t pos = atomicAdd(&sl->cnt, 1u);
+                                    if (pos < uint32_t(A_L)) log[pos] = cnd;
+                                }
+                            }
+                        }
                     }
                 }
             }
+#ifdef WB_PHASE_TIMERS
+            ts_proc += clock64() - tw1;
+#endif
+        };
+        const uint32_t full_chunks = n / A_CH;
+        {
+            using one = std::integral_constant<int, 1>;
+            using two = std::integral_constant<int, 2>;
+            uint32_t c = 0;
+            for (; c + 2 <= full_chunks && !st_fail; c += 2) stage(c, two{}, std::false_type{});
+            if (!st_fail && c < full_chunks) {
+                // one full stage left, maybe followed by the partial one
+                if (full_chunks < n_chunks) stage(c, two{}, std::true_type{});
+                else stage(c, one{}, std::false_type{});
+            } else if (!st_fail && full_chunks < n_chunks) {
+                stage(c, one{}, std::true_type{});
+            }
         }
+        if (st_fail) return;
+        // a NaN logit poisons the f32 sum: such rows are redone by the multi-pass kernel, which counts NaN as -inf
+        saw_nan = !greedy && (s_t != s_t);
+        if (__any_sync(0xffffffffu, saw_nan) && lane == 0) atomicOr(&sl->cnt, 0x80000000u);
         // ---- the row is through for this warp: partials, then close
         {
             const float wm = warp_max(m_t);
@@ -526,10 +680,16 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         __syncwarp();
         if (lane == 0) mbar_arrive(&closed[p]);
     }
+#ifdef WB_PHASE_TIMERS
+    if (g.tid == 0) {
+        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 4);
+        atomicAdd(&dbg[4], (unsigned long long)ts_wait), atomicAdd(&dbg[5], (unsigned long long)ts_proc), atomicAdd(&dbg[6], (unsigned long long)ts_setup);
+    }
+#endif
 }
 
 static size_t async_fixed_smem(bool pen, int pen_words, int ch_bytes) {
-    return size_t(ch_bytes) + size_t(2) * A_L * 8 + SEL_BINS * 4 + size_t(kAsyncMaxK) * 8 + (kAsyncMaxK + 2 * A_TW) * 8 +
+    return size_t(ch_bytes) + size_t(2) * A_L * 8 + SEL_BINS * 4 + size_t(kAsyncMaxK) * 8 + 2 * (kAsyncMaxK + 2 * A_TW) * 8 +
            (2 * A_MAXSTAGES + 8) * 8 + sizeof(AShared) + (pen ? size_t(pen_words) * 4 + kPenSlots * 4 : 0) + 128;
 }
 

@@ -67,8 +67,9 @@ sample_stream_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
     unsigned long long* buf = reinterpret_cast<unsigned long long*>(ring + size_t(stages) * ch_bytes);  // BUF_CAP
     uint32_t* hist = reinterpret_cast<uint32_t*>(buf + BUF_CAP);                  // NBINS (8 KiB: also 1024 staged candidates)
     unsigned long long* hand_c = reinterpret_cast<unsigned long long*>(hist + NBINS);  // HAND * kStreamMaxK
-    double* tail_p = reinterpret_cast<double*>(hand_c + HAND * kStreamMaxK);       // kStreamMaxK + 2 * EW
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tail_p + kStreamMaxK + 2 * EW);   // 2 * stages + 2 * HAND
+    double* tail_p = reinterpret_cast<double*>(hand_c + HAND * kStreamMaxK);       // 2 * (kStreamMaxK + 2 * EW)
+    double* tail_q = tail_p + kStreamMaxK + 2 * EW;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail_q + kStreamMaxK + 2 * EW);   // 2 * stages + 2 * HAND
     StreamShared* sh = reinterpret_cast<StreamShared*>(bars + 2 * 32 + 2 * HAND);
     uint32_t* pen_mem = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));
     uint64_t *full = bars, *empty = bars + 32, *hfull = bars + 64, *hempty = bars + 64 + HAND;
@@ -164,7 +165,8 @@ sample_stream_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
                 in.top_p = P.top_p ? P.top_p[row] : 1.0, in.min_p = P.min_p ? P.min_p[row] : 0.0, in.u = P.u ? P.u[row] : 0.0;
                 in.m = hd.m, in.sum = hd.sum, in.cnt = hd.cnt, in.cap = cap, in.V = n;
                 in.race = P.race_key != nullptr, in.race_key = P.race_key ? P.race_key[row] : 0;
-                sample_tail<ET>(g, in, reinterpret_cast<uint64_t*>(cand), tail_p, &sh->res);
+                in.presorted = 0;
+                sample_tail<ET>(g, in, reinterpret_cast<uint64_t*>(cand), tail_p, tail_q, &sh->res);
                 const TailOut r = sh->res;
                 if (g.tid == 0) {
                     a.out.token[row] = int32_t(r.token);
@@ -419,7 +421,7 @@ sample_stream_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
 }
 
 static size_t stream_fixed_smem(bool pen, int pen_words) {
-    return size_t(BUF_CAP) * 8 + NBINS * 4 + size_t(HAND) * kStreamMaxK * 8 + (kStreamMaxK + 2 * EW) * 8 + (2 * 32 + 2 * HAND) * 8 +
+    return size_t(BUF_CAP) * 8 + NBINS * 4 + size_t(HAND) * kStreamMaxK * 8 + 2 * (kStreamMaxK + 2 * EW) * 8 + (2 * 32 + 2 * HAND) * 8 +
            sizeof(StreamShared) + (pen ? size_t(pen_words) * 4 + kPenSlots * 4 : 0) + 128;
 }
 

@@ -261,9 +261,11 @@ __device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_ma
     in.inv_t = inv_t, in.top_k = top_k, in.top_p = P.top_p ? P.top_p[row] : 1.0, in.min_p = P.min_p ? P.min_p[row] : 0.0;
     in.u = P.u ? P.u[row] : 0.0, in.m = sh->m, in.sum = sh->sum, in.cnt = K, in.cap = cap, in.V = n;
     in.race = P.race_key != nullptr, in.race_key = P.race_key ? P.race_key[row] : 0;
-    double* p = reinterpret_cast<double*>(a.ws) + size_t(blockIdx.x) * (size_t(cap_max) + 2 * GT / 32);
+    double* p = reinterpret_cast<double*>(a.ws) + size_t(blockIdx.x) * 2 * (size_t(cap_max) + 2 * GT / 32);
+    double* q = p + size_t(cap_max) + 2 * GT / 32;
     // the tail's race scratch sits at p + in.cap; keep it inside this row's slice
-    sample_tail<GT>(g, in, cand, p, &sh->res);
+    in.presorted = 0;
+    sample_tail<GT>(g, in, cand, p, q, &sh->res);
     const TailOut r = sh->res;
     if (tid == 0) {
         a.out.token[row] = int32_t(r.token);
@@ -290,7 +292,7 @@ static int pow2_at_least(int k) {
 }
 
 size_t select_generic_ws_bytes(int ctas, int K) {
-    return size_t(ctas) * (size_t(pow2_at_least(K < 1 ? 1 : K)) + 2 * GT / 32) * sizeof(double);
+    return size_t(ctas) * 2 * (size_t(pow2_at_least(K < 1 ? 1 : K)) + 2 * GT / 32) * sizeof(double);
 }
 
 cudaError_t select_generic_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st) {

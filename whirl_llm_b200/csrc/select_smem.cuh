@@ -13,7 +13,51 @@ constexpr int SEL_LIST = 256;  // rank directly when the target bin holds at mos
 struct SelScratch {
     unsigned long long lo, hi, kth;
     uint32_t bin, need, eq, lcnt, wcnt;
+    uint32_t wsum[32];
 };
+
+
+// Scanning the SEL_BINS counters of hist from the top bin down, find the bin where the running count reaches `need`
+// (1 <= need <= total).  Every thread owns SEL_BINS / NT consecutive bins in registers; one barrier pair.  Results in
+// sc->bin (the bin), sc->need (rank wanted inside that bin), sc->eq (entries in that bin).  nb <= SEL_BINS bins are used.
+template <int NT>
+__device__ void find_bin_desc(const Group<NT>& g, const uint32_t* hist, uint32_t need, SelScratch* sc, uint32_t* wsum) {
+    constexpr int PER = SEL_BINS / NT;
+    static_assert(PER >= 4 && PER % 4 == 0, "bins per thread");
+    uint32_t c[PER];
+    // thread t owns bins [SEL_BINS - (t + 1) * PER, SEL_BINS - t * PER), scanned from its top down
+    const uint4* src = reinterpret_cast<const uint4*>(hist + SEL_BINS - (g.tid + 1) * PER);
+#pragma unroll
+    for (int q = 0; q < PER / 4; ++q) {
+        const uint4 v = src[q];
+        c[q * 4] = v.x, c[q * 4 + 1] = v.y, c[q * 4 + 2] = v.z, c[q * 4 + 3] = v.w;
+    }
+    uint32_t s = 0;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) s += c[j];
+    const uint32_t incl_w = warp_scan_incl(s);
+    if ((g.tid & 31) == 31) wsum[g.tid >> 5] = incl_w;
+    g.sync();
+    uint32_t before = 0;
+    for (int w = 0; w < (g.tid >> 5); ++w) before += wsum[w];
+    const uint32_t incl = before + incl_w, excl = incl - s;
+    if (excl < need && incl >= need) {
+        uint32_t r = need - excl;
+        bool found = false;
+#pragma unroll
+        for (int j = PER - 1; j >= 0; --j) {  // c[PER - 1] is the thread's top bin
+            if (!found) {
+                if (c[j] >= r) {
+                    sc->bin = SEL_BINS - (g.tid + 1) * PER + j, sc->need = r, sc->eq = c[j];
+                    found = true;
+                } else {
+                    r -= c[j];
+                }
+            }
+        }
+    }
+    g.sync();
+}
 
 // The K-th largest of buf[0..cnt) (1 <= K <= cnt; entries distinct; zeros allowed as "empty", they rank last).
 // hist: SEL_BINS words of shared scratch (also used as a list of up to SEL_LIST candidates).  Every thread of the
@@ -44,33 +88,15 @@ __device__ unsigned long long select_kth(const Group<NT>& g, const unsigned long
         if (range == 0) return lo;
         const int bits = 64 - __clzll((long long)range);
         const int sa = bits > 11 ? bits - 11 : 0;  // (range >> sa) < SEL_BINS
-        for (int i = g.tid; i < SEL_BINS; i += NT) hist[i] = 0;
+        for (int i = g.tid; i < SEL_BINS / 4; i += NT) reinterpret_cast<uint4*>(hist)[i] = make_uint4(0, 0, 0, 0);
         g.sync();
         for (uint32_t i = g.tid; i < cnt; i += NT) {
             const unsigned long long c = buf[i];
             if (c >= lo && c <= hi) atomicAdd(&hist[uint32_t((c - lo) >> sa)], 1u);
         }
         g.sync();
-        if (g.tid < 32) {
-            // bins from the top down; lane l owns 64 consecutive bins in that order
-            constexpr int per = SEL_BINS / 32;
-            uint32_t s = 0;
-            for (int j = 0; j < per; ++j) s += hist[SEL_BINS - 1 - (g.tid * per + j)];
-            const uint32_t incl = warp_scan_incl(s), excl = incl - s;
-            if (excl < need && incl >= need) {
-                uint32_t r = need - excl;
-                for (int j = 0; j < per; ++j) {
-                    const int b = SEL_BINS - 1 - (g.tid * per + j);
-                    const uint32_t c = hist[b];
-                    if (c >= r) {
-                        sc->bin = b, sc->need = r, sc->eq = c;
-                        break;
-                    }
-                    r -= c;
-                }
-            }
-            if (g.tid == 0) sc->lcnt = 0;
-        }
+        find_bin_desc<NT>(g, hist, need, sc, sc->wsum);
+        if (g.tid == 0) sc->lcnt = 0;
         g.sync();
         const uint32_t b = sc->bin, cb = sc->eq;
         need = sc->need;
@@ -123,44 +149,26 @@ __device__ void write_survivors(const Group<NT>& g, const unsigned long long* bu
     g.sync();
 }
 
-// The K-th largest ordering key among n floats in shared memory (1 <= K <= n), by three digit passes (11 + 11 + 10).
-// NaN ranks lowest.  hist: SEL_BINS words.
+// A lower bound of the K-th largest ordering key among n floats in shared memory (1 <= K <= n): the key's top 22 bits
+// by two digit passes (11 + 11), low bits zero, so at least K elements have a key at or above the result.  NaN ranks
+// lowest.  hist: SEL_BINS words.
 template <int NT, typename T>
-__device__ uint32_t select_key_kth(const Group<NT>& g, const T* x, uint32_t n, uint32_t K, uint32_t* hist, SelScratch* sc) {
+__device__ uint32_t select_key_bound(const Group<NT>& g, const T* x, uint32_t n, uint32_t K, uint32_t* hist, SelScratch* sc) {
     uint32_t prefix = 0, mask = 0, need = K;
-    const int shifts[3] = {21, 10, 0}, widths[3] = {11, 11, 10};
-    for (int ps = 0; ps < 3; ++ps) {
-        const uint32_t bm = (1u << widths[ps]) - 1;
-        for (int i = g.tid; i < SEL_BINS; i += NT) hist[i] = 0;
+    const int shifts[2] = {21, 10};
+    for (int ps = 0; ps < 2; ++ps) {
+        for (int i = g.tid; i < SEL_BINS / 4; i += NT) reinterpret_cast<uint4*>(hist)[i] = make_uint4(0, 0, 0, 0);
         g.sync();
         for (uint32_t i = g.tid; i < n; i += NT) {
             const float v = sizeof(T) == 4 ? reinterpret_cast<const float*>(x)[i] : bf16_to_f32(reinterpret_cast<const uint16_t*>(x)[i]);
             const uint32_t k = key_of(v);
-            if ((k & mask) == prefix) atomicAdd(&hist[(k >> shifts[ps]) & bm], 1u);
+            if ((k & mask) == prefix) atomicAdd(&hist[(k >> shifts[ps]) & 2047u], 1u);
         }
         g.sync();
-        if (g.tid < 32) {
-            const int nb = 1 << widths[ps], per = nb / 32;
-            uint32_t s = 0;
-            for (int j = 0; j < per; ++j) s += hist[nb - 1 - (g.tid * per + j)];
-            const uint32_t incl = warp_scan_incl(s), excl = incl - s;
-            if (excl < need && incl >= need) {
-                uint32_t r = need - excl;
-                for (int j = 0; j < per; ++j) {
-                    const int b = nb - 1 - (g.tid * per + j);
-                    const uint32_t c = hist[b];
-                    if (c >= r) {
-                        sc->bin = b, sc->need = r;
-                        break;
-                    }
-                    r -= c;
-                }
-            }
-        }
-        g.sync();
+        find_bin_desc<NT>(g, hist, need, sc, sc->wsum);
         prefix |= sc->bin << shifts[ps];
         need = sc->need;
-        mask |= bm << shifts[ps];
+        mask |= 2047u << shifts[ps];
         g.sync();
     }
     return prefix;

@@ -27,6 +27,7 @@ struct TailIn {
     uint32_t V;         // row width (cnt == V means the candidates are the whole row)
     uint64_t race_key;  // spec::raceBase(seed, pos) when race != 0
     int32_t race;
+    int32_t presorted;  // cand[0..cnt) is already in descending order
 };
 struct TailOut {
     int32_t status;
@@ -68,18 +69,21 @@ __device__ void sort_desc(const Group<NT>& g, uint64_t* cand, uint32_t cap) {
     }
 }
 
-// cand: shared, the exact candidate set (any order, padded with zeros up to cap); p: shared scratch of cap doubles;
-// res: one shared TailOut.  On return (after the group's barrier) cand is sorted, p[0..n) holds the kept
-// probabilities (renormalised when closed) and *res the outcome.
+// cand: the exact candidate set (any order unless in.presorted, padded with zeros up to cap); p, q: scratch of
+// cap + 2 * NT / 32 doubles each; res: one shared TailOut.  On return (after the group's barrier) cand is sorted,
+// p[0..n) holds the kept probabilities (renormalised when closed) and *res the outcome.
+// The order of operations of every sum follows the host code: one thread adds the terms in candidate order; only the
+// independent exponentials and divisions run in parallel.
 template <int NT>
-__device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand, double* p, TailOut* res) {
-    sort_desc<NT>(g, cand, in.cap);
+__device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand, double* p, double* q, TailOut* res) {
+    if (!in.presorted) sort_desc<NT>(g, cand, in.cap);
     const double inv_t = double(in.inv_t), sum = double(in.sum);
     for (uint32_t i = g.tid; i < in.cnt; i += NT) {
         const float l = float_of_key(cand_key(cand[i]));
         p[i] = exp(double(__fsub_rn(l, in.m)) * inv_t) / sum;
     }
     g.sync();
+    // ---- top-k, and the normaliser of the top-p walk (sampler.cpp:35-49)
     if (g.tid == 0) {
         uint32_t n = in.cnt;
         bool closed = in.cnt == in.V, esc = false;
@@ -87,16 +91,31 @@ __device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand
             if (in.top_k <= in.cnt) n = in.top_k, closed = true;
             else if (!closed) esc = true;
         }
-        if (!esc && in.top_p < 1.0) {
-            double z = 1.0;
-            if (closed) {
-                z = 0;
-                for (uint32_t i = 0; i < n; ++i) z += p[i];
-            }
+        double z = 1.0;
+        if (!esc && in.top_p < 1.0 && closed) {
+            z = 0;
+            for (uint32_t i = 0; i < n; ++i) z += p[i];
+        }
+        res->status = esc ? ROW_ESCALATE : ROW_DONE;
+        res->n = n, res->closed = closed, res->cum = z, res->token = 0;
+    }
+    g.sync();
+    if (res->status == ROW_ESCALATE) return;
+    if (in.top_p < 1.0) {
+        const double z = res->cum;
+        const uint32_t n0 = res->n;
+        for (uint32_t i = g.tid; i < n0; i += NT) q[i] = p[i] / z;
+        g.sync();
+    }
+    // ---- top-p cut, min-p cut, the renormaliser (sampler.cpp:50-74)
+    if (g.tid == 0) {
+        uint32_t n = res->n;
+        bool closed = res->closed != 0, esc = false;
+        if (in.top_p < 1.0) {
             double cum = 0;
             bool found = false;
             for (uint32_t j = 0; j < n; ++j) {
-                cum += p[j] / z;
+                cum += q[j];
                 if (cum >= in.top_p) {
                     n = j + 1;
                     found = true;
@@ -119,10 +138,7 @@ __device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand
             for (uint32_t i = 0; i < n; ++i) z += p[i];
         }
         res->status = esc ? ROW_ESCALATE : ROW_DONE;
-        res->n = n;
-        res->closed = closed;
-        res->cum = z;  // the normaliser, read back below
-        res->token = 0;
+        res->n = n, res->closed = closed, res->cum = z;
     }
     g.sync();
     if (res->status == ROW_ESCALATE) return;
