@@ -100,6 +100,17 @@ int whirl_draft_pick(const void* x, int dtype, int n, int* tok, float* prob, int
 int whirl_draft_pick_rows(const void* x, int dtype, int rows, int n, int* ctl_all, const int* area, int r, int n_min,
                           float p_min, const int* map, void* ws, size_t ws_bytes, void* stream);
 
+/* The greedy pick of whirl_argmax_rows without a workspace and without any allocation.  No counterpart in the reference.
+ * It is for hosts that cannot give the library device memory at call time: an engine that fixes its whole memory plan at
+ * start-up and bans cudaMalloc afterwards, or a call site with no workspace pointer to pass.  The scratch that splits a row
+ * over several thread blocks sits in a fixed array inside the library (about 257 KiB on every GPU that loads it, held
+ * until the process exits), sized for at most WHIRL_STATIC_MAX_ROWS rows; more rows are refused with
+ * WHIRL_ERR_UNSUPPORTED.  The first call on each device looks the array's device address up (make that call before any
+ * stream capture begins).  All calls share the one array, which keeps the previous call's contents (the call clears the
+ * part that must start at zero): two calls that overlap on the GPU, on different streams, race on it. */
+#define WHIRL_STATIC_MAX_ROWS 256
+int whirl_argmax_rows_static(const void* x, int dtype, int rows, int n, int* out, void* stream);
+
 /* ------------------------------------------------------------------------------------------------------------------
  * Candidates.
  * ---------------------------------------------------------------------------------------------------------------- */

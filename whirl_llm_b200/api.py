@@ -17,6 +17,7 @@ F32, BF16 = 0, 1
 ROW_DONE, ROW_ESCALATE, ROW_OPEN_TAIL = 0, 1, 2
 CNT_ESCALATED, CNT_OPEN_TAIL, CNT_UNRESOLVED, CNT_WORDS = 0, 1, 2, 8
 MAX_K, STREAM_MAX_K, MAX_HIST, Q_WORDS, Q_MAX, CTL_WORDS = 16384, 1024, 4096, 72, 32, 64
+STATIC_MAX_ROWS = 256
 
 
 class WhirlError(RuntimeError):
@@ -52,6 +53,7 @@ def _load() -> C.CDLL:
         "whirl_argmax": (i, [vp, i, i, vp, vp, vp, i, vp, sz, vp]),
         "whirl_argmax_rows": (i, [vp, i, i, i, vp, vp, sz, vp]),
         "whirl_argmax_rows_to": (i, [vp, i, i, i, vp, vp, vp, sz, vp]),
+        "whirl_argmax_rows_static": (i, [vp, i, i, i, vp, vp]),
         "whirl_argmax_prob": (i, [vp, i, i, i, vp, vp, vp, sz, vp]),
         "whirl_draft_pick": (i, [vp, i, i, vp, vp, vp, i, i, f, vp, vp, sz, vp]),
         "whirl_draft_pick_rows": (i, [vp, i, i, i, vp, vp, i, i, f, vp, vp, sz, vp]),
@@ -70,7 +72,7 @@ def _load() -> C.CDLL:
 
 lib = _load()
 DECLARED = ["whirl_status_string", "whirl_last_error", "whirl_version", "whirl_workspace_bytes", "whirl_argmax",
-            "whirl_argmax_rows", "whirl_argmax_rows_to", "whirl_argmax_prob", "whirl_draft_pick", "whirl_draft_pick_rows",
+            "whirl_argmax_rows", "whirl_argmax_rows_static", "whirl_argmax_rows_to", "whirl_argmax_prob", "whirl_draft_pick", "whirl_draft_pick_rows",
             "whirl_topk_rows", "whirl_sample_rows", "whirl_sample_rows_host", "whirl_host_release", "whirl_host_last_error",
             "whirl_launch_counts"]
 
@@ -140,6 +142,15 @@ def argmax_rows(x, out=None, ws=None):
     out = torch.empty(rows, dtype=torch.int32, device=x.device) if out is None else out
     ws = workspace(rows, n, x.device) if ws is None else ws
     _check(lib.whirl_argmax_rows(x.data_ptr(), _dtype(x), rows, n, out.data_ptr(), ws.data_ptr(), ws.numel(), _stream(x)))
+    return out
+
+
+def argmax_rows_static(x, out=None):
+    """The greedy pick with the library's own fixed scratch: no workspace, no allocation by the library (at most
+    WHIRL_STATIC_MAX_ROWS rows).  `out` is the caller's."""
+    x, rows, n = _rows(x)
+    out = torch.empty(rows, dtype=torch.int32, device=x.device) if out is None else out
+    _check(lib.whirl_argmax_rows_static(x.data_ptr(), _dtype(x), rows, n, out.data_ptr(), _stream(x)))
     return out
 
 

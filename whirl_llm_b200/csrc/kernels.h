@@ -8,6 +8,10 @@
 
 namespace wb {
 
+// set by api.cu: the calling thread's error message and the launch counters
+void set_last_error(const char* msg);
+void count_launch(int family);
+
 // ---- greedy picks (rowscan.cu)
 enum { RS_ARGMAX = 0, RS_ARGMAX_PROB = 1, RS_DRAFT_PICK = 2 };
 

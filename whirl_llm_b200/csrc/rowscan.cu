@@ -7,6 +7,10 @@
 // one pass instead of two (online max / sum), a row may be split over several CTAs when there are fewer rows than
 // SMs (partials meet in a small workspace; the last CTA to arrive combines them), and per-row tables are device
 // arrays instead of 32-entry by-value structs.
+#include "../../include/whirl_b200.h"
+
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -235,3 +239,85 @@ cudaError_t rowscan_launch(const RowScanArgs& a, int dtype, int mode, int rows, 
 }
 
 }  // namespace wb
+
+// ---------------------------------------------------------------------------------------------------------------------
+// whirl_argmax_rows_static: the greedy pick for callers that may not allocate device memory.
+//
+// Some hosts hand a sampler no allocator at all: an engine that sizes every device buffer once at start-up and forbids
+// cudaMalloc afterwards (an allocation synchronises the device and can fail late), or a plugin that is called where no
+// workspace pointer can be threaded through.  For them the split-row scratch of the greedy pick (one ticket per row and
+// one partial result per row and split) lives in the file-scope device array below instead of a caller workspace.
+// Every GPU that loads this library holds the array (about 257 KiB) until the process exits.
+// ---------------------------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kStaticSplits = 64;
+constexpr size_t kStaticBytes = size_t((WHIRL_STATIC_MAX_ROWS + 3) & ~3) * sizeof(int) +
+                                size_t(WHIRL_STATIC_MAX_ROWS) * kStaticSplits * sizeof(wb::Part);
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+// In host code the array's name is only a handle: the address a kernel can use comes from cudaGetSymbolAddress, asked once
+// per device with that device current.
+std::mutex g_static_mu;
+void* g_static_ptr[64] = {nullptr};
+
+cudaError_t static_scratch(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return e;
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return cudaSuccess;
+}
+
+}  // namespace
+
+#pragma GCC visibility push(default)
+extern "C" int whirl_argmax_rows_static(const void* x, int dtype, int rows, int n, int* out, void* stream) {
+    if (!x || !out || rows < 0 || n <= 0 || (dtype != WHIRL_F32 && dtype != WHIRL_BF16)) {
+        wb::set_last_error("argmax_rows_static: bad pointer / rows / n / dtype");
+        return WHIRL_ERR_INVALID;
+    }
+    if (rows > WHIRL_STATIC_MAX_ROWS) {
+        wb::set_last_error("argmax_rows_static: more than WHIRL_STATIC_MAX_ROWS rows; use whirl_argmax_rows with a workspace");
+        return WHIRL_ERR_UNSUPPORTED;
+    }
+    if (rows == 0) return WHIRL_OK;
+    void* scratch = nullptr;
+    cudaError_t e = static_scratch(&scratch);  // the first call on a device looks the address up
+    if (e != cudaSuccess) {
+        wb::set_last_error(cudaGetErrorString(e));
+        return WHIRL_ERR_CUDA;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int sms = 148;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int splits = wb::rowscan_splits(rows, n, sms);
+    if (splits > kStaticSplits) splits = kStaticSplits;
+    if (splits > 1) {
+        // the tickets must start at zero; the array keeps whatever the last call left
+        e = cudaMemsetAsync(scratch, 0, size_t((rows + 3) & ~3) * sizeof(int), st);
+        if (e != cudaSuccess) {
+            wb::set_last_error(cudaGetErrorString(e));
+            return WHIRL_ERR_CUDA;
+        }
+    }
+    wb::RowScanArgs a{};
+    a.x = x, a.n = n, a.out = out, a.ws = scratch;
+    e = wb::rowscan_launch(a, dtype, wb::RS_ARGMAX, rows, splits, st);
+    wb::count_launch(0);
+    if (e != cudaSuccess) {
+        wb::set_last_error(cudaGetErrorString(e));
+        return WHIRL_ERR_CUDA;
+    }
+    return WHIRL_OK;
+}
+#pragma GCC visibility pop
