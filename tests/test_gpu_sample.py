@@ -107,6 +107,9 @@ def test_config2_penalised(api, oracle):
     want = oracle.sample_rows(x, kept_cap=50, u=u, threads=4, **prm, **{k: (v.astype(np.uint32) if k == "hist_len" else v) for k, v in pen.items()})
     res = api.sample_rows(dev(x), row_params(prm, u=u, **pen), kept_cap=50)
     compare_rows(res, want, u=u)
+    # without the row statistics the kernel normalises over the candidates only: same tokens, kept sets, probabilities
+    res = api.sample_rows(dev(x), row_params(prm, u=u, **pen), kept_cap=50, want_stats=False)
+    compare_rows(res, want, u=u)
     # the penalties changed something: the unpenalised run differs in at least one kept set
     plain = oracle.sample_rows(x, kept_cap=50, u=u, threads=4, **prm)
     assert any(not np.array_equal(plain["kept_ids"][r], want["kept_ids"][r]) for r in range(R))
@@ -125,6 +128,8 @@ def test_config1_draws(api, oracle):
         want = oracle.sample_rows(xs, kept_cap=40, u=u, threads=4, **prm)
         res = api.sample_rows(dev(xs), row_params(prm, u=u), kept_cap=40)
         compare_rows(res, want, u=u)
+        res = api.sample_rows(dev(xs), row_params(prm, u=u), kept_cap=40, want_stats=False)
+        compare_rows(res, want, u=u)
     g = api.sample_rows(dev(x), row_params(dict(greedy=np.ones(1, dtype=np.uint8))))
     assert g.token.item() == oracle.first_max(x[0])
 
@@ -142,6 +147,8 @@ def test_config4_bf16_mix(api, oracle):
     u = synth.hash_u01(44, R, 3)
     want = oracle.sample_rows(bits, kept_cap=1024, u=u, threads=4, **prm)
     res = api.sample_rows(bf16_tensor(bits), row_params(prm, u=u), kept_cap=1024)
+    compare_rows(res, want, u=u)
+    res = api.sample_rows(bf16_tensor(bits), row_params(prm, u=u), kept_cap=1024, want_stats=False)
     compare_rows(res, want, u=u)
 
 

@@ -241,13 +241,14 @@ class SampleResult:
     status: torch.Tensor
     n_kept: torch.Tensor
     closed: torch.Tensor
-    stats: torch.Tensor
+    stats: Optional[torch.Tensor]
     kept_ids: Optional[torch.Tensor]
     kept_p: Optional[torch.Tensor]
     counters: torch.Tensor
 
 
-def sample_rows(x, params: RowParams, kept_cap: int = 0, ws=None, result: Optional[SampleResult] = None) -> SampleResult:
+def sample_rows(x, params: RowParams, kept_cap: int = 0, ws=None, result: Optional[SampleResult] = None,
+                want_stats: bool = True) -> SampleResult:
     """One token per row: penalties -> candidates -> top-k / top-p / min-p -> draw (whirl_sample_rows)."""
     x, rows, n = _rows(x)
     dev = x.device
@@ -255,7 +256,7 @@ def sample_rows(x, params: RowParams, kept_cap: int = 0, ws=None, result: Option
         result = SampleResult(
             token=torch.empty(rows, dtype=torch.int32, device=dev), status=torch.empty(rows, dtype=torch.int32, device=dev),
             n_kept=torch.empty(rows, dtype=torch.int32, device=dev), closed=torch.empty(rows, dtype=torch.int32, device=dev),
-            stats=torch.empty((rows, 2), dtype=torch.float32, device=dev),
+            stats=torch.empty((rows, 2), dtype=torch.float32, device=dev) if want_stats else None,
             kept_ids=torch.full((rows, kept_cap), -1, dtype=torch.int32, device=dev) if kept_cap else None,
             kept_p=torch.zeros((rows, kept_cap), dtype=torch.float64, device=dev) if kept_cap else None,
             counters=torch.zeros(CNT_WORDS, dtype=torch.int32, device=dev))

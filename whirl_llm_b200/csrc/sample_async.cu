@@ -32,8 +32,9 @@ constexpr int A_TW = 4;                       // tail warps
 constexpr int A_TT = A_TW * 32;
 constexpr int A_THREADS = 32 + A_ST + A_TT;
 constexpr int A_CH = 4096;                    // logits per ring stage
-constexpr int A_L = 4096;                     // candidate log entries per row slot
+constexpr int A_L = 3072;                     // candidate log entries per row slot
 constexpr int A_MAXSTAGES = 16;
+constexpr int A_HITS = 64;                    // per stream warp: history-token logits waiting for their penalty
 
 struct ASlot {
     unsigned long long tau;  // current threshold candidate; elements must beat it to be logged
@@ -57,11 +58,11 @@ __device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned lon
 __device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) { return *reinterpret_cast<const volatile uint32_t*>(p); }
 
 template <typename T>
-__global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
+__global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes, int boot_elems) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;                                                          // stages * ch_bytes
-    uint8_t* boot = ring + size_t(stages) * ch_bytes;                              // ch_bytes: first stage of the next row
-    unsigned long long* logs = reinterpret_cast<unsigned long long*>(boot + ch_bytes);  // 2 * A_L
+    uint8_t* boot = ring + size_t(stages) * ch_bytes;                              // boot_elems logits: the head of the next row
+    unsigned long long* logs = reinterpret_cast<unsigned long long*>(boot + size_t(boot_elems) * sizeof(T));  // 2 * A_L
     uint32_t* hist = reinterpret_cast<uint32_t*>(logs + 2 * A_L);                 // SEL_BINS
     unsigned long long* hand = reinterpret_cast<unsigned long long*>(hist + SEL_BINS);   // kAsyncMaxK
     double* tail_p = reinterpret_cast<double*>(hand + kAsyncMaxK);                 // 2 * (kAsyncMaxK + 2 * A_TW)
@@ -69,6 +70,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail_q + kAsyncMaxK + 2 * A_TW);  // 2 * 16 + 8
     AShared* sh = reinterpret_cast<AShared*>(bars + 2 * A_MAXSTAGES + 8);
     uint32_t* pen_mem = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));
+    uint2* hitbuf = reinterpret_cast<uint2*>(pen_mem + pen_words + (pen_words ? kPenSlots : 0));  // A_SW * A_HITS (penalties only)
+    uint32_t* wbound = reinterpret_cast<uint32_t*>(hitbuf + (pen_words ? A_SW * A_HITS : 0));  // 2 * A_SW: per slot, each stream warp's bound key
     uint64_t *full = bars, *empty = bars + A_MAXSTAGES;
     uint64_t *closed = bars + 2 * A_MAXSTAGES, *boot_done = closed + 2, *boot_full = closed + 4, *boot_empty = closed + 5;
     uint64_t* tbl = closed + 6;  // rendezvous of the stream threads around the rebuild of the penalty table
@@ -98,7 +101,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], A_SW);
         for (int p = 0; p < 2; ++p) mbar_init(&closed[p], A_SW), mbar_init(&boot_done[p], 1);
-        mbar_init(boot_full, 1), mbar_init(boot_empty, 1), mbar_init(tbl, A_ST);
+        mbar_init(boot_full, 1), mbar_init(boot_empty, 1), mbar_init(tbl, A_SW);
         mbar_fence_init();
     }
     for (int i = tid; i < 2 * A_L; i += A_THREADS) logs[i] = 0ull;
@@ -112,7 +115,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     // =========================================================== producer
     if (warp == 0) {
         if (lane_id() != 0) return;
-        const uint32_t boot_bytes = uint32_t(row_bytes < size_t(ch_bytes) ? row_bytes : size_t(ch_bytes));
+        const uint32_t boot_bytes = uint32_t(row_bytes < size_t(boot_elems) * sizeof(T) ? row_bytes : size_t(boot_elems) * sizeof(T));
         uint32_t it = 0;
         int ord = 0;  // ordinal of the row among this CTA's rows that are not skipped
 #ifdef WB_PHASE_TIMERS
@@ -174,6 +177,17 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         return K > n ? n : K;
     };
 
+    // Rows whose kept set is closed by their own top_k need no softmax normaliser: every probability the filter compares
+    // is a ratio inside the candidate set, so the row sum cancels.  When the caller does not ask for the row statistics
+    // either, the stream warps skip the exponentials and the tail normalises over the candidates.
+    auto no_sum_row = [&](int row) -> bool {
+        if (!sample) return false;
+        if (P.greedy && P.greedy[row]) return true;
+        if (a.out.stats || !P.top_k) return false;
+        const int tk = P.top_k[row];
+        return tk >= 1 && tk <= kAsyncMaxK && uint32_t(tk) <= n;
+    };
+
     // =========================================================== tail
     if (warp > A_SW) {
         const Group<A_TT> g{tid - 32 - A_ST, 2};
@@ -187,7 +201,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             if (g.sync_or(!ok)) return false;
             if (g.tid != 0) mbar_wait(boot_full, o & 1);
             const int row = row_of(k);
-            const uint32_t ne = n < uint32_t(A_CH) ? n : uint32_t(A_CH);
+            const uint32_t ne = n < uint32_t(boot_elems) ? n : uint32_t(boot_elems);
             uint32_t K = k_of(row);
             if (sample && P.hist && P.hist_len[row] > 0) {
                 const int32_t* h = P.hist + size_t(row) * P.hist_stride;
@@ -235,6 +249,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 tau = (unsigned long long)select_key_bound<A_TT, T>(g, reinterpret_cast<const T*>(boot), ne, K, hist, &sh->sel) << 32;
             }
             g.sync();
+            if (g.tid < A_SW) wbound[p * A_SW + g.tid] = 0u;  // no bound from the stream warps yet
+            g.sync();
             if (g.tid == 0) {
                 sh->slot[p].tau = tau;
                 sh->slot[p].cnt = 0;
@@ -260,6 +276,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             return;
         }
         int ord = 0;
+        uint32_t carry_last = 0, carry_step = 0;  // refinement state of the next row, when its first one ran early
         for (int k = next_row(-1); k < my_rows; ++ord) {
             const int kn = next_row(k);
             const int p = ord & 1;
@@ -268,12 +285,13 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             const int row = row_of(k);
             const uint32_t K = k_of(row);
             bool booted = kn >= my_rows;
-            uint32_t n_last = 0;
+            uint32_t n_last = carry_last;
 #ifdef WB_PHASE_TIMERS
             uint32_t n_refine = 0;
 #endif
             // the first refinement as soon as the log holds K entries, later ones when it has grown by a few K
-            uint32_t step = 0;
+            uint32_t step = carry_step;
+            carry_last = carry_step = 0;
             // ---- while the row streams: raise its threshold, prepare the next row
             for (uint32_t spin = 0;; ++spin) {
                 if (g.tid == 0) {
@@ -290,13 +308,14 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                     if (g.tid == 0) atomicExch(a.err, 3u);
                     return;
                 }
-                if (nlog >= K && nlog >= n_last + step) {
+                if (nlog >= K && nlog >= 64 && nlog >= n_last + step) {
 #ifdef WB_PHASE_TIMERS
                     const long long tr0 = clock64();
 #endif
-                    // entries reserved but not written yet read as zero and rank last: the bound stays valid
+                    // the exact K-th largest of the log so far: tighter than the stream warps' own bound from their maxima
+                    // (entries reserved but not written yet read as zero and rank last: the bound stays valid)
                     const unsigned long long kth = select_kth<A_TT>(g, log, nlog, K, hist, &sh->sel);
-                    if (g.tid == 0 && kth > sl->tau) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = kth;
+                    if (g.tid == 0 && kth > ld_volatile_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = kth;
                     n_last = nlog;
                     step = 2 * K > 128 ? 2 * K : 128;
 #ifdef WB_PHASE_TIMERS
@@ -349,7 +368,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 for (int w = 0; w < A_SW; ++w)
                     if (sl->red_m[w] != -INFINITY) S += sl->red_s[w] * exp2(double(sl->red_e[w]) - double(M) * cexp);
             }
-            const float sum = greedy ? 0.f : float(S);
+            const bool no_sum = no_sum_row(row);
+            float sum = no_sum ? 0.f : float(S);
             uint32_t kept = 0;
             bool presorted = false;
             if (!overflow) {
@@ -413,6 +433,27 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 in.inv_t = inv_t;
                 in.top_k = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
                 in.top_p = P.top_p ? P.top_p[row] : 1.0, in.min_p = P.min_p ? P.min_p[row] : 0.0, in.u = P.u ? P.u[row] : 0.0;
+                if (no_sum) {
+                    // normalise over the candidates themselves (sorted or not, hand[] holds exactly the kept ones)
+                    unsigned long long top = 0ull;
+                    for (uint32_t i = g.tid; i < kept; i += A_TT) top = hand[i] > top ? hand[i] : top;
+                    top = warp_max(uint64_t(top));
+                    if ((g.tid & 31) == 0) sh->sel.wsum[g.tid >> 5] = cand_key(top);
+                    g.sync();
+                    uint32_t tk = 0;
+                    for (int w = 0; w < A_TW; ++w) tk = sh->sel.wsum[w] > tk ? sh->sel.wsum[w] : tk;
+                    M = float_of_key(tk);
+                    for (uint32_t i = g.tid; i < kept; i += A_TT)
+                        tail_q[i] = exp(double(__fsub_rn(float_of_key(cand_key(hand[i])), M)) * double(inv_t));
+                    g.sync();
+                    if (g.tid < 32) {
+                        const double z = warp_total(tail_q, kept);
+                        if (g.tid == 0) sh->sel.kth = (unsigned long long)__double_as_longlong(z);
+                    }
+                    g.sync();
+                    sum = float(__longlong_as_double((long long)sh->sel.kth));
+                    g.sync();
+                }
                 in.m = M, in.sum = sum, in.cnt = kept, in.cap = cap, in.V = n;
                 in.race = P.race_key != nullptr, in.race_key = P.race_key ? P.race_key[row] : 0;
                 in.presorted = presorted;
@@ -463,7 +504,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     uint32_t tbl_use = 0;
     // all stream threads meet (bounded wait): false when the wait ran out
     auto rendezvous = [&]() -> bool {
-        mbar_arrive(tbl);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tbl);  // one arrival per warp, after all its lanes are here
         return mbar_wait(tbl, (tbl_use++) & 1);
     };
 #ifdef WB_PHASE_TIMERS
@@ -478,7 +520,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         const int row = row_of(k);
         ASlot* sl = &sh->slot[p];
         unsigned long long* log = logs + size_t(p) * A_L;
-        const bool greedy = sample && P.greedy && P.greedy[row];
+        const bool greedy = no_sum_row(row);  // no exponentials for this row (greedy, or closed by its top_k)
         const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
         const float cexp = inv_t * kLog2e;
         pt.on = false;
@@ -523,6 +565,73 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         bool saw_nan = false, st_fail = false;
         unsigned long long tau_seen = 0ull;
         float tau_f = -INFINITY;
+        uint32_t* wb_row = wbound + p * A_SW;
+        uint32_t iters = 0;
+        const uint32_t rth = (k_of(row) + A_SW - 1) / A_SW;  // each warp's share of the K candidates
+        uint2* whits = hitbuf + size_t(sw) * A_HITS;
+        uint32_t nhits = 0;
+        // One logit joins this lane's running max / sum and, if it can still be among the K best, the row's log.
+        auto inject = [&](float x, uint32_t id) {
+            if (!greedy) {
+                if (x > m_t) {
+                    const float ne = ceilf(x * cexp);
+                    s_t = (m_t == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
+                    e_t = ne, m_t = x;
+                }
+                if (m_t != -INFINITY) s_t += ex2_approx(fmaf(x, cexp, -e_t));
+            } else {
+                m_t = fmaxf(m_t, x);
+            }
+            if (x >= tau_f) {
+                const unsigned long long cnd = make_cand(key_of(x), id);
+                if (cnd > tau_seen) {
+                    const uint32_t pos = atomicAdd(&sl->cnt, 1u);
+                    if (pos < uint32_t(A_L)) log[pos] = cnd;
+                }
+            }
+        };
+        // The first `cntw` waiting history-token logits of this warp get their penalty, one per lane, and join.
+        auto flush_hits = [&](uint32_t cntw) {
+            if (uint32_t(lane) < cntw) {
+                const uint2 e = whits[lane];
+                inject(pt.apply(__uint_as_float(e.y), e.x), e.x);
+            }
+        };
+        // History tokens among this thread's two quads of a stage: their raw logits leave the stage (replaced by -inf, so
+        // the vector loads that follow see them as absent) and wait in the warp's buffer until 32 are there; the penalty
+        // lookup then runs with every lane busy instead of once per scattered hit.
+        auto take_hits = [&](T* stage_mem, uint32_t stage_base, uint32_t id0, bool ok0, uint32_t id1, bool ok1) {
+            uint32_t b = (ok0 ? pt.bits(id0, 4) : 0u) | ((ok1 ? pt.bits(id1, 4) : 0u) << 4);
+            while (__any_sync(0xffffffffu, b != 0)) {
+                const bool has = b != 0;
+                uint32_t id = 0, xb = 0;
+                if (has) {
+                    const int j = __ffs(b) - 1;
+                    b &= b - 1;
+                    id = (j < 4 ? id0 : id1) + (j & 3);
+                    T* at = stage_mem + (id - stage_base);
+                    if (sizeof(T) == 4) {
+                        xb = *reinterpret_cast<uint32_t*>(at);
+                        *reinterpret_cast<uint32_t*>(at) = 0xff800000u;
+                    } else {
+                        xb = uint32_t(*reinterpret_cast<uint16_t*>(at)) << 16;
+                        *reinterpret_cast<uint16_t*>(at) = 0xff80u;
+                    }
+                }
+                const uint32_t bal = __ballot_sync(0xffffffffu, has);
+                if (has) whits[nhits + __popc(bal & ((1u << lane) - 1))] = make_uint2(id, xb);
+                nhits += __popc(bal);
+                __syncwarp();
+                if (nhits >= 32) {
+                    flush_hits(32);
+                    const uint2 mv = (32 + lane) < int(nhits) ? whits[32 + lane] : make_uint2(0, 0);
+                    __syncwarp();
+                    if ((32 + lane) < int(nhits)) whits[lane] = mv;
+                    nhits -= 32;
+                    __syncwarp();
+                }
+            }
+        };
         // NS consecutive stages at once (more independent work per warp, fixed costs paid once); PARTIAL: the last of them is
         // the row's final, shorter stage (vectors past the row's end read as -inf).
         auto stage = [&](uint32_t c, auto ns_tag, auto partial) {
@@ -536,6 +645,11 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             float xv[NE];
             uint32_t qid[NQ];
             bool qv[NQ];
+            {
+                const unsigned long long t = ld_volatile_u64(&sl->tau);
+                if (t != tau_seen) tau_seen = t, tau_f = float_of_key(cand_key(t));
+            }
+            const unsigned long long tau = tau_seen;
 #pragma unroll
             for (int h = 0; h < NS; ++h) {
                 if (!mbar_wait(&full[st_slot], st_phase)) {
@@ -549,6 +663,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 if (sizeof(T) == 4) {
                     qid[2 * h] = (c + h) * A_CH + 4 * g.tid, qid[2 * h + 1] = qid[2 * h] + 4 * A_ST;
                     qv[2 * h] = !part || qid[2 * h] < n, qv[2 * h + 1] = !part || qid[2 * h + 1] < n;
+                    if (pt.on) take_hits(reinterpret_cast<T*>(ring + size_t(st_slot) * ch_bytes), (c + h) * A_CH, qid[2 * h], qv[2 * h], qid[2 * h + 1], qv[2 * h + 1]);
                     const uint4 ninf = make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u);
                     const uint4 q0 = qv[2 * h] ? vec[g.tid] : ninf;
                     const uint4 q1 = qv[2 * h + 1] ? vec[g.tid + A_ST] : ninf;
@@ -557,6 +672,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 } else {
                     qid[2 * h] = (c + h) * A_CH + 8 * g.tid, qid[2 * h + 1] = qid[2 * h] + 4;
                     qv[2 * h] = qv[2 * h + 1] = !part || qid[2 * h] < n;
+                    if (pt.on) take_hits(reinterpret_cast<T*>(ring + size_t(st_slot) * ch_bytes), (c + h) * A_CH, qid[2 * h], qv[2 * h], qid[2 * h + 1], qv[2 * h + 1]);
                     const uint4 q = qv[2 * h] ? vec[g.tid] : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
                     x[0] = __uint_as_float(q.x << 16), x[1] = __uint_as_float(q.x & 0xffff0000u);
                     x[2] = __uint_as_float(q.y << 16), x[3] = __uint_as_float(q.y & 0xffff0000u);
@@ -580,31 +696,6 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             if (lane == 0) {
 #pragma unroll
                 for (int h = 0; h < NS; ++h) mbar_arrive(&empty[st_ring[h]]);
-            }
-            const unsigned long long tau = ld_volatile_u64(&sl->tau);
-            if (tau != tau_seen) tau_seen = tau, tau_f = float_of_key(cand_key(tau));
-            if (pt.on) {
-                // history tokens among this thread's elements: a lane loops over its own hits only
-                uint32_t bits = 0;
-#pragma unroll
-                for (int q = 0; q < NQ; ++q) bits |= (qv[q] ? pt.bits(qid[q], 4) : 0u) << (4 * q);
-                if (bits) {
-                    do {
-                        const int j = __ffs(bits) - 1;
-                        bits &= bits - 1;
-                        float x = xv[0];
-                        uint32_t id = qid[0];
-#pragma unroll
-                        for (int e = 1; e < NE; ++e) x = j == e ? xv[e] : x;
-#pragma unroll
-                        for (int q = 1; q < NQ; ++q) id = (j >> 2) == q ? qid[q] : id;
-                        x = pt.apply(x, id + (j & 3));
-#pragma unroll
-                        for (int e = 0; e < NE; ++e) xv[e] = j == e ? x : xv[e];
-                    } while (bits);
-#pragma unroll
-                    for (int q = 0; q < NQ; ++q) qm[q] = fmaxf(fmaxf(xv[4 * q], xv[4 * q + 1]), fmaxf(xv[4 * q + 2], xv[4 * q + 3]));
-                }
             }
             float vm = qm[0];
 #pragma unroll
@@ -645,6 +736,34 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                     }
                 }
             }
+            // A threshold from the running maxima, with no help from the tail group: if every stream warp names the r-th
+            // largest of its 32 lane maxima, r = ceil(K / 16), then 16 r >= K distinct elements of the row are at or above the
+            // smallest of those 16 values.  Maxima settle fast, so this runs after 1, 2, 4, 8 ... iterations of a row.
+#ifndef WB_NO_WBOUND
+            ++iters;
+            if ((iters & (iters - 1)) == 0) {
+                // the warp's rth largest lane maximum: take the largest away rth - 1 times
+                float v = m_t, rmax = -INFINITY;
+                for (uint32_t i = 0; i < rth; ++i) {
+                    rmax = warp_max(v);
+                    const uint32_t holders = __ballot_sync(0xffffffffu, v == rmax);
+                    if (holders == 0) break;  // only NaN-free maxima exist; an all -inf warp ends here too
+                    if (lane == __ffs(holders) - 1) v = -INFINITY;
+                    if (rmax == -INFINITY) break;
+                }
+                if (lane == 0) wb_row[sw] = key_of(rmax);
+                __syncwarp();
+                uint32_t kmin = lane < A_SW ? ld_volatile_u32(&wb_row[lane]) : 0xffffffffu;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
+                // (a plain compare and store: a lost update only leaves the threshold at another valid, lower bound; a 64-bit
+                // atomic max in shared memory is a contended compare-and-swap loop when 16 warps get here together)
+                if (lane == 0) {
+                    const unsigned long long cand = (unsigned long long)kmin << 32;
+                    if (cand > ld_volatile_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = cand;
+                }
+            }
+#endif
 #ifdef WB_PHASE_TIMERS
             ts_proc += clock64() - tw1;
 #endif
@@ -664,6 +783,11 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             }
         }
         if (st_fail) return;
+        if (pt.on && nhits) {
+            const unsigned long long t = ld_volatile_u64(&sl->tau);
+            if (t != tau_seen) tau_seen = t, tau_f = float_of_key(cand_key(t));
+            flush_hits(nhits);
+        }
         // a NaN logit poisons the f32 sum: such rows are redone by the multi-pass kernel, which counts NaN as -inf
         saw_nan = !greedy && (s_t != s_t);
         if (__any_sync(0xffffffffu, saw_nan) && lane == 0) atomicOr(&sl->cnt, 0x80000000u);
@@ -688,8 +812,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
 #endif
 }
 
-static size_t async_fixed_smem(bool pen, int pen_words, int ch_bytes) {
-    return size_t(ch_bytes) + size_t(2) * A_L * 8 + SEL_BINS * 4 + size_t(kAsyncMaxK) * 8 + 2 * (kAsyncMaxK + 2 * A_TW) * 8 +
+static size_t async_fixed_smem(bool pen, int pen_words, size_t boot_bytes) {
+    return boot_bytes + (pen ? size_t(A_SW) * A_HITS * 8 : 0) + size_t(2) * A_SW * 4 + size_t(2) * A_L * 8 + SEL_BINS * 4 + size_t(kAsyncMaxK) * 8 + 2 * (kAsyncMaxK + 2 * A_TW) * 8 +
            (2 * A_MAXSTAGES + 8) * 8 + sizeof(AShared) + (pen ? size_t(pen_words) * 4 + kPenSlots * 4 : 0) + 128;
 }
 
@@ -700,7 +824,7 @@ bool sample_async_supported(const SelectArgs& a, int dtype) {
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
     const int pen_words = pen ? ((a.n + 31) / 32 + 3) & ~3 : 0;
     const int ch_bytes = int(A_CH * es);
-    return async_fixed_smem(pen, pen_words, ch_bytes) + 3 * size_t(ch_bytes) <= 232448;
+    return async_fixed_smem(pen, pen_words, size_t(A_CH) * es) + 3 * size_t(ch_bytes) <= 232448;
 }
 
 cudaError_t sample_async_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st) {
@@ -708,7 +832,8 @@ cudaError_t sample_async_launch(const SelectArgs& a, int dtype, int sm_count, cu
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
     const int pen_words = pen ? ((a.n + 31) / 32 + 3) & ~3 : 0;
     const int ch_bytes = int(A_CH * es);
-    const size_t fixed = async_fixed_smem(pen, pen_words, ch_bytes);
+    const int boot_elems = A_CH;
+    const size_t fixed = async_fixed_smem(pen, pen_words, size_t(boot_elems) * es);
     int stages = int((232448 - fixed) / ch_bytes);
     if (stages > A_MAXSTAGES) stages = A_MAXSTAGES;
     if (stages < 3) return cudaErrorInvalidConfiguration;
@@ -719,11 +844,11 @@ cudaError_t sample_async_launch(const SelectArgs& a, int dtype, int sm_count, cu
     if (dtype == 0) {
         const cudaError_t e = cudaFuncSetAttribute(sample_async_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        sample_async_kernel<float><<<grid, A_THREADS, smem, st>>>(a, stages, pen_words, ch_bytes);
+        sample_async_kernel<float><<<grid, A_THREADS, smem, st>>>(a, stages, pen_words, ch_bytes, boot_elems);
     } else {
         const cudaError_t e = cudaFuncSetAttribute(sample_async_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        sample_async_kernel<uint16_t><<<grid, A_THREADS, smem, st>>>(a, stages, pen_words, ch_bytes);
+        sample_async_kernel<uint16_t><<<grid, A_THREADS, smem, st>>>(a, stages, pen_words, ch_bytes, boot_elems);
     }
     return cudaGetLastError();
 }

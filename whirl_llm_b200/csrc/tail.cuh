@@ -69,11 +69,53 @@ __device__ void sort_desc(const Group<NT>& g, uint64_t* cand, uint32_t cap) {
     }
 }
 
+// ---- sums over the sorted candidates, by one warp.  Lane l owns the l-th block of ceil(n / 32) consecutive terms: terms are
+// added in candidate order inside a block and the block sums are combined in block order.  (The host adds all terms in one
+// sequence; the two orders differ by rounding in the last place only, the same size as the difference between the
+// device's and the host's exp.)
+__device__ __forceinline__ double warp_excl_scan(double v, double* total) {
+    double incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane_id() >= o) incl += t;
+    }
+    *total = __shfl_sync(0xffffffffu, incl, 31);
+    return incl - v;
+}
+// sum of v[0..n)
+__device__ __forceinline__ double warp_total(const double* v, uint32_t n) {
+    const uint32_t S = (n + 31) / 32, b = lane_id() * S, e = min(n, b + S);
+    double s = 0;
+    for (uint32_t i = b; i < e; ++i) s += v[i];
+    double tot;
+    warp_excl_scan(s, &tot);
+    return tot;
+}
+// smallest j with cum(v[0..j]) >= t (STRICT: > t), n when there is none; *cum_end = the sum of everything walked
+template <bool STRICT>
+__device__ __forceinline__ uint32_t warp_first_reach(const double* v, uint32_t n, double t, double* cum_end) {
+    const uint32_t S = (n + 31) / 32, b = min(n, lane_id() * S), e = min(n, b + S);
+    double s = 0;
+    for (uint32_t i = b; i < e; ++i) s += v[i];
+    double tot;
+    double cum = warp_excl_scan(s, &tot);
+    uint32_t first = n;
+    for (uint32_t i = b; i < e; ++i) {
+        cum += v[i];
+        if (first == n && (STRICT ? cum > t : cum >= t)) first = i;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
+    *cum_end = tot;
+    return first;
+}
+
 // cand: the exact candidate set (any order unless in.presorted, padded with zeros up to cap); p, q: scratch of
 // cap + 2 * NT / 32 doubles each; res: one shared TailOut.  On return (after the group's barrier) cand is sorted,
 // p[0..n) holds the kept probabilities (renormalised when closed) and *res the outcome.
-// The order of operations of every sum follows the host code: one thread adds the terms in candidate order; only the
-// independent exponentials and divisions run in parallel.
+// The steps are those of the host filter (sampler.cpp:15-78); exponentials, divisions and comparisons run on all
+// threads, the running sums on the group's first warp (see above for their order).
 template <int NT>
 __device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand, double* p, double* q, TailOut* res) {
     if (!in.presorted) sort_desc<NT>(g, cand, in.cap);
@@ -84,7 +126,7 @@ __device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand
     }
     g.sync();
     // ---- top-k, and the normaliser of the top-p walk (sampler.cpp:35-49)
-    if (g.tid == 0) {
+    if (g.tid < 32) {
         uint32_t n = in.cnt;
         bool closed = in.cnt == in.V, esc = false;
         if (in.top_k > 0) {
@@ -92,12 +134,11 @@ __device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand
             else if (!closed) esc = true;
         }
         double z = 1.0;
-        if (!esc && in.top_p < 1.0 && closed) {
-            z = 0;
-            for (uint32_t i = 0; i < n; ++i) z += p[i];
+        if (!esc && in.top_p < 1.0 && closed) z = warp_total(p, n);
+        if (g.tid == 0) {
+            res->status = esc ? ROW_ESCALATE : ROW_DONE;
+            res->n = n, res->closed = closed, res->cum = z, res->token = 0;
         }
-        res->status = esc ? ROW_ESCALATE : ROW_DONE;
-        res->n = n, res->closed = closed, res->cum = z, res->token = 0;
     }
     g.sync();
     if (res->status == ROW_ESCALATE) return;
@@ -108,37 +149,34 @@ __device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand
         g.sync();
     }
     // ---- top-p cut, min-p cut, the renormaliser (sampler.cpp:50-74)
-    if (g.tid == 0) {
+    if (g.tid < 32) {
         uint32_t n = res->n;
         bool closed = res->closed != 0, esc = false;
         if (in.top_p < 1.0) {
-            double cum = 0;
-            bool found = false;
-            for (uint32_t j = 0; j < n; ++j) {
-                cum += q[j];
-                if (cum >= in.top_p) {
-                    n = j + 1;
-                    found = true;
-                    break;
-                }
-            }
-            if (found) closed = true;
+            double walked;
+            const uint32_t j = warp_first_reach<false>(q, n, in.top_p, &walked);
+            if (j < n) n = j + 1, closed = true;
             else if (!closed) esc = true;
         }
         if (!esc && in.min_p > 0) {
             const double thr = in.min_p * p[0];
-            uint32_t j = 0;
-            while (j < n && p[j] >= thr) ++j;
+            uint32_t j = n;  // first candidate below the threshold
+            for (uint32_t i = lane_id(); i < n; i += 32)
+                if (!(p[i] >= thr)) {
+                    j = i;
+                    break;
+                }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) j = min(j, __shfl_xor_sync(0xffffffffu, j, o));
             if (j == n && !closed) esc = true;
             else n = j > 1 ? j : 1, closed = true;
         }
         double z = 1.0;
-        if (!esc && closed) {
-            z = 0;
-            for (uint32_t i = 0; i < n; ++i) z += p[i];
+        if (!esc && closed) z = warp_total(p, n);
+        if (g.tid == 0) {
+            res->status = esc ? ROW_ESCALATE : ROW_DONE;
+            res->n = n, res->closed = closed, res->cum = z;
         }
-        res->status = esc ? ROW_ESCALATE : ROW_DONE;
-        res->n = n, res->closed = closed, res->cum = z;
     }
     g.sync();
     if (res->status == ROW_ESCALATE) return;
@@ -152,10 +190,9 @@ __device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand
     bool do_race = in.race != 0;
     if (do_race && !closed) {
         // open target: candidates vs tail by the stream-0 uniform (u < their mass S), src/sampling/sampler.cpp:84-93
-        if (g.tid == 0) {
-            double S = 0;
-            for (uint32_t i = 0; i < n; ++i) S += p[i];
-            res->cum = S;
+        if (g.tid < 32) {
+            const double S = warp_total(p, n);
+            if (g.tid == 0) res->cum = S;
         }
         g.sync();
         do_race = in.u < res->cum;
@@ -196,23 +233,16 @@ __device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand
         g.sync();
         return;
     }
-    if (g.tid == 0) {
-        // inverse CDF over the kept candidates (sampleRow with no excluded token)
-        const double target = in.u;
-        double cum = 0;
-        uint32_t tok = cand_id(cand[0]);
-        bool hit = false;
-        for (uint32_t i = 0; i < n; ++i) {
-            cum += p[i];
-            tok = cand_id(cand[i]);
-            if (cum > target) {
-                hit = true;
-                break;
-            }
+    if (g.tid < 32) {
+        // inverse CDF over the kept candidates (sampleRow with no excluded token): the first i with cum > u
+        double walked;
+        const uint32_t i = warp_first_reach<true>(p, n, in.u, &walked);
+        if (g.tid == 0) {
+            const bool hit = i < n;
+            res->token = cand_id(cand[hit ? i : (n ? n - 1 : 0)]);  // closed and not hit: the last candidate is the fallback
+            res->cum = walked;
+            res->status = (hit || closed) ? ROW_DONE : ROW_OPEN_TAIL;
         }
-        res->token = tok;  // closed and not hit: the last candidate is the fallback
-        res->cum = cum;
-        res->status = (hit || closed) ? ROW_DONE : ROW_OPEN_TAIL;
     }
     g.sync();
 }
