@@ -55,6 +55,9 @@ enum {
 #define WHIRL_Q_MAX 32           /* support of a draft distribution (include/whirl/spec_sample.h:40) */
 #define WHIRL_CTL_WORDS 64       /* i32 words of one sequence's control area (include/whirl/model_types.h:55-61) */
 
+typedef struct whirl_sample_params whirl_sample_params;
+typedef struct whirl_sample_out whirl_sample_out;
+
 const char* whirl_status_string(int status);
 const char* whirl_last_error(void);
 int whirl_version(void);
@@ -125,6 +128,25 @@ int whirl_topk_rows(const void* x, int dtype, int rows, int n, int K, float inv_
                     float* vals, float* stats, void* ws, size_t ws_bytes, void* stream);
 
 /* ------------------------------------------------------------------------------------------------------------------
+ * Vocab-sharded logits (the output of a tensor-parallel lm_head).  No counterpart in the reference, which runs on one GPU
+ * (include/whirl/gpu_select.h:23-25 leaves multi-GPU for later).
+ * ---------------------------------------------------------------------------------------------------------------- */
+
+/* whirl_topk_rows on one vocabulary slice: x is [rows][n] with n the slice width; every id written is id_offset + the
+ * index inside the slice, i.e. a global token id.  Entries beyond min(K, n) are left untouched: pre-fill ids with -1. */
+int whirl_topk_rows_shard(const void* x, int dtype, int rows, int n, int K, int id_offset, float inv_t, const float* inv_t_rows,
+                          int* ids, float* vals, float* stats, void* ws, size_t ws_bytes, void* stream);
+
+/* Merge the slices' candidates and sample: ids / vals are [shards][rows][K_s] and stats [shards][rows][2], the layout an
+ * all-gather of each rank's whirl_topk_rows_shard outputs produces.  Row statistics merge as m = max m_s,
+ * sum = sum_s sum_s * exp((m_s - m) * inv_t); the candidates are the global min(top_k, K_s) best (exact, because the
+ * global K best lie inside the union of the slices' K_s best when K <= K_s), then top-k / top-p / min-p and the draw as
+ * in whirl_sample_rows.  A row whose kept set may reach past K_s candidates comes back WHIRL_ROW_ESCALATE.
+ * Limits: K_s <= 1024, shards * K_s <= 16384; penalties (params->hist) are not accepted here. */
+int whirl_merge_sample_rows(const int* ids, const float* vals, const float* stats, int shards, int rows, int K_s, int n_total,
+                            const whirl_sample_params* params, const whirl_sample_out* out, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------------------
  * The fused sampler: penalties -> candidates -> top-k / top-p / min-p -> draw, one token per row, all on the device.
  * It replaces the round trip topk_rows -> download -> sampling::filterCands -> sampling::sampleRow
  * (src/server/engine_decode.cpp:383-406, src/server/engine_sampling.cpp:51-84, src/sampling/sampler.cpp:15-147).
@@ -132,7 +154,7 @@ int whirl_topk_rows(const void* x, int dtype, int rows, int n, int K, float inv_
 
 /* Per-row parameters, device arrays of `rows` entries; a null pointer means the default in brackets.  These are the
  * fields of sampling::Sampler (src/sampling/sampler.h:26-53) that the arithmetic reads. */
-typedef struct whirl_sample_params {
+struct whirl_sample_params {
     const float* inv_t;         /* [1] 1 / temperature */
     const int32_t* top_k;       /* [0 = off] */
     const double* top_p;        /* [1] */
@@ -148,10 +170,10 @@ typedef struct whirl_sample_params {
     const float* rep;           /* [1] repetition: l > 0 ? l / rep : l * rep */
     const float* pres;          /* [0] presence: l -= pres */
     const float* freq;          /* [0] frequency: l -= freq * count */
-} whirl_sample_params;
+};
 
 /* Outputs, device arrays; only token is required. */
-typedef struct whirl_sample_out {
+struct whirl_sample_out {
     int32_t* token;     /* [rows] */
     int32_t* status;    /* [rows] WHIRL_ROW_* (may be null) */
     int32_t* n_kept;    /* [rows] size of the kept set, Sampler.n */
@@ -161,7 +183,7 @@ typedef struct whirl_sample_out {
     double* kept_p;     /* [rows][kept_cap] their probabilities (renormalised when closed) */
     int32_t kept_cap;
     uint32_t* counters; /* [WHIRL_CNT_WORDS] added to, never cleared */
-} whirl_sample_out;
+};
 
 int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sample_params* params,
                       const whirl_sample_out* out, void* ws, size_t ws_bytes, void* stream);

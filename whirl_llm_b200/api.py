@@ -58,6 +58,8 @@ def _load() -> C.CDLL:
         "whirl_draft_pick": (i, [vp, i, i, vp, vp, vp, i, i, f, vp, vp, sz, vp]),
         "whirl_draft_pick_rows": (i, [vp, i, i, i, vp, vp, i, i, f, vp, vp, sz, vp]),
         "whirl_topk_rows": (i, [vp, i, i, i, i, f, vp, vp, vp, vp, vp, sz, vp]),
+        "whirl_topk_rows_shard": (i, [vp, i, i, i, i, i, f, vp, vp, vp, vp, vp, sz, vp]),
+        "whirl_merge_sample_rows": (i, [vp, vp, vp, i, i, i, i, C.POINTER(SampleParams), C.POINTER(SampleOut), vp]),
         "whirl_sample_rows": (i, [vp, i, i, i, C.POINTER(SampleParams), C.POINTER(SampleOut), vp, sz, vp]),
         "whirl_sample_rows_host": (i, [vp, i, i, i, C.POINTER(SampleParams), C.POINTER(SampleOut), i]),
         "whirl_host_release": (None, []),
@@ -73,7 +75,7 @@ def _load() -> C.CDLL:
 lib = _load()
 DECLARED = ["whirl_status_string", "whirl_last_error", "whirl_version", "whirl_workspace_bytes", "whirl_argmax",
             "whirl_argmax_rows", "whirl_argmax_rows_static", "whirl_argmax_rows_to", "whirl_argmax_prob", "whirl_draft_pick", "whirl_draft_pick_rows",
-            "whirl_topk_rows", "whirl_sample_rows", "whirl_sample_rows_host", "whirl_host_release", "whirl_host_last_error",
+            "whirl_topk_rows", "whirl_topk_rows_shard", "whirl_merge_sample_rows", "whirl_sample_rows", "whirl_sample_rows_host", "whirl_host_release", "whirl_host_last_error",
             "whirl_launch_counts"]
 
 
@@ -199,6 +201,18 @@ def topk_rows(x, K, inv_t=1.0, inv_t_rows=None, ws=None):
     return ids, vals, stats
 
 
+def topk_rows_shard(x, K, id_offset, inv_t=1.0, inv_t_rows=None, ws=None):
+    """topk_rows of one vocabulary slice with global token ids (ids pre-filled with -1)."""
+    x, rows, n = _rows(x)
+    ids = torch.full((rows, K), -1, dtype=torch.int32, device=x.device)
+    vals = torch.zeros((rows, K), dtype=torch.float32, device=x.device)
+    stats = torch.zeros((rows, 2), dtype=torch.float32, device=x.device)
+    ws = workspace(rows, n, x.device) if ws is None else ws
+    _check(lib.whirl_topk_rows_shard(x.data_ptr(), _dtype(x), rows, n, K, int(id_offset), float(inv_t), _p(inv_t_rows),
+                                     ids.data_ptr(), vals.data_ptr(), stats.data_ptr(), ws.data_ptr(), ws.numel(), _stream(x)))
+    return ids, vals, stats
+
+
 @dataclass
 class RowParams:
     """Device tensors of per-row sampler settings (None = the library default)."""
@@ -295,3 +309,23 @@ def sample_rows_host(x_host, params: dict, rows: int, n: int, dtype: int, out: d
     st = lib.whirl_sample_rows_host(x_host.data_ptr(), dtype, rows, n, C.byref(ps), C.byref(o), device)
     if st != 0:
         raise WhirlError(st, (lib.whirl_host_last_error() or b"").decode())
+
+
+def merge_sample_rows(ids, vals, stats, n_total: int, params: RowParams, kept_cap: int = 0) -> SampleResult:
+    """ids / vals [shards, rows, K_s], stats [shards, rows, 2] (all-gathered slices) -> one token per row."""
+    shards, rows, ks = ids.shape
+    dev = ids.device
+    res = SampleResult(
+        token=torch.empty(rows, dtype=torch.int32, device=dev), status=torch.empty(rows, dtype=torch.int32, device=dev),
+        n_kept=torch.empty(rows, dtype=torch.int32, device=dev), closed=torch.empty(rows, dtype=torch.int32, device=dev),
+        stats=torch.empty((rows, 2), dtype=torch.float32, device=dev),
+        kept_ids=torch.full((rows, kept_cap), -1, dtype=torch.int32, device=dev) if kept_cap else None,
+        kept_p=torch.zeros((rows, kept_cap), dtype=torch.float64, device=dev) if kept_cap else None,
+        counters=torch.zeros(CNT_WORDS, dtype=torch.int32, device=dev))
+    o = SampleOut(token=_p(res.token), status=_p(res.status), n_kept=_p(res.n_kept), closed=_p(res.closed), stats=_p(res.stats),
+                  kept_ids=_p(res.kept_ids), kept_p=_p(res.kept_p), kept_cap=kept_cap, counters=_p(res.counters))
+    ps = params.struct(rows)
+    assert ids.is_contiguous() and vals.is_contiguous() and stats.is_contiguous()
+    _check(lib.whirl_merge_sample_rows(ids.data_ptr(), vals.data_ptr(), stats.data_ptr(), shards, rows, ks, n_total, C.byref(ps),
+                                       C.byref(o), torch.cuda.current_stream(dev).cuda_stream))
+    return res

@@ -209,12 +209,18 @@ int whirl_draft_pick_rows(const void* x, int dtype, int rows, int n, int* ctl_al
 
 int whirl_topk_rows(const void* x, int dtype, int rows, int n, int K, float inv_t, const float* inv_t_rows, int* ids,
                     float* vals, float* stats, void* ws, size_t ws_bytes, void* stream) {
+    return whirl_topk_rows_shard(x, dtype, rows, n, K, 0, inv_t, inv_t_rows, ids, vals, stats, ws, ws_bytes, stream);
+}
+
+int whirl_topk_rows_shard(const void* x, int dtype, int rows, int n, int K, int id_offset, float inv_t, const float* inv_t_rows,
+                          int* ids, float* vals, float* stats, void* ws, size_t ws_bytes, void* stream) {
     if (!x || !ids || !vals || !stats || rows < 0 || n <= 0 || bad_dtype(dtype)) return fail(WHIRL_ERR_INVALID, "topk_rows: bad pointer / rows / n / dtype");
     if (K < 1) return fail(WHIRL_ERR_INVALID, "topk_rows: K < 1");
     if (K > WHIRL_MAX_K) return fail(WHIRL_ERR_UNSUPPORTED, "topk_rows: K above WHIRL_MAX_K");
     if (rows == 0) return WHIRL_OK;
     wb::SelectArgs a{};
     a.x = x, a.rows = rows, a.n = n, a.mode = wb::MODE_TOPK, a.K = K, a.ids = ids, a.vals = vals, a.stats = stats;
+    a.id_offset = id_offset;
     a.prm.inv_t = inv_t_rows, a.prm.inv_t_scalar = inv_t;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
@@ -320,6 +326,24 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
 #ifdef WB_PHASE_TIMERS
 size_t whirl_debug_err_offset(int rows) { return ws_layout(rows).off_err; }
 #endif
+
+int whirl_merge_sample_rows(const int* ids, const float* vals, const float* stats, int shards, int rows, int K_s, int n_total,
+                            const whirl_sample_params* prm, const whirl_sample_out* out, void* stream) {
+    if (!ids || !vals || !stats || !prm || !out || !out->token || shards < 1 || rows < 0 || K_s < 1 || n_total < 1)
+        return fail(WHIRL_ERR_INVALID, "merge_sample_rows: bad pointer / shards / rows / K_s / n_total");
+    if (K_s > WHIRL_STREAM_MAX_K || size_t(shards) * K_s > 16384) return fail(WHIRL_ERR_UNSUPPORTED, "merge_sample_rows: K_s above 1024 or shards * K_s above 16384");
+    if (prm->hist) return fail(WHIRL_ERR_UNSUPPORTED, "merge_sample_rows: penalties belong to the per-slice selection");
+    if (rows == 0) return WHIRL_OK;
+    wb::RowParams P{};
+    P.inv_t = prm->inv_t, P.inv_t_scalar = 1.f, P.top_k = prm->top_k, P.top_p = prm->top_p, P.min_p = prm->min_p;
+    P.greedy = prm->greedy, P.u = prm->u, P.race_key = prm->race_key;
+    wb::RowOutputs O{};
+    O.token = out->token, O.status = out->status, O.n_kept = out->n_kept, O.closed = out->closed, O.stats = out->stats;
+    O.kept_ids = out->kept_ids, O.kept_p = out->kept_p, O.kept_cap = out->kept_cap, O.counters = out->counters;
+    const cudaError_t e = wb::merge_sample_launch(ids, vals, stats, shards, rows, K_s, n_total, P, O, sm_count(), static_cast<cudaStream_t>(stream));
+    bump(LC_AUX);
+    return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "merge_sample_rows launch");
+}
 
 void whirl_launch_counts(uint64_t* out, int n) {
     for (int i = 0; i < n && i < 4; ++i) out[i] = g_launch[i].load(std::memory_order_relaxed);

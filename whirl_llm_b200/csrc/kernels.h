@@ -94,6 +94,7 @@ struct SelectArgs {
     const int32_t* row_count; // optional device count overriding `rows` (with row_list)
     int level_k;              // candidates for rows without a usable top_k (256 first level, 16384 second)
     void* ws;                 // generic: [rows][level cap] doubles of probability scratch
+    int32_t id_offset;        // MODE_TOPK: added to every id written (a vocabulary slice's first token id)
     uint32_t* err;            // device error word (bounded waits that ran out)
     int only_large_k;         // large-K kernel: 0 = every row, 1 = only rows whose top_k is above kAsyncMaxK
 };
@@ -111,5 +112,9 @@ bool sample_async_supported(const SelectArgs& a, int dtype);
 constexpr int kStreamMaxK = 1024;
 cudaError_t sample_stream_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
 bool sample_stream_supported(const SelectArgs& a, int dtype);
+
+// ---- vocab-sharded candidates (merge.cu)
+cudaError_t merge_sample_launch(const int32_t* ids, const float* vals, const float* stats, int shards, int rows, int Ks,
+                                int n_total, const RowParams& P, const RowOutputs& out, int sm_count, cudaStream_t st);
 
 }  // namespace wb

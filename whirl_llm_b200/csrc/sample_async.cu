@@ -413,7 +413,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 const T* xr = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
                 for (uint32_t j = g.tid; j < kept; j += A_TT) {
                     const uint32_t id = cand_id(hand[j]);
-                    a.ids[size_t(row) * a.K + j] = int32_t(id);
+                    a.ids[size_t(row) * a.K + j] = int32_t(id) + a.id_offset;
                     a.vals[size_t(row) * a.K + j] = sizeof(T) == 4 ? reinterpret_cast<const float*>(xr)[id] : bf16_to_f32(reinterpret_cast<const uint16_t*>(xr)[id]);
                 }
                 if (g.tid == 0) a.stats[2 * row] = M, a.stats[2 * row + 1] = sum;

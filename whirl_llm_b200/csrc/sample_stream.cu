@@ -143,7 +143,7 @@ sample_stream_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes) {
                 const T* xr = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
                 for (uint32_t j = g.tid; j < hd.cnt; j += ET) {
                     const uint32_t id = cand_id(cand[j]);
-                    a.ids[size_t(row) * a.K + j] = int32_t(id);
+                    a.ids[size_t(row) * a.K + j] = int32_t(id) + a.id_offset;
                     a.vals[size_t(row) * a.K + j] = sizeof(T) == 4 ? reinterpret_cast<const float*>(xr)[id] : bf16_to_f32(reinterpret_cast<const uint16_t*>(xr)[id]);
                 }
                 if (g.tid == 0) a.stats[2 * row] = hd.m, a.stats[2 * row + 1] = hd.sum;

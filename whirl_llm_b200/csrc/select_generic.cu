@@ -247,7 +247,7 @@ __device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_ma
         sort_desc<GT>(g, cand, cap);
         for (uint32_t j = tid; j < K; j += GT) {
             const uint32_t id = cand_id(cand[j]);
-            a.ids[size_t(row) * a.K + j] = int32_t(id);
+            a.ids[size_t(row) * a.K + j] = int32_t(id) + a.id_offset;
             a.vals[size_t(row) * a.K + j] = raw_elem(x, id);
         }
         if (tid == 0) {
