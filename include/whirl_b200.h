@@ -114,6 +114,27 @@ int whirl_draft_pick_rows(const void* x, int dtype, int rows, int n, int* ctl_al
 #define WHIRL_STATIC_MAX_ROWS 256
 int whirl_argmax_rows_static(const void* x, int dtype, int rows, int n, int* out, void* stream);
 
+/* draft_sample_rows(x, n, ctl_all, RowIdx area, r, map, DSampArgs a, qbuf): kernels/spec_sample.hip:34-205 (launch:
+ * src/model/qwen35/forward/mtp_verify.cpp:344).  Rows with on != 0 replace their greedy draft r by a token drawn from the
+ * draft distribution q by the race coupled to the target sampler: q = softmax at the request temperature over the
+ * min(top_k, 32) largest logits (32 when top_k is 0; NaN logits never ahead of numbers), then top-k / top-p / min-p in
+ * f32, renormalised; token = argmin E(id) / q.  Writes the token to word 16 + r of the row's control area and q
+ * ([n | ids[32] | p bits[32]], WHIRL_Q_WORDS words) to qbuf + qoff[row].  A row whose chain was stopped by the p-min
+ * cut-off at or before r (words 48 / 49) is skipped.  The reference's by-value DSampArgs of eight 32-entry arrays
+ * (kernels/kernel_args.h:55-66) becomes eight device arrays of `rows` entries. */
+typedef struct whirl_dsamp_args {
+    const int32_t* on;
+    const int32_t* top_k;
+    const int32_t* qoff;
+    const float* inv_t;
+    const float* top_p;
+    const float* min_p;
+    const uint32_t* key_lo; /* spec::raceBase(seed, output index of draft r), include/whirl/spec_sample.h:58-60 */
+    const uint32_t* key_hi;
+} whirl_dsamp_args;
+int whirl_draft_sample_rows(const void* x, int dtype, int rows, int n, int* ctl_all, const int* area, int r, const int* map,
+                            const whirl_dsamp_args* args, int* qbuf, void* stream);
+
 /* ------------------------------------------------------------------------------------------------------------------
  * Candidates.
  * ---------------------------------------------------------------------------------------------------------------- */

@@ -33,6 +33,11 @@ class SampleParams(C.Structure):
                 ("freq", C.c_void_p)]
 
 
+class DSampArgs(C.Structure):
+    _fields_ = [("on", C.c_void_p), ("top_k", C.c_void_p), ("qoff", C.c_void_p), ("inv_t", C.c_void_p), ("top_p", C.c_void_p),
+                ("min_p", C.c_void_p), ("key_lo", C.c_void_p), ("key_hi", C.c_void_p)]
+
+
 class SampleOut(C.Structure):
     _fields_ = [("token", C.c_void_p), ("status", C.c_void_p), ("n_kept", C.c_void_p), ("closed", C.c_void_p),
                 ("stats", C.c_void_p), ("kept_ids", C.c_void_p), ("kept_p", C.c_void_p), ("kept_cap", C.c_int32),
@@ -58,6 +63,7 @@ def _load() -> C.CDLL:
         "whirl_draft_pick": (i, [vp, i, i, vp, vp, vp, i, i, f, vp, vp, sz, vp]),
         "whirl_draft_pick_rows": (i, [vp, i, i, i, vp, vp, i, i, f, vp, vp, sz, vp]),
         "whirl_topk_rows": (i, [vp, i, i, i, i, f, vp, vp, vp, vp, vp, sz, vp]),
+        "whirl_draft_sample_rows": (i, [vp, i, i, i, vp, vp, i, vp, C.POINTER(DSampArgs), vp, vp]),
         "whirl_topk_rows_shard": (i, [vp, i, i, i, i, i, f, vp, vp, vp, vp, vp, sz, vp]),
         "whirl_merge_sample_rows": (i, [vp, vp, vp, i, i, i, i, C.POINTER(SampleParams), C.POINTER(SampleOut), vp]),
         "whirl_sample_rows": (i, [vp, i, i, i, C.POINTER(SampleParams), C.POINTER(SampleOut), vp, sz, vp]),
@@ -74,7 +80,7 @@ def _load() -> C.CDLL:
 
 lib = _load()
 DECLARED = ["whirl_status_string", "whirl_last_error", "whirl_version", "whirl_workspace_bytes", "whirl_argmax",
-            "whirl_argmax_rows", "whirl_argmax_rows_static", "whirl_argmax_rows_to", "whirl_argmax_prob", "whirl_draft_pick", "whirl_draft_pick_rows",
+            "whirl_argmax_rows", "whirl_argmax_rows_static", "whirl_argmax_rows_to", "whirl_argmax_prob", "whirl_draft_pick", "whirl_draft_pick_rows", "whirl_draft_sample_rows",
             "whirl_topk_rows", "whirl_topk_rows_shard", "whirl_merge_sample_rows", "whirl_sample_rows", "whirl_sample_rows_host", "whirl_host_release", "whirl_host_last_error",
             "whirl_launch_counts"]
 
@@ -187,6 +193,17 @@ def draft_pick_rows(x, ctl_all, area, r, n_min, p_min, vmap=None, ws=None):
     ws = workspace(rows, n, x.device) if ws is None else ws
     _check(lib.whirl_draft_pick_rows(x.data_ptr(), _dtype(x), rows, n, ctl_all.data_ptr(), area.data_ptr(), r, n_min, p_min,
                                      _p(vmap), ws.data_ptr(), ws.numel(), _stream(x)))
+
+
+def draft_sample_rows(x, ctl_all, area, r, on, top_k, qoff, inv_t, top_p, min_p, race_key, qbuf, vmap=None):
+    """draft_sample_rows: per-row arrays are device tensors (int32 / float32); race_key int64 holding the uint64 keys."""
+    x, rows, n = _rows(x)
+    lo = (race_key & 0xFFFFFFFF).to(torch.int32).contiguous()
+    hi = ((race_key >> 32) & 0xFFFFFFFF).to(torch.int32).contiguous()
+    d = DSampArgs(on=_p(on), top_k=_p(top_k), qoff=_p(qoff), inv_t=_p(inv_t), top_p=_p(top_p), min_p=_p(min_p), key_lo=_p(lo),
+                  key_hi=_p(hi))
+    _check(lib.whirl_draft_sample_rows(x.data_ptr(), _dtype(x), rows, n, ctl_all.data_ptr(), area.data_ptr(), r, _p(vmap),
+                                       C.byref(d), qbuf.data_ptr(), _stream(x)))
 
 
 def topk_rows(x, K, inv_t=1.0, inv_t_rows=None, ws=None):

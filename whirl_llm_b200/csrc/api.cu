@@ -327,6 +327,24 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
 size_t whirl_debug_err_offset(int rows) { return ws_layout(rows).off_err; }
 #endif
 
+int whirl_draft_sample_rows(const void* x, int dtype, int rows, int n, int* ctl_all, const int* area, int r, const int* map,
+                            const whirl_dsamp_args* da, int* qbuf, void* stream) {
+    if (!x || !ctl_all || !area || !da || !qbuf || rows < 0 || n <= 0 || bad_dtype(dtype) || r < 0 || r >= 16)
+        return fail(WHIRL_ERR_INVALID, "draft_sample_rows: bad pointer / rows / n / dtype / r");
+    if (!da->on || !da->top_k || !da->qoff || !da->inv_t || !da->top_p || !da->min_p || !da->key_lo || !da->key_hi)
+        return fail(WHIRL_ERR_INVALID, "draft_sample_rows: every array of whirl_dsamp_args is required");
+    if (rows == 0) return WHIRL_OK;
+    wb::SelectArgs a{};
+    a.x = x, a.rows = rows, a.n = n, a.mode = wb::MODE_DRAFT;
+    a.prm.inv_t_scalar = 1.f;
+    a.draft.on = da->on, a.draft.top_k = da->top_k, a.draft.qoff = da->qoff, a.draft.inv_t = da->inv_t, a.draft.top_p = da->top_p;
+    a.draft.min_p = da->min_p, a.draft.key_lo = da->key_lo, a.draft.key_hi = da->key_hi;
+    a.draft.ctl_all = ctl_all, a.draft.area = area, a.draft.r = r, a.draft.map = map, a.draft.qbuf = qbuf;
+    const cudaError_t e = wb::select_generic_launch(a, dtype, sm_count(), static_cast<cudaStream_t>(stream));
+    bump(LC_GENERIC);
+    return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "draft_sample_rows launch");
+}
+
 int whirl_merge_sample_rows(const int* ids, const float* vals, const float* stats, int shards, int rows, int K_s, int n_total,
                             const whirl_sample_params* prm, const whirl_sample_out* out, void* stream) {
     if (!ids || !vals || !stats || !prm || !out || !out->token || shards < 1 || rows < 0 || K_s < 1 || n_total < 1)

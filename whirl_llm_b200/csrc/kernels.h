@@ -75,7 +75,24 @@ struct RowOutputs {
     uint32_t* counters;  // [8] batch counters (may be null), see WHIRL_CNT_*
 };
 
-enum { MODE_TOPK = 0, MODE_SAMPLE = 1 };
+enum { MODE_TOPK = 0, MODE_SAMPLE = 1, MODE_DRAFT = 2 };
+
+// draft_sample_rows per-row parameters (the reference passes them by value: kernels/kernel_args.h:55-66), device arrays
+struct DraftArgs {
+    const int32_t* on;
+    const int32_t* top_k;
+    const int32_t* qoff;  // i32 word offset of the row's q entry in qbuf
+    const float* inv_t;
+    const float* top_p;
+    const float* min_p;
+    const uint32_t* key_lo;  // race key base, spec::raceBase(seed, output index of draft r)
+    const uint32_t* key_hi;
+    int32_t* ctl_all;
+    const int32_t* area;  // word offset of each row's 64-word control area
+    int32_t r;
+    const int32_t* map;   // token id of each logits row entry (draft-head vocabulary subset), may be null
+    int32_t* qbuf;
+};
 
 struct SelectArgs {
     const void* x;  // [rows][n]
@@ -94,6 +111,7 @@ struct SelectArgs {
     const int32_t* row_count; // optional device count overriding `rows` (with row_list)
     int level_k;              // candidates for rows without a usable top_k (256 first level, 16384 second)
     void* ws;                 // generic: [rows][level cap] doubles of probability scratch
+    DraftArgs draft;          // MODE_DRAFT
     int32_t id_offset;        // MODE_TOPK: added to every id written (a vocabulary slice's first token id)
     uint32_t* err;            // device error word (bounded waits that ran out)
     int only_large_k;         // large-K kernel: 0 = every row, 1 = only rows whose top_k is above kAsyncMaxK

@@ -82,6 +82,79 @@ template <typename T>
 __device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_max, int pen_words, uint64_t* cand,
                            uint32_t* hist, GShared* sh, uint32_t* pen_mem);
 
+// The serial tail of draft_sample_rows (kernels/spec_sample.hip:132-205), by one thread on at most 32 candidates: map the
+// ids, sort by (logit desc, id asc), q = softmax at the request temperature over the candidates in f32 (same operation
+// order as spec::draftDist, src/common/spec_sample.cpp:33-81), top-k / top-p / min-p, renormalise, then the race draw
+// argmin E(id) / q in f64; writes the token to the control area and q to qbuf.
+__device__ void draft_tail(const SelectArgs& a, int row, const unsigned long long* cand, uint32_t K, float m, float sum, float inv_t) {
+    const DraftArgs& d = a.draft;
+    int id[32];
+    float lg[32], p[32];
+    for (uint32_t i = 0; i < K; ++i) {
+        const uint32_t raw = cand_id(cand[i]);
+        id[i] = d.map ? d.map[raw] : int(raw);
+        const uint32_t k = cand_key(cand[i]);
+        lg[i] = k ? float_of_key(k) : -INFINITY;  // a NaN logit only fills a slot past the numbers, with p = 0
+    }
+    for (uint32_t i = 1; i < K; ++i) {
+        uint32_t j = i;
+        while (j > 0 && (lg[j - 1] < lg[j] || (lg[j - 1] == lg[j] && id[j - 1] > id[j]))) {
+            const float tl = lg[j - 1];
+            lg[j - 1] = lg[j], lg[j] = tl;
+            const int ti = id[j - 1];
+            id[j - 1] = id[j], id[j] = ti;
+            --j;
+        }
+    }
+    for (uint32_t i = 0; i < K; ++i) p[i] = __fdiv_rn(expf(__fmul_rn(__fsub_rn(lg[i], m), inv_t)), sum);
+    const int tk = d.top_k[row];
+    uint32_t nk = K;
+    const bool closed = tk > 0 && uint32_t(tk) <= K;
+    if (closed) nk = uint32_t(tk);
+    const float top_p = d.top_p[row];
+    if (top_p < 1.f) {
+        float z = 1.f;
+        if (closed) {
+            z = 0.f;
+            for (uint32_t i = 0; i < nk; ++i) z = __fadd_rn(z, p[i]);
+        }
+        float cum = 0.f;
+        for (uint32_t j = 0; j < nk; ++j) {
+            cum = __fadd_rn(cum, __fdiv_rn(p[j], z));
+            if (cum >= top_p) {
+                nk = j + 1;
+                break;
+            }
+        }
+    }
+    const float min_p = d.min_p[row];
+    if (min_p > 0.f && nk > 0) {
+        const float th = __fmul_rn(min_p, p[0]);
+        uint32_t j = 0;
+        while (j < nk && p[j] >= th) ++j;
+        nk = j > 1 ? j : 1;
+    }
+    float z = 0.f;
+    for (uint32_t i = 0; i < nk; ++i) z = __fadd_rn(z, p[i]);
+    for (uint32_t i = 0; i < nk; ++i) p[i] = __fdiv_rn(p[i], z);
+    const unsigned long long rkey = ((unsigned long long)d.key_hi[row] << 32) | d.key_lo[row];
+    uint32_t pick = 0;
+    double bk = __longlong_as_double(0x7FF0000000000000ll);
+    for (uint32_t i = 0; i < nk; ++i) {
+        if (!(p[i] > 0.f)) continue;
+        const double k = race_e(rkey, uint32_t(id[i])) / double(p[i]);
+        if (k < bk) bk = k, pick = i;
+    }
+    int32_t* c = d.ctl_all + d.area[row];
+    c[16 + d.r] = id[pick];
+    int32_t* q = d.qbuf + d.qoff[row];
+    q[0] = int32_t(nk);
+    for (uint32_t i = 0; i < nk; ++i) {
+        q[1 + i] = id[i];
+        q[1 + 32 + i] = __float_as_int(p[i]);
+    }
+}
+
 // grid-strided over the rows (or over the entries of row_list); one row at a time per CTA
 template <typename T>
 __global__ void __launch_bounds__(GT) select_generic_kernel(SelectArgs a, int cap_max, int pen_words) {
@@ -107,8 +180,16 @@ __device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_ma
     const T* x = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
     const int tid = threadIdx.x;
     const bool sample = a.mode == MODE_SAMPLE;
+    const bool draft = a.mode == MODE_DRAFT;
+    if (draft) {
+        // kernels/spec_sample.hip:42-45: rows that do not sample keep their greedy draft; a chain stopped by the p-min
+        // cut-off at or before r is skipped
+        if (a.draft.on[row] == 0) return;
+        const int32_t* c = a.draft.ctl_all + a.draft.area[row];
+        if (c[49] != 0 && c[48] <= a.draft.r) return;
+    }
     const RowParams& P = a.prm;
-    const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
+    const float inv_t = draft ? a.draft.inv_t[row] : (P.inv_t ? P.inv_t[row] : P.inv_t_scalar);
 
     // ---- penalties table
     PenaltyTable pt;
@@ -164,6 +245,10 @@ __device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_ma
     if (sample) {
         top_k = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
         K = (top_k > 0 && top_k <= uint32_t(level_k)) ? top_k : uint32_t(level_k);
+    } else if (draft) {
+        // draftCands (include/whirl/spec_sample.h:94): min(top_k, 32), 32 when top_k is off
+        const int tk = a.draft.top_k[row];
+        K = (tk > 0 && tk < 32) ? uint32_t(tk) : 32u;
     } else {
         K = uint32_t(a.K);
     }
@@ -243,6 +328,10 @@ __device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_ma
     for (uint32_t i = K + tid; i < cap; i += GT) cand[i] = 0;
     __syncthreads();
     const Group<GT> g{tid, 0};
+    if (draft) {
+        if (tid == 0) draft_tail(a, row, reinterpret_cast<const unsigned long long*>(cand), K, sh->m, sh->sum, inv_t);
+        return;
+    }
     if (!sample) {
         sort_desc<GT>(g, cand, cap);
         for (uint32_t j = tid; j < K; j += GT) {
@@ -297,7 +386,7 @@ size_t select_generic_ws_bytes(int ctas, int K) {
 
 cudaError_t select_generic_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st) {
     const int grid = a.rows < 2 * sm_count ? a.rows : 2 * sm_count;
-    const int kmax = a.mode == MODE_TOPK ? a.K : a.level_k;
+    const int kmax = a.mode == MODE_TOPK ? a.K : (a.mode == MODE_DRAFT ? 32 : a.level_k);
     const int cap = pow2_at_least(kmax < 1 ? 1 : (kmax > a.n ? a.n : kmax));
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
     const int pen_words = pen ? ((a.n + 31) / 32 + 3) & ~3 : 0;
