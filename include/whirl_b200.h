@@ -209,6 +209,30 @@ struct whirl_sample_out {
 int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sample_params* params,
                       const whirl_sample_out* out, void* ws, size_t ws_bytes, void* stream);
 
+/* ------------------------------------------------------------------------------------------------------------------
+ * Speculative acceptance.
+ * ---------------------------------------------------------------------------------------------------------------- */
+
+/* The accept loop of sampling::Acceptor::sample (src/sampling/acceptor.cpp:63-100, exact rules: `sample` and `specsample`)
+ * on the device: tokens[row] is the sampler's token of every verify row (whirl_sample_rows; with race_key it is the race
+ * draw that drafts from whirl_draft_sample_rows are coupled to).  Sequence s checks drafts[s * draft_stride + 0 .. nd[s])
+ * against rows row0[s] + 0 ..: acc[s] = drafts kept, chosen[s] = tokens[row0[s] + acc[s]].  This removes the per-cycle
+ * readCtl synchronisation and candidate download (src/server/engine_decode.cpp:399-405). */
+int whirl_accept_tokens(const int* tokens, const int* drafts, int draft_stride, const int* nd, const int* row0, int seqs, int* acc,
+                        int* chosen, void* stream);
+
+/* The accept / residual rule (Leviathan et al., Chen et al. 2023) that the reference replaced by the race coupling
+ * (include/whirl/spec_sample.h:21-24); its residual helper sampleRow(src, s, ex, p_ex) is still in the reference
+ * (src/sampling/sampler.cpp:118-131).  Per sequence: target is [L + 1][n] logits, draft [L][n], full-vocabulary
+ * p = softmax(target * inv_t), q = softmax(draft * inv_t).  For j = 0 .. L-1 draft_tok[j] is accepted iff
+ * u_acc[j] * q(d) < p(d) (or q(d) == 0); at the first rejection next_tok is drawn from max(0, p - q) by inverse CDF in
+ * id order with u_res[j]; after L acceptances next_tok is drawn from p of row L with u_res[L].  n_acc = drafts kept.
+ * Arrays: draft_tok [seqs][L], inv_t [seqs] (null = 1), u_acc [seqs][L], u_res [seqs][L + 1]. */
+size_t whirl_spec_workspace_bytes(int seqs, int L);
+int whirl_spec_accept_residual(const void* target, const void* draft, int dtype, int seqs, int L, int n, const int* draft_tok,
+                               const float* inv_t, const double* u_acc, const double* u_res, int* n_acc, int* next_tok, void* ws,
+                               size_t ws_bytes, void* stream);
+
 /* The same call on HOST buffers: logits, parameters and outputs are host pointers; the call copies them to the device
  * (workspace + staging it allocates on first use and keeps), runs whirl_sample_rows in row chunks that overlap the
  * copies, copies the outputs back and synchronises.  For callers that hold logits in host memory and for end-to-end

@@ -64,6 +64,9 @@ def _load() -> C.CDLL:
         "whirl_draft_pick_rows": (i, [vp, i, i, i, vp, vp, i, i, f, vp, vp, sz, vp]),
         "whirl_topk_rows": (i, [vp, i, i, i, i, f, vp, vp, vp, vp, vp, sz, vp]),
         "whirl_draft_sample_rows": (i, [vp, i, i, i, vp, vp, i, vp, C.POINTER(DSampArgs), vp, vp]),
+        "whirl_accept_tokens": (i, [vp, vp, i, vp, vp, i, vp, vp, vp]),
+        "whirl_spec_workspace_bytes": (sz, [i, i]),
+        "whirl_spec_accept_residual": (i, [vp, vp, i, i, i, i, vp, vp, vp, vp, vp, vp, vp, sz, vp]),
         "whirl_topk_rows_shard": (i, [vp, i, i, i, i, i, f, vp, vp, vp, vp, vp, sz, vp]),
         "whirl_merge_sample_rows": (i, [vp, vp, vp, i, i, i, i, C.POINTER(SampleParams), C.POINTER(SampleOut), vp]),
         "whirl_sample_rows": (i, [vp, i, i, i, C.POINTER(SampleParams), C.POINTER(SampleOut), vp, sz, vp]),
@@ -80,7 +83,8 @@ def _load() -> C.CDLL:
 
 lib = _load()
 DECLARED = ["whirl_status_string", "whirl_last_error", "whirl_version", "whirl_workspace_bytes", "whirl_argmax",
-            "whirl_argmax_rows", "whirl_argmax_rows_static", "whirl_argmax_rows_to", "whirl_argmax_prob", "whirl_draft_pick", "whirl_draft_pick_rows", "whirl_draft_sample_rows",
+            "whirl_argmax_rows", "whirl_argmax_rows_static", "whirl_argmax_rows_to", "whirl_argmax_prob", "whirl_draft_pick", "whirl_draft_pick_rows", "whirl_draft_sample_rows", "whirl_accept_tokens", "whirl_spec_workspace_bytes",
+            "whirl_spec_accept_residual",
             "whirl_topk_rows", "whirl_topk_rows_shard", "whirl_merge_sample_rows", "whirl_sample_rows", "whirl_sample_rows_host", "whirl_host_release", "whirl_host_last_error",
             "whirl_launch_counts"]
 
@@ -346,3 +350,28 @@ def merge_sample_rows(ids, vals, stats, n_total: int, params: RowParams, kept_ca
     _check(lib.whirl_merge_sample_rows(ids.data_ptr(), vals.data_ptr(), stats.data_ptr(), shards, rows, ks, n_total, C.byref(ps),
                                        C.byref(o), torch.cuda.current_stream(dev).cuda_stream))
     return res
+
+
+def accept_tokens(tokens, drafts, nd, row0):
+    """Device accept loop: tokens [rows] i32, drafts [seqs, D] i32, nd / row0 [seqs] i32 -> (acc, chosen) [seqs] i32."""
+    seqs = drafts.shape[0]
+    acc = torch.empty(seqs, dtype=torch.int32, device=tokens.device)
+    chosen = torch.empty(seqs, dtype=torch.int32, device=tokens.device)
+    _check(lib.whirl_accept_tokens(tokens.data_ptr(), drafts.data_ptr(), drafts.shape[1], nd.data_ptr(), row0.data_ptr(), seqs,
+                                   acc.data_ptr(), chosen.data_ptr(), torch.cuda.current_stream(tokens.device).cuda_stream))
+    return acc, chosen
+
+
+def spec_accept_residual(target, draft, draft_tok, inv_t, u_acc, u_res):
+    """target [seqs, L + 1, n], draft [seqs, L, n] logits; draft_tok [seqs, L] i32; inv_t [seqs] f32 or None;
+    u_acc [seqs, L], u_res [seqs, L + 1] f64 -> (n_acc, next_tok) [seqs] i32."""
+    seqs, L1, n = target.shape
+    L = L1 - 1
+    dev = target.device
+    n_acc = torch.empty(seqs, dtype=torch.int32, device=dev)
+    nxt = torch.empty(seqs, dtype=torch.int32, device=dev)
+    ws = torch.empty(lib.whirl_spec_workspace_bytes(seqs, L), dtype=torch.uint8, device=dev)
+    _check(lib.whirl_spec_accept_residual(target.data_ptr(), _p(draft), _dtype(target), seqs, L, n, _p(draft_tok), _p(inv_t), _p(u_acc),
+                                          u_res.data_ptr(), n_acc.data_ptr(), nxt.data_ptr(), ws.data_ptr(), ws.numel(),
+                                          torch.cuda.current_stream(dev).cuda_stream))
+    return n_acc, nxt

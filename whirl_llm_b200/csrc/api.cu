@@ -345,6 +345,33 @@ int whirl_draft_sample_rows(const void* x, int dtype, int rows, int n, int* ctl_
     return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "draft_sample_rows launch");
 }
 
+int whirl_accept_tokens(const int* tokens, const int* drafts, int draft_stride, const int* nd, const int* row0, int seqs, int* acc,
+                        int* chosen, void* stream) {
+    if (!tokens || !drafts || !nd || !row0 || !acc || !chosen || seqs < 0 || draft_stride < 0)
+        return fail(WHIRL_ERR_INVALID, "accept_tokens: bad pointer / seqs / draft_stride");
+    if (seqs == 0) return WHIRL_OK;
+    const cudaError_t e = wb::accept_tokens_launch(tokens, drafts, draft_stride, nd, row0, seqs, acc, chosen, static_cast<cudaStream_t>(stream));
+    bump(LC_AUX);
+    return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "accept_tokens launch");
+}
+
+size_t whirl_spec_workspace_bytes(int seqs, int L) { return wb::spec_stats_bytes(seqs < 0 ? 0 : seqs, L < 0 ? 0 : L) + 256; }
+
+int whirl_spec_accept_residual(const void* target, const void* draft, int dtype, int seqs, int L, int n, const int* draft_tok,
+                               const float* inv_t, const double* u_acc, const double* u_res, int* n_acc, int* next_tok, void* ws,
+                               size_t ws_bytes, void* stream) {
+    if (!target || (!draft && L > 0) || (!draft_tok && L > 0) || (!u_acc && L > 0) || !u_res || !n_acc || !next_tok || seqs < 0 ||
+        L < 0 || n <= 0 || bad_dtype(dtype))
+        return fail(WHIRL_ERR_INVALID, "spec_accept_residual: bad pointer / seqs / L / n / dtype");
+    if (seqs == 0) return WHIRL_OK;
+    if (!ws || ws_bytes < whirl_spec_workspace_bytes(seqs, L)) return fail(WHIRL_ERR_WORKSPACE, "spec_accept_residual: workspace (whirl_spec_workspace_bytes)");
+    void* aligned = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(ws) + 255) & ~uintptr_t(255));
+    const cudaError_t e = wb::accept_residual_launch(target, draft, dtype, seqs, L, n, draft_tok, inv_t, u_acc, u_res, aligned, n_acc,
+                                                     next_tok, static_cast<cudaStream_t>(stream));
+    bump(LC_AUX, 3);
+    return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "spec_accept_residual launch");
+}
+
 int whirl_merge_sample_rows(const int* ids, const float* vals, const float* stats, int shards, int rows, int K_s, int n_total,
                             const whirl_sample_params* prm, const whirl_sample_out* out, void* stream) {
     if (!ids || !vals || !stats || !prm || !out || !out->token || shards < 1 || rows < 0 || K_s < 1 || n_total < 1)

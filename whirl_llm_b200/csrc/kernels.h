@@ -131,6 +131,14 @@ constexpr int kStreamMaxK = 1024;
 cudaError_t sample_stream_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
 bool sample_stream_supported(const SelectArgs& a, int dtype);
 
+// ---- speculative acceptance (spec_accept.cu)
+size_t spec_stats_bytes(int seqs, int L);
+cudaError_t accept_tokens_launch(const int32_t* tokens, const int32_t* dr, int dr_stride, const int32_t* nd, const int32_t* row0,
+                                 int seqs, int32_t* acc, int32_t* chosen, cudaStream_t st);
+cudaError_t accept_residual_launch(const void* target, const void* draft, int dtype, int seqs, int L, int n, const int32_t* draft_tok,
+                                   const float* inv_t, const double* u_acc, const double* u_res, void* stats_ws, int32_t* n_acc,
+                                   int32_t* next_tok, cudaStream_t st);
+
 // ---- vocab-sharded candidates (merge.cu)
 cudaError_t merge_sample_launch(const int32_t* ids, const float* vals, const float* stats, int shards, int rows, int Ks,
                                 int n_total, const RowParams& P, const RowOutputs& out, int sm_count, cudaStream_t st);
