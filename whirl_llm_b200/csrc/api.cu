@@ -92,8 +92,9 @@ __global__ void gather_rows_kernel(const int32_t* status, int rows, int want, in
 }
 
 // After the small-K single-pass kernel: rows left to the large-K kernel -> list_a; rows for the multi-pass kernel ->
-// list_b (a row whose candidate log overflowed is redone at the first level: bit 30; a row whose kept set may reach past
-// its candidates goes to the second level).  counts[0], counts[1].
+// list_b (a row whose candidate log overflowed, or an open set whose draw fell past its candidates and needs the
+// id-order walk of the row, is redone at the first level: bit 30; a row whose kept set may reach past its candidates goes
+// to the second level).  counts[0], counts[1].
 __global__ void gather_two_kernel(const int32_t* status, int rows, int32_t* list_a, int32_t* list_b, int32_t* counts) {
     __shared__ int s_a, s_b;
     if (threadIdx.x == 0) s_a = 0, s_b = 0;
@@ -104,7 +105,7 @@ __global__ void gather_two_kernel(const int32_t* status, int rows, int32_t* list
         const int st = status[r];
         if (st == wb::ROW_LARGE_K) list_a[atomicAdd(&s_a, 1)] = r;
         else if (st == wb::ROW_ESCALATE) list_b[atomicAdd(&s_b, 1)] = r;
-        else if (st == wb::ROW_RETRY) list_b[atomicAdd(&s_b, 1)] = r | (1 << 30);
+        else if (st == wb::ROW_RETRY || st == wb::ROW_OPEN_TAIL) list_b[atomicAdd(&s_b, 1)] = r | (1 << 30);
     }
     __syncthreads();
     if (threadIdx.x == 0) counts[0] = s_a, counts[1] = s_b;

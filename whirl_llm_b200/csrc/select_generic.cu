@@ -355,7 +355,69 @@ __device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_ma
     // the tail's race scratch sits at p + in.cap; keep it inside this row's slice
     in.presorted = 0;
     sample_tail<GT>(g, in, cand, p, q, &sh->res);
-    const TailOut r = sh->res;
+    TailOut r = sh->res;
+    if (r.status == ROW_OPEN_TAIL) {
+        // An open set (no top-k / top-p / min-p at all) whose draw fell past its candidates: the reference walks the rest of
+        // the vocabulary in id order, adding exp((x - m) * inv_t) / sum until the running sum passes u
+        // (src/sampling/sampler.cpp:132-146).  Here: every thread sums a contiguous block of ids, a scan places the blocks,
+        // and the thread whose block the draw falls into walks it again.
+        __syncthreads();
+        uint32_t* set = hist;  // GBINS slots: the candidates' ids, open addressing (0 = empty, id + 1 stored)
+        for (uint32_t i = tid; i < r.n; i += GT) {
+            const uint32_t id = cand_id(cand[i]);
+            uint32_t h = (id * 2654435761u) >> 21;
+            while (atomicCAS(&set[h], 0u, id + 1) != 0u) h = (h + 1) & (GBINS - 1);
+        }
+        __syncthreads();
+        auto member = [&](uint32_t id) -> bool {
+            uint32_t h = (id * 2654435761u) >> 21;
+            for (;;) {
+                const uint32_t v = set[h];
+                if (v == 0) return false;
+                if (v == id + 1) return true;
+                h = (h + 1) & (GBINS - 1);
+            }
+        };
+        const double it = double(inv_t), zs = double(sh->sum);
+        const uint32_t S = (n + GT - 1) / GT, b0 = min(n, uint32_t(tid) * S), b1 = min(n, b0 + S);
+        double loc = 0;
+        int my_last = -1;
+        for (uint32_t v = b0; v < b1; ++v) {
+            if (member(v)) continue;
+            loc += exp(double(__fsub_rn(elem(x, v, pt), sh->m)) * it) / zs;
+            my_last = int(v);
+        }
+        double incl = loc;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const double up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane_id() >= o) incl += up;
+        }
+        if (lane_id() == 31) sh->red_s[tid >> 5] = incl;
+        if (tid == 0) sh->cnt = 0xffffffffu, sh->eq = 0;
+        __syncthreads();
+        double before = r.cum;  // the candidates' mass, already walked
+        for (int w = 0; w < (tid >> 5); ++w) before += sh->red_s[w];
+        const double excl = before + incl - loc;
+        if (my_last >= 0) atomicMax(&sh->eq, uint32_t(my_last) + 1);
+        if (excl <= in.u && excl + loc > in.u) {
+            double cum = excl;
+            for (uint32_t v = b0; v < b1; ++v) {
+                if (member(v)) continue;
+                cum += exp(double(__fsub_rn(elem(x, v, pt), sh->m)) * it) / zs;
+                if (cum > in.u) {
+                    atomicMin(&sh->cnt, v);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+        // not reached (rounding): the last id walked, or the top candidate when nothing was walked
+        r.token = sh->cnt != 0xffffffffu ? sh->cnt : (sh->eq ? sh->eq - 1 : cand_id(cand[0]));
+        r.status = ROW_DONE;
+        __syncthreads();
+        for (int i = tid; i < GBINS; i += GT) hist[i] = 0;
+    }
     if (tid == 0) {
         a.out.token[row] = int32_t(r.token);
         a.out.status[row] = r.status;
@@ -363,7 +425,7 @@ __device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_ma
         if (a.out.closed) a.out.closed[row] = r.closed;
         if (a.out.stats) a.out.stats[2 * row] = sh->m, a.out.stats[2 * row + 1] = sh->sum;
         if (a.out.counters && r.status == ROW_ESCALATE) atomicAdd(&a.out.counters[0], 1u);
-        if (a.out.counters && r.status == ROW_OPEN_TAIL) atomicAdd(&a.out.counters[1], 1u);
+        if (a.out.counters && sh->res.status == ROW_OPEN_TAIL) atomicAdd(&a.out.counters[1], 1u);
     }
     if (r.status != ROW_ESCALATE) {
         const uint32_t nk = min(r.n, uint32_t(max(a.out.kept_cap, 0)));
