@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libwhirl_b200.so")
-SOURCES = ["api.cu", "host_api.cu", "rowscan.cu", "select_generic.cu", "sample_stream.cu", "sample_async.cu", "merge.cu", "spec_accept.cu"]
+SOURCES = ["api.cu", "host_api.cu", "rowscan.cu", "select_generic.cu", "sample_stream.cu", "sample_async.cu", "history_lists.cu", "merge.cu", "spec_accept.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math=false",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared", "-cudart", "shared"]
 

@@ -51,7 +51,7 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // workspace layout (all offsets 256-byte aligned)
 struct Ws {
-    size_t off_scan, off_status, off_list, off_list2, off_count, off_err, off_p, total;
+    size_t off_scan, off_status, off_list, off_list2, off_count, off_err, off_p, off_hits, total;
 };
 Ws ws_layout(int rows) {
     Ws w;
@@ -70,6 +70,8 @@ Ws ws_layout(int rows) {
     o = align_up(o + 16, 256);
     w.off_p = o;
     o = align_up(o + wb::select_generic_ws_bytes(std::min(rows, 2 * kSmBound), wb::kGenericMaxK), 256);
+    w.off_hits = o;  // the rows' hit lists (penalties of the single-pass sampler): lists, then starts
+    o = align_up(o + wb::history_lists_ws_bytes(rows), 256);
     w.total = o;
     return w;
 }
@@ -291,6 +293,11 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
     int32_t* counts = reinterpret_cast<int32_t*>(base + w.off_count);
     cudaError_t e;
     if (wb::sample_async_supported(a, dtype)) {
+        if (prm->hist) {
+            e = wb::history_lists_launch(a.prm, rows, n, dtype, base + w.off_hits, sm_count(), st);
+            bump(LC_AUX);
+            if (e != cudaSuccess) return fail_cuda(e, "sample_rows history lists");
+        }
         // small-K rows in one pass; rows with top_k in (256, 1024] are marked for the large-K single-pass kernel
         e = wb::sample_async_launch(a, dtype, sm_count(), st);
         bump(LC_STREAM);

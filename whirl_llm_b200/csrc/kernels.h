@@ -61,6 +61,9 @@ struct RowParams {
     const float* rep;          // [1]
     const float* pres;         // [0]
     const float* freq;         // [0]
+    // (single-pass sampler only) the rows' hit lists, built by history_lists_launch from the fields above
+    const uint32_t* hit_list;  // [rows][kHitListStride]
+    const uint32_t* hit_start; // [rows][kHitStartStride]
 };
 
 struct RowOutputs {
@@ -123,6 +126,10 @@ cudaError_t select_generic_launch(const SelectArgs& a, int dtype, int sm_count, 
 
 // small-K single-pass kernel (sample_async.cu)
 constexpr int kAsyncMaxK = 256;
+// per-row lists of the distinct history tokens with their counts, in the order the single-pass sampler meets them
+size_t history_lists_ws_bytes(int rows);
+// (ws: history_lists_ws_bytes(rows) bytes, 16-byte aligned; prm.hit_list / prm.hit_start are set to point into it)
+cudaError_t history_lists_launch(RowParams& prm, int rows, int n, int dtype, void* ws, int sm_count, cudaStream_t st);
 cudaError_t sample_async_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
 bool sample_async_supported(const SelectArgs& a, int dtype);
 

@@ -30,19 +30,19 @@ constexpr int A_SW = 16;                      // stream warps
 constexpr int A_ST = A_SW * 32;
 constexpr int A_TW = 4;                       // tail warps
 constexpr int A_TT = A_TW * 32;
-constexpr int A_THREADS = 32 + A_ST + A_TT;
+constexpr int A_PW = 3;                       // penalty warps (with them 24 warps: six per scheduler, 80 registers each)
+constexpr int A_THREADS = 32 + A_ST + A_TT + A_PW * 32;  // copies, stream warps, tail warps, penalty warps
 constexpr int A_CH = 4096;                    // logits per ring stage
 constexpr int A_L = 3072;                     // candidate log entries per row slot
 constexpr int A_MAXSTAGES = 16;
-constexpr int A_HITS = 64;                    // per stream warp: history-token logits waiting for their penalty
 
 struct ASlot {
     unsigned long long tau;  // current threshold candidate; elements must beat it to be logged
     uint32_t cnt;            // log entries reserved so far (may exceed A_L: overflow)
     int32_t row;
-    float red_m[A_SW];       // per stream warp: max, reference exponent, scaled sum
-    float red_e[A_SW];
-    double red_s[A_SW];
+    float red_m[A_SW + A_PW];  // per stream warp, then per penalty warp: max, reference exponent, scaled sum
+    float red_e[A_SW + A_PW];
+    double red_s[A_SW + A_PW];
 };
 
 struct AShared {
@@ -58,7 +58,7 @@ __device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned lon
 __device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) { return *reinterpret_cast<const volatile uint32_t*>(p); }
 
 template <typename T>
-__global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a, int stages, int pen_words, int ch_bytes, int boot_elems) {
+__global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a, int stages, int pen, int ch_bytes, int boot_elems) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;                                                          // stages * ch_bytes
     uint8_t* boot = ring + size_t(stages) * ch_bytes;                              // boot_elems logits: the head of the next row
@@ -68,13 +68,10 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     double* tail_p = reinterpret_cast<double*>(hand + kAsyncMaxK);                 // 2 * (kAsyncMaxK + 2 * A_TW)
     double* tail_q = tail_p + kAsyncMaxK + 2 * A_TW;
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail_q + kAsyncMaxK + 2 * A_TW);  // 2 * 16 + 8
-    AShared* sh = reinterpret_cast<AShared*>(bars + 2 * A_MAXSTAGES + 8);
-    uint32_t* pen_mem = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));
-    uint2* hitbuf = reinterpret_cast<uint2*>(pen_mem + pen_words + (pen_words ? kPenSlots : 0));  // A_SW * A_HITS (penalties only)
-    uint32_t* wbound = reinterpret_cast<uint32_t*>(hitbuf + (pen_words ? A_SW * A_HITS : 0));  // 2 * A_SW: per slot, each stream warp's bound key
-    uint64_t *full = bars, *empty = bars + A_MAXSTAGES;
-    uint64_t *closed = bars + 2 * A_MAXSTAGES, *boot_done = closed + 2, *boot_full = closed + 4, *boot_empty = closed + 5;
-    uint64_t* tbl = closed + 6;  // rendezvous of the stream threads around the rebuild of the penalty table
+    AShared* sh = reinterpret_cast<AShared*>(bars + 3 * A_MAXSTAGES + 8);
+    uint32_t* wbound = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));  // 2 * A_SW: per slot, each stream warp's bound key
+    uint64_t *full = bars, *empty = bars + A_MAXSTAGES, *patched = bars + 2 * A_MAXSTAGES;
+    uint64_t *closed = bars + 3 * A_MAXSTAGES, *boot_done = closed + 2, *boot_full = closed + 4, *boot_empty = closed + 5;
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const uint32_t n = uint32_t(a.n);
@@ -99,9 +96,9 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     };
 
     if (tid == 0) {
-        for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], A_SW);
-        for (int p = 0; p < 2; ++p) mbar_init(&closed[p], A_SW), mbar_init(&boot_done[p], 1);
-        mbar_init(boot_full, 1), mbar_init(boot_empty, 1), mbar_init(tbl, A_SW);
+        for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], A_SW), mbar_init(&patched[s], 1);
+        for (int p = 0; p < 2; ++p) mbar_init(&closed[p], A_SW + (pen ? A_PW : 0)), mbar_init(&boot_done[p], 1);
+        mbar_init(boot_full, 1), mbar_init(boot_empty, 1);
         mbar_fence_init();
     }
     for (int i = tid; i < 2 * A_L; i += A_THREADS) logs[i] = 0ull;
@@ -149,6 +146,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
 #endif
                     const size_t off = size_t(c) * ch_bytes;
                     const uint32_t bytes = uint32_t(row_bytes - off < size_t(ch_bytes) ? row_bytes - off : size_t(ch_bytes));
+                    // (with penalties the stage was also written to: those writes, seen through the barriers, stay before the copy)
+                    if (pen) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     mbar_expect_tx(&full[s], bytes);
                     bulk_g2s(ring + size_t(s) * ch_bytes, src + off, bytes, &full[s]);
                 }
@@ -188,8 +187,147 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         return tk >= 1 && tk <= kAsyncMaxK && uint32_t(tk) <= n;
     };
 
+    // =========================================================== penalty warps
+    // They walk the row's hit list (its distinct history tokens with their counts, stage by stage; history_lists_kernel)
+    // while the row streams, taking the stages in turn: as soon as a stage has landed its warp takes the raw logits of the
+    // stage's history tokens out (replaced by -inf, so the stream warps see them as absent), hands the stage on to the
+    // stream warps, and adds the penalised values to the row itself: each is one more contributor to the row's maximum,
+    // sum and candidate log.  The places of the row's stages in the list sit in registers (four per lane), and the first
+    // 32 entries of a warp's next stage are already on their way while it works on the current one.
+    if (warp >= 1 + A_SW + A_TW) {
+        if (!pen) return;
+        const int lane = lane_id(), pw = warp - (1 + A_SW + A_TW);
+        constexpr uint32_t none = 0xffffffffu;
+        uint32_t it0 = 0;  // stages of the CTA's earlier rows (ring position of this row's first stage)
+        int ord = 0;
+        for (int k = next_row(-1); k < my_rows; k = next_row(k), ++ord, it0 += n_chunks) {
+            const int p = ord & 1;
+            const int row = row_of(k);
+            ASlot* sl = &sh->slot[p];
+            unsigned long long* log = logs + size_t(p) * A_L;
+            const bool greedy = no_sum_row(row);
+            const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
+            const float cexp = inv_t * kLog2e;
+            bool pen_on = false;
+            float pen_rep = 1.f, pen_pres = 0.f, pen_freq = 0.f;
+            if (sample && P.hit_list && P.hist_len[row] > 0) {
+                pen_rep = P.rep ? P.rep[row] : 1.f, pen_pres = P.pres ? P.pres[row] : 0.f, pen_freq = P.freq ? P.freq[row] : 0.f;
+                pen_on = pen_rep != 1.f || pen_pres != 0.f || pen_freq != 0.f;
+            }
+            const uint32_t* hl_row = P.hit_list + size_t(row) * kHitListStride;
+            // place of stage c's first entry, c = 0 .. n_chunks: lane l holds c = l, l + 32, l + 64, l + 96, and c = 128
+            uint32_t bnd[5] = {0, 0, 0, 0, 0};
+            if (pen_on) {
+                const uint32_t* hs = P.hit_start + size_t(row) * kHitStartStride;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) bnd[u] = (uint32_t(lane) + 32u * u <= n_chunks) ? min(hs[lane + 32 * u], uint32_t(kMaxHist)) : 0u;
+                bnd[4] = n_chunks >= 128 ? min(hs[128], uint32_t(kMaxHist)) : 0u;
+            }
+            auto place = [&](uint32_t c) -> uint32_t {
+                const uint32_t r = c >> 5;
+                const uint32_t v = r == 0 ? bnd[0] : (r == 1 ? bnd[1] : (r == 2 ? bnd[2] : bnd[3]));
+                const uint32_t g = __shfl_sync(0xffffffffu, v, c & 31u);
+                return c >= 128 ? bnd[4] : g;
+            };
+            // this warp's stages of the row: c0, c0 + A_PW, ...
+            uint32_t c = (uint32_t(pw) + A_PW - it0 % A_PW) % A_PW;
+            uint32_t s_nx = 0, e_nx = 0, win_nx = none;
+            auto prefetch = [&](uint32_t cc) {
+                s_nx = e_nx = 0, win_nx = none;
+                if (pen_on && cc < n_chunks) {
+                    s_nx = place(cc), e_nx = place(cc + 1);
+                    win_nx = s_nx + lane < e_nx ? hl_row[s_nx + lane] : none;
+                }
+            };
+            prefetch(c);
+            // the row's log and threshold belong to the row before until the tail group says otherwise
+            if (!mbar_wait(&boot_done[p], (ord >> 1) & 1)) {
+                if (lane == 0) atomicExch(a.err, 6u);
+                return;
+            }
+            float m_t = -INFINITY, e_t = 0.f, s_t = 0.f;
+            unsigned long long tau_seen = 0ull;
+            float tau_f = -INFINITY;
+            // one history token of the row: penalty on its raw logit, then max / sum / candidate log as for any logit
+            auto inject = [&](uint32_t ent, float l) {
+                l = (l > 0.f) ? __fdiv_rn(l, pen_rep) : __fmul_rn(l, pen_rep);
+                const float x = __fsub_rn(l, __fadd_rn(pen_pres, __fmul_rn(pen_freq, float(ent >> kPenIdBits))));
+                if (!greedy) {
+                    if (x > m_t) {
+                        const float ne = ceilf(x * cexp);
+                        s_t = (m_t == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
+                        e_t = ne, m_t = x;
+                    }
+                    if (m_t != -INFINITY) s_t += ex2_approx(fmaf(x, cexp, -e_t));
+                } else {
+                    m_t = fmaxf(m_t, x);
+                }
+                if (x >= tau_f) {
+                    const unsigned long long cnd = make_cand(key_of(x), ent & kPenMaxV);
+                    if (cnd > tau_seen) {
+                        const uint32_t pos = atomicAdd(&sl->cnt, 1u);
+                        if (pos < uint32_t(A_L)) log[pos] = cnd;
+                    }
+                }
+            };
+            for (; c < n_chunks; c += A_PW) {
+                const uint32_t it = it0 + c, st_slot = it % uint32_t(stages), st_phase = (it / uint32_t(stages)) & 1u;
+                uint32_t cur = s_nx;
+                const uint32_t end = e_nx;
+                uint32_t win = win_nx;
+                if (!mbar_wait(&full[st_slot], st_phase)) {
+                    if (lane == 0) atomicExch(a.err, 7u);
+                    return;
+                }
+                T* stage_mem = reinterpret_cast<T*>(ring + size_t(st_slot) * ch_bytes);
+                bool have = false;  // this lane holds a token taken out of the stage and not added to the row yet
+                uint32_t h_ent = 0;
+                float h_raw = 0.f;
+                while (cur < end) {
+                    if (have) inject(h_ent, h_raw);
+                    have = win != none;
+                    if (have) {
+                        h_ent = win;
+                        T* at = stage_mem + ((win & kPenMaxV) - c * A_CH);
+                        if (sizeof(T) == 4) {
+                            h_raw = *reinterpret_cast<float*>(at);
+                            *reinterpret_cast<uint32_t*>(at) = 0xff800000u;
+                        } else {
+                            h_raw = __uint_as_float(uint32_t(*reinterpret_cast<uint16_t*>(at)) << 16);
+                            *reinterpret_cast<uint16_t*>(at) = 0xff80u;
+                        }
+                    }
+                    cur += 32;
+                    if (cur < end) win = cur + lane < end ? hl_row[cur + lane] : none;  // (a stage with more than 32 tokens: rare)
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&patched[st_slot]);  // the stream warps may read the stage
+                prefetch(c + A_PW);
+                if (have) {
+                    const unsigned long long t = ld_volatile_u64(&sl->tau);
+                    if (t != tau_seen) tau_seen = t, tau_f = float_of_key(cand_key(t));
+                    inject(h_ent, h_raw);
+                }
+            }
+            const bool saw_nan = !greedy && (s_t != s_t);
+            if (__any_sync(0xffffffffu, saw_nan) && lane == 0) atomicOr(&sl->cnt, 0x80000000u);
+            {
+                const float wm = warp_max(m_t);
+                float we = e_t;
+                if (m_t == -INFINITY) we = -INFINITY;
+                we = warp_max(we);
+                double ds = (m_t == -INFINITY) ? 0.0 : double(s_t) * double(ex2_approx(e_t - we));
+                ds = warp_sum(ds);
+                if (lane == 0) sl->red_m[A_SW + pw] = wm, sl->red_e[A_SW + pw] = we, sl->red_s[A_SW + pw] = ds;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&closed[p]);
+        }
+        return;
+    }
+
     // =========================================================== tail
-    if (warp > A_SW) {
+    if (warp > A_SW) {  // (the penalty warps have returned above)
         const Group<A_TT> g{tid - 32 - A_ST, 2};
 
         // first threshold of row k (slot k & 1) from its first stage: the (K + h)-th largest raw logit there, h = history
@@ -203,24 +341,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             const int row = row_of(k);
             const uint32_t ne = n < uint32_t(boot_elems) ? n : uint32_t(boot_elems);
             uint32_t K = k_of(row);
-            if (sample && P.hist && P.hist_len[row] > 0) {
-                const int32_t* h = P.hist + size_t(row) * P.hist_stride;
-                const int hl = min(P.hist_len[row], kMaxHist);
-                // distinct history tokens inside the stage: mark them in a small bit map (the select scratch), count bits
-                for (int i = g.tid; i < A_CH / 32; i += A_TT) hist[i] = 0;
-                g.sync();
-                for (int i = g.tid; i < hl; i += A_TT) {
-                    const uint32_t t = uint32_t(h[i]);
-                    if (t < ne) atomicOr(&hist[t >> 5], 1u << (t & 31));
-                }
-                if (g.tid == 0) sh->flag[0] = 0;
-                g.sync();
-                uint32_t c = g.tid < A_CH / 32 ? uint32_t(__popc(hist[g.tid])) : 0u;
-                c = warp_sum(c);
-                if ((g.tid & 31) == 0) atomicAdd(&sh->flag[0], c);
-                g.sync();
-                K += sh->flag[0];
-            }
+            if (sample && P.hit_start) K += P.hit_start[size_t(row) * kHitStartStride + 1];  // (counted with the row's hit list)
             // A valid bound without looking at every order statistic: split the stage into G interleaved groups, take each
             // group's maximum; the K-th largest of the G maxima has K distinct elements at or above it.
             unsigned long long tau = 0ull;
@@ -364,8 +485,9 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             double S = 0;
             {
                 const double cexp = double(inv_t * kLog2e);
-                for (int w = 0; w < A_SW; ++w) M = fmaxf(M, sl->red_m[w]);
-                for (int w = 0; w < A_SW; ++w)
+                const int n_red = A_SW + (pen ? A_PW : 0);
+                for (int w = 0; w < n_red; ++w) M = fmaxf(M, sl->red_m[w]);
+                for (int w = 0; w < n_red; ++w)
                     if (sl->red_m[w] != -INFINITY) S += sl->red_s[w] * exp2(double(sl->red_e[w]) - double(M) * cexp);
             }
             const bool no_sum = no_sum_row(row);
@@ -498,16 +620,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     static_assert(A_CH / EPV / A_ST * EPV == 8, "eight elements per thread per stage");
     uint32_t st_slot = 0, st_phase = 0;  // ring position of this warp and the parity it waits for
     uint32_t st_ring[2] = {0, 0};
-    PenaltyTable pt;
-    pt.bitmap = pen_mem, pt.slots = pen_mem + pen_words;
-
-    uint32_t tbl_use = 0;
-    // all stream threads meet (bounded wait): false when the wait ran out
-    auto rendezvous = [&]() -> bool {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tbl);  // one arrival per warp, after all its lanes are here
-        return mbar_wait(tbl, (tbl_use++) & 1);
-    };
+    static_assert(A_CH == kHitStage, "the hit lists are grouped by this kernel's stages");
+    uint64_t* ready = pen ? patched : full;  // with penalties a stage is read only after the penalty warp has been over it
 #ifdef WB_PHASE_TIMERS
     long long ts_wait = 0, ts_proc = 0, ts_setup = 0;
 #endif
@@ -523,35 +637,6 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         const bool greedy = no_sum_row(row);  // no exponentials for this row (greedy, or closed by its top_k)
         const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
         const float cexp = inv_t * kLog2e;
-        pt.on = false;
-        if (sample && P.hist && P.hist_len[row] > 0) {
-            pt.rep = P.rep ? P.rep[row] : 1.f, pt.pres = P.pres ? P.pres[row] : 0.f, pt.freq = P.freq ? P.freq[row] : 0.f;
-            pt.on = pt.rep != 1.f || pt.pres != 0.f || pt.freq != 0.f;
-        }
-        if (sample && P.hist) {
-            // one table for the CTA: every stream warp must be done with the previous row before it is rebuilt
-            bool ok = rendezvous();
-            if (pt.on && ok) {
-                const int32_t* hrow = P.hist + size_t(row) * P.hist_stride;
-                const int hl = min(P.hist_len[row], kMaxHist);
-                int32_t hv[kMaxHist / A_ST];
-#pragma unroll
-                for (int j = 0; j < kMaxHist / A_ST; ++j) hv[j] = (g.tid + j * A_ST) < hl ? hrow[g.tid + j * A_ST] : -1;
-                pt.clear(g.tid, A_ST, n);
-                ok = rendezvous();
-#pragma unroll
-                for (int j = 0; j < kMaxHist / A_ST; ++j) {
-                    // equal ids inside a warp insert once, with their multiplicity
-                    const uint32_t peers = __match_any_sync(0xffffffffu, hv[j]);
-                    if ((__ffs(peers) - 1) == lane) pt.insert_n(hv[j], n, uint32_t(__popc(peers)));
-                }
-                ok = rendezvous() && ok;
-            }
-            if (!ok) {
-                if (lane == 0) atomicExch(a.err, 6u);
-                return;
-            }
-        }
         // the row's first threshold (and the slot being free again) come from the tail group
         if (!mbar_wait(&boot_done[p], (ord >> 1) & 1)) {
             if (lane == 0) atomicExch(a.err, 4u);
@@ -568,70 +653,6 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         uint32_t* wb_row = wbound + p * A_SW;
         uint32_t iters = 0;
         const uint32_t rth = (k_of(row) + A_SW - 1) / A_SW;  // each warp's share of the K candidates
-        uint2* whits = hitbuf + size_t(sw) * A_HITS;
-        uint32_t nhits = 0;
-        // One logit joins this lane's running max / sum and, if it can still be among the K best, the row's log.
-        auto inject = [&](float x, uint32_t id) {
-            if (!greedy) {
-                if (x > m_t) {
-                    const float ne = ceilf(x * cexp);
-                    s_t = (m_t == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
-                    e_t = ne, m_t = x;
-                }
-                if (m_t != -INFINITY) s_t += ex2_approx(fmaf(x, cexp, -e_t));
-            } else {
-                m_t = fmaxf(m_t, x);
-            }
-            if (x >= tau_f) {
-                const unsigned long long cnd = make_cand(key_of(x), id);
-                if (cnd > tau_seen) {
-                    const uint32_t pos = atomicAdd(&sl->cnt, 1u);
-                    if (pos < uint32_t(A_L)) log[pos] = cnd;
-                }
-            }
-        };
-        // The first `cntw` waiting history-token logits of this warp get their penalty, one per lane, and join.
-        auto flush_hits = [&](uint32_t cntw) {
-            if (uint32_t(lane) < cntw) {
-                const uint2 e = whits[lane];
-                inject(pt.apply(__uint_as_float(e.y), e.x), e.x);
-            }
-        };
-        // History tokens among this thread's two quads of a stage: their raw logits leave the stage (replaced by -inf, so
-        // the vector loads that follow see them as absent) and wait in the warp's buffer until 32 are there; the penalty
-        // lookup then runs with every lane busy instead of once per scattered hit.
-        auto take_hits = [&](T* stage_mem, uint32_t stage_base, uint32_t id0, bool ok0, uint32_t id1, bool ok1) {
-            uint32_t b = (ok0 ? pt.bits(id0, 4) : 0u) | ((ok1 ? pt.bits(id1, 4) : 0u) << 4);
-            while (__any_sync(0xffffffffu, b != 0)) {
-                const bool has = b != 0;
-                uint32_t id = 0, xb = 0;
-                if (has) {
-                    const int j = __ffs(b) - 1;
-                    b &= b - 1;
-                    id = (j < 4 ? id0 : id1) + (j & 3);
-                    T* at = stage_mem + (id - stage_base);
-                    if (sizeof(T) == 4) {
-                        xb = *reinterpret_cast<uint32_t*>(at);
-                        *reinterpret_cast<uint32_t*>(at) = 0xff800000u;
-                    } else {
-                        xb = uint32_t(*reinterpret_cast<uint16_t*>(at)) << 16;
-                        *reinterpret_cast<uint16_t*>(at) = 0xff80u;
-                    }
-                }
-                const uint32_t bal = __ballot_sync(0xffffffffu, has);
-                if (has) whits[nhits + __popc(bal & ((1u << lane) - 1))] = make_uint2(id, xb);
-                nhits += __popc(bal);
-                __syncwarp();
-                if (nhits >= 32) {
-                    flush_hits(32);
-                    const uint2 mv = (32 + lane) < int(nhits) ? whits[32 + lane] : make_uint2(0, 0);
-                    __syncwarp();
-                    if ((32 + lane) < int(nhits)) whits[lane] = mv;
-                    nhits -= 32;
-                    __syncwarp();
-                }
-            }
-        };
         // NS consecutive stages at once (more independent work per warp, fixed costs paid once); PARTIAL: the last of them is
         // the row's final, shorter stage (vectors past the row's end read as -inf).
         auto stage = [&](uint32_t c, auto ns_tag, auto partial) {
@@ -652,7 +673,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             const unsigned long long tau = tau_seen;
 #pragma unroll
             for (int h = 0; h < NS; ++h) {
-                if (!mbar_wait(&full[st_slot], st_phase)) {
+                if (!mbar_wait(&ready[st_slot], st_phase)) {
                     if (lane == 0) atomicExch(a.err, 5u);
                     st_fail = true;
                     return;
@@ -663,7 +684,6 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 if (sizeof(T) == 4) {
                     qid[2 * h] = (c + h) * A_CH + 4 * g.tid, qid[2 * h + 1] = qid[2 * h] + 4 * A_ST;
                     qv[2 * h] = !part || qid[2 * h] < n, qv[2 * h + 1] = !part || qid[2 * h + 1] < n;
-                    if (pt.on) take_hits(reinterpret_cast<T*>(ring + size_t(st_slot) * ch_bytes), (c + h) * A_CH, qid[2 * h], qv[2 * h], qid[2 * h + 1], qv[2 * h + 1]);
                     const uint4 ninf = make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u);
                     const uint4 q0 = qv[2 * h] ? vec[g.tid] : ninf;
                     const uint4 q1 = qv[2 * h + 1] ? vec[g.tid + A_ST] : ninf;
@@ -672,7 +692,6 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 } else {
                     qid[2 * h] = (c + h) * A_CH + 8 * g.tid, qid[2 * h + 1] = qid[2 * h] + 4;
                     qv[2 * h] = qv[2 * h + 1] = !part || qid[2 * h] < n;
-                    if (pt.on) take_hits(reinterpret_cast<T*>(ring + size_t(st_slot) * ch_bytes), (c + h) * A_CH, qid[2 * h], qv[2 * h], qid[2 * h + 1], qv[2 * h + 1]);
                     const uint4 q = qv[2 * h] ? vec[g.tid] : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
                     x[0] = __uint_as_float(q.x << 16), x[1] = __uint_as_float(q.x & 0xffff0000u);
                     x[2] = __uint_as_float(q.y << 16), x[3] = __uint_as_float(q.y & 0xffff0000u);
@@ -783,11 +802,6 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             }
         }
         if (st_fail) return;
-        if (pt.on && nhits) {
-            const unsigned long long t = ld_volatile_u64(&sl->tau);
-            if (t != tau_seen) tau_seen = t, tau_f = float_of_key(cand_key(t));
-            flush_hits(nhits);
-        }
         // a NaN logit poisons the f32 sum: such rows are redone by the multi-pass kernel, which counts NaN as -inf
         saw_nan = !greedy && (s_t != s_t);
         if (__any_sync(0xffffffffu, saw_nan) && lane == 0) atomicOr(&sl->cnt, 0x80000000u);
@@ -812,9 +826,10 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
 #endif
 }
 
-static size_t async_fixed_smem(bool pen, int pen_words, size_t boot_bytes) {
-    return boot_bytes + (pen ? size_t(A_SW) * A_HITS * 8 : 0) + size_t(2) * A_SW * 4 + size_t(2) * A_L * 8 + SEL_BINS * 4 + size_t(kAsyncMaxK) * 8 + 2 * (kAsyncMaxK + 2 * A_TW) * 8 +
-           (2 * A_MAXSTAGES + 8) * 8 + sizeof(AShared) + (pen ? size_t(pen_words) * 4 + kPenSlots * 4 : 0) + 128;
+static size_t async_fixed_smem(bool pen, size_t boot_bytes) {
+    (void)pen;
+    return boot_bytes + size_t(2) * A_SW * 4 + size_t(2) * A_L * 8 + SEL_BINS * 4 + size_t(kAsyncMaxK) * 8 + 2 * (kAsyncMaxK + 2 * A_TW) * 8 +
+           (3 * A_MAXSTAGES + 8) * 8 + sizeof(AShared) + 128;
 }
 
 bool sample_async_supported(const SelectArgs& a, int dtype) {
@@ -822,18 +837,18 @@ bool sample_async_supported(const SelectArgs& a, int dtype) {
     if (reinterpret_cast<uintptr_t>(a.x) % 16 != 0 || (size_t(a.n) * es) % 16 != 0) return false;  // bulk copies need 16-byte rows
     if (a.mode == MODE_TOPK && a.K > kAsyncMaxK) return false;
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
-    const int pen_words = pen ? ((a.n + 31) / 32 + 3) & ~3 : 0;
     const int ch_bytes = int(A_CH * es);
-    return async_fixed_smem(pen, pen_words, size_t(A_CH) * es) + 3 * size_t(ch_bytes) <= 232448;
+    return async_fixed_smem(pen, size_t(A_CH) * es) + 3 * size_t(ch_bytes) <= 232448;
 }
 
+// (with penalties: a.prm.hit_list / hit_start must have been filled by history_lists_launch on the same stream)
 cudaError_t sample_async_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st) {
     const size_t es = dtype == 0 ? 4 : 2;
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
-    const int pen_words = pen ? ((a.n + 31) / 32 + 3) & ~3 : 0;
+    if (pen && (!a.prm.hit_list || !a.prm.hit_start)) return cudaErrorInvalidValue;
     const int ch_bytes = int(A_CH * es);
     const int boot_elems = A_CH;
-    const size_t fixed = async_fixed_smem(pen, pen_words, size_t(boot_elems) * es);
+    const size_t fixed = async_fixed_smem(pen, size_t(boot_elems) * es);
     int stages = int((232448 - fixed) / ch_bytes);
     if (stages > A_MAXSTAGES) stages = A_MAXSTAGES;
     if (stages < 3) return cudaErrorInvalidConfiguration;
@@ -844,11 +859,11 @@ cudaError_t sample_async_launch(const SelectArgs& a, int dtype, int sm_count, cu
     if (dtype == 0) {
         const cudaError_t e = cudaFuncSetAttribute(sample_async_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        sample_async_kernel<float><<<grid, A_THREADS, smem, st>>>(a, stages, pen_words, ch_bytes, boot_elems);
+        sample_async_kernel<float><<<grid, A_THREADS, smem, st>>>(a, stages, pen ? 1 : 0, ch_bytes, boot_elems);
     } else {
         const cudaError_t e = cudaFuncSetAttribute(sample_async_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        sample_async_kernel<uint16_t><<<grid, A_THREADS, smem, st>>>(a, stages, pen_words, ch_bytes, boot_elems);
+        sample_async_kernel<uint16_t><<<grid, A_THREADS, smem, st>>>(a, stages, pen ? 1 : 0, ch_bytes, boot_elems);
     }
     return cudaGetLastError();
 }
