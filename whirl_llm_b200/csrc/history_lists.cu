@@ -41,8 +41,12 @@ __global__ void __launch_bounds__(HL_THREADS) history_lists_kernel(const int32_t
         __syncthreads();
         // pass 1: count every token in the table; the first sight of a token also counts it in its stage
         const int32_t* hrow = hist + size_t(row) * hist_stride;
-        for (int j = tid; j < hl; j += HL_THREADS) {
-            const uint32_t t = uint32_t(hrow[j]);
+        int32_t hv[kMaxHist / HL_THREADS];  // (all loads first: one trip to memory instead of one per token)
+#pragma unroll
+        for (int u = 0; u < kMaxHist / HL_THREADS; ++u) hv[u] = (tid + u * HL_THREADS) < hl ? hrow[tid + u * HL_THREADS] : -1;
+#pragma unroll
+        for (int u = 0; u < kMaxHist / HL_THREADS; ++u) {
+            const uint32_t t = uint32_t(hv[u]);
             if (t >= n) continue;  // (negative ids too)
             const uint32_t tag = t + 1;
             uint32_t h = PenaltyTable::hash(t);
@@ -102,7 +106,7 @@ cudaError_t history_lists_launch(RowParams& prm, int rows, int n, int dtype, voi
     uint32_t* lists = static_cast<uint32_t*>(ws);
     uint32_t* starts = lists + size_t(rows) * kHitListStride;
     prm.hit_list = lists, prm.hit_start = starts;
-    const int grid = rows < 4 * sm_count ? rows : 4 * sm_count;
+    const int grid = rows < 6 * sm_count ? rows : 6 * sm_count;  // (six CTAs of 33 KiB fit an SM)
     history_lists_kernel<<<grid, HL_THREADS, 0, st>>>(prm.hist, prm.hist_len, prm.hist_stride, rows, uint32_t(n), lists, starts);
     return cudaGetLastError();
 }

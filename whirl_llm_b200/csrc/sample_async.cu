@@ -30,8 +30,8 @@ constexpr int A_SW = 16;                      // stream warps
 constexpr int A_ST = A_SW * 32;
 constexpr int A_TW = 4;                       // tail warps
 constexpr int A_TT = A_TW * 32;
-constexpr int A_PW = 3;                       // penalty warps (with them 24 warps: six per scheduler, 80 registers each)
-constexpr int A_THREADS = 32 + A_ST + A_TT + A_PW * 32;  // copies, stream warps, tail warps, penalty warps
+constexpr int A_PW = 2;                       // penalty warps (with them 24 warps: six per scheduler, 80 registers each)
+constexpr int A_THREADS = 32 + A_ST + A_TT + 32 + A_PW * 32;  // copies, stream warps, tail warps, draw warp, penalty warps
 constexpr int A_CH = 4096;                    // logits per ring stage
 constexpr int A_L = 3072;                     // candidate log entries per row slot
 constexpr int A_MAXSTAGES = 16;
@@ -45,8 +45,18 @@ struct ASlot {
     double red_s[A_SW + A_PW];
 };
 
+// what the tail group hands to the draw warp with a row's candidates
+struct DrawIn {
+    int32_t row;
+    uint32_t kept, cap;  // candidates, and the power of two they are padded to
+    float M, sum;        // row maximum and normaliser (unused when the row is normalised over its candidates)
+    uint32_t presorted;
+    uint32_t skip;       // nothing to draw (the tail group finished the row itself)
+};
+
 struct AShared {
     ASlot slot[2];
+    DrawIn draw[2];
     SelScratch sel;
     TailOut res;
     uint32_t flag[4];
@@ -64,14 +74,15 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     uint8_t* boot = ring + size_t(stages) * ch_bytes;                              // boot_elems logits: the head of the next row
     unsigned long long* logs = reinterpret_cast<unsigned long long*>(boot + size_t(boot_elems) * sizeof(T));  // 2 * A_L
     uint32_t* hist = reinterpret_cast<uint32_t*>(logs + 2 * A_L);                 // SEL_BINS
-    unsigned long long* hand = reinterpret_cast<unsigned long long*>(hist + SEL_BINS);   // kAsyncMaxK
-    double* tail_p = reinterpret_cast<double*>(hand + kAsyncMaxK);                 // 2 * (kAsyncMaxK + 2 * A_TW)
+    unsigned long long* hand = reinterpret_cast<unsigned long long*>(hist + SEL_BINS);   // 2 * kAsyncMaxK: a row's candidates, per slot
+    double* tail_p = reinterpret_cast<double*>(hand + 2 * kAsyncMaxK);                 // 2 * (kAsyncMaxK + 2 * A_TW)
     double* tail_q = tail_p + kAsyncMaxK + 2 * A_TW;
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail_q + kAsyncMaxK + 2 * A_TW);  // 2 * 16 + 8
-    AShared* sh = reinterpret_cast<AShared*>(bars + 3 * A_MAXSTAGES + 8);
+    AShared* sh = reinterpret_cast<AShared*>(bars + 3 * A_MAXSTAGES + 12);
     uint32_t* wbound = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));  // 2 * A_SW: per slot, each stream warp's bound key
     uint64_t *full = bars, *empty = bars + A_MAXSTAGES, *patched = bars + 2 * A_MAXSTAGES;
     uint64_t *closed = bars + 3 * A_MAXSTAGES, *boot_done = closed + 2, *boot_full = closed + 4, *boot_empty = closed + 5;
+    uint64_t *draw_full = closed + 6, *draw_empty = closed + 8;  // per slot: the candidates are there / the draw warp is done with them
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const uint32_t n = uint32_t(a.n);
@@ -99,6 +110,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], A_SW), mbar_init(&patched[s], 1);
         for (int p = 0; p < 2; ++p) mbar_init(&closed[p], A_SW + (pen ? A_PW : 0)), mbar_init(&boot_done[p], 1);
         mbar_init(boot_full, 1), mbar_init(boot_empty, 1);
+        for (int p = 0; p < 2; ++p) mbar_init(&draw_full[p], 1), mbar_init(&draw_empty[p], 1);
         mbar_fence_init();
     }
     for (int i = tid; i < 2 * A_L; i += A_THREADS) logs[i] = 0ull;
@@ -127,6 +139,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                     atomicExch(a.err, 1u);
                     return;
                 }
+                if (pen) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // (the tail group writes to its copy too)
                 mbar_expect_tx(boot_full, boot_bytes);
                 bulk_g2s(boot, reinterpret_cast<const uint8_t*>(a.x) + size_t(row_of(kn)) * row_bytes, boot_bytes, boot_full);
             }
@@ -187,6 +200,13 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         return tk >= 1 && tk <= kAsyncMaxK && uint32_t(tk) <= n;
     };
 
+    // does the row have penalties to apply (every role must agree)
+    auto pen_row = [&](int row) -> bool {
+        if (!sample || !P.hit_list || P.hist_len[row] <= 0) return false;
+        const float r = P.rep ? P.rep[row] : 1.f, pr = P.pres ? P.pres[row] : 0.f, fr = P.freq ? P.freq[row] : 0.f;
+        return r != 1.f || pr != 0.f || fr != 0.f;
+    };
+
     // =========================================================== penalty warps
     // They walk the row's hit list (its distinct history tokens with their counts, stage by stage; history_lists_kernel)
     // while the row streams, taking the stages in turn: as soon as a stage has landed its warp takes the raw logits of the
@@ -194,9 +214,9 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     // stream warps, and adds the penalised values to the row itself: each is one more contributor to the row's maximum,
     // sum and candidate log.  The places of the row's stages in the list sit in registers (four per lane), and the first
     // 32 entries of a warp's next stage are already on their way while it works on the current one.
-    if (warp >= 1 + A_SW + A_TW) {
+    if (warp >= 2 + A_SW + A_TW) {
         if (!pen) return;
-        const int lane = lane_id(), pw = warp - (1 + A_SW + A_TW);
+        const int lane = lane_id(), pw = warp - (2 + A_SW + A_TW);
         constexpr uint32_t none = 0xffffffffu;
         uint32_t it0 = 0;  // stages of the CTA's earlier rows (ring position of this row's first stage)
         int ord = 0;
@@ -208,12 +228,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             const bool greedy = no_sum_row(row);
             const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
             const float cexp = inv_t * kLog2e;
-            bool pen_on = false;
-            float pen_rep = 1.f, pen_pres = 0.f, pen_freq = 0.f;
-            if (sample && P.hit_list && P.hist_len[row] > 0) {
-                pen_rep = P.rep ? P.rep[row] : 1.f, pen_pres = P.pres ? P.pres[row] : 0.f, pen_freq = P.freq ? P.freq[row] : 0.f;
-                pen_on = pen_rep != 1.f || pen_pres != 0.f || pen_freq != 0.f;
-            }
+            const bool pen_on = pen_row(row);
+            const float pen_rep = (pen_on && P.rep) ? P.rep[row] : 1.f, pen_pres = (pen_on && P.pres) ? P.pres[row] : 0.f, pen_freq = (pen_on && P.freq) ? P.freq[row] : 0.f;
             const uint32_t* hl_row = P.hit_list + size_t(row) * kHitListStride;
             // place of stage c's first entry, c = 0 .. n_chunks: lane l holds c = l, l + 32, l + 64, l + 96, and c = 128
             uint32_t bnd[5] = {0, 0, 0, 0, 0};
@@ -286,6 +302,11 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 while (cur < end) {
                     if (have) inject(h_ent, h_raw);
                     have = win != none;
+                    if (have && ((win & kPenMaxV) - c * A_CH) >= uint32_t(A_CH)) {
+                        // (cannot happen with a list from history_lists_kernel: never write outside the stage)
+                        atomicExch(a.err, 20u);
+                        have = false;
+                    }
                     if (have) {
                         h_ent = win;
                         T* at = stage_mem + ((win & kPenMaxV) - c * A_CH);
@@ -326,8 +347,72 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         return;
     }
 
+    // =========================================================== draw warp
+    // Takes a row's candidates from the tail group and does the rest of the row on its own: probabilities, the top-k /
+    // top-p / min-p cuts, the draw and the row's outputs, while the tail group is already busy with the next row.
+    if (warp == 1 + A_SW + A_TW) {
+        if (!sample) return;
+        const int lane = lane_id();
+        const Group<32> gw{lane, 0};
+        int ord = 0;
+        for (int k = next_row(-1); k < my_rows; k = next_row(k), ++ord) {
+            const int p = ord & 1;
+            if (!mbar_wait(&draw_full[p], (ord >> 1) & 1)) {
+                if (lane == 0) atomicExch(a.err, 8u);
+                return;
+            }
+            const DrawIn d = sh->draw[p];
+            if (!d.skip) {
+                const int row = d.row;
+                unsigned long long* hd = hand + size_t(p) * kAsyncMaxK;
+                const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
+                const uint32_t kept = d.kept;
+                float M = d.M, sum = d.sum;
+                TailIn in;
+                in.inv_t = inv_t;
+                in.top_k = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
+                in.top_p = P.top_p ? P.top_p[row] : 1.0, in.min_p = P.min_p ? P.min_p[row] : 0.0, in.u = P.u ? P.u[row] : 0.0;
+                if (no_sum_row(row)) {
+                    // normalise over the candidates themselves (sorted or not, hd[] holds exactly the kept ones)
+                    unsigned long long top = 0ull;
+                    for (uint32_t i = lane; i < kept; i += 32) top = hd[i] > top ? hd[i] : top;
+                    top = warp_max(uint64_t(top));
+                    M = float_of_key(cand_key(top));
+                    for (uint32_t i = lane; i < kept; i += 32) tail_q[i] = exp(double(__fsub_rn(float_of_key(cand_key(hd[i])), M)) * double(inv_t));
+                    __syncwarp();
+                    sum = float(warp_total(tail_q, kept));
+                    __syncwarp();
+                }
+                in.m = M, in.sum = sum, in.cnt = kept, in.cap = d.cap, in.V = n;
+                in.race = P.race_key != nullptr, in.race_key = P.race_key ? P.race_key[row] : 0;
+                in.presorted = d.presorted != 0;
+                sample_tail<32>(gw, in, reinterpret_cast<uint64_t*>(hd), tail_p, tail_q, &sh->res);
+                const TailOut r = sh->res;
+                if (lane == 0) {
+                    a.out.token[row] = int32_t(r.token);
+                    a.out.status[row] = r.status;
+                    if (a.out.n_kept) a.out.n_kept[row] = int32_t(r.n);
+                    if (a.out.closed) a.out.closed[row] = r.closed;
+                    if (a.out.stats) a.out.stats[2 * row] = M, a.out.stats[2 * row + 1] = sum;
+                    if (a.out.counters && r.status == ROW_ESCALATE) atomicAdd(&a.out.counters[0], 1u);
+                    if (a.out.counters && r.status == ROW_OPEN_TAIL) atomicAdd(&a.out.counters[1], 1u);
+                }
+                if (r.status != ROW_ESCALATE) {
+                    const uint32_t nk = min(r.n, uint32_t(max(a.out.kept_cap, 0)));
+                    for (uint32_t j = lane; j < nk; j += 32) {
+                        if (a.out.kept_ids) a.out.kept_ids[size_t(row) * a.out.kept_cap + j] = int32_t(cand_id(hd[j]));
+                        if (a.out.kept_p) a.out.kept_p[size_t(row) * a.out.kept_cap + j] = tail_p[j];
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&draw_empty[p]);
+        }
+        return;
+    }
+
     // =========================================================== tail
-    if (warp > A_SW) {  // (the penalty warps have returned above)
+    if (warp > A_SW) {  // (the draw warp and the penalty warps have returned above)
         const Group<A_TT> g{tid - 32 - A_ST, 2};
 
         // first threshold of row k (slot k & 1) from its first stage: the (K + h)-th largest raw logit there, h = history
@@ -341,7 +426,20 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             const int row = row_of(k);
             const uint32_t ne = n < uint32_t(boot_elems) ? n : uint32_t(boot_elems);
             uint32_t K = k_of(row);
-            if (sample && P.hit_start) K += P.hit_start[size_t(row) * kHitStartStride + 1];  // (counted with the row's hit list)
+            if (pen_row(row)) {
+                // The row's history tokens inside this stage change value: take them out of this private copy of the stage,
+                // so that the bound below rests on logits that stay as they are.
+                const uint32_t* hl_row = P.hit_list + size_t(row) * kHitListStride;
+                const uint32_t cnt0 = min(P.hit_start[size_t(row) * kHitStartStride + 1], uint32_t(kMaxHist));
+                for (uint32_t i = g.tid; i < cnt0; i += A_TT) {
+                    const uint32_t id = hl_row[i] & kPenMaxV;
+                    if (id < ne) {
+                        if (sizeof(T) == 4) reinterpret_cast<uint32_t*>(boot)[id] = 0xff800000u;
+                        else reinterpret_cast<uint16_t*>(boot)[id] = 0xff80u;
+                    }
+                }
+                g.sync();
+            }
             // A valid bound without looking at every order statistic: split the stage into G interleaved groups, take each
             // group's maximum; the K-th largest of the G maxima has K distinct elements at or above it.
             unsigned long long tau = 0ull;
@@ -383,7 +481,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         };
 
 #ifdef WB_PHASE_TIMERS
-        long long tt[4] = {0, 0, 0, 0};  // bootstrap, refine, final, total
+        long long tt[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // bootstrap, refine, final, total; final split: combine, rank, clear, draw
         const long long tt0 = clock64();
 #define TT_ADD(i, t0) do { if (g.tid == 0) tt[i] += clock64() - (t0); } while (0)
 #else
@@ -478,20 +576,31 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             }
 #endif
             const uint32_t nlog = overflow ? uint32_t(A_L) : total;
-            // row max and normaliser: combine the stream warps' partials
+            // row max and normaliser: combine the warps' partials, one per lane (not needed when the row is normalised
+            // over its candidates)
             const bool greedy = sample && P.greedy && P.greedy[row];
             const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
-            float M = -INFINITY;
-            double S = 0;
-            {
-                const double cexp = double(inv_t * kLog2e);
-                const int n_red = A_SW + (pen ? A_PW : 0);
-                for (int w = 0; w < n_red; ++w) M = fmaxf(M, sl->red_m[w]);
-                for (int w = 0; w < n_red; ++w)
-                    if (sl->red_m[w] != -INFINITY) S += sl->red_s[w] * exp2(double(sl->red_e[w]) - double(M) * cexp);
-            }
             const bool no_sum = no_sum_row(row);
-            float sum = no_sum ? 0.f : float(S);
+            float M = -INFINITY, sum = 0.f;
+            if (!no_sum) {
+                const int n_red = A_SW + (pen ? A_PW : 0), ln = g.tid & 31;
+                static_assert(A_SW + A_PW <= 32, "one partial per lane");
+                const float mw = ln < n_red ? sl->red_m[ln] : -INFINITY;
+                M = warp_max(mw);
+                const double cexp = double(inv_t * kLog2e);
+                const double term = (ln < n_red && mw != -INFINITY) ? sl->red_s[ln] * exp2(double(sl->red_e[ln]) - double(M) * cexp) : 0.0;
+                sum = float(warp_sum(term));
+            }
+            unsigned long long* hand_p = hand + size_t(p) * kAsyncMaxK;
+            // the draw warp is done with this slot's candidates (its row two rows ago)
+            if (sample && !mbar_wait(&draw_empty[p], ((ord >> 1) & 1) ^ 1)) {
+                if (g.tid == 0) atomicExch(a.err, 9u);
+                return;
+            }
+#ifdef WB_PHASE_TIMERS
+            const long long tf1 = clock64();
+            TT_ADD(4, tf0);
+#endif
             uint32_t kept = 0;
             bool presorted = false;
             if (!overflow) {
@@ -506,107 +615,81 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                         const unsigned long long mine = list[t];
                         uint32_t rank = 0;
                         for (uint32_t j = 0; j < m; ++j) rank += list[j] > mine;
-                        if (rank < K) hand[rank] = mine;
+                        if (rank < K) hand_p[rank] = mine;
                     }
                     kept = m < K ? m : K;
                     presorted = true;
                 } else if (nlog > K) {
                     const unsigned long long kth = select_kth<A_TT>(g, log, nlog, K, hist, &sh->sel);
-                    write_survivors<A_TT>(g, log, nlog, kth, hand, kAsyncMaxK, &sh->sel);
+                    write_survivors<A_TT>(g, log, nlog, kth, hand_p, kAsyncMaxK, &sh->sel);
                     kept = sh->sel.wcnt < uint32_t(kAsyncMaxK) ? sh->sel.wcnt : uint32_t(kAsyncMaxK);
                 } else {
-                    for (uint32_t i = g.tid; i < nlog; i += A_TT) hand[i] = log[i];
+                    for (uint32_t i = g.tid; i < nlog; i += A_TT) hand_p[i] = log[i];
                     kept = nlog;
                 }
             }
+#ifdef WB_PHASE_TIMERS
+            const long long tf2 = clock64();
+            TT_ADD(5, tf1);
+#endif
             uint32_t cap = 1;
             while (cap < kept) cap <<= 1;
             g.sync();
-            for (uint32_t i = kept + g.tid; i < cap; i += A_TT) hand[i] = 0ull;
+            for (uint32_t i = kept + g.tid; i < cap; i += A_TT) hand_p[i] = 0ull;
             // the log is free for row k + 2 once it is zero again
             for (uint32_t i = g.tid; i < nlog; i += A_TT) log[i] = 0ull;
             g.sync();
+#ifdef WB_PHASE_TIMERS
+            const long long tf3 = clock64();
+            TT_ADD(6, tf2);
+#endif
             if (overflow) {
                 // more candidates than the log holds (rows in adversarial order): the multi-pass kernel takes the row
                 if (g.tid == 0) a.out.status[row] = ROW_RETRY;
             } else if (!sample) {
                 if (g.tid == 0) a.out.status[row] = ROW_DONE;
-                if (!presorted) sort_desc<A_TT>(g, reinterpret_cast<uint64_t*>(hand), cap);
+                if (!presorted) sort_desc<A_TT>(g, reinterpret_cast<uint64_t*>(hand_p), cap);
                 const T* xr = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
                 for (uint32_t j = g.tid; j < kept; j += A_TT) {
-                    const uint32_t id = cand_id(hand[j]);
+                    const uint32_t id = cand_id(hand_p[j]);
                     a.ids[size_t(row) * a.K + j] = int32_t(id) + a.id_offset;
                     a.vals[size_t(row) * a.K + j] = sizeof(T) == 4 ? reinterpret_cast<const float*>(xr)[id] : bf16_to_f32(reinterpret_cast<const uint16_t*>(xr)[id]);
                 }
                 if (g.tid == 0) a.stats[2 * row] = M, a.stats[2 * row + 1] = sum;
             } else if (greedy) {
                 if (g.tid == 0) {
-                    const uint32_t tok = kept ? cand_id(hand[0]) : 0;
+                    const uint32_t tok = kept ? cand_id(hand_p[0]) : 0;
                     a.out.token[row] = int32_t(tok);
                     a.out.status[row] = ROW_DONE;
                     if (a.out.n_kept) a.out.n_kept[row] = 1;
                     if (a.out.closed) a.out.closed[row] = 1;
-                    if (a.out.stats) a.out.stats[2 * row] = kept ? float_of_key(cand_key(hand[0])) : -INFINITY, a.out.stats[2 * row + 1] = 0.f;
+                    if (a.out.stats) a.out.stats[2 * row] = kept ? float_of_key(cand_key(hand_p[0])) : -INFINITY, a.out.stats[2 * row + 1] = 0.f;
                     if (a.out.kept_ids && a.out.kept_cap > 0) a.out.kept_ids[size_t(row) * a.out.kept_cap] = int32_t(tok);
                     if (a.out.kept_p && a.out.kept_cap > 0) a.out.kept_p[size_t(row) * a.out.kept_cap] = 1.0;
                 }
-            } else {
-                TailIn in;
-                in.inv_t = inv_t;
-                in.top_k = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
-                in.top_p = P.top_p ? P.top_p[row] : 1.0, in.min_p = P.min_p ? P.min_p[row] : 0.0, in.u = P.u ? P.u[row] : 0.0;
-                if (no_sum) {
-                    // normalise over the candidates themselves (sorted or not, hand[] holds exactly the kept ones)
-                    unsigned long long top = 0ull;
-                    for (uint32_t i = g.tid; i < kept; i += A_TT) top = hand[i] > top ? hand[i] : top;
-                    top = warp_max(uint64_t(top));
-                    if ((g.tid & 31) == 0) sh->sel.wsum[g.tid >> 5] = cand_key(top);
-                    g.sync();
-                    uint32_t tk = 0;
-                    for (int w = 0; w < A_TW; ++w) tk = sh->sel.wsum[w] > tk ? sh->sel.wsum[w] : tk;
-                    M = float_of_key(tk);
-                    for (uint32_t i = g.tid; i < kept; i += A_TT)
-                        tail_q[i] = exp(double(__fsub_rn(float_of_key(cand_key(hand[i])), M)) * double(inv_t));
-                    g.sync();
-                    if (g.tid < 32) {
-                        const double z = warp_total(tail_q, kept);
-                        if (g.tid == 0) sh->sel.kth = (unsigned long long)__double_as_longlong(z);
-                    }
-                    g.sync();
-                    sum = float(__longlong_as_double((long long)sh->sel.kth));
-                    g.sync();
-                }
-                in.m = M, in.sum = sum, in.cnt = kept, in.cap = cap, in.V = n;
-                in.race = P.race_key != nullptr, in.race_key = P.race_key ? P.race_key[row] : 0;
-                in.presorted = presorted;
-                sample_tail<A_TT>(g, in, reinterpret_cast<uint64_t*>(hand), tail_p, tail_q, &sh->res);
-                const TailOut r = sh->res;
+            }
+            if (sample) {
+                // hand the candidates to the draw warp (or tell it that this row needs none of its work)
                 if (g.tid == 0) {
-                    a.out.token[row] = int32_t(r.token);
-                    a.out.status[row] = r.status;
-                    if (a.out.n_kept) a.out.n_kept[row] = int32_t(r.n);
-                    if (a.out.closed) a.out.closed[row] = r.closed;
-                    if (a.out.stats) a.out.stats[2 * row] = M, a.out.stats[2 * row + 1] = sum;
-                    if (a.out.counters && r.status == ROW_ESCALATE) atomicAdd(&a.out.counters[0], 1u);
-                    if (a.out.counters && r.status == ROW_OPEN_TAIL) atomicAdd(&a.out.counters[1], 1u);
-                }
-                if (r.status != ROW_ESCALATE) {
-                    const uint32_t nk = min(r.n, uint32_t(max(a.out.kept_cap, 0)));
-                    for (uint32_t j = g.tid; j < nk; j += A_TT) {
-                        if (a.out.kept_ids) a.out.kept_ids[size_t(row) * a.out.kept_cap + j] = int32_t(cand_id(hand[j]));
-                        if (a.out.kept_p) a.out.kept_p[size_t(row) * a.out.kept_cap + j] = tail_p[j];
-                    }
+                    DrawIn d;
+                    d.row = row, d.kept = kept, d.cap = cap, d.M = M, d.sum = sum, d.presorted = presorted ? 1u : 0u;
+                    d.skip = (overflow || greedy) ? 1u : 0u;
+                    sh->draw[p] = d;
+                    mbar_arrive(&draw_full[p]);  // (after the barrier above: every thread's candidates are written)
                 }
             }
             g.sync();
             TT_ADD(2, tf0);
+#ifdef WB_PHASE_TIMERS
+            TT_ADD(7, tf3);
+#endif
             k = kn;
         }
 #ifdef WB_PHASE_TIMERS
         if (g.tid == 0) {
             tt[3] = clock64() - tt0;
             unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 4);
-            for (int i = 0; i < 4; ++i) atomicAdd(&dbg[i], (unsigned long long)tt[i]);
+            for (int i = 0; i < 4; ++i) atomicAdd(&dbg[i], (unsigned long long)tt[i]), atomicAdd(&dbg[8 + i], (unsigned long long)tt[4 + i]);
         }
 #endif
         return;
@@ -623,7 +706,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     static_assert(A_CH == kHitStage, "the hit lists are grouped by this kernel's stages");
     uint64_t* ready = pen ? patched : full;  // with penalties a stage is read only after the penalty warp has been over it
 #ifdef WB_PHASE_TIMERS
-    long long ts_wait = 0, ts_proc = 0, ts_setup = 0;
+    long long ts_wait = 0, ts_proc = 0, ts_setup = 0, ts_slow = 0, ts_bound = 0;
+    unsigned long long n_early = 0, n_all = 0;
 #endif
     int ord = 0;
     for (int k = next_row(-1); k < my_rows; k = next_row(k), ++ord) {
@@ -736,6 +820,9 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             } else {
                 m_t = fmaxf(m_t, vm);
             }
+#ifdef WB_PHASE_TIMERS
+            const long long tsl0 = clock64();
+#endif
             if (vm >= tau_f) {
                 // rare: this lane holds an element that may beat the threshold
 #pragma unroll
@@ -749,12 +836,21 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                                 if (cnd > tau) {
                                     const uint32_t pos = atomicAdd(&sl->cnt, 1u);
                                     if (pos < uint32_t(A_L)) log[pos] = cnd;
+#ifdef WB_PHASE_TIMERS
+                                    ++n_all;
+                                    if (c < 8) ++n_early;
+#endif
                                 }
                             }
                         }
                     }
                 }
             }
+#ifdef WB_PHASE_TIMERS
+            __syncwarp();
+            const long long tsl1 = clock64();
+            ts_slow += tsl1 - tsl0;
+#endif
             // A threshold from the running maxima, with no help from the tail group: if every stream warp names the r-th
             // largest of its 32 lane maxima, r = ceil(K / 16), then 16 r >= K distinct elements of the row are at or above the
             // smallest of those 16 values.  Maxima settle fast, so this runs after 1, 2, 4, 8 ... iterations of a row.
@@ -784,6 +880,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             }
 #endif
 #ifdef WB_PHASE_TIMERS
+            __syncwarp();
+            ts_bound += clock64() - tsl1;
             ts_proc += clock64() - tw1;
 #endif
         };
@@ -822,14 +920,16 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     if (g.tid == 0) {
         unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 4);
         atomicAdd(&dbg[4], (unsigned long long)ts_wait), atomicAdd(&dbg[5], (unsigned long long)ts_proc), atomicAdd(&dbg[6], (unsigned long long)ts_setup);
+        atomicAdd(&dbg[12], (unsigned long long)ts_slow), atomicAdd(&dbg[13], (unsigned long long)ts_bound);
     }
+    atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 4) + 14, n_early), atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 4) + 15, n_all);
 #endif
 }
 
 static size_t async_fixed_smem(bool pen, size_t boot_bytes) {
     (void)pen;
-    return boot_bytes + size_t(2) * A_SW * 4 + size_t(2) * A_L * 8 + SEL_BINS * 4 + size_t(kAsyncMaxK) * 8 + 2 * (kAsyncMaxK + 2 * A_TW) * 8 +
-           (3 * A_MAXSTAGES + 8) * 8 + sizeof(AShared) + 128;
+    return boot_bytes + size_t(2) * A_SW * 4 + size_t(2) * A_L * 8 + SEL_BINS * 4 + size_t(2) * kAsyncMaxK * 8 + 2 * (kAsyncMaxK + 2 * A_TW) * 8 +
+           (3 * A_MAXSTAGES + 12) * 8 + sizeof(AShared) + 128;
 }
 
 bool sample_async_supported(const SelectArgs& a, int dtype) {
