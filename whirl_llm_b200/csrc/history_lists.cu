@@ -99,13 +99,14 @@ __global__ void __launch_bounds__(HL_THREADS) history_lists_kernel(const int32_t
     }
     }
 
-size_t history_lists_ws_bytes(int rows) { return size_t(rows) * (size_t(kHitListStride) + kHitStartStride) * 4; }
+size_t history_lists_ws_bytes(int rows) { return size_t(rows) * (2 * size_t(kHitListStride) + kHitStartStride) * 4; }
 
 cudaError_t history_lists_launch(RowParams& prm, int rows, int n, int dtype, void* ws, int sm_count, cudaStream_t st) {
     (void)dtype;
     uint32_t* lists = static_cast<uint32_t*>(ws);
     uint32_t* starts = lists + size_t(rows) * kHitListStride;
     prm.hit_list = lists, prm.hit_start = starts;
+    prm.hit_val = reinterpret_cast<float*>(starts + size_t(rows) * kHitStartStride);
     const int grid = rows < 6 * sm_count ? rows : 6 * sm_count;  // (six CTAs of 33 KiB fit an SM)
     history_lists_kernel<<<grid, HL_THREADS, 0, st>>>(prm.hist, prm.hist_len, prm.hist_stride, rows, uint32_t(n), lists, starts);
     return cudaGetLastError();

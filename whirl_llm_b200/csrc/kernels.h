@@ -64,6 +64,7 @@ struct RowParams {
     // (single-pass sampler only) the rows' hit lists, built by history_lists_launch from the fields above
     const uint32_t* hit_list;  // [rows][kHitListStride]
     const uint32_t* hit_start; // [rows][kHitStartStride]
+    float* hit_val;            // [rows][kHitListStride] scratch: penalised logits of the tokens in a row's first stages
 };
 
 struct RowOutputs {

@@ -35,14 +35,15 @@ constexpr int A_THREADS = 32 + A_ST + A_TT + 32 + A_PW * 32;  // copies, stream 
 constexpr int A_CH = 4096;                    // logits per ring stage
 constexpr int A_L = 3072;                     // candidate log entries per row slot
 constexpr int A_MAXSTAGES = 16;
+constexpr int A_S0 = 8;                       // stages at the head of a row that are read twice (see the stream warps)
 
 struct ASlot {
     unsigned long long tau;  // current threshold candidate; elements must beat it to be logged
     uint32_t cnt;            // log entries reserved so far (may exceed A_L: overflow)
     int32_t row;
-    float red_m[A_SW + A_PW];  // per stream warp, then per penalty warp: max, reference exponent, scaled sum
-    float red_e[A_SW + A_PW];
-    double red_s[A_SW + A_PW];
+    float red_m[A_SW + 1];   // per stream warp, then the draw warp (history tokens): max, reference exponent, scaled sum
+    float red_e[A_SW + 1];
+    double red_s[A_SW + 1];
 };
 
 // what the tail group hands to the draw warp with a row's candidates
@@ -68,27 +69,29 @@ __device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned lon
 __device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) { return *reinterpret_cast<const volatile uint32_t*>(p); }
 
 template <typename T>
-__global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a, int stages, int pen, int ch_bytes, int boot_elems) {
+__global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a, int stages, int pen, int ch_bytes) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;                                                          // stages * ch_bytes
-    uint8_t* boot = ring + size_t(stages) * ch_bytes;                              // boot_elems logits: the head of the next row
-    unsigned long long* logs = reinterpret_cast<unsigned long long*>(boot + size_t(boot_elems) * sizeof(T));  // 2 * A_L
+    unsigned long long* logs = reinterpret_cast<unsigned long long*>(ring + size_t(stages) * ch_bytes);  // 2 * A_L
     uint32_t* hist = reinterpret_cast<uint32_t*>(logs + 2 * A_L);                 // SEL_BINS
     unsigned long long* hand = reinterpret_cast<unsigned long long*>(hist + SEL_BINS);   // 2 * kAsyncMaxK: a row's candidates, per slot
     double* tail_p = reinterpret_cast<double*>(hand + 2 * kAsyncMaxK);                 // 2 * (kAsyncMaxK + 2 * A_TW)
     double* tail_q = tail_p + kAsyncMaxK + 2 * A_TW;
     uint64_t* bars = reinterpret_cast<uint64_t*>(tail_q + kAsyncMaxK + 2 * A_TW);  // 2 * 16 + 8
-    AShared* sh = reinterpret_cast<AShared*>(bars + 3 * A_MAXSTAGES + 12);
+    AShared* sh = reinterpret_cast<AShared*>(bars + 3 * A_MAXSTAGES + 14);
     uint32_t* wbound = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));  // 2 * A_SW: per slot, each stream warp's bound key
     uint64_t *full = bars, *empty = bars + A_MAXSTAGES, *patched = bars + 2 * A_MAXSTAGES;
-    uint64_t *closed = bars + 3 * A_MAXSTAGES, *boot_done = closed + 2, *boot_full = closed + 4, *boot_empty = closed + 5;
-    uint64_t *draw_full = closed + 6, *draw_empty = closed + 8;  // per slot: the candidates are there / the draw warp is done with them
+    uint64_t *closed = bars + 3 * A_MAXSTAGES, *boot_done = closed + 2, *head_done = closed + 4;  // per slot: the slot is the row's / every stream warp has named its bound
+    uint64_t *draw_full = closed + 6, *draw_empty = closed + 8, *hv_ready = closed + 10;  // per slot: the candidates are there / the draw warp is done with them
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const uint32_t n = uint32_t(a.n);
     const int n_rows = a.row_count ? min(*a.row_count, a.rows) : a.rows;
     const int my_rows = n_rows > int(blockIdx.x) ? (n_rows - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
     const uint32_t n_chunks = (n + A_CH - 1) / A_CH;
+    // A row goes through the ring as: its first s0 stages, those s0 stages once more, then the rest (see the stream warps).
+    const uint32_t s0 = n_chunks < uint32_t(A_S0) ? n_chunks : uint32_t(A_S0), n_seq = n_chunks + s0;
+    auto seq_stage = [&](uint32_t i) -> uint32_t { return i < s0 ? i : i - s0; };
     const size_t row_bytes = size_t(n) * sizeof(T);
     auto row_of = [&](int k) -> int {
         const int li = int(blockIdx.x) + k * int(gridDim.x);
@@ -108,9 +111,9 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
 
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], A_SW), mbar_init(&patched[s], 1);
-        for (int p = 0; p < 2; ++p) mbar_init(&closed[p], A_SW + (pen ? A_PW : 0)), mbar_init(&boot_done[p], 1);
-        mbar_init(boot_full, 1), mbar_init(boot_empty, 1);
-        for (int p = 0; p < 2; ++p) mbar_init(&draw_full[p], 1), mbar_init(&draw_empty[p], 1);
+        for (int p = 0; p < 2; ++p) mbar_init(&closed[p], A_SW + (pen ? 1 : 0)), mbar_init(&boot_done[p], 1);
+        for (int p = 0; p < 2; ++p) mbar_init(&head_done[p], A_SW);
+        for (int p = 0; p < 2; ++p) mbar_init(&draw_full[p], 1), mbar_init(&draw_empty[p], 1), mbar_init(&hv_ready[p], A_PW);
         mbar_fence_init();
     }
     for (int i = tid; i < 2 * A_L; i += A_THREADS) logs[i] = 0ull;
@@ -124,49 +127,32 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     // =========================================================== producer
     if (warp == 0) {
         if (lane_id() != 0) return;
-        const uint32_t boot_bytes = uint32_t(row_bytes < size_t(boot_elems) * sizeof(T) ? row_bytes : size_t(boot_elems) * sizeof(T));
         uint32_t it = 0;
-        int ord = 0;  // ordinal of the row among this CTA's rows that are not skipped
 #ifdef WB_PHASE_TIMERS
         long long tp_wait = 0;
 #endif
-        for (int k = -1; k < my_rows;) {
-            const int kn = next_row(k);
-            if (kn < my_rows) {
-                // the first stage of the next row for the tail group's bootstrap
-                const int o = k < 0 ? 0 : ord + 1;
-                if (!mbar_wait(boot_empty, (o & 1) ^ 1)) {
+        for (int k = next_row(-1); k < my_rows; k = next_row(k)) {
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x) + size_t(row_of(k)) * row_bytes;
+            for (uint32_t i = 0; i < n_seq; ++i, ++it) {
+                const uint32_t c = seq_stage(i);
+                const uint32_t s = it % stages, use = it / stages;
+#ifdef WB_PHASE_TIMERS
+                const long long tw0 = clock64();
+#endif
+                if (!mbar_wait(&empty[s], (use & 1) ^ 1)) {
                     atomicExch(a.err, 1u);
                     return;
                 }
-                if (pen) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // (the tail group writes to its copy too)
-                mbar_expect_tx(boot_full, boot_bytes);
-                bulk_g2s(boot, reinterpret_cast<const uint8_t*>(a.x) + size_t(row_of(kn)) * row_bytes, boot_bytes, boot_full);
-            }
-            if (k >= 0) {
-                const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x) + size_t(row_of(k)) * row_bytes;
-                for (uint32_t c = 0; c < n_chunks; ++c, ++it) {
-                    const uint32_t s = it % stages, use = it / stages;
 #ifdef WB_PHASE_TIMERS
-                    const long long tw0 = clock64();
+                tp_wait += clock64() - tw0;
 #endif
-                    if (!mbar_wait(&empty[s], (use & 1) ^ 1)) {
-                        atomicExch(a.err, 1u);
-                        return;
-                    }
-#ifdef WB_PHASE_TIMERS
-                    tp_wait += clock64() - tw0;
-#endif
-                    const size_t off = size_t(c) * ch_bytes;
-                    const uint32_t bytes = uint32_t(row_bytes - off < size_t(ch_bytes) ? row_bytes - off : size_t(ch_bytes));
-                    // (with penalties the stage was also written to: those writes, seen through the barriers, stay before the copy)
-                    if (pen) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    mbar_expect_tx(&full[s], bytes);
-                    bulk_g2s(ring + size_t(s) * ch_bytes, src + off, bytes, &full[s]);
-                }
-                ++ord;
+                const size_t off = size_t(c) * ch_bytes;
+                const uint32_t bytes = uint32_t(row_bytes - off < size_t(ch_bytes) ? row_bytes - off : size_t(ch_bytes));
+                // (with penalties the stage was also written to: those writes, seen through the barriers, stay before the copy)
+                if (pen) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_expect_tx(&full[s], bytes);
+                bulk_g2s(ring + size_t(s) * ch_bytes, src + off, bytes, &full[s]);
             }
-            k = kn;
         }
 #ifdef WB_PHASE_TIMERS
         atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 4) + 7, (unsigned long long)tp_wait);
@@ -210,27 +196,25 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     // =========================================================== penalty warps
     // They walk the row's hit list (its distinct history tokens with their counts, stage by stage; history_lists_kernel)
     // while the row streams, taking the stages in turn: as soon as a stage has landed its warp takes the raw logits of the
-    // stage's history tokens out (replaced by -inf, so the stream warps see them as absent), hands the stage on to the
-    // stream warps, and adds the penalised values to the row itself: each is one more contributor to the row's maximum,
-    // sum and candidate log.  The places of the row's stages in the list sit in registers (four per lane), and the first
-    // 32 entries of a warp's next stage are already on their way while it works on the current one.
+    // stage's history tokens out (replaced by -inf, so the stream warps see them as absent), puts them aside in global
+    // memory, and hands the stage on to the stream warps.  Nothing else: the draw warp applies the penalties and adds the
+    // tokens to the row once the row has streamed.  They depend on no threshold and no row slot, so they run as far ahead
+    // of the stream warps as the ring allows.  The first s0 stages come twice (see the stream warps); the second time their
+    // tokens are only taken out again.  Entries are read in blocks of 128 (four per lane, loaded together), the first
+    // block of a warp's next stage while it works on the current one.
     if (warp >= 2 + A_SW + A_TW) {
         if (!pen) return;
         const int lane = lane_id(), pw = warp - (2 + A_SW + A_TW);
         constexpr uint32_t none = 0xffffffffu;
-        uint32_t it0 = 0;  // stages of the CTA's earlier rows (ring position of this row's first stage)
+        constexpr uint32_t PB = 128;  // entries per block: four per lane
+        uint32_t it0 = 0;             // ring position of this row's first stage
         int ord = 0;
-        for (int k = next_row(-1); k < my_rows; k = next_row(k), ++ord, it0 += n_chunks) {
+        for (int k = next_row(-1); k < my_rows; k = next_row(k), ++ord, it0 += n_seq) {
             const int p = ord & 1;
             const int row = row_of(k);
-            ASlot* sl = &sh->slot[p];
-            unsigned long long* log = logs + size_t(p) * A_L;
-            const bool greedy = no_sum_row(row);
-            const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
-            const float cexp = inv_t * kLog2e;
             const bool pen_on = pen_row(row);
-            const float pen_rep = (pen_on && P.rep) ? P.rep[row] : 1.f, pen_pres = (pen_on && P.pres) ? P.pres[row] : 0.f, pen_freq = (pen_on && P.freq) ? P.freq[row] : 0.f;
             const uint32_t* hl_row = P.hit_list + size_t(row) * kHitListStride;
+            float* hv_row = P.hit_val + size_t(row) * kHitListStride;
             // place of stage c's first entry, c = 0 .. n_chunks: lane l holds c = l, l + 32, l + 64, l + 96, and c = 128
             uint32_t bnd[5] = {0, 0, 0, 0, 0};
             if (pen_on) {
@@ -245,104 +229,74 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 const uint32_t g = __shfl_sync(0xffffffffu, v, c & 31u);
                 return c >= 128 ? bnd[4] : g;
             };
-            // this warp's stages of the row: c0, c0 + A_PW, ...
-            uint32_t c = (uint32_t(pw) + A_PW - it0 % A_PW) % A_PW;
-            uint32_t s_nx = 0, e_nx = 0, win_nx = none;
-            auto prefetch = [&](uint32_t cc) {
-                s_nx = e_nx = 0, win_nx = none;
-                if (pen_on && cc < n_chunks) {
+            uint32_t s_nx = 0, e_nx = 0, w_nx[4] = {none, none, none, none};
+            auto load_block = [&](uint32_t from, uint32_t end, uint32_t* w) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) w[j] = from + 32 * j + lane < end ? hl_row[from + 32 * j + lane] : none;
+            };
+            auto prefetch = [&](uint32_t i) {
+                s_nx = e_nx = 0;
+                if (pen_on && i < n_seq) {
+                    const uint32_t cc = seq_stage(i);
                     s_nx = place(cc), e_nx = place(cc + 1);
-                    win_nx = s_nx + lane < e_nx ? hl_row[s_nx + lane] : none;
                 }
+                load_block(s_nx, e_nx, w_nx);
             };
-            prefetch(c);
-            // the row's log and threshold belong to the row before until the tail group says otherwise
-            if (!mbar_wait(&boot_done[p], (ord >> 1) & 1)) {
-                if (lane == 0) atomicExch(a.err, 6u);
-                return;
-            }
-            float m_t = -INFINITY, e_t = 0.f, s_t = 0.f;
-            unsigned long long tau_seen = 0ull;
-            float tau_f = -INFINITY;
-            // one history token of the row: penalty on its raw logit, then max / sum / candidate log as for any logit
-            auto inject = [&](uint32_t ent, float l) {
-                l = (l > 0.f) ? __fdiv_rn(l, pen_rep) : __fmul_rn(l, pen_rep);
-                const float x = __fsub_rn(l, __fadd_rn(pen_pres, __fmul_rn(pen_freq, float(ent >> kPenIdBits))));
-                if (!greedy) {
-                    if (x > m_t) {
-                        const float ne = ceilf(x * cexp);
-                        s_t = (m_t == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
-                        e_t = ne, m_t = x;
-                    }
-                    if (m_t != -INFINITY) s_t += ex2_approx(fmaf(x, cexp, -e_t));
-                } else {
-                    m_t = fmaxf(m_t, x);
-                }
-                if (x >= tau_f) {
-                    const unsigned long long cnd = make_cand(key_of(x), ent & kPenMaxV);
-                    if (cnd > tau_seen) {
-                        const uint32_t pos = atomicAdd(&sl->cnt, 1u);
-                        if (pos < uint32_t(A_L)) log[pos] = cnd;
-                    }
-                }
-            };
-            for (; c < n_chunks; c += A_PW) {
-                const uint32_t it = it0 + c, st_slot = it % uint32_t(stages), st_phase = (it / uint32_t(stages)) & 1u;
+            // this warp's places in the row's sequence of stages: i0, i0 + A_PW, ...
+            uint32_t i = (uint32_t(pw) + A_PW - it0 % A_PW) % A_PW;
+            prefetch(i);
+            for (; i < n_seq; i += A_PW) {
+                const uint32_t c = seq_stage(i);
+                const bool keep = i < s0 || i >= 2 * s0;  // (not on the second visit of the first stages)
+                const uint32_t it = it0 + i, st_slot = it % uint32_t(stages), st_phase = (it / uint32_t(stages)) & 1u;
                 uint32_t cur = s_nx;
                 const uint32_t end = e_nx;
-                uint32_t win = win_nx;
+                uint32_t w[4] = {w_nx[0], w_nx[1], w_nx[2], w_nx[3]};
                 if (!mbar_wait(&full[st_slot], st_phase)) {
                     if (lane == 0) atomicExch(a.err, 7u);
                     return;
                 }
                 T* stage_mem = reinterpret_cast<T*>(ring + size_t(st_slot) * ch_bytes);
-                bool have = false;  // this lane holds a token taken out of the stage and not added to the row yet
-                uint32_t h_ent = 0;
-                float h_raw = 0.f;
-                while (cur < end) {
-                    if (have) inject(h_ent, h_raw);
-                    have = win != none;
-                    if (have && ((win & kPenMaxV) - c * A_CH) >= uint32_t(A_CH)) {
+                // entry e, at place idx of the list, leaves the stage
+                auto take_out = [&](uint32_t e, uint32_t idx) {
+                    if (e == none) return;
+                    const uint32_t off = (e & kPenMaxV) - c * A_CH;
+                    if (off >= uint32_t(A_CH)) {
                         // (cannot happen with a list from history_lists_kernel: never write outside the stage)
                         atomicExch(a.err, 20u);
-                        have = false;
+                        return;
                     }
-                    if (have) {
-                        h_ent = win;
-                        T* at = stage_mem + ((win & kPenMaxV) - c * A_CH);
-                        if (sizeof(T) == 4) {
-                            h_raw = *reinterpret_cast<float*>(at);
-                            *reinterpret_cast<uint32_t*>(at) = 0xff800000u;
-                        } else {
-                            h_raw = __uint_as_float(uint32_t(*reinterpret_cast<uint16_t*>(at)) << 16);
-                            *reinterpret_cast<uint16_t*>(at) = 0xff80u;
-                        }
+                    T* at = stage_mem + off;
+                    if (sizeof(T) == 4) {
+                        if (keep) hv_row[idx] = *reinterpret_cast<float*>(at);
+                        *reinterpret_cast<uint32_t*>(at) = 0xff800000u;
+                    } else {
+                        if (keep) hv_row[idx] = __uint_as_float(uint32_t(*reinterpret_cast<uint16_t*>(at)) << 16);
+                        *reinterpret_cast<uint16_t*>(at) = 0xff80u;
                     }
-                    cur += 32;
-                    if (cur < end) win = cur + lane < end ? hl_row[cur + lane] : none;  // (a stage with more than 32 tokens: rare)
+                };
+                if (cur < end) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) take_out(w[j], cur + 32 * j + lane);
+                    cur += PB;
+                }
+                // (a stage with more than 128 tokens, the low ids as a rule: 512 entries per trip to memory)
+                while (cur < end) {
+                    uint32_t big[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) big[j] = cur + 32 * j + lane < end ? hl_row[cur + 32 * j + lane] : none;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) take_out(big[j], cur + 32 * j + lane);
+                    cur += 4 * PB;
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&patched[st_slot]);  // the stream warps may read the stage
-                prefetch(c + A_PW);
-                if (have) {
-                    const unsigned long long t = ld_volatile_u64(&sl->tau);
-                    if (t != tau_seen) tau_seen = t, tau_f = float_of_key(cand_key(t));
-                    inject(h_ent, h_raw);
-                }
+                prefetch(i + A_PW);
             }
-            const bool saw_nan = !greedy && (s_t != s_t);
-            if (__any_sync(0xffffffffu, saw_nan) && lane == 0) atomicOr(&sl->cnt, 0x80000000u);
-            {
-                const float wm = warp_max(m_t);
-                float we = e_t;
-                if (m_t == -INFINITY) we = -INFINITY;
-                we = warp_max(we);
-                double ds = (m_t == -INFINITY) ? 0.0 : double(s_t) * double(ex2_approx(e_t - we));
-                ds = warp_sum(ds);
-                if (lane == 0) sl->red_m[A_SW + pw] = wm, sl->red_e[A_SW + pw] = we, sl->red_s[A_SW + pw] = ds;
-            }
+            // every raw logit of the row's history tokens is put aside: the draw warp may read them
+            __threadfence_block();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&closed[p]);
+            if (lane == 0) mbar_arrive(&hv_ready[p]);
         }
         return;
     }
@@ -357,6 +311,85 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         int ord = 0;
         for (int k = next_row(-1); k < my_rows; k = next_row(k), ++ord) {
             const int p = ord & 1;
+            if (pen) {
+                // The row has streamed (or nearly): its history tokens, taken out of the stages by the penalty warps, get their
+                // penalty and join the row here: this warp is one more contributor to the row's maximum, sum and log.
+                const int row = row_of(k);
+                ASlot* sl = &sh->slot[p];
+                unsigned long long* log = logs + size_t(p) * A_L;
+                const bool greedy = no_sum_row(row);
+                const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
+                const float cexp = inv_t * kLog2e;
+                const bool pen_on = pen_row(row);
+                const float pen_rep = (pen_on && P.rep) ? P.rep[row] : 1.f, pen_pres = (pen_on && P.pres) ? P.pres[row] : 0.f, pen_freq = (pen_on && P.freq) ? P.freq[row] : 0.f;
+                // the raw logits are all put aside; the slot is the row's; the row has its first threshold
+                if (!mbar_wait(&hv_ready[p], (ord >> 1) & 1) || !mbar_wait(&boot_done[p], (ord >> 1) & 1) || !mbar_wait(&head_done[p], (ord >> 1) & 1)) {
+                    if (lane == 0) atomicExch(a.err, 6u);
+                    return;
+                }
+                float m_t = -INFINITY, e_t = 0.f, s_t = 0.f;
+                if (pen_on) {
+                    constexpr uint32_t none = 0xffffffffu;
+                    const uint32_t* hl_row = P.hit_list + size_t(row) * kHitListStride;
+                    const float* hv_row = P.hit_val + size_t(row) * kHitListStride;
+                    const uint32_t total = min(P.hit_start[size_t(row) * kHitStartStride + n_chunks], uint32_t(kMaxHist));
+                    uint32_t en[4];
+                    float rn[4];
+                    auto fetch = [&](uint32_t from) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t idx = from + 32 * j + lane;
+                            en[j] = idx < total ? hl_row[idx] : none;
+                            rn[j] = idx < total ? hv_row[idx] : 0.f;
+                        }
+                    };
+                    fetch(0);
+                    for (uint32_t from = 0; from < total; from += 128) {
+                        uint32_t e4[4];
+                        float r4[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) e4[j] = en[j], r4[j] = rn[j];
+                        fetch(from + 128);  // (the next block is on its way while this one joins)
+                        const unsigned long long tau = ld_volatile_u64(&sl->tau);
+                        const float tau_f = float_of_key(cand_key(tau));
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (e4[j] == none) continue;
+                            float l = r4[j];
+                            l = (l > 0.f) ? __fdiv_rn(l, pen_rep) : __fmul_rn(l, pen_rep);
+                            const float x = __fsub_rn(l, __fadd_rn(pen_pres, __fmul_rn(pen_freq, float(e4[j] >> kPenIdBits))));
+                            if (!greedy) {
+                                if (x > m_t) {
+                                    const float ne = ceilf(x * cexp);
+                                    s_t = (m_t == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
+                                    e_t = ne, m_t = x;
+                                }
+                                if (m_t != -INFINITY) s_t += ex2_approx(fmaf(x, cexp, -e_t));
+                            } else {
+                                m_t = fmaxf(m_t, x);
+                            }
+                            if (x >= tau_f) {
+                                const unsigned long long cnd = make_cand(key_of(x), e4[j] & kPenMaxV);
+                                if (cnd > tau) {
+                                    const uint32_t pos = atomicAdd(&sl->cnt, 1u);
+                                    if (pos < uint32_t(A_L)) log[pos] = cnd;
+                                }
+                            }
+                        }
+                    }
+                }
+                const bool saw_nan = !greedy && (s_t != s_t);
+                if (__any_sync(0xffffffffu, saw_nan) && lane == 0) atomicOr(&sl->cnt, 0x80000000u);
+                const float wm = warp_max(m_t);
+                float we = e_t;
+                if (m_t == -INFINITY) we = -INFINITY;
+                we = warp_max(we);
+                double ds = (m_t == -INFINITY) ? 0.0 : double(s_t) * double(ex2_approx(e_t - we));
+                ds = warp_sum(ds);
+                if (lane == 0) sl->red_m[A_SW] = wm, sl->red_e[A_SW] = we, sl->red_s[A_SW] = ds;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&closed[p]);
+            }
             if (!mbar_wait(&draw_full[p], (ord >> 1) & 1)) {
                 if (lane == 0) atomicExch(a.err, 8u);
                 return;
@@ -415,66 +448,16 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     if (warp > A_SW) {  // (the draw warp and the penalty warps have returned above)
         const Group<A_TT> g{tid - 32 - A_ST, 2};
 
-        // first threshold of row k (slot k & 1) from its first stage: the (K + h)-th largest raw logit there, h = history
-        // tokens inside the stage (at most h of the best can be pushed down by the penalties, so K stay at or above it)
-        auto bootstrap = [&](int k, int o) -> bool {  // row ordinal o (slot o & 1) is the CTA's k-th row
+        // slot o & 1 becomes the row's (the CTA's k-th): no threshold yet, an empty log (zeroed when its last row finished)
+        auto bootstrap = [&](int k, int o) -> bool {
             const int p = o & 1;
-            bool ok = true;
-            if (g.tid == 0) ok = mbar_wait(boot_full, o & 1);
-            if (g.sync_or(!ok)) return false;
-            if (g.tid != 0) mbar_wait(boot_full, o & 1);
-            const int row = row_of(k);
-            const uint32_t ne = n < uint32_t(boot_elems) ? n : uint32_t(boot_elems);
-            uint32_t K = k_of(row);
-            if (pen_row(row)) {
-                // The row's history tokens inside this stage change value: take them out of this private copy of the stage,
-                // so that the bound below rests on logits that stay as they are.
-                const uint32_t* hl_row = P.hit_list + size_t(row) * kHitListStride;
-                const uint32_t cnt0 = min(P.hit_start[size_t(row) * kHitStartStride + 1], uint32_t(kMaxHist));
-                for (uint32_t i = g.tid; i < cnt0; i += A_TT) {
-                    const uint32_t id = hl_row[i] & kPenMaxV;
-                    if (id < ne) {
-                        if (sizeof(T) == 4) reinterpret_cast<uint32_t*>(boot)[id] = 0xff800000u;
-                        else reinterpret_cast<uint16_t*>(boot)[id] = 0xff80u;
-                    }
-                }
-                g.sync();
-            }
-            // A valid bound without looking at every order statistic: split the stage into G interleaved groups, take each
-            // group's maximum; the K-th largest of the G maxima has K distinct elements at or above it.
-            unsigned long long tau = 0ull;
-            const uint32_t G = K <= 96 ? 128u : (K <= 384 ? 512u : 0u);
-            if (K <= ne && G != 0 && ne >= 4 * G) {
-                unsigned long long* gm = reinterpret_cast<unsigned long long*>(hist);  // G group maxima as (key, group)
-                const T* bx = reinterpret_cast<const T*>(boot);
-                for (uint32_t grp = g.tid; grp < G; grp += A_TT) {
-                    float m = -INFINITY;
-                    for (uint32_t i = grp; i < ne; i += G) {
-                        const float v = sizeof(T) == 4 ? reinterpret_cast<const float*>(bx)[i] : bf16_to_f32(reinterpret_cast<const uint16_t*>(bx)[i]);
-                        m = fmaxf(m, v);  // NaN is ignored
-                    }
-                    gm[grp] = (unsigned long long)key_of(m) << 32 | grp;
-                }
-                g.sync();
-                for (uint32_t t = g.tid; t < G; t += A_TT) {
-                    const unsigned long long mine = gm[t];
-                    uint32_t rank = 0;
-                    for (uint32_t j = 0; j < G; ++j) rank += gm[j] > mine;
-                    if (rank == K - 1) sh->sel.kth = mine;
-                }
-                g.sync();
-                tau = sh->sel.kth & 0xffffffff00000000ull;
-            } else if (K <= ne) {
-                tau = (unsigned long long)select_key_bound<A_TT, T>(g, reinterpret_cast<const T*>(boot), ne, K, hist, &sh->sel) << 32;
-            }
             g.sync();
-            if (g.tid < A_SW) wbound[p * A_SW + g.tid] = 0u;  // no bound from the stream warps yet
+            if (g.tid < A_SW) wbound[p * A_SW + g.tid] = 0u;
             g.sync();
             if (g.tid == 0) {
-                sh->slot[p].tau = tau;
+                sh->slot[p].tau = 0ull;
                 sh->slot[p].cnt = 0;
-                sh->slot[p].row = row;
-                mbar_arrive(boot_empty);
+                sh->slot[p].row = row_of(k);
                 mbar_arrive(&boot_done[p]);
             }
             return true;
@@ -583,8 +566,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             const bool no_sum = no_sum_row(row);
             float M = -INFINITY, sum = 0.f;
             if (!no_sum) {
-                const int n_red = A_SW + (pen ? A_PW : 0), ln = g.tid & 31;
-                static_assert(A_SW + A_PW <= 32, "one partial per lane");
+                const int n_red = A_SW + (pen ? 1 : 0), ln = g.tid & 31;
+                static_assert(A_SW + 1 <= 32, "one partial per lane");
                 const float mw = ln < n_red ? sl->red_m[ln] : -INFINITY;
                 M = warp_max(mw);
                 const double cexp = double(inv_t * kLog2e);
@@ -696,18 +679,23 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     }
 
     // =========================================================== stream
-    const Group<A_ST> g{tid - 32, 1};
-    (void)g.bar;
+    // Each warp reads its share of every stage (f32: logits [128 w, 128 w + 128) of each half stage; bf16: logits [256 w,
+    // 256 w + 256)), keeps per-lane running maxima and sums, and appends the logits that can still be among the K best to
+    // the row's log.  What "can still be" means needs a threshold, and a row has none when it starts.  So the first s0
+    // stages of a row come through the ring twice: the first time the warps only accumulate; then every warp names the
+    // r-th largest of its 32 lane maxima, r = ceil(K / 16) (16 r >= K distinct logits of the row are at or above the
+    // smallest of those 16 values, so it is a valid threshold); the second time (a re-read a few microseconds later, from
+    // L2) the warps only log, against that threshold.  The rest of the row does both at once, and the threshold keeps
+    // rising: from the warps' maxima again after more of the row, and from the tail group's exact K-th best of the log.
     const int lane = lane_id(), sw = (tid - 32) >> 5;
-    constexpr int EPV = 16 / sizeof(T);
-    static_assert(A_CH / EPV / A_ST * EPV == 8, "eight elements per thread per stage");
+    static_assert(A_CH / 8 == A_ST, "eight elements per thread per stage");
+    static_assert(A_CH == kHitStage, "the hit lists are grouped by this kernel's stages");
     uint32_t st_slot = 0, st_phase = 0;  // ring position of this warp and the parity it waits for
     uint32_t st_ring[2] = {0, 0};
-    static_assert(A_CH == kHitStage, "the hit lists are grouped by this kernel's stages");
-    uint64_t* ready = pen ? patched : full;  // with penalties a stage is read only after the penalty warp has been over it
+    uint64_t* ready = pen ? patched : full;  // with penalties a stage is read only after a penalty warp has been over it
+    constexpr int M_BOTH = 0, M_ACC = 1, M_LOG = 2;
 #ifdef WB_PHASE_TIMERS
     long long ts_wait = 0, ts_proc = 0, ts_setup = 0, ts_slow = 0, ts_bound = 0;
-    unsigned long long n_early = 0, n_all = 0;
 #endif
     int ord = 0;
     for (int k = next_row(-1); k < my_rows; k = next_row(k), ++ord) {
@@ -721,7 +709,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         const bool greedy = no_sum_row(row);  // no exponentials for this row (greedy, or closed by its top_k)
         const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
         const float cexp = inv_t * kLog2e;
-        // the row's first threshold (and the slot being free again) come from the tail group
+        // the slot (log, threshold, partials) is this row's once the tail group says so
         if (!mbar_wait(&boot_done[p], (ord >> 1) & 1)) {
             if (lane == 0) atomicExch(a.err, 4u);
             return;
@@ -730,18 +718,16 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
 #ifdef WB_PHASE_TIMERS
         ts_setup += clock64() - tsu0;
 #endif
-
-        bool saw_nan = false, st_fail = false;
+        bool st_fail = false;
         unsigned long long tau_seen = 0ull;
         float tau_f = -INFINITY;
         uint32_t* wb_row = wbound + p * A_SW;
-        uint32_t iters = 0;
         const uint32_t rth = (k_of(row) + A_SW - 1) / A_SW;  // each warp's share of the K candidates
-        // NS consecutive stages at once (more independent work per warp, fixed costs paid once); PARTIAL: the last of them is
-        // the row's final, shorter stage (vectors past the row's end read as -inf).
-        auto stage = [&](uint32_t c, auto ns_tag, auto partial) {
+
+        // NS consecutive stages at once (more independent work per warp, fixed costs paid once)
+        auto stage = [&](uint32_t c, auto ns_tag, auto mode_tag) {
             constexpr int NS = decltype(ns_tag)::value;
-            constexpr bool PARTIAL = decltype(partial)::value;
+            constexpr int MODE = decltype(mode_tag)::value;
             constexpr int NE = 8 * NS;   // elements per thread
             constexpr int NQ = 2 * NS;   // quads of 4 consecutive elements
 #ifdef WB_PHASE_TIMERS
@@ -750,9 +736,9 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             float xv[NE];
             uint32_t qid[NQ];
             bool qv[NQ];
-            {
+            if (MODE != M_ACC) {
                 const unsigned long long t = ld_volatile_u64(&sl->tau);
-                if (t != tau_seen) tau_seen = t, tau_f = float_of_key(cand_key(t));
+                if (t > tau_seen) tau_seen = t, tau_f = float_of_key(cand_key(t));
             }
             const unsigned long long tau = tau_seen;
 #pragma unroll
@@ -763,20 +749,20 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                     return;
                 }
                 const uint4* vec = reinterpret_cast<const uint4*>(ring + size_t(st_slot) * ch_bytes);
-                const bool part = PARTIAL && h == NS - 1;
                 float* x = xv + 8 * h;
+                const int st_tid = tid - 32;
                 if (sizeof(T) == 4) {
-                    qid[2 * h] = (c + h) * A_CH + 4 * g.tid, qid[2 * h + 1] = qid[2 * h] + 4 * A_ST;
-                    qv[2 * h] = !part || qid[2 * h] < n, qv[2 * h + 1] = !part || qid[2 * h + 1] < n;
+                    qid[2 * h] = (c + h) * A_CH + 4 * st_tid, qid[2 * h + 1] = qid[2 * h] + 4 * A_ST;
+                    qv[2 * h] = qid[2 * h] < n, qv[2 * h + 1] = qid[2 * h + 1] < n;  // (only the row's last stage can be short)
                     const uint4 ninf = make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u);
-                    const uint4 q0 = qv[2 * h] ? vec[g.tid] : ninf;
-                    const uint4 q1 = qv[2 * h + 1] ? vec[g.tid + A_ST] : ninf;
+                    const uint4 q0 = qv[2 * h] ? vec[st_tid] : ninf;
+                    const uint4 q1 = qv[2 * h + 1] ? vec[st_tid + A_ST] : ninf;
                     x[0] = __uint_as_float(q0.x), x[1] = __uint_as_float(q0.y), x[2] = __uint_as_float(q0.z), x[3] = __uint_as_float(q0.w);
                     x[4] = __uint_as_float(q1.x), x[5] = __uint_as_float(q1.y), x[6] = __uint_as_float(q1.z), x[7] = __uint_as_float(q1.w);
                 } else {
-                    qid[2 * h] = (c + h) * A_CH + 8 * g.tid, qid[2 * h + 1] = qid[2 * h] + 4;
-                    qv[2 * h] = qv[2 * h + 1] = !part || qid[2 * h] < n;
-                    const uint4 q = qv[2 * h] ? vec[g.tid] : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
+                    qid[2 * h] = (c + h) * A_CH + 8 * st_tid, qid[2 * h + 1] = qid[2 * h] + 4;
+                    qv[2 * h] = qv[2 * h + 1] = qid[2 * h] < n;
+                    const uint4 q = qv[2 * h] ? vec[st_tid] : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
                     x[0] = __uint_as_float(q.x << 16), x[1] = __uint_as_float(q.x & 0xffff0000u);
                     x[2] = __uint_as_float(q.y << 16), x[3] = __uint_as_float(q.y & 0xffff0000u);
                     x[4] = __uint_as_float(q.z << 16), x[5] = __uint_as_float(q.z & 0xffff0000u);
@@ -803,27 +789,29 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             float vm = qm[0];
 #pragma unroll
             for (int q = 1; q < NQ; ++q) vm = fmaxf(vm, qm[q]);
-            if (!greedy) {
-                if (vm > m_t) {
-                    // new reference exponent: an integer at or above m * cexp, so every term is at most 1 and x * cexp - e
-                    // is one fused operation with a single rounding
-                    const float ne = ceilf(vm * cexp);
-                    s_t = (m_t == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
-                    e_t = ne, m_t = vm;
-                }
-                if (m_t != -INFINITY) {
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            if (MODE != M_LOG) {
+                if (!greedy) {
+                    if (vm > m_t) {
+                        // new reference exponent: an integer at or above m * cexp, so every term is at most 1 and
+                        // x * cexp - e is one fused operation with a single rounding
+                        const float ne = ceilf(vm * cexp);
+                        s_t = (m_t == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
+                        e_t = ne, m_t = vm;
+                    }
+                    if (m_t != -INFINITY) {
+                        float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-                    for (int j = 0; j < NE; ++j) acc[j & 3] += ex2_approx(fmaf(xv[j], cexp, -e_t));
-                    s_t += (acc[0] + acc[1]) + (acc[2] + acc[3]);
+                        for (int j = 0; j < NE; ++j) acc[j & 3] += ex2_approx(fmaf(xv[j], cexp, -e_t));
+                        s_t += (acc[0] + acc[1]) + (acc[2] + acc[3]);
+                    }
+                } else {
+                    m_t = fmaxf(m_t, vm);
                 }
-            } else {
-                m_t = fmaxf(m_t, vm);
             }
 #ifdef WB_PHASE_TIMERS
             const long long tsl0 = clock64();
 #endif
-            if (vm >= tau_f) {
+            if (MODE != M_ACC && vm >= tau_f) {
                 // rare: this lane holds an element that may beat the threshold
 #pragma unroll
                 for (int q = 0; q < NQ; ++q) {
@@ -836,10 +824,6 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                                 if (cnd > tau) {
                                     const uint32_t pos = atomicAdd(&sl->cnt, 1u);
                                     if (pos < uint32_t(A_L)) log[pos] = cnd;
-#ifdef WB_PHASE_TIMERS
-                                    ++n_all;
-                                    if (c < 8) ++n_early;
-#endif
                                 }
                             }
                         }
@@ -847,61 +831,82 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 }
             }
 #ifdef WB_PHASE_TIMERS
-            __syncwarp();
             const long long tsl1 = clock64();
             ts_slow += tsl1 - tsl0;
+            ts_proc += tsl1 - tw1;
 #endif
-            // A threshold from the running maxima, with no help from the tail group: if every stream warp names the r-th
-            // largest of its 32 lane maxima, r = ceil(K / 16), then 16 r >= K distinct elements of the row are at or above the
-            // smallest of those 16 values.  Maxima settle fast, so this runs after 1, 2, 4, 8 ... iterations of a row.
-#ifndef WB_NO_WBOUND
-            ++iters;
-            if ((iters & (iters - 1)) == 0) {
-                // the warp's rth largest lane maximum: take the largest away rth - 1 times
-                float v = m_t, rmax = -INFINITY;
-                for (uint32_t i = 0; i < rth; ++i) {
-                    rmax = warp_max(v);
-                    const uint32_t holders = __ballot_sync(0xffffffffu, v == rmax);
-                    if (holders == 0) break;  // only NaN-free maxima exist; an all -inf warp ends here too
-                    if (lane == __ffs(holders) - 1) v = -INFINITY;
-                    if (rmax == -INFINITY) break;
-                }
-                if (lane == 0) wb_row[sw] = key_of(rmax);
+        };
+        // this warp's bound: the rth largest of its lane maxima (the largest is taken away rth - 1 times; keys are
+        // order-preserving, 0 is below every logit)
+        auto own_bound = [&]() -> uint32_t {
+            uint32_t kv = key_of(m_t), kr = 0;
+            for (uint32_t i = 0; i < rth; ++i) {
+                kr = __reduce_max_sync(0xffffffffu, kv);
+                if (kr == 0) break;
+                const uint32_t holders = __ballot_sync(0xffffffffu, kv == kr);
+                if (lane == __ffs(holders) - 1) kv = 0;
+            }
+            return kr;
+        };
+        auto run = [&](uint32_t c0, uint32_t c1, auto mode_tag) {
+            using one = std::integral_constant<int, 1>;
+            using two = std::integral_constant<int, 2>;
+            uint32_t c = c0;
+            for (; c + 2 <= c1 && !st_fail; c += 2) stage(c, two{}, mode_tag);
+            if (c < c1 && !st_fail) stage(c, one{}, mode_tag);
+        };
+        // ---- the head of the row: accumulate, agree on the first threshold, then log
+        run(0, s0, std::integral_constant<int, M_ACC>{});
+        if (st_fail) return;
+        {
+#ifdef WB_PHASE_TIMERS
+            const long long tb0 = clock64();
+#endif
+            const uint32_t kr = own_bound();
+            if (lane == 0) {
+                wb_row[sw] = kr;
+                mbar_arrive(&head_done[p]);
+            }
+            if (!mbar_wait(&head_done[p], (ord >> 1) & 1)) {
+                if (lane == 0) atomicExch(a.err, 11u);
+                return;
+            }
+            const uint32_t kmin = __reduce_min_sync(0xffffffffu, lane < A_SW ? ld_volatile_u32(&wb_row[lane]) : 0xffffffffu);
+            tau_seen = (unsigned long long)kmin << 32, tau_f = float_of_key(kmin);
+            if (sw == 0 && lane == 0 && tau_seen > ld_volatile_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = tau_seen;
+#ifdef WB_PHASE_TIMERS
+            ts_bound += clock64() - tb0;
+#endif
+        }
+        run(0, s0, std::integral_constant<int, M_LOG>{});
+        // ---- the rest of the row, with a fresh bound from the maxima each time the row seen so far has grown by half
+        for (uint32_t c0 = s0, nb = s0 + (s0 + 1) / 2; c0 < n_chunks && !st_fail;) {
+            const uint32_t c1 = nb < n_chunks ? ((nb + 1) & ~1u) < n_chunks ? ((nb + 1) & ~1u) : n_chunks : n_chunks;
+            run(c0, c1, std::integral_constant<int, M_BOTH>{});
+            c0 = c1;
+            if (c0 < n_chunks && !st_fail) {
+#ifdef WB_PHASE_TIMERS
+                const long long tb0 = clock64();
+#endif
+                // (the other warps' entries may be older: any of their bounds for this row is valid)
+                const uint32_t kr = own_bound();
+                if (lane == 0) wb_row[sw] = kr;
                 __syncwarp();
-                uint32_t kmin = lane < A_SW ? ld_volatile_u32(&wb_row[lane]) : 0xffffffffu;
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) kmin = min(kmin, __shfl_xor_sync(0xffffffffu, kmin, o));
-                // (a plain compare and store: a lost update only leaves the threshold at another valid, lower bound; a 64-bit
-                // atomic max in shared memory is a contended compare-and-swap loop when 16 warps get here together)
+                const uint32_t kmin = __reduce_min_sync(0xffffffffu, lane < A_SW ? ld_volatile_u32(&wb_row[lane]) : 0xffffffffu);
+                // (a plain compare and store: a lost update only leaves the threshold at another valid, lower bound)
                 if (lane == 0) {
                     const unsigned long long cand = (unsigned long long)kmin << 32;
                     if (cand > ld_volatile_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = cand;
                 }
-            }
-#endif
 #ifdef WB_PHASE_TIMERS
-            __syncwarp();
-            ts_bound += clock64() - tsl1;
-            ts_proc += clock64() - tw1;
+                ts_bound += clock64() - tb0;
 #endif
-        };
-        const uint32_t full_chunks = n / A_CH;
-        {
-            using one = std::integral_constant<int, 1>;
-            using two = std::integral_constant<int, 2>;
-            uint32_t c = 0;
-            for (; c + 2 <= full_chunks && !st_fail; c += 2) stage(c, two{}, std::false_type{});
-            if (!st_fail && c < full_chunks) {
-                // one full stage left, maybe followed by the partial one
-                if (full_chunks < n_chunks) stage(c, two{}, std::true_type{});
-                else stage(c, one{}, std::false_type{});
-            } else if (!st_fail && full_chunks < n_chunks) {
-                stage(c, one{}, std::true_type{});
             }
+            nb = c0 + (c0 + 1) / 2;
         }
         if (st_fail) return;
         // a NaN logit poisons the f32 sum: such rows are redone by the multi-pass kernel, which counts NaN as -inf
-        saw_nan = !greedy && (s_t != s_t);
+        const bool saw_nan = !greedy && (s_t != s_t);
         if (__any_sync(0xffffffffu, saw_nan) && lane == 0) atomicOr(&sl->cnt, 0x80000000u);
         // ---- the row is through for this warp: partials, then close
         {
@@ -917,28 +922,25 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         if (lane == 0) mbar_arrive(&closed[p]);
     }
 #ifdef WB_PHASE_TIMERS
-    if (g.tid == 0) {
+    if (tid == 32) {
         unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 4);
         atomicAdd(&dbg[4], (unsigned long long)ts_wait), atomicAdd(&dbg[5], (unsigned long long)ts_proc), atomicAdd(&dbg[6], (unsigned long long)ts_setup);
         atomicAdd(&dbg[12], (unsigned long long)ts_slow), atomicAdd(&dbg[13], (unsigned long long)ts_bound);
     }
-    atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 4) + 14, n_early), atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 4) + 15, n_all);
 #endif
 }
 
-static size_t async_fixed_smem(bool pen, size_t boot_bytes) {
-    (void)pen;
-    return boot_bytes + size_t(2) * A_SW * 4 + size_t(2) * A_L * 8 + SEL_BINS * 4 + size_t(2) * kAsyncMaxK * 8 + 2 * (kAsyncMaxK + 2 * A_TW) * 8 +
-           (3 * A_MAXSTAGES + 12) * 8 + sizeof(AShared) + 128;
+static size_t async_fixed_smem() {
+    return size_t(2) * A_SW * 4 + size_t(2) * A_L * 8 + SEL_BINS * 4 + size_t(2) * kAsyncMaxK * 8 + 2 * (kAsyncMaxK + 2 * A_TW) * 8 +
+           (3 * A_MAXSTAGES + 14) * 8 + sizeof(AShared) + 128;
 }
 
 bool sample_async_supported(const SelectArgs& a, int dtype) {
     const size_t es = dtype == 0 ? 4 : 2;
     if (reinterpret_cast<uintptr_t>(a.x) % 16 != 0 || (size_t(a.n) * es) % 16 != 0) return false;  // bulk copies need 16-byte rows
     if (a.mode == MODE_TOPK && a.K > kAsyncMaxK) return false;
-    const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
     const int ch_bytes = int(A_CH * es);
-    return async_fixed_smem(pen, size_t(A_CH) * es) + 3 * size_t(ch_bytes) <= 232448;
+    return async_fixed_smem() + 3 * size_t(ch_bytes) <= 232448;
 }
 
 // (with penalties: a.prm.hit_list / hit_start must have been filled by history_lists_launch on the same stream)
@@ -947,8 +949,7 @@ cudaError_t sample_async_launch(const SelectArgs& a, int dtype, int sm_count, cu
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
     if (pen && (!a.prm.hit_list || !a.prm.hit_start)) return cudaErrorInvalidValue;
     const int ch_bytes = int(A_CH * es);
-    const int boot_elems = A_CH;
-    const size_t fixed = async_fixed_smem(pen, size_t(boot_elems) * es);
+    const size_t fixed = async_fixed_smem();
     int stages = int((232448 - fixed) / ch_bytes);
     if (stages > A_MAXSTAGES) stages = A_MAXSTAGES;
     if (stages < 3) return cudaErrorInvalidConfiguration;
@@ -959,11 +960,11 @@ cudaError_t sample_async_launch(const SelectArgs& a, int dtype, int sm_count, cu
     if (dtype == 0) {
         const cudaError_t e = cudaFuncSetAttribute(sample_async_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        sample_async_kernel<float><<<grid, A_THREADS, smem, st>>>(a, stages, pen ? 1 : 0, ch_bytes, boot_elems);
+        sample_async_kernel<float><<<grid, A_THREADS, smem, st>>>(a, stages, pen ? 1 : 0, ch_bytes);
     } else {
         const cudaError_t e = cudaFuncSetAttribute(sample_async_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        sample_async_kernel<uint16_t><<<grid, A_THREADS, smem, st>>>(a, stages, pen ? 1 : 0, ch_bytes, boot_elems);
+        sample_async_kernel<uint16_t><<<grid, A_THREADS, smem, st>>>(a, stages, pen ? 1 : 0, ch_bytes);
     }
     return cudaGetLastError();
 }
