@@ -64,10 +64,9 @@ Ws ws_layout(int rows) {
     o = align_up(o + size_t(rows) * 4, 256);
     w.off_list2 = o;
     o = align_up(o + size_t(rows) * 4, 256);
-    w.off_count = o;
-    o = align_up(o + 16, 256);
-    w.off_err = o;
-    o = align_up(o + 16, 256);
+    w.off_err = o;  // four error words, then four count / ticket words (cleared together), then the profiling build's timers
+    w.off_count = o + 16;
+    o = align_up(o + 512, 256);
     w.off_p = o;
     o = align_up(o + wb::select_generic_ws_bytes(std::min(rows, 2 * kSmBound), wb::kGenericMaxK), 256);
     w.off_hits = o;  // the rows' hit lists (penalties of the single-pass sampler): lists, then starts
@@ -298,19 +297,22 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
             bump(LC_AUX);
             if (e != cudaSuccess) return fail_cuda(e, "sample_rows history lists");
         }
-        // small-K rows in one pass; rows with top_k in (256, 1024] are marked for the large-K single-pass kernel
+        // Rows keeping at most 256 candidates in one pass.  The kernel's last CTA lists what is left for the multi-pass
+        // kernel below: rows with top_k above 256, rows whose kept set may reach past 256 candidates (second level, up to
+        // 16384: k_big, src/server/engine_sampling.h:21), and rows to redo (candidate log overflow, NaN, open-set walk).
+        a.fin_list = list_b, a.fin_counts = counts;
         e = wb::sample_async_launch(a, dtype, sm_count(), st);
         bump(LC_STREAM);
-        if (e != cudaSuccess) return fail_cuda(e, "sample_rows small-K kernel");
-        gather_two_kernel<<<1, 1024, 0, st>>>(a.out.status, rows, list_a, list_b, counts);
-        bump(LC_AUX);
-        if (prm->top_k && wb::sample_stream_supported(a, dtype)) {
-            wb::SelectArgs c = a;
-            c.row_list = list_a, c.row_count = counts;
-            e = wb::sample_stream_launch(c, dtype, sm_count(), st);
-            bump(LC_STREAM);
-            if (e != cudaSuccess) return fail_cuda(e, "sample_rows large-K kernel");
-        }
+        if (e != cudaSuccess) return fail_cuda(e, "sample_rows single-pass kernel");
+        wb::SelectArgs b = a;
+        b.level_k = wb::kGenericMaxK, b.row_list = list_b, b.row_count = counts + 1;
+        b.out.counters = nullptr;  // (counters[0] and [1] were counted by the first kernel)
+        b.unresolved = out->counters ? out->counters + WHIRL_CNT_UNRESOLVED : nullptr;
+        e = wb::select_generic_launch(b, dtype, sm_count(), st);
+        bump(LC_GENERIC);
+        if (e != cudaSuccess) return fail_cuda(e, "sample_rows multi-pass kernel");
+        e = cudaGetLastError();
+        return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "sample_rows");
     } else {
         e = wb::select_generic_launch(a, dtype, sm_count(), st);
         bump(LC_GENERIC);

@@ -119,6 +119,12 @@ struct SelectArgs {
     int32_t id_offset;        // MODE_TOPK: added to every id written (a vocabulary slice's first token id)
     uint32_t* err;            // device error word (bounded waits that ran out)
     int only_large_k;         // large-K kernel: 0 = every row, 1 = only rows whose top_k is above kAsyncMaxK
+    // single-pass sampler, MODE_SAMPLE: its last CTA lists the rows it left to the multi-pass kernel in fin_list (rows with
+    // top_k above its limit, and rows whose kept set may reach past 256 candidates; with bit 30: rows to redo at the first
+    // level) and their number in fin_counts[1].  fin_counts[2] and [3] are the two kernels' tickets (zero before a launch).
+    int32_t* fin_list;
+    int32_t* fin_counts;
+    uint32_t* unresolved;     // multi-pass kernel: its last CTA adds the batch's rows still without an answer here (or null)
 };
 
 constexpr int kGenericMaxK = 16384;

@@ -68,6 +68,40 @@ __device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned lon
 }
 __device__ __forceinline__ uint32_t ld_volatile_u32(const uint32_t* p) { return *reinterpret_cast<const volatile uint32_t*>(p); }
 
+// Called by one warp of every CTA once all the CTA's rows have their status.  The CTA that gets here last lists the rows
+// the multi-pass kernel has to take (a.fin_list, a.fin_counts[1]; bit 30: redo at the first level), so that no helper
+// launch is needed between the two kernels.  a.fin_counts[2] is the ticket (zero before the launch, zero again after).
+__device__ void list_leftovers(const SelectArgs& a) {
+    const int lane = lane_id();
+    __threadfence();
+    uint32_t last = 0;
+    if (lane == 0) last = atomicAdd(reinterpret_cast<unsigned int*>(a.fin_counts + 2), 1u) == gridDim.x - 1 ? 1u : 0u;
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (!last) return;
+    __threadfence();
+    const int32_t* status = a.out.status;
+    int cnt = 0;
+    for (int base = 0; base < a.rows; base += 256) {
+        int st8[8];  // (eight loads on their way at once: this is the last thing the kernel does)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int r = base + 32 * j + lane;
+            st8[j] = r < a.rows ? __ldcg(status + r) : int(ROW_DONE);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int r = base + 32 * j + lane;
+            const int st = st8[j];
+            const bool redo = st == ROW_RETRY || st == ROW_OPEN_TAIL;
+            const bool take = redo || st == ROW_LARGE_K || st == ROW_ESCALATE;
+            const uint32_t bal = __ballot_sync(0xffffffffu, take);
+            if (take) a.fin_list[cnt + __popc(bal & ((1u << lane) - 1))] = r | (redo ? (1 << 30) : 0);
+            cnt += __popc(bal);
+        }
+    }
+    if (lane == 0) a.fin_counts[1] = cnt, a.fin_counts[2] = 0;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a, int stages, int pen, int ch_bytes) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -121,6 +155,11 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     if (my_rows == 0 || next_row(-1) >= my_rows) {
         if (tid < my_rows && a.out.status && a.mode == MODE_SAMPLE)
             for (int k = tid; k < my_rows; k += A_THREADS) a.out.status[row_of(k)] = ROW_LARGE_K;
+        if (a.fin_list) {
+            __threadfence();
+            __syncthreads();
+            if (warp == 0) list_leftovers(a);
+        }
         return;
     }
 
@@ -130,6 +169,9 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         uint32_t it = 0;
 #ifdef WB_PHASE_TIMERS
         long long tp_wait = 0;
+#endif
+#ifdef WB_STAGGER
+        for (uint32_t d = 0; d < (blockIdx.x & 7u) * WB_STAGGER; ++d) __nanosleep(1000);
 #endif
         for (int k = next_row(-1); k < my_rows; k = next_row(k)) {
             const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x) + size_t(row_of(k)) * row_bytes;
@@ -155,7 +197,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             }
         }
 #ifdef WB_PHASE_TIMERS
-        atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 4) + 7, (unsigned long long)tp_wait);
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 8) + 7, (unsigned long long)tp_wait);
 #endif
         return;
     }
@@ -441,6 +483,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             __syncwarp();
             if (lane == 0) mbar_arrive(&draw_empty[p]);
         }
+        // Every row of this CTA has its status (the tail group's writes came before its last hand-over).
+        if (a.fin_list) list_leftovers(a);
         return;
     }
 
@@ -658,6 +702,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                     d.row = row, d.kept = kept, d.cap = cap, d.M = M, d.sum = sum, d.presorted = presorted ? 1u : 0u;
                     d.skip = (overflow || greedy) ? 1u : 0u;
                     sh->draw[p] = d;
+                    __threadfence();  // (a status written above is read by another CTA at the end of the kernel)
                     mbar_arrive(&draw_full[p]);  // (after the barrier above: every thread's candidates are written)
                 }
             }
@@ -671,7 +716,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
 #ifdef WB_PHASE_TIMERS
         if (g.tid == 0) {
             tt[3] = clock64() - tt0;
-            unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 4);
+            unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 8);
             for (int i = 0; i < 4; ++i) atomicAdd(&dbg[i], (unsigned long long)tt[i]), atomicAdd(&dbg[8 + i], (unsigned long long)tt[4 + i]);
         }
 #endif
@@ -709,11 +754,6 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         const bool greedy = no_sum_row(row);  // no exponentials for this row (greedy, or closed by its top_k)
         const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
         const float cexp = inv_t * kLog2e;
-        // the slot (log, threshold, partials) is this row's once the tail group says so
-        if (!mbar_wait(&boot_done[p], (ord >> 1) & 1)) {
-            if (lane == 0) atomicExch(a.err, 4u);
-            return;
-        }
         float m_t = -INFINITY, e_t = 0.f, s_t = 0.f;  // running max, reference exponent ceil(m_t * cexp), sum 2^(x * cexp - e_t)
 #ifdef WB_PHASE_TIMERS
         ts_setup += clock64() - tsu0;
@@ -858,6 +898,11 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         // ---- the head of the row: accumulate, agree on the first threshold, then log
         run(0, s0, std::integral_constant<int, M_ACC>{});
         if (st_fail) return;
+        // the slot (log, threshold, bounds, partials) is this row's once the tail group says so: not needed before here
+        if (!mbar_wait(&boot_done[p], (ord >> 1) & 1)) {
+            if (lane == 0) atomicExch(a.err, 4u);
+            return;
+        }
         {
 #ifdef WB_PHASE_TIMERS
             const long long tb0 = clock64();
@@ -923,7 +968,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     }
 #ifdef WB_PHASE_TIMERS
     if (tid == 32) {
-        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 4);
+        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 8);
         atomicAdd(&dbg[4], (unsigned long long)ts_wait), atomicAdd(&dbg[5], (unsigned long long)ts_proc), atomicAdd(&dbg[6], (unsigned long long)ts_setup);
         atomicAdd(&dbg[12], (unsigned long long)ts_slow), atomicAdd(&dbg[13], (unsigned long long)ts_bound);
     }
@@ -955,7 +1000,7 @@ cudaError_t sample_async_launch(const SelectArgs& a, int dtype, int sm_count, cu
     if (stages < 3) return cudaErrorInvalidConfiguration;
     const size_t smem = fixed + size_t(stages) * ch_bytes;
     const int grid = a.rows < sm_count ? a.rows : sm_count;
-    const cudaError_t em = cudaMemsetAsync(a.err, 0, 16, st);
+    const cudaError_t em = cudaMemsetAsync(a.err, 0, 32, st);  // the error words, then the list count and the tickets
     if (em != cudaSuccess) return em;
     if (dtype == 0) {
         const cudaError_t e = cudaFuncSetAttribute(sample_async_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));

@@ -171,6 +171,24 @@ __global__ void __launch_bounds__(GT) select_generic_kernel(SelectArgs a, int ca
         // bit 30 of a list entry: redo the row at the first candidate level (the single-pass kernel gave it up)
         select_row<T>(a, entry & 0x3fffffff, (entry >> 30) & 1 ? min(a.level_k, kAsyncMaxK) : a.level_k, cap_max, pen_words, cand, hist, sh, pen_mem);
     }
+    // the CTA that finishes last counts the rows of the whole batch that are still without an answer
+    if (a.unresolved && a.fin_counts) {
+        __shared__ uint32_t s_last;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            s_last = atomicAdd(reinterpret_cast<unsigned int*>(a.fin_counts + 3), 1u) == gridDim.x - 1 ? 1u : 0u;
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            uint32_t c = 0;
+            for (int r = threadIdx.x; r < a.rows; r += blockDim.x) c += __ldcg(a.out.status + r) != ROW_DONE;
+            c = warp_sum(c);
+            if ((threadIdx.x & 31) == 0 && c) atomicAdd(a.unresolved, c);
+            if (threadIdx.x == 0) a.fin_counts[3] = 0;
+        }
+    }
 }
 
 template <typename T>
