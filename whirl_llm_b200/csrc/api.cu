@@ -51,9 +51,9 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // workspace layout (all offsets 256-byte aligned)
 struct Ws {
-    size_t off_scan, off_status, off_list, off_list2, off_count, off_err, off_p, off_hits, total;
+    size_t off_scan, off_status, off_list, off_list2, off_count, off_err, off_locks, off_p, off_hits, off_full, total;
 };
-Ws ws_layout(int rows) {
+Ws ws_layout(int rows, int n = 0) {
     Ws w;
     size_t o = 0;
     w.off_scan = o;
@@ -64,13 +64,17 @@ Ws ws_layout(int rows) {
     o = align_up(o + size_t(rows) * 4, 256);
     w.off_list2 = o;
     o = align_up(o + size_t(rows) * 4, 256);
-    w.off_err = o;  // four error words, then four count / ticket words (cleared together), then the profiling build's timers
+    w.off_err = o;  // four error words, four count / ticket words, eight scratch-area locks (cleared together: 64 bytes),
+                    // then the profiling build's timers
     w.off_count = o + 16;
+    w.off_locks = o + 32;
     o = align_up(o + 512, 256);
     w.off_p = o;
     o = align_up(o + wb::select_generic_ws_bytes(std::min(rows, 2 * kSmBound), wb::kGenericMaxK), 256);
     w.off_hits = o;  // the rows' hit lists (penalties of the single-pass sampler): lists, then starts
     o = align_up(o + wb::history_lists_ws_bytes(rows), 256);
+    w.off_full = o;  // the third escalation level's scratch areas (the only part that depends on the row length)
+    o = align_up(o + wb::select_full_ws_bytes(n), 256);
     w.total = o;
     return w;
 }
@@ -163,8 +167,7 @@ const char* whirl_last_error(void) { return g_err.c_str(); }
 int whirl_version(void) { return 100; }
 
 size_t whirl_workspace_bytes(int rows, int n) {
-    (void)n;
-    return ws_layout(rows < 1 ? 1 : rows).total;
+    return ws_layout(rows < 1 ? 1 : rows, n).total;
 }
 
 int whirl_argmax(const void* x, int dtype, int n, int* out, int* ids, int* pos, int advance, void* ws, size_t ws_bytes,
@@ -263,7 +266,7 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
                       void* ws, size_t ws_bytes, void* stream) {
     if (!x || !prm || !out || !out->token || rows < 0 || n <= 0 || bad_dtype(dtype)) return fail(WHIRL_ERR_INVALID, "sample_rows: bad pointer / rows / n / dtype");
     if (rows == 0) return WHIRL_OK;
-    const Ws w = ws_layout(rows);
+    const Ws w = ws_layout(rows, n);
     if (!ws || ws_bytes < w.total) return fail(WHIRL_ERR_WORKSPACE, "sample_rows: workspace missing or too small (whirl_workspace_bytes)");
     if (prm->hist) {
         if (!prm->hist_len) return fail(WHIRL_ERR_INVALID, "sample_rows: hist without hist_len");
@@ -308,6 +311,10 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
         b.level_k = wb::kGenericMaxK, b.row_list = list_b, b.row_count = counts + 1;
         b.out.counters = nullptr;  // (counters[0] and [1] were counted by the first kernel)
         b.unresolved = out->counters ? out->counters + WHIRL_CNT_UNRESOLVED : nullptr;
+        if (wb::select_full_ws_bytes(n) != 0) {
+            b.full_ws = base + w.off_full, b.full_locks = reinterpret_cast<uint32_t*>(base + w.off_locks);
+            b.full_slots = wb::kFullSlots, b.full_npad = wb::select_full_npad(n);
+        }
         e = wb::select_generic_launch(b, dtype, sm_count(), st);
         bump(LC_GENERIC);
         if (e != cudaSuccess) return fail_cuda(e, "sample_rows multi-pass kernel");
@@ -325,6 +332,12 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
     wb::SelectArgs b = a;
     b.level_k = wb::kGenericMaxK, b.row_list = list_b, b.row_count = counts + 1;
     b.out.counters = nullptr;  // counters[0] counted the level-1 escalations already
+    if (wb::select_full_ws_bytes(n) != 0) {
+        e = cudaMemsetAsync(base + w.off_locks, 0, 32, st);
+        if (e != cudaSuccess) return fail_cuda(e, "cudaMemsetAsync");
+        b.full_ws = base + w.off_full, b.full_locks = reinterpret_cast<uint32_t*>(base + w.off_locks);
+        b.full_slots = wb::kFullSlots, b.full_npad = wb::select_full_npad(n);
+    }
     e = wb::select_generic_launch(b, dtype, sm_count(), st);
     bump(LC_GENERIC);
     if (e != cudaSuccess) return fail_cuda(e, "sample_rows level 2");

@@ -125,10 +125,19 @@ struct SelectArgs {
     int32_t* fin_list;
     int32_t* fin_counts;
     uint32_t* unresolved;     // multi-pass kernel: its last CTA adds the batch's rows still without an answer here (or null)
+    // multi-pass kernel, third level (the whole row: the reference's last escalation step, src/server/engine_sampling.cpp:79-83):
+    // full_slots scratch areas of 16 * full_npad bytes each in global memory, handed out through full_locks (zero = free)
+    void* full_ws;
+    uint32_t* full_locks;
+    int full_slots;
+    uint32_t full_npad;       // row length rounded up to a power of two
 };
 
 constexpr int kGenericMaxK = 16384;
 size_t select_generic_ws_bytes(int ctas, int K);  // ctas = min(rows, 2 * SMs)
+constexpr int kFullSlots = 4;
+size_t select_full_ws_bytes(int n);               // 0 when the row is too long for the third level (n > 2^20)
+uint32_t select_full_npad(int n);
 cudaError_t select_generic_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
 
 // small-K single-pass kernel (sample_async.cu)

@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             }
         }
 #ifdef WB_PHASE_TIMERS
-        atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 8) + 7, (unsigned long long)tp_wait);
+        atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 16) + 7, (unsigned long long)tp_wait);
 #endif
         return;
     }
@@ -716,7 +716,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
 #ifdef WB_PHASE_TIMERS
         if (g.tid == 0) {
             tt[3] = clock64() - tt0;
-            unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 8);
+            unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 16);
             for (int i = 0; i < 4; ++i) atomicAdd(&dbg[i], (unsigned long long)tt[i]), atomicAdd(&dbg[8 + i], (unsigned long long)tt[4 + i]);
         }
 #endif
@@ -968,7 +968,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     }
 #ifdef WB_PHASE_TIMERS
     if (tid == 32) {
-        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 8);
+        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 16);
         atomicAdd(&dbg[4], (unsigned long long)ts_wait), atomicAdd(&dbg[5], (unsigned long long)ts_proc), atomicAdd(&dbg[6], (unsigned long long)ts_setup);
         atomicAdd(&dbg[12], (unsigned long long)ts_slow), atomicAdd(&dbg[13], (unsigned long long)ts_bound);
     }
@@ -1000,7 +1000,7 @@ cudaError_t sample_async_launch(const SelectArgs& a, int dtype, int sm_count, cu
     if (stages < 3) return cudaErrorInvalidConfiguration;
     const size_t smem = fixed + size_t(stages) * ch_bytes;
     const int grid = a.rows < sm_count ? a.rows : sm_count;
-    const cudaError_t em = cudaMemsetAsync(a.err, 0, 32, st);  // the error words, then the list count and the tickets
+    const cudaError_t em = cudaMemsetAsync(a.err, 0, 64, st);  // the error words, the list count and tickets, the scratch locks
     if (em != cudaSuccess) return em;
     if (dtype == 0) {
         const cudaError_t e = cudaFuncSetAttribute(sample_async_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));

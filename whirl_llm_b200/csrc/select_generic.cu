@@ -79,8 +79,14 @@ __device__ void pick_bin(uint32_t* hist, GShared* sh, int shift, int bits) {
 }
 
 template <typename T>
-__device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_max, int pen_words, uint64_t* cand,
-                           uint32_t* hist, GShared* sh, uint32_t* pen_mem);
+__device__ void full_row(const SelectArgs& a, int row, int cap_max, int pen_words, uint64_t* tile, GShared* sh, uint32_t* pen_mem,
+                         uint64_t* fc, double* fp);
+template <typename T>
+__device__ int select_row(const SelectArgs& a, int row, int level_k, int cap_max, int pen_words, uint64_t* cand,
+                          uint32_t* hist, GShared* sh, uint32_t* pen_mem);
+template <typename T>
+__device__ void full_row(const SelectArgs& a, int row, int cap_max, int pen_words, uint64_t* tile, GShared* sh,
+                         uint32_t* pen_mem, uint64_t* fc, double* fp);
 
 // The serial tail of draft_sample_rows (kernels/spec_sample.hip:132-205), by one thread on at most 32 candidates: map the
 // ids, sort by (logit desc, id asc), q = softmax at the request temperature over the candidates in f32 (same operation
@@ -169,7 +175,41 @@ __global__ void __launch_bounds__(GT) select_generic_kernel(SelectArgs a, int ca
         __syncthreads();  // the previous row's shared state is dead
         const int entry = a.row_list ? a.row_list[li] : li;
         // bit 30 of a list entry: redo the row at the first candidate level (the single-pass kernel gave it up)
-        select_row<T>(a, entry & 0x3fffffff, (entry >> 30) & 1 ? min(a.level_k, kAsyncMaxK) : a.level_k, cap_max, pen_words, cand, hist, sh, pen_mem);
+        const int row = entry & 0x3fffffff;
+        const int level = (entry >> 30) & 1 ? min(a.level_k, kAsyncMaxK) : a.level_k;
+        const int st = select_row<T>(a, row, level, cap_max, pen_words, cand, hist, sh, pen_mem);
+        // Third level: the kept set may reach past 16384 candidates, so the whole row is sorted (the reference's last
+        // escalation step, src/server/engine_sampling.cpp:79-83, filterCands with complete = true).  That needs 16 bytes
+        // per logit of global scratch: a few areas are shared by the CTAs through locks, and the wait for one is bounded
+        // (a row that gets none stays reported as not answered).
+        if (st == ROW_ESCALATE && level == kGenericMaxK && a.full_ws && a.mode == MODE_SAMPLE) {
+            __shared__ int s_slot;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                s_slot = -1;
+                for (uint32_t spin = 0; spin < (1u << 20) && s_slot < 0; ++spin) {
+                    for (int q = 0; q < a.full_slots; ++q)
+                        if (atomicCAS(&a.full_locks[q], 0u, 1u) == 0u) {
+                            s_slot = q;
+                            break;
+                        }
+                    if (s_slot < 0) __nanosleep(2000);
+                }
+                __threadfence();
+            }
+            __syncthreads();
+            const int slot = s_slot;
+            if (slot >= 0) {
+                uint64_t* fc = reinterpret_cast<uint64_t*>(static_cast<uint8_t*>(a.full_ws) + size_t(slot) * 16 * a.full_npad);
+                double* fp = reinterpret_cast<double*>(fc + a.full_npad);
+                full_row<T>(a, row, cap_max, pen_words, cand, sh, pen_mem, fc, fp);
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    __threadfence();
+                    atomicExch(&a.full_locks[slot], 0u);
+                }
+            }
+        }
     }
     // the CTA that finishes last counts the rows of the whole batch that are still without an answer
     if (a.unresolved && a.fin_counts) {
@@ -191,9 +231,10 @@ __global__ void __launch_bounds__(GT) select_generic_kernel(SelectArgs a, int ca
     }
 }
 
+// returns the row's status (ROW_DONE for the modes that have none)
 template <typename T>
-__device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_max, int pen_words, uint64_t* cand,
-                           uint32_t* hist, GShared* sh, uint32_t* pen_mem) {
+__device__ int select_row(const SelectArgs& a, int row, int level_k, int cap_max, int pen_words, uint64_t* cand,
+                          uint32_t* hist, GShared* sh, uint32_t* pen_mem) {
     const uint32_t n = uint32_t(a.n);
     const T* x = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
     const int tid = threadIdx.x;
@@ -202,9 +243,9 @@ __device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_ma
     if (draft) {
         // kernels/spec_sample.hip:42-45: rows that do not sample keep their greedy draft; a chain stopped by the p-min
         // cut-off at or before r is skipped
-        if (a.draft.on[row] == 0) return;
+        if (a.draft.on[row] == 0) return ROW_DONE;
         const int32_t* c = a.draft.ctl_all + a.draft.area[row];
-        if (c[49] != 0 && c[48] <= a.draft.r) return;
+        if (c[49] != 0 && c[48] <= a.draft.r) return ROW_DONE;
     }
     const RowParams& P = a.prm;
     const float inv_t = draft ? a.draft.inv_t[row] : (P.inv_t ? P.inv_t[row] : P.inv_t_scalar);
@@ -255,7 +296,7 @@ __device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_ma
                 if (a.out.kept_p && a.out.kept_cap > 0) a.out.kept_p[size_t(row) * a.out.kept_cap] = 1.0;
             }
         }
-        return;
+        return ROW_DONE;
     }
 
     // ---- candidates wanted for this row
@@ -348,7 +389,7 @@ __device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_ma
     const Group<GT> g{tid, 0};
     if (draft) {
         if (tid == 0) draft_tail(a, row, reinterpret_cast<const unsigned long long*>(cand), K, sh->m, sh->sum, inv_t);
-        return;
+        return ROW_DONE;
     }
     if (!sample) {
         sort_desc<GT>(g, cand, cap);
@@ -361,7 +402,7 @@ __device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_ma
             a.stats[2 * row] = sh->m, a.stats[2 * row + 1] = sh->sum;
             if (a.out.status) a.out.status[row] = ROW_DONE;
         }
-        return;
+        return ROW_DONE;
     }
     // ---- filter and draw
     TailIn in;
@@ -452,6 +493,225 @@ __device__ void select_row(const SelectArgs& a, int row, int level_k, int cap_ma
             if (a.out.kept_p) a.out.kept_p[size_t(row) * a.out.kept_cap + j] = p[j];
         }
     }
+    return int(r.status);
+}
+
+// ---- third level: the whole row ---------------------------------------------------------------------------------
+// fc[0 .. npad): every logit of the row as a candidate (penalties applied; NaN ranks below everything and gets p = 0),
+// padded with zeros to a power of two and sorted (logit desc, id asc) by a bitonic network: exchanges at a distance of a
+// tile or more run on global memory (L2), the rest on one tile at a time in shared memory.  fp[i]: the probability of
+// fc[i].  Then the steps of filterCands with complete = true (src/sampling/sampler.cpp:15-78: exact maximum, fp64
+// normaliser cast to fp32, top-k, top-p against the kept mass, min-p, renormalise; the set is closed) and the draw
+// (sampleRow :118-131 / sampleRace :94-106).  Sums that the host accumulates one by one are accumulated here per thread
+// over a contiguous run and combined in order, so they differ from the host's in the last bits only.
+__device__ __forceinline__ void cmp_swap_desc(uint64_t& lo, uint64_t& hi, bool up) {
+    // `up` half of the network keeps the larger element first (the final order is descending)
+    if (up ? lo < hi : lo > hi) {
+        const uint64_t t = lo;
+        lo = hi, hi = t;
+    }
+}
+
+// sum of v[i] / z over i < count (combined in index order); every thread returns the total
+__device__ double block_sum_over(const double* v, uint32_t count, double z, GShared* sh) {
+    const int tid = threadIdx.x;
+    const uint32_t S = (count + GT - 1) / GT, b0 = min(count, uint32_t(tid) * S), b1 = min(count, b0 + S);
+    double loc = 0;
+    for (uint32_t i = b0; i < b1; ++i) loc += v[i] / z;
+    double incl = loc;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane_id() >= o) incl += up;
+    }
+    __syncthreads();
+    if (lane_id() == 31) sh->red_s[tid >> 5] = incl;
+    __syncthreads();
+    double tot = 0;
+    for (int w = 0; w < GT / 32; ++w) tot += sh->red_s[w];
+    return tot;
+}
+
+// smallest j < count with cum_j >= t (STRICT: > t), cum_j = sum of v[i] / z over i <= j; count when there is none
+template <bool STRICT>
+__device__ uint32_t block_first_reach(const double* v, uint32_t count, double z, double t, GShared* sh) {
+    const int tid = threadIdx.x;
+    const uint32_t S = (count + GT - 1) / GT, b0 = min(count, uint32_t(tid) * S), b1 = min(count, b0 + S);
+    double loc = 0;
+    for (uint32_t i = b0; i < b1; ++i) loc += v[i] / z;
+    double incl = loc;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane_id() >= o) incl += up;
+    }
+    __syncthreads();
+    if (lane_id() == 31) sh->red_s[tid >> 5] = incl;
+    if (tid == 0) sh->cnt = count;
+    __syncthreads();
+    double cum = incl - loc;
+    for (int w = 0; w < (tid >> 5); ++w) cum += sh->red_s[w];
+    for (uint32_t i = b0; i < b1; ++i) {
+        cum += v[i] / z;
+        if (STRICT ? cum > t : cum >= t) {
+            atomicMin(&sh->cnt, i);
+            break;
+        }
+    }
+    __syncthreads();
+    const uint32_t r = sh->cnt;
+    __syncthreads();
+    return r;
+}
+
+template <typename T>
+__device__ void full_row(const SelectArgs& a, int row, int cap_max, int pen_words, uint64_t* tile, GShared* sh, uint32_t* pen_mem,
+                         uint64_t* fc, double* fp) {
+    const uint32_t n = uint32_t(a.n), npad = a.full_npad;
+    const T* x = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
+    const int tid = threadIdx.x;
+    const RowParams& P = a.prm;
+    const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
+    // the penalty table built for the row by select_row is still in shared memory
+    PenaltyTable pt;
+    pt.on = false;
+    if (P.hist && P.hist_len && P.hist_len[row] > 0) {
+        pt.rep = P.rep ? P.rep[row] : 1.f, pt.pres = P.pres ? P.pres[row] : 0.f, pt.freq = P.freq ? P.freq[row] : 0.f;
+        pt.on = pt.rep != 1.f || pt.pres != 0.f || pt.freq != 0.f;
+    }
+    pt.bitmap = pen_mem, pt.slots = pen_mem + pen_words;
+
+    for (uint32_t i = tid; i < npad; i += GT) fc[i] = i < n ? make_cand(key_of(elem(x, i, pt)), i) : 0ull;
+    __syncthreads();
+    // ---- sort
+    const uint32_t TS = uint32_t(cap_max) < npad ? uint32_t(cap_max) : npad;  // tile (a power of two, as npad is)
+    // all exchanges of the stages k_lo .. k_hi at distances below the tile size, tile by tile
+    auto tiles = [&](uint32_t k_lo, uint32_t k_hi) {
+        for (uint32_t base = 0; base < npad; base += TS) {
+            for (uint32_t i = tid; i < TS; i += GT) tile[i] = fc[base + i];
+            __syncthreads();
+            for (uint32_t k = k_lo; k <= k_hi; k <<= 1) {
+                for (uint32_t j = min(k >> 1, TS >> 1); j > 0; j >>= 1) {
+                    for (uint32_t q = tid; q < TS / 2; q += GT) {
+                        const uint32_t t = ((q & ~(j - 1)) << 1) | (q & (j - 1));
+                        cmp_swap_desc(tile[t], tile[t | j], ((base + t) & k) == 0);
+                    }
+                    __syncthreads();
+                }
+            }
+            for (uint32_t i = tid; i < TS; i += GT) fc[base + i] = tile[i];
+            __syncthreads();
+        }
+    };
+    tiles(2, TS);
+    for (uint32_t k = TS << 1; k <= npad && k != 0; k <<= 1) {
+        for (uint32_t j = k >> 1; j >= TS; j >>= 1) {
+            for (uint32_t q = tid; q < npad / 2; q += GT) {
+                const uint32_t t = ((q & ~(j - 1)) << 1) | (q & (j - 1));
+                uint64_t lo = fc[t], hi = fc[t | j];
+                const uint64_t lo0 = lo;
+                cmp_swap_desc(lo, hi, (t & k) == 0);
+                if (lo != lo0) fc[t] = lo, fc[t | j] = hi;
+            }
+            __syncthreads();
+        }
+        tiles(k, k);
+    }
+    // ---- probabilities (sampler.cpp:23-34 with complete = true)
+    const float m = float_of_key(cand_key(fc[0]));
+    const double it = double(inv_t);
+    for (uint32_t i = tid; i < n; i += GT) {
+        const uint32_t key = cand_key(fc[i]);
+        fp[i] = key ? exp(double(__fsub_rn(float_of_key(key), m)) * it) : 0.0;
+    }
+    __syncthreads();
+    const float sum = float(block_sum_over(fp, n, 1.0, sh));
+    for (uint32_t i = tid; i < n; i += GT) fp[i] = fp[i] / double(sum);
+    __syncthreads();
+    // ---- top-k, top-p, min-p, renormalise (the set is closed from the start: every logit is a candidate)
+    const uint32_t top_k = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
+    const double top_p = P.top_p ? P.top_p[row] : 1.0, min_p = P.min_p ? P.min_p[row] : 0.0, u = P.u ? P.u[row] : 0.0;
+    uint32_t nk = n;
+    if (top_k > 0 && top_k <= n) nk = top_k;
+    if (top_p < 1.0) {
+        const double z = block_sum_over(fp, nk, 1.0, sh);
+        const uint32_t j = block_first_reach<false>(fp, nk, z, top_p, sh);
+        if (j < nk) nk = j + 1;
+    }
+    if (min_p > 0) {
+        const double thr = min_p * fp[0];
+        if (tid == 0) sh->cnt = nk;
+        __syncthreads();
+        for (uint32_t i = tid; i < nk; i += GT)
+            if (!(fp[i] >= thr)) {
+                atomicMin(&sh->cnt, i);
+                break;  // (later ones of this thread are larger indices)
+            }
+        __syncthreads();
+        const uint32_t j = sh->cnt;
+        __syncthreads();
+        nk = j > 1 ? j : 1;
+    }
+    {
+        const double z = block_sum_over(fp, nk, 1.0, sh);
+        for (uint32_t i = tid; i < nk; i += GT) fp[i] = fp[i] / z;
+        __syncthreads();
+    }
+    // ---- the draw
+    uint32_t token;
+    if (P.race_key != nullptr) {
+        // argmin over the kept candidates of E(id) / p, the first on ties
+        const uint64_t rk = P.race_key[row];
+        double bk = __longlong_as_double(0x7FF0000000000000ll);
+        uint32_t bi = 0xffffffffu;
+        for (uint32_t i = tid; i < nk; i += GT) {
+            if (!(fp[i] > 0)) continue;
+            const double kk = race_e(rk, cand_id(fc[i])) / fp[i];
+            if (kk < bk) bk = kk, bi = i;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const double ok = __shfl_xor_sync(0xffffffffu, bk, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ok < bk || (ok == bk && oi < bi)) bk = ok, bi = oi;
+        }
+        __syncthreads();
+        if (lane_id() == 0) sh->red_s[tid >> 5] = bk, sh->red_c[tid >> 5] = bi;
+        __syncthreads();
+        for (int w = 0; w < GT / 32; ++w) {
+            const double ok = sh->red_s[w];
+            const uint32_t oi = uint32_t(sh->red_c[w]);
+            if (w == 0 || ok < bk || (ok == bk && oi < bi)) bk = ok, bi = oi;
+        }
+        token = cand_id(fc[bi == 0xffffffffu ? 0 : bi]);
+        __syncthreads();
+    } else {
+        const uint32_t j = block_first_reach<true>(fp, nk, 1.0, u, sh);
+        token = cand_id(fc[j < nk ? j : nk - 1]);  // not reached (rounding): the last kept candidate
+    }
+    if (tid == 0) {
+        a.out.token[row] = int32_t(token);
+        a.out.status[row] = ROW_DONE;
+        if (a.out.n_kept) a.out.n_kept[row] = int32_t(nk);
+        if (a.out.closed) a.out.closed[row] = 1;
+        if (a.out.stats) a.out.stats[2 * row] = m, a.out.stats[2 * row + 1] = sum;
+    }
+    const uint32_t ncap = min(nk, uint32_t(max(a.out.kept_cap, 0)));
+    for (uint32_t j = tid; j < ncap; j += GT) {
+        if (a.out.kept_ids) a.out.kept_ids[size_t(row) * a.out.kept_cap + j] = int32_t(cand_id(fc[j]));
+        if (a.out.kept_p) a.out.kept_p[size_t(row) * a.out.kept_cap + j] = fp[j];
+    }
+    __syncthreads();
+}
+
+uint32_t select_full_npad(int n) {
+    uint32_t p = 1;
+    while (p < uint32_t(n)) p <<= 1;
+    return p;
+}
+size_t select_full_ws_bytes(int n) {
+    if (n <= 0 || n > (1 << 20)) return 0;
+    return size_t(kFullSlots) * 16 * select_full_npad(n);
 }
 
 static int pow2_at_least(int k) {
