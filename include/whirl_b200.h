@@ -35,7 +35,8 @@ enum { WHIRL_F32 = 0, WHIRL_BF16 = 1 };
 /* per-row outcome written by whirl_sample_rows */
 enum {
     WHIRL_ROW_DONE = 0,      /* token drawn */
-    WHIRL_ROW_ESCALATE = 1,  /* the kept set may reach past every candidate level this library has (see limits) */
+    WHIRL_ROW_ESCALATE = 1,  /* the kept set may reach past 16384 candidates and the whole-row level could not run (a row of
+                                more than 2^20 logits, or no scratch area came free in time): not answered */
     WHIRL_ROW_OPEN_TAIL = 2  /* open set whose draw fell past the candidates and the row walk is not available */
 };
 
