@@ -50,8 +50,11 @@ __global__ void __launch_bounds__(HL_THREADS) history_lists_kernel(const int32_t
             if (t >= n) continue;  // (negative ids too)
             const uint32_t tag = t + 1;
             uint32_t h = PenaltyTable::hash(t);
+            // (a few tokens make up much of a skewed history: a repeat of a token already in the table is one add whose
+            // result nobody waits for, found with a plain load; only a first sight pays for a compare-and-swap)
             for (int probe = 0; probe < kPenSlots; ++probe) {
-                const uint32_t old = atomicCAS(&table[h], 0u, tag | (1u << kPenIdBits));
+                uint32_t old = *reinterpret_cast<volatile uint32_t*>(&table[h]);
+                if (old == 0) old = atomicCAS(&table[h], 0u, tag | (1u << kPenIdBits));
                 if (old == 0) {
                     atomicAdd(&bounds[1 + t / kHitStage], 1u);
                     break;
@@ -84,13 +87,12 @@ __global__ void __launch_bounds__(HL_THREADS) history_lists_kernel(const int32_t
         for (uint32_t i = tid; i < kPenSlots / 4; i += HL_THREADS) {
             const uint4 q = reinterpret_cast<const uint4*>(table)[i];
             const uint32_t e4[4] = {q.x, q.y, q.z, q.w};
+            uint32_t pos[4];  // (the four places first, then the four stores: the atomics' round trips overlap)
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (e4[u]) {
-                    const uint32_t t = (e4[u] & kPenMaxV) - 1;
-                    list[atomicAdd(&bounds[1 + t / kHitStage], 1u)] = t | (e4[u] & ~kPenMaxV);
-                }
-            }
+            for (int u = 0; u < 4; ++u) pos[u] = e4[u] ? atomicAdd(&bounds[1 + ((e4[u] & kPenMaxV) - 1) / kHitStage], 1u) : 0u;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (e4[u]) list[pos[u]] = ((e4[u] & kPenMaxV) - 1) | (e4[u] & ~kPenMaxV);
         }
         __syncthreads();
         // (the scatter moved every stage's start to its end: bounds[c] is now the start of stage c, and of the list's end)

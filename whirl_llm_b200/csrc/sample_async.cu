@@ -1,16 +1,19 @@
-// The single-pass fused sampler for rows that keep at most 256 candidates: every logits row is read from HBM once and
-// the warps that read it never wait for one another.
+// The single-pass fused sampler for rows that keep at most 256 candidates: every logits row is read from HBM once.
 //
-// One persistent CTA per SM, three roles:
-//   producer (1 warp)   bulk async copies (TMA, cp.async.bulk + mbarrier) of the CTA's rows into a ring of shared
-//                       memory stages, running ahead across row boundaries; it also fetches the first stage of the NEXT
-//                       row into a side buffer, from which the tail group derives that row's first threshold.
-//   stream (16 warps)   consume the stages: penalties from a shared bit map, running max / sum exp for the softmax
-//                       normaliser, and a threshold test; the few elements above the threshold are appended to the
-//                       row's candidate log.  No barrier between stream warps while a row streams.
-//   tail   (4 warps)    concurrently: raise the row's threshold (the K-th largest of the log so far is a valid lower
-//                       bound of the row's K-th largest), bootstrap the next row's threshold, and when a row is through:
-//                       exact K best of its log, sort, top-k / top-p / min-p in f64, the draw, the outputs.
+// One persistent CTA per SM, 24 warps in five roles that never meet at a CTA-wide barrier while rows stream:
+//   producer (1 thread)     bulk async copies (TMA, cp.async.bulk + mbarrier) of the CTA's rows into a ring of shared
+//                           memory stages, running ahead across row boundaries.  The first few stages of a row go
+//                           through the ring twice (the second time they come from L2).
+//   stream (16 warps)       consume the stages: running max / sum exp for the softmax normaliser and a threshold test;
+//                           the few logits above the threshold are appended to the row's candidate log.  The first
+//                           pass over a row's head only accumulates; then the warps agree on a first threshold (their
+//                           one meeting per row); the second pass over the head only logs.
+//   penalty warps (2)       only when histories are given: take the raw logits of a stage's history tokens out before
+//                           the stream warps read it (lists prepared by history_lists_kernel) and put them aside.
+//   tail group (4 warps)    concurrently: raise the row's threshold (the K-th largest of the log so far is a valid
+//                           lower bound of the row's K-th largest), and when a row is through: its exact K best, in order.
+//   draw warp (1)           applies the penalties to the tokens put aside and adds them to the row; then, with the
+//                           row's candidates from the tail group: top-k / top-p / min-p in f64, the draw, the outputs.
 //
 // Why a threshold from partial data is exact: an element is dropped only when it is below a value that at least K
 // elements of the same row reach, so the K best are always in the log; the final select over the log is exact.
@@ -61,6 +64,7 @@ struct AShared {
     SelScratch sel;
     TailOut res;
     uint32_t flag[4];
+    uint32_t pbnd[A_PW][136];  // per penalty warp: the places of the current row's stages in its hit list
 };
 
 __device__ __forceinline__ unsigned long long ld_volatile_u64(const unsigned long long* p) {
@@ -111,7 +115,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     unsigned long long* hand = reinterpret_cast<unsigned long long*>(hist + SEL_BINS);   // 2 * kAsyncMaxK: a row's candidates, per slot
     double* tail_p = reinterpret_cast<double*>(hand + 2 * kAsyncMaxK);                 // 2 * (kAsyncMaxK + 2 * A_TW)
     double* tail_q = tail_p + kAsyncMaxK + 2 * A_TW;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tail_q + kAsyncMaxK + 2 * A_TW);  // 2 * 16 + 8
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail_q + kAsyncMaxK + 2 * A_TW);  // 3 * A_MAXSTAGES + 14
     AShared* sh = reinterpret_cast<AShared*>(bars + 3 * A_MAXSTAGES + 14);
     uint32_t* wbound = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));  // 2 * A_SW: per slot, each stream warp's bound key
     uint64_t *full = bars, *empty = bars + A_MAXSTAGES, *patched = bars + 2 * A_MAXSTAGES;
@@ -251,38 +255,39 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         constexpr uint32_t PB = 128;  // entries per block: four per lane
         uint32_t it0 = 0;             // ring position of this row's first stage
         int ord = 0;
+#ifdef WB_PHASE_TIMERS
+        long long tq_wait = 0, tq_take = 0, tq_pref = 0, tq_row = 0;
+        const long long tq_begin = clock64();
+#endif
         for (int k = next_row(-1); k < my_rows; k = next_row(k), ++ord, it0 += n_seq) {
             const int p = ord & 1;
             const int row = row_of(k);
             const bool pen_on = pen_row(row);
             const uint32_t* hl_row = P.hit_list + size_t(row) * kHitListStride;
             float* hv_row = P.hit_val + size_t(row) * kHitListStride;
-            // place of stage c's first entry, c = 0 .. n_chunks: lane l holds c = l, l + 32, l + 64, l + 96, and c = 128
-            uint32_t bnd[5] = {0, 0, 0, 0, 0};
+            // The places of the row's stages in its list, [c] = first entry of stage c (c = 0 .. n_chunks), in shared memory:
+            // this warp runs one instruction after the other next to five busy warps on its scheduler, so what it does
+            // per stage is kept short (two broadcast loads here; one 32-entry block in the common case below).
+            uint32_t* bnd = sh->pbnd[pw];
             if (pen_on) {
                 const uint32_t* hs = P.hit_start + size_t(row) * kHitStartStride;
-#pragma unroll
-                for (int u = 0; u < 4; ++u) bnd[u] = (uint32_t(lane) + 32u * u <= n_chunks) ? min(hs[lane + 32 * u], uint32_t(kMaxHist)) : 0u;
-                bnd[4] = n_chunks >= 128 ? min(hs[128], uint32_t(kMaxHist)) : 0u;
+                for (uint32_t c = lane; c <= n_chunks; c += 32) bnd[c] = min(hs[c], uint32_t(kMaxHist));
             }
-            auto place = [&](uint32_t c) -> uint32_t {
-                const uint32_t r = c >> 5;
-                const uint32_t v = r == 0 ? bnd[0] : (r == 1 ? bnd[1] : (r == 2 ? bnd[2] : bnd[3]));
-                const uint32_t g = __shfl_sync(0xffffffffu, v, c & 31u);
-                return c >= 128 ? bnd[4] : g;
-            };
+            __syncwarp();
             uint32_t s_nx = 0, e_nx = 0, w_nx[4] = {none, none, none, none};
-            auto load_block = [&](uint32_t from, uint32_t end, uint32_t* w) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) w[j] = from + 32 * j + lane < end ? hl_row[from + 32 * j + lane] : none;
-            };
             auto prefetch = [&](uint32_t i) {
                 s_nx = e_nx = 0;
+                w_nx[0] = w_nx[1] = w_nx[2] = w_nx[3] = none;
                 if (pen_on && i < n_seq) {
                     const uint32_t cc = seq_stage(i);
-                    s_nx = place(cc), e_nx = place(cc + 1);
+                    s_nx = bnd[cc], e_nx = bnd[cc + 1];
+                    if (s_nx + lane < e_nx) w_nx[0] = hl_row[s_nx + lane];
+                    if (e_nx - s_nx > 32) {  // (seldom: the same for the whole warp)
+#pragma unroll
+                        for (int j = 1; j < 4; ++j)
+                            if (s_nx + 32 * j + lane < e_nx) w_nx[j] = hl_row[s_nx + 32 * j + lane];
+                    }
                 }
-                load_block(s_nx, e_nx, w_nx);
             };
             // this warp's places in the row's sequence of stages: i0, i0 + A_PW, ...
             uint32_t i = (uint32_t(pw) + A_PW - it0 % A_PW) % A_PW;
@@ -294,10 +299,17 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 uint32_t cur = s_nx;
                 const uint32_t end = e_nx;
                 uint32_t w[4] = {w_nx[0], w_nx[1], w_nx[2], w_nx[3]};
+#ifdef WB_PHASE_TIMERS
+                const long long tq0 = clock64();
+#endif
                 if (!mbar_wait(&full[st_slot], st_phase)) {
                     if (lane == 0) atomicExch(a.err, 7u);
                     return;
                 }
+#ifdef WB_PHASE_TIMERS
+                const long long tq1 = clock64();
+                tq_wait += tq1 - tq0;
+#endif
                 T* stage_mem = reinterpret_cast<T*>(ring + size_t(st_slot) * ch_bytes);
                 // entry e, at place idx of the list, leaves the stage
                 auto take_out = [&](uint32_t e, uint32_t idx) {
@@ -318,8 +330,11 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                     }
                 };
                 if (cur < end) {
+                    take_out(w[0], cur + lane);
+                    if (end - cur > 32) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) take_out(w[j], cur + 32 * j + lane);
+                        for (int j = 1; j < 4; ++j) take_out(w[j], cur + 32 * j + lane);
+                    }
                     cur += PB;
                 }
                 // (a stage with more than 128 tokens, the low ids as a rule: 512 entries per trip to memory)
@@ -333,13 +348,33 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&patched[st_slot]);  // the stream warps may read the stage
+#ifdef WB_PHASE_TIMERS
+                const long long tq2 = clock64();
+                tq_take += tq2 - tq1;
+#endif
                 prefetch(i + A_PW);
+#ifdef WB_PHASE_TIMERS
+                tq_pref += clock64() - tq2;
+#endif
             }
+#ifdef WB_PHASE_TIMERS
+            const long long tq3 = clock64();
+#endif
             // every raw logit of the row's history tokens is put aside: the draw warp may read them
             __threadfence_block();
             __syncwarp();
             if (lane == 0) mbar_arrive(&hv_ready[p]);
+#ifdef WB_PHASE_TIMERS
+            tq_row += clock64() - tq3;
+#endif
         }
+#ifdef WB_PHASE_TIMERS
+        if (pw == 0 && lane == 0) {
+            unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 16);
+            atomicAdd(&dbg[24], (unsigned long long)tq_wait), atomicAdd(&dbg[25], (unsigned long long)tq_take), atomicAdd(&dbg[26], (unsigned long long)tq_pref);
+            atomicAdd(&dbg[27], (unsigned long long)tq_row), atomicAdd(&dbg[28], (unsigned long long)(clock64() - tq_begin));
+        }
+#endif
         return;
     }
 

@@ -1,8 +1,8 @@
 // General candidate selection: the K best of each row for any K up to 16384 and any row width / alignment, one CTA
-// per row, several passes over the row (which stays in L2).  This is the path for what the single-pass kernel
-// (sample_stream.cu) does not take: K above its limit (the reference's 16384-candidate escalation launch,
-// src/server/engine_sampling.cpp:65-78), rows that are not 16-byte aligned, and the second escalation level of the
-// fused sampler.
+// per row, several passes over the row (which stays in L2); and, past that, the whole row sorted.  This is the path
+// for what the single-pass kernel (sample_async.cu) does not take: K above its limit (the reference's 16384-candidate
+// escalation launch, src/server/engine_sampling.cpp:65-78, and its whole-row step, :79-83), rows that are not 16-byte
+// aligned, rows to redo, and the id-order walk of open rows.
 //
 // Replaces topk_rows (kernels/shared/sample_cand_topk_rows.h:11-98) with two differences in results: ties at the K-th
 // logit are broken by the lower token id (the rule of every host comparator of the path,
