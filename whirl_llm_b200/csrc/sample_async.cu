@@ -44,9 +44,9 @@ struct ASlot {
     unsigned long long tau;  // current threshold candidate; elements must beat it to be logged
     uint32_t cnt;            // log entries reserved so far (may exceed A_L: overflow)
     int32_t row;
-    float red_m[A_SW + 1];   // per stream warp, then the draw warp (history tokens): max, reference exponent, scaled sum
-    float red_e[A_SW + 1];
-    double red_s[A_SW + 1];
+    float red_m[A_SW + A_TW];  // per stream warp, then per tail warp (the row's history tokens): max, reference exponent, scaled sum
+    float red_e[A_SW + A_TW];
+    double red_s[A_SW + A_TW];
 };
 
 // what the tail group hands to the draw warp with a row's candidates
@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
 
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], A_SW), mbar_init(&patched[s], 1);
-        for (int p = 0; p < 2; ++p) mbar_init(&closed[p], A_SW + (pen ? 1 : 0)), mbar_init(&boot_done[p], 1);
+        for (int p = 0; p < 2; ++p) mbar_init(&closed[p], A_SW), mbar_init(&boot_done[p], 1);
         for (int p = 0; p < 2; ++p) mbar_init(&head_done[p], A_SW);
         for (int p = 0; p < 2; ++p) mbar_init(&draw_full[p], 1), mbar_init(&draw_empty[p], 1), mbar_init(&hv_ready[p], A_PW);
         mbar_fence_init();
@@ -388,85 +388,6 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
         int ord = 0;
         for (int k = next_row(-1); k < my_rows; k = next_row(k), ++ord) {
             const int p = ord & 1;
-            if (pen) {
-                // The row has streamed (or nearly): its history tokens, taken out of the stages by the penalty warps, get their
-                // penalty and join the row here: this warp is one more contributor to the row's maximum, sum and log.
-                const int row = row_of(k);
-                ASlot* sl = &sh->slot[p];
-                unsigned long long* log = logs + size_t(p) * A_L;
-                const bool greedy = no_sum_row(row);
-                const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
-                const float cexp = inv_t * kLog2e;
-                const bool pen_on = pen_row(row);
-                const float pen_rep = (pen_on && P.rep) ? P.rep[row] : 1.f, pen_pres = (pen_on && P.pres) ? P.pres[row] : 0.f, pen_freq = (pen_on && P.freq) ? P.freq[row] : 0.f;
-                // the raw logits are all put aside; the slot is the row's; the row has its first threshold
-                if (!mbar_wait(&hv_ready[p], (ord >> 1) & 1) || !mbar_wait(&boot_done[p], (ord >> 1) & 1) || !mbar_wait(&head_done[p], (ord >> 1) & 1)) {
-                    if (lane == 0) atomicExch(a.err, 6u);
-                    return;
-                }
-                float m_t = -INFINITY, e_t = 0.f, s_t = 0.f;
-                if (pen_on) {
-                    constexpr uint32_t none = 0xffffffffu;
-                    const uint32_t* hl_row = P.hit_list + size_t(row) * kHitListStride;
-                    const float* hv_row = P.hit_val + size_t(row) * kHitListStride;
-                    const uint32_t total = min(P.hit_start[size_t(row) * kHitStartStride + n_chunks], uint32_t(kMaxHist));
-                    uint32_t en[4];
-                    float rn[4];
-                    auto fetch = [&](uint32_t from) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint32_t idx = from + 32 * j + lane;
-                            en[j] = idx < total ? hl_row[idx] : none;
-                            rn[j] = idx < total ? hv_row[idx] : 0.f;
-                        }
-                    };
-                    fetch(0);
-                    for (uint32_t from = 0; from < total; from += 128) {
-                        uint32_t e4[4];
-                        float r4[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) e4[j] = en[j], r4[j] = rn[j];
-                        fetch(from + 128);  // (the next block is on its way while this one joins)
-                        const unsigned long long tau = ld_volatile_u64(&sl->tau);
-                        const float tau_f = float_of_key(cand_key(tau));
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (e4[j] == none) continue;
-                            float l = r4[j];
-                            l = (l > 0.f) ? __fdiv_rn(l, pen_rep) : __fmul_rn(l, pen_rep);
-                            const float x = __fsub_rn(l, __fadd_rn(pen_pres, __fmul_rn(pen_freq, float(e4[j] >> kPenIdBits))));
-                            if (!greedy) {
-                                if (x > m_t) {
-                                    const float ne = ceilf(x * cexp);
-                                    s_t = (m_t == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
-                                    e_t = ne, m_t = x;
-                                }
-                                if (m_t != -INFINITY) s_t += ex2_approx(fmaf(x, cexp, -e_t));
-                            } else {
-                                m_t = fmaxf(m_t, x);
-                            }
-                            if (x >= tau_f) {
-                                const unsigned long long cnd = make_cand(key_of(x), e4[j] & kPenMaxV);
-                                if (cnd > tau) {
-                                    const uint32_t pos = atomicAdd(&sl->cnt, 1u);
-                                    if (pos < uint32_t(A_L)) log[pos] = cnd;
-                                }
-                            }
-                        }
-                    }
-                }
-                const bool saw_nan = !greedy && (s_t != s_t);
-                if (__any_sync(0xffffffffu, saw_nan) && lane == 0) atomicOr(&sl->cnt, 0x80000000u);
-                const float wm = warp_max(m_t);
-                float we = e_t;
-                if (m_t == -INFINITY) we = -INFINITY;
-                we = warp_max(we);
-                double ds = (m_t == -INFINITY) ? 0.0 : double(s_t) * double(ex2_approx(e_t - we));
-                ds = warp_sum(ds);
-                if (lane == 0) sl->red_m[A_SW] = wm, sl->red_e[A_SW] = we, sl->red_s[A_SW] = ds;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&closed[p]);
-            }
             if (!mbar_wait(&draw_full[p], (ord >> 1) & 1)) {
                 if (lane == 0) atomicExch(a.err, 8u);
                 return;
@@ -628,7 +549,72 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             const long long tf0 = clock64();
 #endif
             // ---- the row is through
-            const uint32_t total = sl->cnt;  // bit 31: a stream warp met a NaN logit
+            if (pen) {
+                // The row's history tokens, taken out of the stages by the penalty warps, get their penalty and join the row
+                // here (all the group's threads: one warp took a third of a row's time for it): each tail warp is one more
+                // contributor to the row's maximum and sum, and the tokens that can be among the K best go to the log.
+                if (!mbar_wait(&hv_ready[p], (ord >> 1) & 1)) {
+                    if (g.tid == 0) atomicExch(a.err, 6u);
+                    return;
+                }
+                const bool skip_sum = no_sum_row(row);
+                const float inv_t_j = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
+                const float cexp = inv_t_j * kLog2e;
+                float m_t = -INFINITY, e_t = 0.f, s_t = 0.f;
+                if (pen_row(row)) {
+                    const float pen_rep = P.rep ? P.rep[row] : 1.f, pen_pres = P.pres ? P.pres[row] : 0.f, pen_freq = P.freq ? P.freq[row] : 0.f;
+                    const uint32_t* hl_row = P.hit_list + size_t(row) * kHitListStride;
+                    const float* hv_row = P.hit_val + size_t(row) * kHitListStride;
+                    const uint32_t n_hit = min(P.hit_start[size_t(row) * kHitStartStride + n_chunks], uint32_t(kMaxHist));
+                    const unsigned long long tau = ld_volatile_u64(&sl->tau);
+                    const float tau_f = float_of_key(cand_key(tau));
+                    for (uint32_t base = 0; base < n_hit; base += 4 * A_TT) {
+                        uint32_t e4[4];
+                        float r4[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {  // (the loads first, then the arithmetic)
+                            const uint32_t idx = base + j * A_TT + g.tid;
+                            e4[j] = idx < n_hit ? hl_row[idx] : 0xffffffffu;
+                            r4[j] = idx < n_hit ? __ldcg(hv_row + idx) : 0.f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (e4[j] == 0xffffffffu) continue;
+                            float l = r4[j];
+                            l = (l > 0.f) ? __fdiv_rn(l, pen_rep) : __fmul_rn(l, pen_rep);
+                            const float x = __fsub_rn(l, __fadd_rn(pen_pres, __fmul_rn(pen_freq, float(e4[j] >> kPenIdBits))));
+                            if (!skip_sum) {
+                                if (x > m_t) {
+                                    const float ne = ceilf(x * cexp);
+                                    s_t = (m_t == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
+                                    e_t = ne, m_t = x;
+                                }
+                                if (m_t != -INFINITY) s_t += ex2_approx(fmaf(x, cexp, -e_t));
+                            } else {
+                                m_t = fmaxf(m_t, x);
+                            }
+                            if (x >= tau_f) {
+                                const unsigned long long cnd = make_cand(key_of(x), e4[j] & kPenMaxV);
+                                if (cnd > tau) {
+                                    const uint32_t pos = atomicAdd(&sl->cnt, 1u);
+                                    if (pos < uint32_t(A_L)) log[pos] = cnd;
+                                }
+                            }
+                        }
+                    }
+                }
+                const bool saw_nan = !skip_sum && (s_t != s_t);
+                if (__any_sync(0xffffffffu, saw_nan) && (g.tid & 31) == 0) atomicOr(&sl->cnt, 0x80000000u);
+                const float wm = warp_max(m_t);
+                float we = e_t;
+                if (m_t == -INFINITY) we = -INFINITY;
+                we = warp_max(we);
+                double ds = (m_t == -INFINITY) ? 0.0 : double(s_t) * double(ex2_approx(e_t - we));
+                ds = warp_sum(ds);
+                if ((g.tid & 31) == 0) sl->red_m[A_SW + (g.tid >> 5)] = wm, sl->red_e[A_SW + (g.tid >> 5)] = we, sl->red_s[A_SW + (g.tid >> 5)] = ds;
+                g.sync();
+            }
+            const uint32_t total = sl->cnt;  // bit 31: a warp met a NaN logit
             const bool overflow = total > uint32_t(A_L);
 #ifdef WB_PHASE_TIMERS
             if (g.tid == 0) {
@@ -645,8 +631,8 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
             const bool no_sum = no_sum_row(row);
             float M = -INFINITY, sum = 0.f;
             if (!no_sum) {
-                const int n_red = A_SW + (pen ? 1 : 0), ln = g.tid & 31;
-                static_assert(A_SW + 1 <= 32, "one partial per lane");
+                const int n_red = A_SW + (pen ? A_TW : 0), ln = g.tid & 31;
+                static_assert(A_SW + A_TW <= 32, "one partial per lane");
                 const float mw = ln < n_red ? sl->red_m[ln] : -INFINITY;
                 M = warp_max(mw);
                 const double cexp = double(inv_t * kLog2e);
