@@ -11,9 +11,10 @@
 //   penalty warps (2)       only when histories are given: take the raw logits of a stage's history tokens out before
 //                           the stream warps read it (lists prepared by history_lists_kernel) and put them aside.
 //   tail group (4 warps)    concurrently: raise the row's threshold (the K-th largest of the log so far is a valid
-//                           lower bound of the row's K-th largest), and when a row is through: its exact K best, in order.
-//   draw warp (1)           applies the penalties to the tokens put aside and adds them to the row; then, with the
-//                           row's candidates from the tail group: top-k / top-p / min-p in f64, the draw, the outputs.
+//                           lower bound of the row's K-th largest); when a row is through: apply the penalties to the
+//                           tokens put aside and add them to the row, then its exact K best, in order.
+//   draw warp (1)           with the row's candidates from the tail group: top-k / top-p / min-p in f64, the draw, the
+//                           outputs, while the tail group is already on the next row.
 //
 // Why a threshold from partial data is exact: an element is dropped only when it is below a value that at least K
 // elements of the same row reach, so the K best are always in the log; the final select over the log is exact.
@@ -243,7 +244,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
     // They walk the row's hit list (its distinct history tokens with their counts, stage by stage; history_lists_kernel)
     // while the row streams, taking the stages in turn: as soon as a stage has landed its warp takes the raw logits of the
     // stage's history tokens out (replaced by -inf, so the stream warps see them as absent), puts them aside in global
-    // memory, and hands the stage on to the stream warps.  Nothing else: the draw warp applies the penalties and adds the
+    // memory, and hands the stage on to the stream warps.  Nothing else: the tail group applies the penalties and adds the
     // tokens to the row once the row has streamed.  They depend on no threshold and no row slot, so they run as far ahead
     // of the stream warps as the ring allows.  The first s0 stages come twice (see the stream warps); the second time their
     // tokens are only taken out again.  Entries are read in blocks of 128 (four per lane, loaded together), the first
@@ -360,7 +361,7 @@ __global__ void __launch_bounds__(A_THREADS, 1) sample_async_kernel(SelectArgs a
 #ifdef WB_PHASE_TIMERS
             const long long tq3 = clock64();
 #endif
-            // every raw logit of the row's history tokens is put aside: the draw warp may read them
+            // every raw logit of the row's history tokens is put aside: the tail group may read them
             __threadfence_block();
             __syncwarp();
             if (lane == 0) mbar_arrive(&hv_ready[p]);
