@@ -725,7 +725,9 @@ size_t select_generic_ws_bytes(int ctas, int K) {
 }
 
 cudaError_t select_generic_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st) {
-    const int grid = a.rows < 2 * sm_count ? a.rows : 2 * sm_count;
+    // (a launch over a list of leftover rows, usually empty or short, gets one CTA per SM: its CTAs loop over the list)
+    const int per_sm = a.row_list ? 1 : 2;
+    const int grid = a.rows < per_sm * sm_count ? a.rows : per_sm * sm_count;
     const int kmax = a.mode == MODE_TOPK ? a.K : (a.mode == MODE_DRAFT ? 32 : a.level_k);
     const int cap = pow2_at_least(kmax < 1 ? 1 : (kmax > a.n ? a.n : kmax));
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
