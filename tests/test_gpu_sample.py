@@ -103,6 +103,37 @@ def test_third_level_rows(api, oracle):
     compare_rows(res, want, u=u)
 
 
+def test_adversarial_and_special_rows(api, oracle):
+    """Element orders and values that stress the single-pass kernel: rising rows (every logit beats the threshold so far,
+    the candidate log overflows and the row is redone by the multi-pass kernel), falling rows, constant rows (all ties:
+    the lower id wins), rows with +-inf entries, a row length that is no multiple of the stage size, and more rows than
+    SMs so that CTAs take several rows; then the same with a token history and penalties."""
+    R, V = 320, 36868  # 9 stages and a 4-logit remainder
+    x = synth.normalish(71, (R, V), 2.0)
+    x[0::8] = np.sort(x[0::8], axis=1)                    # rising
+    x[1::8] = -np.sort(-x[1::8], axis=1)                  # falling
+    x[2::8] = 1.25                                        # constant
+    x[3::8, ::97] = -np.inf
+    x[4::8, 5::1013] = np.inf                             # several +inf: ties at the top
+    x[5::8] = np.round(x[5::8] * 2) / 2                   # heavy ties
+    f = lambda v, dt=np.float32: np.full(R, v, dtype=dt)
+    prm = dict(inv_t=f(1 / 0.9), top_k=f(40, np.uint32), top_p=f(0.92, np.float64), min_p=f(0.01, np.float64))
+    prm["top_k"][6::8] = 256
+    prm["top_k"][7::8] = 1
+    u = synth.hash_u01(72, R, 0)
+    want = oracle.sample_rows(x, kept_cap=256, u=u, threads=4, **prm)
+    res = api.sample_rows(dev(x), row_params(prm, u=u), kept_cap=256)
+    compare_rows(res, want, u=u)
+    assert int(res.counters[api.CNT_UNRESOLVED].item()) == 0
+    hist = synth.zipf_history(73, R, 512, V, 1.1)
+    hist_len = np.full(R, 512, dtype=np.int32)
+    hist_len[::5] = 17
+    pen = dict(hist=hist, hist_len=hist_len, rep=f(1.3), pres=f(0.2), freq=f(0.1))
+    want = oracle.sample_rows(x, kept_cap=256, u=u, threads=4, **prm, **{k: (v.astype(np.uint32) if k == "hist_len" else v) for k, v in pen.items()})
+    res = api.sample_rows(dev(x), row_params(prm, u=u, **pen), kept_cap=256)
+    compare_rows(res, want, u=u)
+
+
 def test_open_rows_large_vocab(api, oracle):
     """Pure temperature sampling (no filter): the single-pass kernel hands rows whose draw falls past the 256 candidates to
     the multi-pass kernel, which walks the row in id order."""
