@@ -37,7 +37,8 @@ enum {
     WHIRL_ROW_DONE = 0,      /* token drawn */
     WHIRL_ROW_ESCALATE = 1,  /* the kept set may reach past 16384 candidates and the whole-row level could not run (a row of
                                 more than 2^20 logits, or no scratch area came free in time): not answered */
-    WHIRL_ROW_OPEN_TAIL = 2  /* open set whose draw fell past the candidates and the row walk is not available */
+    WHIRL_ROW_OPEN_TAIL = 2  /* open set whose draw fell past the candidates; whirl_sample_rows walks the row itself, so this
+                                is only seen from whirl_merge_sample_rows (no row to walk there) */
 };
 
 /* indices into the counters array of whirl_sample_rows */
