@@ -1,6 +1,6 @@
 // The single-pass fused sampler for rows that keep at most 256 candidates: every logits row is read from HBM once.
 //
-// One persistent CTA per SM, 24 warps in five roles that never meet at a CTA-wide barrier while rows stream:
+// One persistent CTA per SM, 25 warps in five roles that never meet at a CTA-wide barrier while rows stream:
 //   producer (1 thread)     bulk async copies (TMA, cp.async.bulk + mbarrier) of the CTA's rows into a ring of shared
 //                           memory stages, running ahead across row boundaries.  The first few stages of a row go
 //                           through the ring twice (the second time they come from L2).
@@ -8,7 +8,7 @@
 //                           the few logits above the threshold are appended to the row's candidate log.  The first
 //                           pass over a row's head only accumulates; then the warps agree on a first threshold (their
 //                           one meeting per row); the second pass over the head only logs.
-//   penalty warps (2)       only when histories are given: take the raw logits of a stage's history tokens out before
+//   penalty warps (3)       only when histories are given: take the raw logits of a stage's history tokens out before
 //                           the stream warps read it (lists prepared by history_lists_kernel) and put them aside.
 //   tail group (4 warps)    concurrently: raise the row's threshold (the K-th largest of the log so far is a valid
 //                           lower bound of the row's K-th largest); when a row is through: apply the penalties to the
@@ -34,7 +34,8 @@ constexpr int A_SW = 16;                      // stream warps
 constexpr int A_ST = A_SW * 32;
 constexpr int A_TW = 4;                       // tail warps
 constexpr int A_TT = A_TW * 32;
-constexpr int A_PW = 2;                       // penalty warps (with them 24 warps: six per scheduler, 80 registers each)
+constexpr int A_PW = 3;                       // penalty warps (with them 25 warps: at most seven per scheduler, 72 registers
+                                              // each, which the kernel fits without spilling; two were 7 % slower with penalties)
 constexpr int A_THREADS = 32 + A_ST + A_TT + 32 + A_PW * 32;  // copies, stream warps, tail warps, draw warp, penalty warps
 constexpr int A_CH = 4096;                    // logits per ring stage
 constexpr int A_L = 3072;                     // candidate log entries per row slot
