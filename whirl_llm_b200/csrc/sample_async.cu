@@ -38,7 +38,7 @@ constexpr int A_PW = 3;                       // penalty warps (with them 25 war
                                               // each, which the kernel fits without spilling; two were 7 % slower with penalties)
 constexpr int A_THREADS = 32 + A_ST + A_TT + 32 + A_PW * 32;  // copies, stream warps, tail warps, draw warp, penalty warps
 constexpr int A_CH = 4096;                    // logits per ring stage
-constexpr int A_L = 3072;                     // candidate log entries per row slot
+constexpr int A_L = 3040;                     // candidate log entries per row slot (sized so that a 10th ring stage fits)
 constexpr int A_MAXSTAGES = 16;
 constexpr int A_S0 = 8;                       // stages at the head of a row that are read twice (see the stream warps)
 
