@@ -17,7 +17,7 @@
 
 namespace wb {
 
-constexpr int HL_THREADS = 256;
+constexpr int HL_THREADS = 512;  // (a row takes half as long as with 256, and the rows spread over the SMs more evenly)
 
 __global__ void __launch_bounds__(HL_THREADS) history_lists_kernel(const int32_t* hist, const int32_t* hist_len, int64_t hist_stride, int rows,
                                                                     uint32_t n, uint32_t* lists, uint32_t* starts) {
@@ -109,7 +109,8 @@ cudaError_t history_lists_launch(RowParams& prm, int rows, int n, int dtype, voi
     uint32_t* starts = lists + size_t(rows) * kHitListStride;
     prm.hit_list = lists, prm.hit_start = starts;
     prm.hit_val = reinterpret_cast<float*>(starts + size_t(rows) * kHitStartStride);
-    const int grid = rows < 6 * sm_count ? rows : 6 * sm_count;  // (six CTAs of 33 KiB fit an SM)
+    (void)sm_count;
+    const int grid = rows;  // one CTA per row: four of them fit an SM, and a free SM takes the next row
     history_lists_kernel<<<grid, HL_THREADS, 0, st>>>(prm.hist, prm.hist_len, prm.hist_stride, rows, uint32_t(n), lists, starts);
     return cudaGetLastError();
 }
