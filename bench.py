@@ -215,7 +215,7 @@ def run_ours(args):
     per_row = algorithmic_bytes_per_row(vocab, esize, HIST)
     achieved = rows * per_row / (ms_per_step * 1e-3) / 1e9
     traffic = None
-    tp = os.path.join(ROOT, "profiles", "sample_async_kernel_traffic.txt")
+    tp = os.path.join(ROOT, "profiles", "single_pass_kernel_traffic.txt")
     if os.path.exists(tp):
         try:
             tj = json.load(open(tp))
@@ -240,7 +240,7 @@ def run_ours(args):
         "launches_by_kernel": {k: int(lc1[k] - lc0[k]) for k in lc1},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_kind": peak_kind, "algorithmic_bytes_per_row": per_row,
-                     "kernel": "sample_async_kernel<float>" if args.dtype == "f32" else "sample_async_kernel<uint16_t>"},
+                     "kernel": "single_pass_kernel<float>" if args.dtype == "f32" else "single_pass_kernel<uint16_t>"},
     }
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline(xs[0], hist, us[0], rows, vocab, args.dtype)

@@ -338,6 +338,22 @@ class Reference(_Lib):
                                 C.c_void_p])
         f("case_relax_bytes", C.c_uint32, [C.c_uint32])
         f("case_max_rows", C.c_uint32, [])
+        f("bench_rows", C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(Batch), C.c_int, C.c_int, C.POINTER(C.c_double),
+                                  C.c_void_p])
+
+    def bench_rows(self, x, *, threads=1, reps=1, **params):
+        """The timed CPU arm: persistent workers over the reference's real SampleBuffers -> filterCands -> sampleRow (this
+        repository's penalty rule applied to each row first).  Returns (seconds for rows * reps samplings, first-pass tokens)."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        rows, V = x.shape
+        b, keep = self._batch(rows, **params)
+        sec = C.c_double(0.0)
+        tok = np.zeros(rows, dtype=np.uint32)
+        rc = self._bench_rows(_ptr(x), rows, V, C.byref(b), threads, reps, C.byref(sec), _ptr(tok))
+        if rc != 0:
+            raise RuntimeError("ref_bench_rows refused the batch")
+        del keep
+        return sec.value, tok
 
     def sampler_uniform(self, seed, pos):
         return self._sampler_uniform(seed, pos)

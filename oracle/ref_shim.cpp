@@ -22,6 +22,8 @@
 
 #include <algorithm>
 #include <array>
+#include <atomic>
+#include <chrono>
 #include <cmath>
 #include <cstdint>
 #include <cstdlib>
@@ -283,6 +285,90 @@ int ref_sample_rows(const float* x, const std::uint16_t* xb, std::uint32_t rows,
                         static_cast<std::uint32_t>(static_cast<std::uint64_t>(rows) * (t + 1) / threads));
     engineRows(x, V, b, out, kept_ids, kept_p, kept_cap, 0, static_cast<std::uint32_t>(static_cast<std::uint64_t>(rows) / threads));
     for (auto& t : th) t.join();
+    return 0;
+}
+
+// The timed CPU arm of the benchmark: `threads` persistent workers, each with ONE FakeServerModel + SampleBuffers kept for
+// the whole call, each sampling its own block of rows `reps` times (output index pos_idx + rep * rows, so every pass
+// draws with fresh uniforms).  Per row and pass: the raw row is copied into the model's logits buffer (the stand-in for
+// the forward pass that leaves logits there), this repository's penalty rule is applied to it (the reference has no
+// penalties, src/server/engine_start.cpp:70-73; rule: oracle/whirl_oracle.c, orc_apply_penalties), then the reference's
+// own launchTopk -> download -> SampleBuffers::prepareRow -> sampleRow runs unchanged
+// (src/server/engine_prefill.cpp:204-211).  Set-up (allocations, thread start) is outside the time: *seconds is the
+// span from the moment every worker is ready to the moment the last one is done.  tokens[rows]: the first pass.
+int ref_bench_rows(const float* x, std::uint32_t rows, std::uint32_t V, const Batch* b, int threads, int reps, double* seconds,
+                   std::uint32_t* tokens) {
+    if (!x || !seconds || b->u || V < server::k_big || rows == 0 || reps < 1) return -1;
+    if (threads < 1) threads = 1;
+    if (static_cast<std::uint32_t>(threads) > rows) threads = static_cast<int>(rows);
+    std::atomic<int> ready{0};
+    std::atomic<bool> go{false};
+    using clk = std::chrono::steady_clock;
+    std::vector<clk::time_point> t_end(threads);
+    clk::time_point t_start;
+    auto worker = [&](int t) {
+        const std::uint32_t r0 = static_cast<std::uint32_t>(static_cast<std::uint64_t>(rows) * t / threads);
+        const std::uint32_t r1 = static_cast<std::uint32_t>(static_cast<std::uint64_t>(rows) * (t + 1) / threads);
+        HostBackend hb;
+        test::FakeServerModel model(hb, V);
+        server::SampleBuffers sb(model, hb);
+        sb.alloc(1, false, 0);
+        auto* lg = reinterpret_cast<float*>(model.logits());
+        std::vector<std::uint16_t> cnt(V, 0);
+        std::vector<std::uint32_t> seen;
+        seen.reserve(4096);
+        ready.fetch_add(1);
+        while (!go.load(std::memory_order_acquire)) std::this_thread::yield();
+        for (int rep = 0; rep < reps; ++rep) {
+            for (std::uint32_t r = r0; r < r1; ++r) {
+                std::memcpy(lg, x + static_cast<std::size_t>(r) * V, static_cast<std::size_t>(V) * 4);
+                if (b->hist && b->hist_len && b->hist_len[r] > 0) {
+                    const float rp = b->rep ? b->rep[r] : 1.f, pr = b->pres ? b->pres[r] : 0.f, fr = b->freq ? b->freq[r] : 0.f;
+                    const std::int32_t* h = b->hist + static_cast<std::size_t>(r) * b->hist_stride;
+                    seen.clear();
+                    for (std::uint32_t i = 0; i < b->hist_len[r]; ++i) {
+                        const std::uint32_t tk = static_cast<std::uint32_t>(h[i]);
+                        if (tk >= V) continue;
+                        if (cnt[tk]++ == 0) seen.push_back(tk);
+                    }
+                    for (const std::uint32_t tk : seen) {
+                        float l = lg[tk];
+                        l = (l > 0.f) ? l / rp : l * rp;
+                        volatile float fc = fr * static_cast<float>(cnt[tk]);
+                        volatile float sub = pr + fc;
+                        lg[tk] = l - sub;
+                        cnt[tk] = 0;
+                    }
+                }
+                sampling::Sampler s;
+                s.cands = sb.cands();
+                s.inv_t = b->inv_t ? b->inv_t[r] : 1.f;
+                s.temp = 1.0 / s.inv_t;
+                s.top_k = b->top_k ? b->top_k[r] : 0;
+                s.top_p = b->top_p ? b->top_p[r] : 1.0;
+                s.min_p = b->min_p ? b->min_p[r] : 0.0;
+                s.seed = b->seed ? b->seed[r] : 0;
+                s.pos_idx = (b->pos_idx ? b->pos_idx[r] : 0) + static_cast<std::uint64_t>(rep) * rows;
+                s.race = b->race && b->race[r];
+                s.row_base = 0;
+                sb.launchTopk(0, 1, server::k_small, s.inv_t, sb.sampDev(), server::max_rows, 0);
+                hb.download(sb.sampHost().data(), sb.sampDev(), server::SampleBuffers::sampBytes());
+                sb.prepareRow(s, 0);
+                const std::uint32_t tok = sampling::sampleRow(sb, s, std::nullopt, 0);
+                if (rep == 0 && tokens) tokens[r] = tok;
+            }
+        }
+        t_end[t] = clk::now();
+    };
+    std::vector<std::thread> th;
+    for (int t = 0; t < threads; ++t) th.emplace_back(worker, t);
+    while (ready.load() < threads) std::this_thread::yield();
+    t_start = clk::now();
+    go.store(true, std::memory_order_release);
+    for (auto& t : th) t.join();
+    clk::time_point last = t_end[0];
+    for (int t = 1; t < threads; ++t) last = std::max(last, t_end[t]);
+    *seconds = std::chrono::duration<double>(last - t_start).count();
     return 0;
 }
 

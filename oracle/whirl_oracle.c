@@ -131,11 +131,16 @@ ORC_API int orc_apply_penalties(float* x, uint32_t V, const int32_t* hist, uint3
  * greedy picks
  * ---------------------------------------------------------------------------------------------- */
 
-/* tests/kernels/test_misc.cpp:30-35 (firstMax) == kernels/shared/block_argmax.h (strict >, ties to the lower index) */
+/* kernels/shared/block_argmax.h:1-22: every thread starts from best = -inf, idx = 0 and takes x[i] only when x[i] > best
+ * (strict), the tree reduction prefers the lower index on ties.  So the result is the first index of the maximum, a NaN
+ * logit is never taken (x > best is false for it), and a row with nothing above -inf answers 0.  The host helper of the
+ * kernel test (tests/kernels/test_misc.cpp:30-35, firstMax) agrees except when x[0] is NaN, where it stays at 0; the kernel
+ * is the behaviour followed here. */
 ORC_API int32_t orc_first_max(const float* x, uint32_t n) {
     uint32_t b = 0;
-    for (uint32_t i = 1; i < n; ++i)
-        if (x[i] > x[b]) b = i;
+    float best = -INFINITY;
+    for (uint32_t i = 0; i < n; ++i)
+        if (x[i] > best) best = x[i], b = i;
     return (int32_t)b;
 }
 

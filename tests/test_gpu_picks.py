@@ -60,7 +60,11 @@ def test_argmax_many_rows_and_special_values(api, oracle):
     x[4, 9] = 7.0
     x[5] = 0.0
     x[5, 100] = -0.0
+    x[6, 0] = np.nan   # a NaN in the first place is skipped like any other (kernels/shared/block_argmax.h:1-8 starts from -inf)
+    x[7, :3] = np.nan
+    x[8] = np.nan      # nothing above -inf: index 0
     want = np.array([oracle.first_max(r) for r in x])
+    assert want[6] != 0 and want[7] >= 3 and want[8] == 0
     assert np.array_equal(api.argmax_rows(dev(x)).cpu().numpy(), want)
 
 

@@ -15,7 +15,7 @@ from gpu_util import dev
 pytestmark = pytest.mark.gpu
 
 
-def test_static_scratch_matches_workspace_variant_twice():
+def test_static_scratch_matches_workspace_variant_twice(oracle):
     from whirl_llm_b200 import api
     n = 248320
     for call, (rows, seed) in enumerate([(5, 11), (37, 12)]):
@@ -28,6 +28,7 @@ def test_static_scratch_matches_workspace_variant_twice():
         got = api.argmax_rows_static(xd, out=out)   # the library's fixed scratch
         torch.cuda.synchronize()
         assert torch.equal(got, want), (call, got.tolist(), want.tolist())
+        assert got.cpu().tolist() == [oracle.first_max(r) for r in x]   # and both agree with the CPU checker
         assert got[1].item() == 100 and got[2].item() == n - 1
 
 

@@ -308,7 +308,7 @@ def launch_counts() -> dict:
     """Kernel launches made through the library by this process so far, per family."""
     a = (C.c_uint64 * 4)()
     lib.whirl_launch_counts(a, 4)
-    return dict(rowscan=a[0], select_generic=a[1], sample_stream=a[2], aux=a[3])
+    return dict(rowscan=a[0], select_generic=a[1], single_pass=a[2], aux=a[3])
 
 
 def sample_rows_host(x_host, params: dict, rows: int, n: int, dtype: int, out: dict, kept_cap: int = 0, device: int = 0):

@@ -20,7 +20,7 @@ thread_local std::string g_err;
 
 // host-side launch counters per kernel family (whirl_launch_counts)
 std::atomic<uint64_t> g_launch[4];
-enum { LC_ROWSCAN = 0, LC_GENERIC = 1, LC_STREAM = 2, LC_AUX = 3 };
+enum { LC_ROWSCAN = 0, LC_GENERIC = 1, LC_SINGLE = 2, LC_AUX = 3 };
 void bump(int which, uint64_t n = 1) { g_launch[which].fetch_add(n, std::memory_order_relaxed); }
 
 int fail(int code, const char* msg) {
@@ -51,7 +51,7 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // workspace layout (all offsets 256-byte aligned)
 struct Ws {
-    size_t off_scan, off_status, off_list, off_list2, off_count, off_err, off_locks, off_p, off_hits, off_full, total;
+    size_t off_scan, off_status, off_list, off_list2, off_count, off_err, off_locks, off_p, off_full, total;
 };
 Ws ws_layout(int rows, int n = 0) {
     Ws w;
@@ -64,15 +64,12 @@ Ws ws_layout(int rows, int n = 0) {
     o = align_up(o + size_t(rows) * 4, 256);
     w.off_list2 = o;
     o = align_up(o + size_t(rows) * 4, 256);
-    w.off_err = o;  // four error words, four count / ticket words, eight scratch-area locks (cleared together: 64 bytes),
-                    // then the profiling build's timers
+    w.off_err = o;  // four error words, four count / ticket words, eight scratch-area locks (cleared together: 64 bytes)
     w.off_count = o + 16;
     w.off_locks = o + 32;
     o = align_up(o + 512, 256);
     w.off_p = o;
     o = align_up(o + wb::select_generic_ws_bytes(std::min(rows, 2 * kSmBound), wb::kGenericMaxK), 256);
-    w.off_hits = o;  // the rows' hit lists (penalties of the single-pass sampler): lists, then starts
-    o = align_up(o + wb::history_lists_ws_bytes(rows), 256);
     w.off_full = o;  // the third escalation level's scratch areas (the only part that depends on the row length)
     o = align_up(o + wb::select_full_ws_bytes(n), 256);
     w.total = o;
@@ -237,9 +234,9 @@ int whirl_topk_rows_shard(const void* x, int dtype, int rows, int n, int K, int 
         a.err = reinterpret_cast<uint32_t*>(base + w.off_err);
         a.out.status = reinterpret_cast<int32_t*>(base + w.off_status);
     }
-    if (have_ws && wb::sample_async_supported(a, dtype)) {
-        e = wb::sample_async_launch(a, dtype, sm_count(), st);
-        bump(LC_STREAM);
+    if (have_ws && wb::single_pass_supported(a, dtype)) {
+        e = wb::single_pass_launch(a, dtype, sm_count(), st);
+        bump(LC_SINGLE);
         if (e == cudaSuccess) {
             // rows whose candidate log overflowed (adversarial element order) are redone by the multi-pass kernel
             int32_t* list = reinterpret_cast<int32_t*>(base + w.off_list);
@@ -251,9 +248,6 @@ int whirl_topk_rows_shard(const void* x, int dtype, int rows, int n, int K, int 
             bump(LC_AUX);
             bump(LC_GENERIC);
         }
-    } else if (have_ws && wb::sample_stream_supported(a, dtype)) {
-        e = wb::sample_stream_launch(a, dtype, sm_count(), st);
-        bump(LC_STREAM);
     } else {
         a.out.status = nullptr;
         e = wb::select_generic_launch(a, dtype, sm_count(), st);
@@ -289,23 +283,18 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
     a.err = reinterpret_cast<uint32_t*>(base + w.off_err);
     // level 1: top_k candidates (the set closes there), or 256 of them as the reference's first launch does
     // (k_small, src/server/engine_sampling.h:20)
-    a.level_k = 256;
+    a.level_k = wb::kFirstLevelK;
     int32_t* list_a = reinterpret_cast<int32_t*>(base + w.off_list);
     int32_t* list_b = reinterpret_cast<int32_t*>(base + w.off_list2);
     int32_t* counts = reinterpret_cast<int32_t*>(base + w.off_count);
     cudaError_t e;
-    if (wb::sample_async_supported(a, dtype)) {
-        if (prm->hist) {
-            e = wb::history_lists_launch(a.prm, rows, n, dtype, base + w.off_hits, sm_count(), st);
-            bump(LC_AUX);
-            if (e != cudaSuccess) return fail_cuda(e, "sample_rows history lists");
-        }
+    if (wb::single_pass_supported(a, dtype)) {
         // Rows keeping at most 256 candidates in one pass.  The kernel's last CTA lists what is left for the multi-pass
         // kernel below: rows with top_k above 256, rows whose kept set may reach past 256 candidates (second level, up to
         // 16384: k_big, src/server/engine_sampling.h:21), and rows to redo (candidate log overflow, NaN, open-set walk).
         a.fin_list = list_b, a.fin_counts = counts;
-        e = wb::sample_async_launch(a, dtype, sm_count(), st);
-        bump(LC_STREAM);
+        e = wb::single_pass_launch(a, dtype, sm_count(), st);
+        bump(LC_SINGLE);
         if (e != cudaSuccess) return fail_cuda(e, "sample_rows single-pass kernel");
         wb::SelectArgs b = a;
         b.level_k = wb::kGenericMaxK, b.row_list = list_b, b.row_count = counts + 1;
@@ -345,10 +334,6 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
     e = cudaGetLastError();
     return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "sample_rows");
 }
-
-#ifdef WB_PHASE_TIMERS
-size_t whirl_debug_err_offset(int rows) { return ws_layout(rows).off_err; }
-#endif
 
 int whirl_draft_sample_rows(const void* x, int dtype, int rows, int n, int* ctl_all, const int* area, int r, const int* map,
                             const whirl_dsamp_args* da, int* qbuf, void* stream) {

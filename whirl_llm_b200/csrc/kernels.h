@@ -41,7 +41,7 @@ size_t rowscan_ws_bytes(int rows, int splits);
 int rowscan_splits(int rows, int n, int sm_count);
 cudaError_t rowscan_launch(const RowScanArgs& a, int dtype, int mode, int rows, int splits, cudaStream_t st);
 
-// ---- selection + sampling (select_generic.cu, sample_stream.cu)
+// ---- selection + sampling (select_generic.cu, single_pass.cu)
 
 // Per-row parameters as device arrays (null = the default in brackets); the fields of the reference's
 // sampling::Sampler (src/sampling/sampler.h:26-53) plus this build's penalties.
@@ -61,10 +61,6 @@ struct RowParams {
     const float* rep;          // [1]
     const float* pres;         // [0]
     const float* freq;         // [0]
-    // (single-pass sampler only) the rows' hit lists, built by history_lists_launch from the fields above
-    const uint32_t* hit_list;  // [rows][kHitListStride]
-    const uint32_t* hit_start; // [rows][kHitStartStride]
-    float* hit_val;            // [rows][kHitListStride] scratch: penalised logits of the tokens in a row's first stages
 };
 
 struct RowOutputs {
@@ -118,7 +114,6 @@ struct SelectArgs {
     DraftArgs draft;          // MODE_DRAFT
     int32_t id_offset;        // MODE_TOPK: added to every id written (a vocabulary slice's first token id)
     uint32_t* err;            // device error word (bounded waits that ran out)
-    int only_large_k;         // large-K kernel: 0 = every row, 1 = only rows whose top_k is above kAsyncMaxK
     // single-pass sampler, MODE_SAMPLE: its last CTA lists the rows it left to the multi-pass kernel in fin_list (rows with
     // top_k above its limit, and rows whose kept set may reach past 256 candidates; with bit 30: rows to redo at the first
     // level) and their number in fin_counts[1].  fin_counts[2] and [3] are the two kernels' tickets (zero before a launch).
@@ -140,19 +135,12 @@ size_t select_full_ws_bytes(int n);               // 0 when the row is too long 
 uint32_t select_full_npad(int n);
 cudaError_t select_generic_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
 
-// small-K single-pass kernel (sample_async.cu)
-constexpr int kAsyncMaxK = 256;
-// per-row lists of the distinct history tokens with their counts, in the order the single-pass sampler meets them
-size_t history_lists_ws_bytes(int rows);
-// (ws: history_lists_ws_bytes(rows) bytes, 16-byte aligned; prm.hit_list / prm.hit_start are set to point into it)
-cudaError_t history_lists_launch(RowParams& prm, int rows, int n, int dtype, void* ws, int sm_count, cudaStream_t st);
-cudaError_t sample_async_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
-bool sample_async_supported(const SelectArgs& a, int dtype);
-
-// large-K single-pass kernel (sample_stream.cu)
-constexpr int kStreamMaxK = 1024;
-cudaError_t sample_stream_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
-bool sample_stream_supported(const SelectArgs& a, int dtype);
+// single-pass kernel (single_pass.cu): rows keeping at most kSinglePassMaxK candidates, 16-byte aligned rows
+constexpr int kFirstLevelK = 256;     // candidates of a row without a usable top_k at the first level (the reference's k_small,
+                                      // src/server/engine_sampling.h:20)
+constexpr int kSinglePassMaxK = 256;
+cudaError_t single_pass_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
+bool single_pass_supported(const SelectArgs& a, int dtype);
 
 // ---- speculative acceptance (spec_accept.cu)
 size_t spec_stats_bytes(int seqs, int L);

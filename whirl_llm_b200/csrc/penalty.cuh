@@ -19,16 +19,6 @@ constexpr int kPenSlots = 8192;  // table slots (power of two, at least 2 * kMax
 constexpr uint32_t kPenIdBits = 19;
 constexpr uint32_t kPenMaxV = (1u << kPenIdBits) - 1;
 
-// ---- per-row hit lists for the single-pass sampler ---------------------------------------------------------------
-// history_lists_kernel turns each row's history into one list of its DISTINCT tokens with their counts (entry =
-// token | count << 19), grouped by the 4096-logit stage the token falls into, stages in rising order.  One warp of the
-// sampler walks the list while the row streams through shared memory: it takes the raw logits of a stage's history
-// tokens out of the stage before the other warps read it, and adds their penalised values to the row itself.
-constexpr int kHitStage = 4096;                     // logits per stage
-constexpr int kHitListStride = kMaxHist + 64;       // entries per row (room for a whole 32-entry window past the end)
-constexpr int kHitStartStride = 132;                // words per row: [c] = place of stage c's first entry, c = 0 .. number of
-                                                    // stages (the last one is the length of the list; at most 128 stages)
-
 struct PenaltyTable {
     uint32_t* bitmap;  // ceil(V / 32) words
     uint32_t* slots;   // kPenSlots words

@@ -1,6 +1,6 @@
 // General candidate selection: the K best of each row for any K up to 16384 and any row width / alignment, one CTA
 // per row, several passes over the row (which stays in L2); and, past that, the whole row sorted.  This is the path
-// for what the single-pass kernel (sample_async.cu) does not take: K above its limit (the reference's 16384-candidate
+// for what the single-pass kernel (single_pass.cu) does not take: K above its limit (the reference's 16384-candidate
 // escalation launch, src/server/engine_sampling.cpp:65-78, and its whole-row step, :79-83), rows that are not 16-byte
 // aligned, rows to redo, and the id-order walk of open rows.
 //
@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(GT) select_generic_kernel(SelectArgs a, int ca
         const int entry = a.row_list ? a.row_list[li] : li;
         // bit 30 of a list entry: redo the row at the first candidate level (the single-pass kernel gave it up)
         const int row = entry & 0x3fffffff;
-        const int level = (entry >> 30) & 1 ? min(a.level_k, kAsyncMaxK) : a.level_k;
+        const int level = (entry >> 30) & 1 ? min(a.level_k, kFirstLevelK) : a.level_k;
         const int st = select_row<T>(a, row, level, cap_max, pen_words, cand, hist, sh, pen_mem);
         // Third level: the kept set may reach past 16384 candidates, so the whole row is sorted (the reference's last
         // escalation step, src/server/engine_sampling.cpp:79-83, filterCands with complete = true).  That needs 16 bytes

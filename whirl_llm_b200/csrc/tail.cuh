@@ -14,7 +14,7 @@ enum RowStatus : int32_t {
     ROW_ESCALATE = 1,   // the kept set may reach past the candidates: needs a larger candidate set
     ROW_OPEN_TAIL = 2,  // open set and the draw fell past the candidates: needs the id-order walk of the row
     ROW_RETRY = 3,      // internal: the single-pass kernel's candidate log overflowed; the multi-pass kernel redoes the row
-    ROW_LARGE_K = 4,    // internal: top_k above the small-K kernel's limit; the large-K kernel takes the row
+    ROW_LARGE_K = 4,    // internal: top_k above the single-pass kernel's limit; the multi-pass kernel takes the row
 };
 
 struct TailIn {
