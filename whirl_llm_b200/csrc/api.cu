@@ -51,7 +51,7 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // workspace layout (all offsets 256-byte aligned)
 struct Ws {
-    size_t off_scan, off_status, off_list, off_list2, off_count, off_err, off_locks, off_p, off_full, total;
+    size_t off_scan, off_status, off_list, off_list2, off_count, off_err, off_locks, off_p, off_side, off_full, total;
 };
 Ws ws_layout(int rows, int n = 0) {
     Ws w;
@@ -70,6 +70,8 @@ Ws ws_layout(int rows, int n = 0) {
     o = align_up(o + 512, 256);
     w.off_p = o;
     o = align_up(o + wb::select_generic_ws_bytes(std::min(rows, 2 * kSmBound), wb::kGenericMaxK), 256);
+    w.off_side = o;  // the single-pass sampler's side buffers (penalised rows that need their normaliser)
+    o = align_up(o + wb::single_pass_side_bytes(std::min(rows, kSmBound)), 256);
     w.off_full = o;  // the third escalation level's scratch areas (the only part that depends on the row length)
     o = align_up(o + wb::select_full_ws_bytes(n), 256);
     w.total = o;
@@ -281,6 +283,7 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
     a.out.status = out->status ? out->status : reinterpret_cast<int32_t*>(base + w.off_status);
     a.ws = base + w.off_p;
     a.err = reinterpret_cast<uint32_t*>(base + w.off_err);
+    a.side_ws = base + w.off_side;
     // level 1: top_k candidates (the set closes there), or 256 of them as the reference's first launch does
     // (k_small, src/server/engine_sampling.h:20)
     a.level_k = wb::kFirstLevelK;
@@ -334,6 +337,10 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
     e = cudaGetLastError();
     return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "sample_rows");
 }
+
+#ifdef WB_PROF
+size_t whirl_debug_err_offset(int rows, int n) { return ws_layout(rows, n).off_err; }
+#endif
 
 int whirl_draft_sample_rows(const void* x, int dtype, int rows, int n, int* ctl_all, const int* area, int r, const int* map,
                             const whirl_dsamp_args* da, int* qbuf, void* stream) {

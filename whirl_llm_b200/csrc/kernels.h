@@ -119,6 +119,7 @@ struct SelectArgs {
     // level) and their number in fin_counts[1].  fin_counts[2] and [3] are the two kernels' tickets (zero before a launch).
     int32_t* fin_list;
     int32_t* fin_counts;
+    void* side_ws;            // single-pass sampler: side buffers for the words kept out of the stream (single_pass_side_bytes)
     uint32_t* unresolved;     // multi-pass kernel: its last CTA adds the batch's rows still without an answer here (or null)
     // multi-pass kernel, third level (the whole row: the reference's last escalation step, src/server/engine_sampling.cpp:79-83):
     // full_slots scratch areas of 16 * full_npad bytes each in global memory, handed out through full_locks (zero = free)
@@ -140,6 +141,7 @@ constexpr int kFirstLevelK = 256;     // candidates of a row without a usable to
                                       // src/server/engine_sampling.h:20)
 constexpr int kSinglePassMaxK = 256;
 cudaError_t single_pass_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
+size_t single_pass_side_bytes(int sm_bound);  // bytes of SelectArgs::side_ws for a GPU of up to sm_bound SMs
 bool single_pass_supported(const SelectArgs& a, int dtype);
 
 // ---- speculative acceptance (spec_accept.cu)

@@ -21,7 +21,7 @@ struct SelScratch {
 // (1 <= need <= total).  Every thread owns SEL_BINS / NT consecutive bins in registers; one barrier pair.  Results in
 // sc->bin (the bin), sc->need (rank wanted inside that bin), sc->eq (entries in that bin).  nb <= SEL_BINS bins are used.
 template <int NT>
-__device__ void find_bin_desc(const Group<NT>& g, const uint32_t* hist, uint32_t need, SelScratch* sc, uint32_t* wsum) {
+__device__ __noinline__ void find_bin_desc(const Group<NT>& g, const uint32_t* hist, uint32_t need, SelScratch* sc, uint32_t* wsum) {
     constexpr int PER = SEL_BINS / NT;
     static_assert(PER >= 4 && PER % 4 == 0, "bins per thread");
     uint32_t c[PER];
@@ -39,6 +39,7 @@ __device__ void find_bin_desc(const Group<NT>& g, const uint32_t* hist, uint32_t
     if ((g.tid & 31) == 31) wsum[g.tid >> 5] = incl_w;
     g.sync();
     uint32_t before = 0;
+#pragma unroll 1
     for (int w = 0; w < (g.tid >> 5); ++w) before += wsum[w];
     const uint32_t incl = before + incl_w, excl = incl - s;
     if (excl < need && incl >= need) {
@@ -63,12 +64,13 @@ __device__ void find_bin_desc(const Group<NT>& g, const uint32_t* hist, uint32_t
 // hist: SEL_BINS words of shared scratch (also used as a list of up to SEL_LIST candidates).  Every thread of the
 // group calls it and gets the same answer.
 template <int NT>
-__device__ unsigned long long select_kth(const Group<NT>& g, const unsigned long long* buf, uint32_t cnt, uint32_t K,
+__device__ __noinline__ unsigned long long select_kth(const Group<NT>& g, const unsigned long long* buf, uint32_t cnt, uint32_t K,
                                          uint32_t* hist, SelScratch* sc) {
     if (g.tid == 0) sc->lo = ~0ull, sc->hi = 0ull;
     g.sync();
     {
         unsigned long long lo = ~0ull, hi = 0ull;
+#pragma unroll 1
         for (uint32_t i = g.tid; i < cnt; i += NT) {
             const unsigned long long c = buf[i];
             lo = c < lo ? c : lo, hi = c > hi ? c : hi;
@@ -83,13 +85,16 @@ __device__ unsigned long long select_kth(const Group<NT>& g, const unsigned long
     g.sync();
     unsigned long long lo = sc->lo, hi = sc->hi;
     uint32_t need = K;
+#pragma unroll 1
     for (int pass = 0; pass < 8; ++pass) {
         const unsigned long long range = hi - lo;
         if (range == 0) return lo;
         const int bits = 64 - __clzll((long long)range);
         const int sa = bits > 11 ? bits - 11 : 0;  // (range >> sa) < SEL_BINS
+#pragma unroll 1
         for (int i = g.tid; i < SEL_BINS / 4; i += NT) reinterpret_cast<uint4*>(hist)[i] = make_uint4(0, 0, 0, 0);
         g.sync();
+#pragma unroll 1
         for (uint32_t i = g.tid; i < cnt; i += NT) {
             const unsigned long long c = buf[i];
             if (c >= lo && c <= hi) atomicAdd(&hist[uint32_t((c - lo) >> sa)], 1u);
@@ -106,14 +111,17 @@ __device__ unsigned long long select_kth(const Group<NT>& g, const unsigned long
         nhi = nhi > hi ? hi : nhi;
         if (cb <= SEL_LIST) {
             unsigned long long* list = reinterpret_cast<unsigned long long*>(hist);
+#pragma unroll 1
             for (uint32_t i = g.tid; i < cnt; i += NT) {
                 const unsigned long long c = buf[i];
                 if (c >= nlo && c <= nhi) list[atomicAdd(&sc->lcnt, 1u)] = c;
             }
             g.sync();
+#pragma unroll 1
             for (uint32_t t = g.tid; t < cb; t += NT) {
                 const unsigned long long mine = list[t];
                 uint32_t rank = 0;
+#pragma unroll 1
                 for (uint32_t j = 0; j < cb; ++j) rank += list[j] > mine;
                 if (rank == need - 1) sc->kth = mine;
             }
@@ -128,11 +136,12 @@ __device__ unsigned long long select_kth(const Group<NT>& g, const unsigned long
 
 // Entries >= kth of buf[0..cnt) -> dst[0..), any order; after the call sc->wcnt holds how many.
 template <int NT>
-__device__ void write_survivors(const Group<NT>& g, const unsigned long long* buf, uint32_t cnt, unsigned long long kth,
+__device__ __noinline__ void write_survivors(const Group<NT>& g, const unsigned long long* buf, uint32_t cnt, unsigned long long kth,
                                 unsigned long long* dst, uint32_t dst_cap, SelScratch* sc) {
     if (g.tid == 0) sc->wcnt = 0;
     g.sync();
     const uint32_t rounds = (cnt + NT - 1) / NT;
+#pragma unroll 1
     for (uint32_t r = 0; r < rounds; ++r) {
         const uint32_t i = r * NT + g.tid;
         const unsigned long long c = i < cnt ? buf[i] : 0ull;
@@ -153,12 +162,15 @@ __device__ void write_survivors(const Group<NT>& g, const unsigned long long* bu
 // by two digit passes (11 + 11), low bits zero, so at least K elements have a key at or above the result.  NaN ranks
 // lowest.  hist: SEL_BINS words.
 template <int NT, typename T>
-__device__ uint32_t select_key_bound(const Group<NT>& g, const T* x, uint32_t n, uint32_t K, uint32_t* hist, SelScratch* sc) {
+__device__ __noinline__ uint32_t select_key_bound(const Group<NT>& g, const T* x, uint32_t n, uint32_t K, uint32_t* hist, SelScratch* sc) {
     uint32_t prefix = 0, mask = 0, need = K;
     const int shifts[2] = {21, 10};
+#pragma unroll 1
     for (int ps = 0; ps < 2; ++ps) {
+#pragma unroll 1
         for (int i = g.tid; i < SEL_BINS / 4; i += NT) reinterpret_cast<uint4*>(hist)[i] = make_uint4(0, 0, 0, 0);
         g.sync();
+#pragma unroll 1
         for (uint32_t i = g.tid; i < n; i += NT) {
             const float v = sizeof(T) == 4 ? reinterpret_cast<const float*>(x)[i] : bf16_to_f32(reinterpret_cast<const uint16_t*>(x)[i]);
             const uint32_t k = key_of(v);

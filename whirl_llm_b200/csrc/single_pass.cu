@@ -1,30 +1,39 @@
-// The single-pass fused sampler: every logits row is read from HBM once, by plain 128-bit loads.
+// The single-pass fused sampler: every logits row is read from HBM once, through a ring of shared-memory stages
+// filled by bulk async copies (TMA, cp.async.bulk + mbarrier).
 //
-// One persistent CTA per SM, two roles that never meet at a CTA-wide barrier while rows stream:
-//   stream warps (16)   Each thread keeps P_PF tiles of 64 bytes on their way from global memory in registers (a software
-//                       pipeline that runs on across row boundaries), folds every tile into a per-lane running maximum
-//                       (and, where the row needs its softmax normaliser, a running sum of exponentials), and tests the
-//                       tile's maximum against the row's threshold.  The few logits at or above the threshold are
-//                       appended to the row's candidate log in shared memory.
-//   tail group (8 warps) Before a row streams: its first threshold, from a strided sample of the row (the "scout": the K-th
-//                       largest of a sample is reached by at least K logits of the row), and, with penalties, a bit map of
-//                       the row's history tokens.  While it streams: the exact K-th largest of the log so far is a valid
-//                       and ever tighter threshold.  When it is through: the penalised history tokens join the log, the
-//                       exact K best are ranked, then top-k / top-p / min-p in f64, the draw and the row's outputs.
-// The two roles work on alternating row slots (two logs, two bit maps), so the tail of one row overlaps the streaming of
-// the next.
+// One persistent CTA per SM, three roles that never meet at a CTA-wide barrier while rows stream:
+//   producer (1 thread)  bulk copies of 16 KiB stages of the CTA's rows into the ring, running ahead across row boundaries.
+//   stream warps (16)    consume the stages, two per iteration: per-lane running maxima (the two largest iteration maxima;
+//                        and, where the row needs its softmax normaliser, a running sum of exponentials) and a threshold
+//                        test on the maximum of what the lane just read.  The few logits at or above the threshold are
+//                        appended to the row's candidate log.  The threshold comes from the warps themselves: each names
+//                        the r-th largest of its 64 lane maxima, r = ceil(K / 16), and the smallest of the 16 warps' values
+//                        is reached by at least K logits of the row.  The warps agree on the first one after their first
+//                        iteration (its logits are still in registers and are tested afterwards: the one meeting per row)
+//                        and renew it, without meeting, each time the part of the row seen has grown by half.
+//   tail group (8 warps) when a row is through: its exact K best, ranked; then one warp does top-k / top-p / min-p in f64,
+//                        the draw and the row's outputs, while the others fetch the parameters of the row after the next
+//                        and prepare the penalties of the rows to come.
+// The roles work on alternating row slots (two logs, two word maps), so the tail of one row overlaps the streaming of the
+// next.
 //
 // Why a threshold from partial data is exact: an element is dropped only when it is below a value that at least K
 // elements of the same row reach, so the K best are always in the log; the final select over the log is exact.
 //
-// Penalties.  The tokens of a row's history are kept out of the stream (their raw logits must not count) and join the
-// row with their penalised values at its end.  A row that needs no normaliser looks the bit map up only for the rare
-// logit that passes the threshold; a row that needs one masks every quad of logits with four bits of the map.
+// Penalties.  A raw logit of a history token must count nowhere.  The tail group builds, a row ahead, a bit map of the
+// 16-byte words (4 f32 / 8 bf16 logits) that hold a history token, and, while the row streams, the table of the row's
+// distinct history tokens with their counts (open addressing, warp-aggregated inserts).  The stream warps test one bit per
+// word (one broadcast shared-memory load per warp and word).  Nothing of a row is ever fetched a second time from global
+// memory: random 16-byte reads at that rate are more than the memory can serve while it streams.
+//   * A row that needs no normaliser and whose penalties can only lower a logit (the usual case): a word with a history
+//     token counts for no bound, and one of its logits is looked at only when it passes the threshold raw; it is then
+//     logged with a mark, and the tail group applies the penalty to the few marked entries before it ranks the log.
+//   * Any other penalised row: the stream warps put the marked words aside (from their registers into a side buffer in
+//     global memory that stays in L2) and see -inf instead; the tail group brings them in at the end of the row, history
+//     tokens with their penalty, the others as they are.
 //
 // It replaces the reference's topk_rows kernel (seven passes over the row, kernels/shared/sample_cand_topk_rows.h:11-98),
 // the candidate download, and the host filter and draw (src/sampling/sampler.cpp:15-147).
-#include <type_traits>
-
 #include "kernels.h"
 #include "penalty.cuh"
 #include "select_smem.cuh"
@@ -32,44 +41,82 @@
 
 namespace wb {
 
-constexpr int P_SW = 16;                 // stream warps
-constexpr int P_ST = P_SW * 32;
+constexpr int Q_SW = 16;                 // stream warps
+constexpr int Q_ST = Q_SW * 32;
 #ifndef WB_TW
 #define WB_TW 8
 #endif
-constexpr int P_TW = WB_TW;              // tail warps
-constexpr int P_TT = P_TW * 32;
-constexpr int P_THREADS = P_ST + P_TT;
-#ifndef WB_PF
-#define WB_PF 2
+constexpr int Q_TW = WB_TW;              // tail warps
+constexpr int Q_TT = Q_TW * 32;
+constexpr int Q_THREADS = 32 + Q_ST + Q_TT;  // producer warp, stream warps, tail group
+constexpr int Q_SB = 16384;              // bytes per ring stage
+constexpr int Q_SQ = Q_SB / 16;          // 128-bit words per stage
+constexpr int Q_MAXSTAGES = 8;
+#ifndef WB_NS
+#define WB_NS 2
 #endif
-constexpr int P_PF = WB_PF;              // tiles on their way per stream thread (64 bytes each)
-constexpr int P_L = 4096;                // candidate log entries per row slot
-constexpr int P_RED = P_SW + P_TW;       // partial (max, exponent, sum) triples per row: stream warps, then tail warps
+constexpr int Q_NS = WB_NS;              // ring stages per iteration of a stream warp
+#ifndef WB_QL
+#define WB_QL 3072
+#endif
+constexpr int Q_L = WB_QL;               // candidate log entries per row slot
+constexpr int Q_RED = Q_SW + Q_TW;       // partial (max, exponent, sum) triples per row: stream warps, then tail warps
+constexpr int Q_PT = Q_TT - 32;          // tail threads that prepare penalties (all tail warps but the first)
+static_assert(Q_SQ == 2 * Q_ST, "two 128-bit words per stream thread and stage");
 
-struct PSlot {
+// What the roles need to know about a row, fetched once (by one tail warp, a row ahead) into shared memory: while the rows
+// stream a load from global memory takes microseconds, so nobody on the path of a row reads parameters from there.
+struct QRow {
+    int32_t row;             // index in the batch
+    uint32_t K;              // candidates wanted
+    uint32_t top_k;
+    uint32_t flags;          // QF_*
+    float inv_t;
+    float rep, pres, freq;
+    int32_t hist_len;        // clamped; 0 without penalties
+    double top_p, min_p, u;
+    unsigned long long race_key;
+};
+// QF_LAZY: penalised, no normaliser wanted, and the penalties can only lower a logit (repetition >= 1, presence and
+// frequency >= 0): a history token then matters only if its RAW logit passes the threshold, which the stream sees.
+enum : uint32_t { QF_NO_SUM = 1u, QF_PEN = 2u, QF_GREEDY = 4u, QF_LAZY = 8u };
+
+struct QSlot {
     unsigned long long tau;  // current threshold candidate; elements must beat it to be logged
-    uint32_t cnt;            // log entries reserved so far (may exceed P_L: overflow); bit 31: a NaN poisoned a sum
-    int32_t row;
-    float red_m[P_RED];
-    float red_e[P_RED];
-    double red_s[P_RED];
-    uint32_t wbound[P_SW];   // per stream warp: its own lower bound (an ordering key)
+    uint32_t cnt;            // log entries reserved so far (may exceed Q_L: overflow); bit 31: a NaN poisoned a sum
+    uint32_t side_cnt;       // words put aside in the side buffer (penalised rows that need their normaliser)
+    QRow cfg;
+    float red_m[Q_RED];
+    float red_e[Q_RED];
+    double red_s[Q_RED];
+    uint32_t wbound[Q_SW];   // per stream warp: its own lower bound (an ordering key)
 };
 
-struct PShared {
-    PSlot slot[2];
+constexpr int Q_MAXR = 512;  // rows per CTA and launch
+
+// The word map's layout: bit `lane` of map word ((it * Q_SW + warp) * 4 + j) is the 128-bit word the stream thread
+// (warp, lane) reads as its j-th of iteration it, so one 128-bit shared-memory load per warp and iteration gives the
+// thread its four bits.  (Needs two stages per iteration.)
+static_assert(Q_NS == 2, "the word map is laid out for two stages per iteration");
+__device__ __forceinline__ uint32_t gbm_word_of(uint32_t wq) {
+    const uint32_t it = wq / (2 * Q_SQ), in = wq % (2 * Q_SQ);
+    return ((it * Q_SW + (in % Q_ST) / 32) << 2) | (in / Q_ST);
+}
+
+struct QShared {
+    QSlot slot[2];
     SelScratch sel;
     TailOut res;
     uint32_t flag[4];
-    uint32_t sbound[P_TW];   // the scout's per-warp bounds
+    uint32_t lcount[32];      // building the row list: rows kept per warp
+    int32_t n_list;
+    int32_t rlist[Q_MAXR];    // the CTA's rows, in order (rows left to the multi-pass kernel are not in it)
 };
 
 __device__ __forceinline__ unsigned long long ldv_u64(const unsigned long long* p) {
     return *reinterpret_cast<const volatile unsigned long long*>(p);
 }
 __device__ __forceinline__ uint32_t ldv_u32(const uint32_t* p) { return *reinterpret_cast<const volatile uint32_t*>(p); }
-__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
 
 // Called by one warp of every CTA once all the CTA's rows have their status.  The CTA that gets here last lists the rows
 // the multi-pass kernel has to take (a.fin_list, a.fin_counts[1]; bit 30: redo at the first level), so that no helper
@@ -128,82 +175,168 @@ __device__ __forceinline__ uint32_t warp_rth_largest(uint32_t (&kv)[G], uint32_t
     return kr;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(P_THREADS, 1) single_pass_kernel(SelectArgs a, int bm_words, int max_k) {
-    extern __shared__ __align__(128) uint8_t smem[];
-    constexpr int VE = 16 / int(sizeof(T));      // logits per 128-bit load
-    constexpr uint32_t TILE_Q = P_ST * 4;        // 128-bit words per tile
-    unsigned long long* logs = reinterpret_cast<unsigned long long*>(smem);              // 2 * P_L
-    uint32_t* hist = reinterpret_cast<uint32_t*>(logs + 2 * P_L);                        // SEL_BINS
-    unsigned long long* hand = reinterpret_cast<unsigned long long*>(hist + SEL_BINS);   // max_k: a row's candidates
-    double* tail_p = reinterpret_cast<double*>(hand + max_k);                            // max_k + 2 * P_TW
-    double* tail_q = tail_p + max_k + 2 * P_TW;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tail_q + max_k + 2 * P_TW);             // 4
-    PShared* sh = reinterpret_cast<PShared*>(bars + 4);
-    uint32_t* bitmaps = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));  // 2 * bm_words
-    uint32_t* pslots = bitmaps + 2 * size_t(bm_words);                                   // kPenSlots (only with penalties)
-    uint64_t *boot_done = bars, *closed = bars + 2;  // per slot: the slot is the row's / every stream warp is through the row
+// ---- the table of a row's distinct history tokens: (token + 1) | count << 19, open addressing, kPenSlots words
+__device__ __forceinline__ void pen_table_insert(uint32_t* pslots, uint32_t t, uint32_t c) {
+    const uint32_t tag = t + 1;
+    uint32_t hsh = PenaltyTable::hash(t);
+#pragma unroll 1
+    for (int probe = 0; probe < kPenSlots; ++probe) {
+        uint32_t old = ldv_u32(&pslots[hsh]);
+        if (old == 0) old = atomicCAS(&pslots[hsh], 0u, tag | (c << kPenIdBits));
+        if (old == 0) return;
+        if ((old & kPenMaxV) == tag) {
+            atomicAdd(&pslots[hsh], c << kPenIdBits);
+            return;
+        }
+        hsh = (hsh + 1) & (kPenSlots - 1);
+    }
+}
+// occurrences of token id in the history (0: not a history token)
+__device__ __forceinline__ uint32_t pen_table_count(const uint32_t* pslots, uint32_t id) {
+    const uint32_t tag = id + 1;
+    uint32_t hsh = PenaltyTable::hash(id);
+#pragma unroll 1
+    for (int probe = 0; probe < kPenSlots; ++probe) {
+        const uint32_t sv = pslots[hsh];
+        if (sv == 0) return 0u;
+        if ((sv & kPenMaxV) == tag) return sv >> kPenIdBits;
+        hsh = (hsh + 1) & (kPenSlots - 1);
+    }
+    return 0u;
+}
 
-    const int tid = threadIdx.x;
+// One candidate into a row's log, if it beats the threshold (x is a number: the caller has compared it).
+// unsure: the logit comes from a word that holds a history token and is logged raw; bit 31 of the entry's low half (always
+// set otherwise: it is ~id) is cleared to say so, and the tail group looks the token up before it ranks the log.
+__device__ __forceinline__ void log_append(QSlot* sl, unsigned long long* log, float x, uint32_t id, unsigned long long tau,
+                                           bool unsure = false) {
+    const uint32_t u = __float_as_uint(x + 0.0f);  // -0 + +0 = +0: the two zeros share a key
+    const uint32_t key = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    unsigned long long cnd = make_cand(key, id);
+    if (cnd > tau) {
+        if (unsure) cnd &= ~0x80000000ull;
+        const uint32_t pos = atomicAdd(&sl->cnt, 1u) & 0x7fffffffu;
+        if (pos < uint32_t(Q_L)) log[pos] = cnd;
+    }
+}
+__device__ __forceinline__ float penalised(float l, uint32_t cnt, float rep, float pres, float freq) {
+    l = (l > 0.f) ? __fdiv_rn(l, rep) : __fmul_rn(l, rep);
+    return __fsub_rn(l, __fadd_rn(pres, __fmul_rn(freq, float(cnt))));
+}
+
+// A 128-bit word w (place wq in the row) that was kept out of the stream comes into its row: history tokens with their
+// penalty, the others as they are: into the caller's running maximum / sum, and into the log when they can be among the
+// K best.
+struct JoinCtx {
+    const uint32_t* pslots;
+    QSlot* sl;
+    unsigned long long* log;
+    float rep, pres, freq, cexp;
+    bool no_sum;
+    float m_t, e_t, s_t;
+    unsigned long long tau;
+    float tau_f;
+};
+template <int VE>
+__device__ __forceinline__ void join_word(JoinCtx& c, uint32_t wq, uint4 w) {
+    const uint32_t w4[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int j = 0; j < VE; ++j) {
+        const uint32_t cnt = pen_table_count(c.pslots, wq * VE + j);
+        float l;
+        if (VE == 4) l = __uint_as_float(w4[j]);
+        else l = __uint_as_float((j & 1) ? (w4[j >> 1] & 0xffff0000u) : (w4[j >> 1] << 16));
+        const float x = cnt ? penalised(l, cnt, c.rep, c.pres, c.freq) : l;
+        if (!c.no_sum) {
+            if (x > c.m_t) {
+                const float ne = ceilf(x * c.cexp);
+                c.s_t = (c.m_t == -INFINITY) ? 0.f : c.s_t * ex2_approx(c.e_t - ne);
+                c.e_t = ne, c.m_t = x;
+            }
+            if (c.m_t != -INFINITY) c.s_t += ex2_approx(fmaf(x, c.cexp, -c.e_t));
+        }
+        if (x >= c.tau_f) log_append(c.sl, c.log, x, wq * VE + j, c.tau);
+    }
+}
+
+#ifdef WB_PROF
+#define PROF_T0(v) const long long v = clock64()
+#define PROF_ADD(i, v) do { if (g.tid == 0) prof[i] += clock64() - (v); } while (0)
+#else
+#define PROF_T0(v)
+#define PROF_ADD(i, v)
+#endif
+
+template <typename T>
+__global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a, int stages, int gbm_words, int max_k) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    constexpr int VE = 16 / int(sizeof(T));      // logits per 128-bit word
+    uint8_t* ring = smem;                                                                // stages * Q_SB
+    unsigned long long* logs = reinterpret_cast<unsigned long long*>(ring + size_t(stages) * Q_SB);  // 2 * Q_L
+    uint32_t* hist = reinterpret_cast<uint32_t*>(logs + 2 * Q_L);                        // SEL_BINS
+    unsigned long long* hand = reinterpret_cast<unsigned long long*>(hist + SEL_BINS);   // max_k: a row's candidates
+    double* tail_p = reinterpret_cast<double*>(hand + max_k);                            // max_k + 2 * Q_TW
+    double* tail_q = tail_p + max_k + 2 * Q_TW;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail_q + max_k + 2 * Q_TW);             // 2 * Q_MAXSTAGES + 6
+    QShared* sh = reinterpret_cast<QShared*>(bars + 2 * Q_MAXSTAGES + 6);
+    uint32_t* gbms = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));  // 2 * gbm_words
+    uint32_t* pslots = gbms + 2 * size_t(gbm_words);                                     // kPenSlots (only with penalties)
+    uint64_t *full = bars, *empty = bars + Q_MAXSTAGES;
+    // per slot: the slot is the row's / every stream warp is through the row / every stream warp has named its first bound
+    uint64_t *boot_done = bars + 2 * Q_MAXSTAGES, *closed = boot_done + 2, *head_done = boot_done + 4;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
     const uint32_t n = uint32_t(a.n);
     const int n_rows = a.row_count ? min(*a.row_count, a.rows) : a.rows;
     const int my_rows = n_rows > int(blockIdx.x) ? (n_rows - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
     const uint32_t row_q = n / VE;  // 128-bit words per row (rows are 16-byte multiples)
-    const uint32_t n_tiles = (row_q + TILE_Q - 1) / TILE_Q;
+    const uint32_t n_chunks = (row_q + Q_SQ - 1) / Q_SQ;
+    const size_t row_bytes = size_t(n) * sizeof(T);
     const bool sample = a.mode == MODE_SAMPLE;
     const RowParams& P = a.prm;
-    auto row_of = [&](int k) -> int {
-        const int li = int(blockIdx.x) + k * int(gridDim.x);
-        return a.row_list ? a.row_list[li] : li;
-    };
-    // rows whose top_k is above this launch's limit are left to the multi-pass kernel (both roles skip them alike)
-    auto is_large = [&](int row) -> bool {
-        if (!sample || !P.top_k) return false;
-        if (P.greedy && P.greedy[row]) return false;
-        return P.top_k[row] > max_k;
-    };
-    auto next_row = [&](int k) -> int {
-        for (++k; k < my_rows && is_large(row_of(k)); ++k) {}
-        return k;
-    };
-    // candidates wanted for a row (both roles must agree)
-    auto k_of = [&](int row) -> uint32_t {
-        uint32_t K;
-        if (sample) {
-            const bool greedy = P.greedy && P.greedy[row];
-            const uint32_t tk = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
-            K = greedy ? 1u : ((tk > 0 && tk <= uint32_t(max_k)) ? tk : uint32_t(min(a.level_k, max_k)));
-        } else {
-            K = uint32_t(a.K);
-        }
-        return K > n ? n : K;
-    };
-    // Rows whose kept set is closed by their own top_k need no softmax normaliser: every probability the filter compares
-    // is a ratio inside the candidate set, so the row sum cancels.  When the caller does not ask for the row statistics
-    // either, the stream warps skip the exponentials and the tail normalises over the candidates.
-    auto no_sum_row = [&](int row) -> bool {
-        if (!sample) return false;
-        if (P.greedy && P.greedy[row]) return true;
-        if (a.out.stats || !P.top_k) return false;
-        const int tk = P.top_k[row];
-        return tk >= 1 && tk <= max_k && uint32_t(tk) <= n;
-    };
-    // does the row have penalties to apply (both roles must agree)
-    auto pen_row = [&](int row) -> bool {
-        if (!sample || !P.hist || bm_words == 0 || P.hist_len[row] <= 0) return false;
-        const float r = P.rep ? P.rep[row] : 1.f, pr = P.pres ? P.pres[row] : 0.f, fr = P.freq ? P.freq[row] : 0.f;
-        return r != 1.f || pr != 0.f || fr != 0.f;
-    };
+    // the CTA's side buffers (one per slot): kMaxHist words and their places in the row
+    uint8_t* const side_base = static_cast<uint8_t*>(a.side_ws) + size_t(blockIdx.x) * 2 * kMaxHist * 20;
+    auto side_w = [&](int p) { return reinterpret_cast<uint4*>(side_base + size_t(p) * kMaxHist * 20); };
+    auto side_q = [&](int p) { return reinterpret_cast<uint32_t*>(side_base + size_t(p) * kMaxHist * 20 + size_t(kMaxHist) * 16); };
 
     if (tid == 0) {
-        for (int p = 0; p < 2; ++p) mbar_init(&boot_done[p], 1), mbar_init(&closed[p], P_SW);
+        for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], Q_SW);
+        for (int p = 0; p < 2; ++p) mbar_init(&boot_done[p], 1), mbar_init(&closed[p], Q_SW), mbar_init(&head_done[p], Q_SW);
         mbar_fence_init();
     }
-    for (int i = tid; i < 2 * P_L; i += P_THREADS) logs[i] = 0ull;
+    for (int i = tid; i < 2 * Q_L; i += Q_THREADS) logs[i] = 0ull;
+    for (int i = tid; i < 2 * gbm_words; i += Q_THREADS) gbms[i] = 0u;
+    // ---- the CTA's rows: rows blockIdx.x, + gridDim.x, ...; rows whose top_k is above this launch's limit are left to the
+    // multi-pass kernel (marked here, not listed).  my_rows <= Q_MAXR <= Q_THREADS: one row per thread.
+    {
+        const int k = tid;
+        int row = -1;
+        bool keep = false;
+        if (k < my_rows) {
+            const int li = int(blockIdx.x) + k * int(gridDim.x);
+            row = a.row_list ? a.row_list[li] : li;
+            keep = true;
+            if (sample && P.top_k && !(P.greedy && P.greedy[row]) && P.top_k[row] > max_k) {
+                keep = false;
+                if (a.out.status) a.out.status[row] = ROW_LARGE_K;
+            }
+        }
+        const uint32_t bal = __ballot_sync(0xffffffffu, keep);
+        if ((tid & 31) == 0 && warp < 32) sh->lcount[warp] = uint32_t(__popc(bal));
+        __syncthreads();
+        uint32_t before = 0;
+        for (int w = 0; w < warp && w < 32; ++w) before += sh->lcount[w];
+        if (keep) sh->rlist[before + __popc(bal & ((1u << (tid & 31)) - 1))] = row;
+        if (tid == 0) {
+            uint32_t tot = 0;
+            for (int w = 0; w < (Q_THREADS + 31) / 32 && w < 32; ++w) tot += sh->lcount[w];
+            sh->n_list = int32_t(tot);
+        }
+    }
     __syncthreads();
-    if (my_rows == 0 || next_row(-1) >= my_rows) {
-        if (a.out.status && sample)
-            for (int k = tid; k < my_rows; k += P_THREADS) a.out.status[row_of(k)] = ROW_LARGE_K;
+    const int n_list = sh->n_list;
+    const int32_t* rlist = sh->rlist;
+    if (n_list == 0) {
         if (a.fin_list) {
             __threadfence();
             __syncthreads();
@@ -212,376 +345,481 @@ __global__ void __launch_bounds__(P_THREADS, 1) single_pass_kernel(SelectArgs a,
         return;
     }
 
-    // =========================================================== tail group
-    if (tid >= P_ST) {
-        const Group<P_TT> g{tid - P_ST, 1};
-        const int lane = lane_id(), tw = g.tid >> 5;
+    // =========================================================== producer
+    if (warp == 0) {
+        if (lane_id() != 0) return;
+        uint32_t s = 0, par = 1;  // ring stage and the parity of its "empty" barrier to wait for
+        const uint64_t once = l2_evict_first_policy();
+#ifdef WB_PROF
+        long long pw = 0;
+        const long long pt0 = clock64();
+#endif
+#pragma unroll 1
+        for (int i = 0; i < n_list; ++i) {
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x) + size_t(rlist[i]) * row_bytes;
+            uint32_t left = uint32_t(row_bytes);  // (a row is below 4 GiB: n < 2^30 elements of at most 4 bytes)
+#pragma unroll 1
+            for (uint32_t c = 0; c < n_chunks; ++c) {
+#ifdef WB_PROF
+                const long long pw0 = clock64();
+#endif
+                if (!mbar_wait(&empty[s], par)) {
+                    atomicExch(a.err, 1u);
+                    return;
+                }
+#ifdef WB_PROF
+                pw += clock64() - pw0;
+#endif
+                const uint32_t bytes = left < uint32_t(Q_SB) ? left : uint32_t(Q_SB);
+                mbar_expect_tx(&full[s], bytes);
+                bulk_g2s_once(ring + size_t(s) * Q_SB, src, bytes, &full[s], once);
+                src += Q_SB, left -= bytes;
+                if (++s == uint32_t(stages)) s = 0, par ^= 1u;
+            }
+        }
+#ifdef WB_PROF
+        {
+            unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 16);
+            atomicAdd(&dbg[12], (unsigned long long)pw), atomicAdd(&dbg[13], (unsigned long long)(clock64() - pt0));
+        }
+#endif
+        return;
+    }
 
-        // ---- a slot becomes a row's: the history bit map, the first threshold (the scout), an empty log
-        auto boot = [&](int k, int o) {
-            const int p = o & 1;
-            PSlot* sl = &sh->slot[p];
-            const int row = row_of(k);
-            const uint32_t K = k_of(row);
-            const bool pen_on = pen_row(row);
-            uint32_t* bm = bitmaps + size_t(p) * bm_words;
-            if (pen_on) {
-                const uint4 z = make_uint4(0, 0, 0, 0);
-                for (int i = g.tid; i < bm_words / 4; i += P_TT) reinterpret_cast<uint4*>(bm)[i] = z;
-                g.sync();
-                const int32_t* h = P.hist + size_t(row) * P.hist_stride;
-                int hl = P.hist_len[row];
-                hl = int64_t(hl) > P.hist_stride ? int(P.hist_stride) : hl;
-                hl = hl > kMaxHist ? kMaxHist : hl;
-                for (int i = g.tid; i < hl; i += P_TT) {
-                    const uint32_t t = uint32_t(h[i]);
-                    if (t < n) atomicOr(&bm[t >> 5], 1u << (t & 31));
+    // =========================================================== tail group
+    if (warp > Q_SW) {
+        const Group<Q_TT> g{tid - 32 - Q_ST, 1};
+        const Group<Q_PT> gp{g.tid - 32, 2};  // the tail warps but the first
+        const int lane = lane_id(), tw = g.tid >> 5;
+#ifdef WB_PROF
+        long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // wait, join, select, draw, prepare, refine, rows, total
+        const long long prof_begin = clock64();
+#endif
+
+        // ---- a row's parameters come into the slot it will stream through (one warp, every lane fetching one of them)
+        auto fetch_params = [&](int p, int row) {
+            QSlot* sl = &sh->slot[p];
+            // lane: 0 inv_t, 1 top_k, 2 greedy, 3 top_p, 4 min_p, 5 u, 6 race_key, 7 hist_len, 8 rep, 9 pres, 10 freq
+            unsigned long long v = 0ull;
+            if (lane == 0) v = __float_as_uint(P.inv_t ? P.inv_t[row] : P.inv_t_scalar);
+            if (sample) {
+                if (lane == 1) v = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
+                if (lane == 2) v = (P.greedy && P.greedy[row]) ? 1u : 0u;
+                if (lane == 3) v = (unsigned long long)__double_as_longlong(P.top_p ? P.top_p[row] : 1.0);
+                if (lane == 4) v = (unsigned long long)__double_as_longlong(P.min_p ? P.min_p[row] : 0.0);
+                if (lane == 5) v = (unsigned long long)__double_as_longlong(P.u ? P.u[row] : 0.0);
+                if (lane == 6) v = P.race_key ? P.race_key[row] : 0ull;
+                if (lane == 7 && P.hist && gbm_words) {
+                    int hl = P.hist_len[row];
+                    hl = hl < 0 ? 0 : hl;
+                    hl = int64_t(hl) > P.hist_stride ? int(P.hist_stride) : hl;
+                    v = uint32_t(hl > kMaxHist ? kMaxHist : hl);
                 }
-                g.sync();
+                if (lane == 8) v = __float_as_uint(P.rep ? P.rep[row] : 1.f);
+                if (lane == 9) v = __float_as_uint(P.pres ? P.pres[row] : 0.f);
+                if (lane == 10) v = __float_as_uint(P.freq ? P.freq[row] : 0.f);
             }
-            // The scout: 32 logits per thread, 8192 per row, in chunks of one warp-wide load spread evenly over the row
-            // (the whole row when it is no longer than that).  Every thread keeps the maxima of its four groups of eight;
-            // each warp names the r-th largest of what it holds, r = ceil(K / warps): the smallest of those bounds is
-            // reached by at least K distinct logits of the row.  History tokens do not count (bit map).
-            constexpr int SC_LD = 32 / VE;                 // loads per thread
-            constexpr uint32_t NC = SC_LD * P_TW;           // chunks
-            constexpr uint32_t CE = 32 * VE;                // logits per chunk
-            const uint4* xr = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.x) + size_t(row) * n);
-            uint4 sv[SC_LD];
-            uint32_t sid[SC_LD];
-#pragma unroll
-            for (int l = 0; l < SC_LD; ++l) {
-                const uint32_t c = uint32_t(l) * P_TW + uint32_t(tw);
-                const uint32_t start = n <= NC * CE ? c * CE : uint32_t((uint64_t(c) * n) / NC) & ~uint32_t(VE - 1);
-                sid[l] = start + uint32_t(lane) * VE;
-                const uint32_t nw = sizeof(T) == 4 ? 0xff800000u : 0xff80ff80u;  // -inf
-                sv[l] = sid[l] + VE <= n ? __ldg(xr + sid[l] / VE) : make_uint4(nw, nw, nw, nw);
+            const float inv_t = __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, v, 0)));
+            const uint32_t top_k = uint32_t(__shfl_sync(0xffffffffu, v, 1));
+            const bool greedy = __shfl_sync(0xffffffffu, v, 2) != 0;
+            const unsigned long long top_p = __shfl_sync(0xffffffffu, v, 3), min_p = __shfl_sync(0xffffffffu, v, 4);
+            const unsigned long long u = __shfl_sync(0xffffffffu, v, 5), race_key = __shfl_sync(0xffffffffu, v, 6);
+            const int hist_len = int(uint32_t(__shfl_sync(0xffffffffu, v, 7)));
+            const float rep = sample ? __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, v, 8))) : 1.f;
+            const float pres = __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, v, 9)));
+            const float freq = __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, v, 10)));
+            if (lane == 0) {
+                QRow c;
+                c.row = row, c.top_k = top_k, c.inv_t = inv_t;
+                // candidates wanted: the row's own top_k when it fits, else the first level's
+                uint32_t K = sample ? (greedy ? 1u : ((top_k > 0 && top_k <= uint32_t(max_k)) ? top_k : uint32_t(min(a.level_k, max_k)))) : uint32_t(a.K);
+                c.K = K > n ? n : K;
+                // Rows whose kept set is closed by their own top_k need no softmax normaliser: every probability the filter
+                // compares is a ratio inside the candidate set, so the row sum cancels.  When the caller does not ask for the
+                // row statistics either, the stream warps skip the exponentials and the tail normalises over the candidates.
+                const bool no_sum = sample && (greedy || (!a.out.stats && P.top_k && top_k >= 1 && top_k <= uint32_t(max_k) && top_k <= n));
+                const bool pen = sample && hist_len > 0 && (rep != 1.f || pres != 0.f || freq != 0.f);
+                const bool lazy = pen && no_sum && rep >= 1.f && pres >= 0.f && freq >= 0.f;
+                c.flags = (no_sum ? QF_NO_SUM : 0u) | (pen ? QF_PEN : 0u) | (greedy ? QF_GREEDY : 0u) | (lazy ? QF_LAZY : 0u);
+                c.rep = rep, c.pres = pres, c.freq = freq, c.hist_len = pen ? hist_len : 0;
+                c.top_p = __longlong_as_double((long long)top_p), c.min_p = __longlong_as_double((long long)min_p);
+                c.u = __longlong_as_double((long long)u), c.race_key = race_key;
+                sl->cfg = c;
             }
-            float gm[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-            for (int l = 0; l < SC_LD; ++l) {
-                float v[VE];
-                const uint32_t w4[4] = {sv[l].x, sv[l].y, sv[l].z, sv[l].w};
-                if (sizeof(T) == 4) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) v[j] = __uint_as_float(w4[j]);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) v[2 * j] = __uint_as_float(w4[j] << 16), v[2 * j + 1] = __uint_as_float(w4[j] & 0xffff0000u);
-                }
-                if (pen_on && sid[l] < n) {
-                    const uint32_t bits = (bm[sid[l] >> 5] >> (sid[l] & 31)) & ((1u << VE) - 1);
-#pragma unroll
-                    for (int j = 0; j < VE; ++j)
-                        if ((bits >> j) & 1u) v[j] = -INFINITY;
-                }
-                float mx = v[0];
-#pragma unroll
-                for (int j = 1; j < VE; ++j) mx = fmaxf(mx, v[j]);
-                const int grp = l * 4 / SC_LD;  // f32: two loads per group of eight; bf16: one
-                gm[grp] = fmaxf(gm[grp], mx);
-            }
-            // (a group that is all -inf, e.g. past the end of a short row, must not count as an element: key 0)
-            const uint32_t r = (K + P_TW - 1) / P_TW;
-            uint32_t kb = 0;
-            if (r <= 8) {
-                uint32_t kv[1];
-                const float mx = fmaxf(fmaxf(gm[0], gm[1]), fmaxf(gm[2], gm[3]));
-                kv[0] = mx == -INFINITY ? 0u : key_of(mx);
-                kb = warp_rth_largest<1>(kv, r);
-            } else if (r <= 64) {
-                uint32_t kv[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) kv[j] = gm[j] == -INFINITY ? 0u : key_of(gm[j]);
-                kb = warp_rth_largest<4>(kv, r);
-            }
-            if (lane == 0) sh->sbound[tw] = kb;
-            g.sync();
-            if (g.tid == 0) {
-                uint32_t kmin = 0xffffffffu;
-                for (int w = 0; w < P_TW; ++w) kmin = min(kmin, sh->sbound[w]);
-                sl->tau = (unsigned long long)kmin << 32;
-                sl->cnt = 0;
-                sl->row = row;
-                for (int w = 0; w < P_SW; ++w) sl->wbound[w] = 0u;
-                mbar_arrive(&boot_done[p]);
-            }
-            g.sync();
+            __syncwarp();
         };
 
-        // ---- raise a streaming row's threshold to the exact K-th largest of its log so far, when the log has grown
-        uint32_t rf_last[2] = {0, 0}, rf_step[2] = {0, 0};
-        auto maybe_refine = [&](int p, uint32_t K) {
-            PSlot* sl = &sh->slot[p];
+        // ---- a slot becomes a row's (the tail warps but the first; the slot's log and word map are zero): parameters, the
+        // map of the words that hold a history token, then the stream warps are told
+        auto slot_boot = [&](int p, int row) {
+            QSlot* sl = &sh->slot[p];
+            if (tw == 1) fetch_params(p, row);
+            gp.sync();
+            const int hl = sl->cfg.hist_len;  // (0 without penalties)
+            if (hl > 0) {
+                uint32_t* gbm = gbms + size_t(p) * gbm_words;
+                const int32_t* h = P.hist + size_t(row) * P.hist_stride;
+                constexpr int HB = (kMaxHist + Q_PT - 1) / Q_PT;
+                int32_t hv[HB];  // (all loads first: one trip to memory)
+#pragma unroll
+                for (int u = 0; u < HB; ++u) hv[u] = (u * Q_PT + gp.tid) < hl ? h[u * Q_PT + gp.tid] : -1;
+#pragma unroll
+                for (int u = 0; u < HB; ++u) {
+                    const uint32_t t = uint32_t(hv[u]);
+                    if (t < n) {
+                        const uint32_t wd = gbm_word_of(t / VE), bit = 1u << ((t / VE) & 31);
+                        if (!(ldv_u32(&gbm[wd]) & bit)) atomicOr(&gbm[wd], bit);
+                    }
+                }
+                gp.sync();
+            }
+            if (gp.tid == 0) {
+                sl->tau = 0ull;
+                sl->cnt = 0;
+                sl->side_cnt = 0;
+                for (int w = 0; w < Q_SW; ++w) sl->wbound[w] = 0u;
+                for (int w = Q_SW; w < Q_RED; ++w) sl->red_m[w] = -INFINITY, sl->red_e[w] = -INFINITY, sl->red_s[w] = 0.0;
+                mbar_arrive(&boot_done[p]);
+            }
+        };
+
+        // ---- the table of the distinct history tokens of the row in slot p, with their counts, for when the row is through
+        // (the tail warps but the first, while the row streams).  Equal tokens of one warp-wide step go in as one insert;
+        // the history comes through the select scratch (which nobody uses now), half of it at a time, so that the loads of a
+        // half are all on their way at once and the inserts are one rolled loop.
+        auto build_table = [&](int p) {
+            const QRow cfg = sh->slot[p].cfg;
+            if (!(cfg.flags & QF_PEN)) return;
+            constexpr int HALF = kMaxHist / 2;
+            constexpr int HP = (HALF + Q_PT - 1) / Q_PT;
+            static_assert(HALF <= SEL_BINS, "half a history fits the scratch");
+            const int32_t* h = P.hist + size_t(cfg.row) * P.hist_stride;
+            const int hl = cfg.hist_len;
+            int32_t* stage_h = reinterpret_cast<int32_t*>(hist);
+            for (int i = gp.tid; i < kPenSlots / 4; i += Q_PT) reinterpret_cast<uint4*>(pslots)[i] = make_uint4(0, 0, 0, 0);
+#pragma unroll 1
+            for (int half = 0; half * HALF < hl; ++half) {
+                int32_t hv[HP];
+#pragma unroll
+                for (int u = 0; u < HP; ++u) {
+                    const int i = half * HALF + u * Q_PT + gp.tid;
+                    hv[u] = (u * Q_PT + gp.tid < HALF && i < hl) ? h[i] : -1;
+                }
+#pragma unroll
+                for (int u = 0; u < HP; ++u)
+                    if (u * Q_PT + gp.tid < HALF) stage_h[u * Q_PT + gp.tid] = hv[u];
+                gp.sync();
+                const int cnt_h = min(HALF, hl - half * HALF);
+#pragma unroll 1
+                for (int base = 0; base < cnt_h; base += Q_PT) {
+                    const int i = base + gp.tid;
+                    const uint32_t t = i < cnt_h ? uint32_t(stage_h[i]) : 0xffffffffu;
+                    const bool valid = t < n;  // (negative ids too)
+                    const uint32_t peers = __match_any_sync(0xffffffffu, valid ? t : 0xfffffff0u - uint32_t(lane));
+                    if (valid && lane == __ffs(peers) - 1) pen_table_insert(pslots, t, uint32_t(__popc(peers)));
+                }
+                gp.sync();
+            }
+        };
+
+        // ---- raise a streaming row's threshold to the exact K-th largest of its log so far.  The stream warps keep the
+        // threshold close to that by themselves; this is for a log that fills up all the same.  (Not for a row whose log
+        // holds marked entries: their raw logits would count.)
+        uint32_t rf_last[2] = {0, 0};
+        auto maybe_refine = [&](int p, uint32_t K, bool allowed) {
+            QSlot* sl = &sh->slot[p];
             if (g.tid == 0) {
                 const uint32_t c = ldv_u32(&sl->cnt) & 0x7fffffffu;
-                sh->flag[2] = c < uint32_t(P_L) ? c : uint32_t(P_L);
+                sh->flag[2] = c < uint32_t(Q_L) ? c : uint32_t(Q_L);
             }
             g.sync();
             const uint32_t nlog = sh->flag[2];
             g.sync();
-            if (!(nlog >= K && nlog >= 64 && nlog >= rf_last[p] + rf_step[p])) return false;
+            const uint32_t step = 2 * K > uint32_t(Q_L) / 4 ? 2 * K : uint32_t(Q_L) / 4;
+            if (!allowed || !(nlog >= K && nlog >= rf_last[p] + step)) return false;
+            PROF_T0(tr0);
             // (entries reserved but not written yet read as zero and rank last: the bound stays valid)
-            const unsigned long long kth = select_kth<P_TT>(g, logs + size_t(p) * P_L, nlog, K, hist, &sh->sel);
+            const unsigned long long kth = select_kth<Q_TT>(g, logs + size_t(p) * Q_L, nlog, K, hist, &sh->sel);
             if (g.tid == 0 && kth > ldv_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = kth;
             rf_last[p] = nlog;
-            rf_step[p] = 2 * K > 128 ? 2 * K : 128;
             g.sync();
+            PROF_ADD(5, tr0);
             return true;
         };
 
-        if (sample && a.out.status)
-            for (int k = g.tid; k < my_rows; k += P_TT)
-                if (is_large(row_of(k))) a.out.status[row_of(k)] = ROW_LARGE_K;
-        {
-            const int k0 = next_row(-1);
-            boot(k0, 0);
-            const int k1 = next_row(k0);
-            if (k1 < my_rows) boot(k1, 1);
-        }
-        int ord = 0;
-        for (int k = next_row(-1); k < my_rows; ++ord) {
-            const int kn = next_row(k);
-            const int kn2 = kn < my_rows ? next_row(kn) : my_rows;
+        // order -1 is the start: nothing to finish, the first two rows' slots to hand out, the first row's table
+#pragma unroll 1
+        for (int ord = -1; ord < n_list; ++ord) {
             const int p = ord & 1;
-            PSlot* sl = &sh->slot[p];
-            unsigned long long* log = logs + size_t(p) * P_L;
-            const int row = row_of(k);
-            const uint32_t K = k_of(row);
-            const uint32_t K_next = kn < my_rows ? k_of(row_of(kn)) : 1u;
-            // ---- while the row streams: raise its threshold
-            for (uint32_t spin = 0;; ++spin) {
-                if (g.tid == 0) sh->flag[1] = mbar_try_wait(&closed[p], (ord >> 1) & 1) ? 1u : 0u;
-                g.sync();
-                const bool done = sh->flag[1] != 0;
-                g.sync();
-                if (done) break;
-                if (spin > (1u << 21)) {
-                    if (g.tid == 0) atomicExch(a.err, 3u);
-                    return;
-                }
-                if (!maybe_refine(p, K)) __nanosleep(500);
-            }
-            mbar_wait(&closed[p], (ord >> 1) & 1);  // acquire the stream warps' writes
-            rf_last[p] = rf_step[p] = 0;
-            // ---- the row is through
-            const bool greedy = sample && P.greedy && P.greedy[row];
-            const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
-            const bool no_sum = no_sum_row(row);
-            const bool pen_on = pen_row(row);
-            if (pen_on) {
-                // The row's distinct history tokens with their counts (an open-addressing table in shared memory), their raw
-                // logits from global memory, the penalty, and their place in the row: one more contributor per tail warp to the
-                // row's maximum and sum, and the tokens that can be among the K best go to the log.
-                const uint4 z = make_uint4(0, 0, 0, 0);
-                for (int i = g.tid; i < kPenSlots / 4; i += P_TT) reinterpret_cast<uint4*>(pslots)[i] = z;
-                g.sync();
-                {
-                    const int32_t* h = P.hist + size_t(row) * P.hist_stride;
-                    int hl = P.hist_len[row];
-                    hl = int64_t(hl) > P.hist_stride ? int(P.hist_stride) : hl;
-                    hl = hl > kMaxHist ? kMaxHist : hl;
-                    int32_t hv[kMaxHist / P_TT];
-#pragma unroll
-                    for (int u = 0; u < kMaxHist / P_TT; ++u) hv[u] = (g.tid + u * P_TT) < hl ? h[g.tid + u * P_TT] : -1;
-#pragma unroll
-                    for (int u = 0; u < kMaxHist / P_TT; ++u) {
-                        const uint32_t t = uint32_t(hv[u]);
-                        if (t >= n) continue;  // (negative ids too)
-                        const uint32_t tag = t + 1;
-                        uint32_t hsh = PenaltyTable::hash(t);
-                        for (int probe = 0; probe < kPenSlots; ++probe) {
-                            uint32_t old = ldv_u32(&pslots[hsh]);
-                            if (old == 0) old = atomicCAS(&pslots[hsh], 0u, tag | (1u << kPenIdBits));
-                            if (old == 0) break;
-                            if ((old & kPenMaxV) == tag) {
-                                atomicAdd(&pslots[hsh], 1u << kPenIdBits);
+            QSlot* sl = &sh->slot[p];
+            unsigned long long* log = logs + size_t(p) * Q_L;
+            QRow cfg;
+            uint32_t kept = 0, cap = 1;
+            bool presorted = false, overflow = false;
+            float M = -INFINITY, sum = 0.f;
+            if (ord >= 0) {
+                cfg = sl->cfg;
+                const uint32_t K = cfg.K;
+                const bool no_sum = (cfg.flags & QF_NO_SUM) != 0, pen_on = (cfg.flags & QF_PEN) != 0, lazy = (cfg.flags & QF_LAZY) != 0;
+                // ---- while the row streams
+                PROF_T0(tw0);
+                // (one thread watches the row; the others wait at the group's barrier, where they take no issue slot from the
+                // stream warps)
+#pragma unroll 1
+                for (;;) {
+                    if (g.tid == 0) {
+                        uint32_t what = 2u;  // 0: the row is through, 1: the log wants a refinement, 2: gave up
+                        const uint32_t step = 2 * K > uint32_t(Q_L) / 4 ? 2 * K : uint32_t(Q_L) / 4;
+#pragma unroll 1
+                        for (uint32_t spin = 0; spin < (1u << 21); ++spin) {
+                            if (mbar_try_wait(&closed[p], (ord >> 1) & 1)) {
+                                what = 0u;
                                 break;
                             }
-                            hsh = (hsh + 1) & (kPenSlots - 1);
+                            const uint32_t c = ldv_u32(&sl->cnt) & 0x7fffffffu;
+                            if (!lazy && c >= K && c >= rf_last[p] + step && c <= uint32_t(Q_L)) {
+                                what = 1u;
+                                break;
+                            }
+                            __nanosleep(300);
                         }
+                        sh->flag[1] = what;
                     }
+                    g.sync();
+                    const uint32_t what = sh->flag[1];
+                    g.sync();
+                    if (what == 0u) break;
+                    if (what == 2u) {
+                        if (g.tid == 0) atomicExch(a.err, 3u);
+                        return;
+                    }
+                    maybe_refine(p, K, true);
                 }
-                g.sync();
-                if (kn < my_rows) maybe_refine(p ^ 1, K_next);
-                const float pen_rep = P.rep ? P.rep[row] : 1.f, pen_pres = P.pres ? P.pres[row] : 0.f, pen_freq = P.freq ? P.freq[row] : 0.f;
-                const T* xr = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
-                const float cexp = inv_t * kLog2e;
-                float m_t = -INFINITY, e_t = 0.f, s_t = 0.f;
-                const unsigned long long tau = ldv_u64(&sl->tau);
-                const float tau_f = cand_key(tau) ? float_of_key(cand_key(tau)) : -INFINITY;
-                for (int base = 0; base < kPenSlots; base += 4 * P_TT) {
-                    const uint4 q = reinterpret_cast<const uint4*>(pslots + base)[g.tid];
-                    const uint32_t e4[4] = {q.x, q.y, q.z, q.w};
-                    float r4[4];
+                mbar_wait(&closed[p], (ord >> 1) & 1);  // acquire the stream warps' writes
+                PROF_ADD(0, tw0);
+                rf_last[p] = 0;
+                // ---- the row is through
+                if (pen_on) {
+                    PROF_T0(tj0);
+                    const unsigned long long tau = sl->tau;
+                    const float tau_f = cand_key(tau) ? float_of_key(cand_key(tau)) : -INFINITY;
+                    if (lazy) {
+                        // the marked entries of the log: logged raw from a word that holds a history token; a history token
+                        // gets its penalty now (another logit of such a word stays as it is)
+                        const uint32_t nl = min(sl->cnt & 0x7fffffffu, uint32_t(Q_L));
+#pragma unroll 1
+                        for (uint32_t i = g.tid; i < nl; i += Q_TT) {
+                            unsigned long long c = log[i];
+                            if (c != 0ull && !(c & 0x80000000ull)) {
+                                const uint32_t id = ~uint32_t(c) & 0x7fffffffu;
+                                const uint32_t cnt = pen_table_count(pslots, id);
+                                float x = float_of_key(cand_key(c));
+                                if (cnt) x = penalised(x, cnt, cfg.rep, cfg.pres, cfg.freq);
+                                log[i] = make_cand(key_of(x), id);
+                            }
+                        }
+                    } else {
+                        // the words put aside by the stream warps come in: history tokens with their penalty, the others as
+                        // they are; every tail warp is one more contributor to the row's maximum and sum
+                        const uint32_t ns = min(sl->side_cnt, uint32_t(kMaxHist));
+                        JoinCtx jc;
+                        jc.pslots = pslots, jc.sl = sl, jc.log = log;
+                        jc.rep = cfg.rep, jc.pres = cfg.pres, jc.freq = cfg.freq, jc.cexp = cfg.inv_t * kLog2e;
+                        jc.no_sum = no_sum;
+                        jc.m_t = -INFINITY, jc.e_t = 0.f, jc.s_t = 0.f;
+                        jc.tau = tau, jc.tau_f = tau_f;
+                        constexpr int PB = 2;  // words per thread and trip to memory
+#pragma unroll 1
+                        for (uint32_t base = 0; base < ns; base += PB * Q_TT) {
+                            uint32_t wq[PB];
+                            uint4 wv[PB];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {  // (the loads first, then the arithmetic)
-                        const uint32_t id = (e4[j] & kPenMaxV) - 1;
-                        r4[j] = 0.f;
-                        if (e4[j]) r4[j] = sizeof(T) == 4 ? __ldg(reinterpret_cast<const float*>(xr) + id) : bf16_to_f32(__ldg(reinterpret_cast<const uint16_t*>(xr) + id));
-                    }
+                            for (int j = 0; j < PB; ++j) {  // (the loads first, then the arithmetic)
+                                const uint32_t i = base + uint32_t(j) * Q_TT + uint32_t(g.tid);
+                                wq[j] = i < ns ? __ldcg(side_q(p) + i) : 0xffffffffu;
+                                wv[j] = i < ns ? __ldcg(side_w(p) + i) : make_uint4(0, 0, 0, 0);
+                            }
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (!e4[j]) continue;
-                        const uint32_t id = (e4[j] & kPenMaxV) - 1;
-                        float l = r4[j];
-                        l = (l > 0.f) ? __fdiv_rn(l, pen_rep) : __fmul_rn(l, pen_rep);
-                        const float x = __fsub_rn(l, __fadd_rn(pen_pres, __fmul_rn(pen_freq, float(e4[j] >> kPenIdBits))));
+                            for (int j = 0; j < PB; ++j)
+                                if (wq[j] < row_q) join_word<VE>(jc, wq[j], wv[j]);
+                        }
                         if (!no_sum) {
-                            if (x > m_t) {
-                                const float ne = ceilf(x * cexp);
-                                s_t = (m_t == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
-                                e_t = ne, m_t = x;
-                            }
-                            if (m_t != -INFINITY) s_t += ex2_approx(fmaf(x, cexp, -e_t));
-                        }
-                        if (x >= tau_f) {
-                            const unsigned long long cnd = make_cand(key_of(x), id);
-                            if (cnd > tau) {
-                                const uint32_t pos = atomicAdd(&sl->cnt, 1u) & 0x7fffffffu;
-                                if (pos < uint32_t(P_L)) log[pos] = cnd;
-                            }
+                            const float m_t = jc.m_t, e_t = jc.e_t, s_t = jc.s_t;
+                            const bool saw_nan = s_t != s_t;
+                            if (__any_sync(0xffffffffu, saw_nan) && lane == 0) atomicOr(&sl->cnt, 0x80000000u);
+                            const float wm = warp_max(m_t);
+                            float we = e_t;
+                            if (m_t == -INFINITY) we = -INFINITY;
+                            we = warp_max(we);
+                            double ds = (m_t == -INFINITY) ? 0.0 : double(s_t) * double(ex2_approx(e_t - we));
+                            ds = warp_sum(ds);
+                            if (lane == 0) sl->red_m[Q_SW + tw] = wm, sl->red_e[Q_SW + tw] = we, sl->red_s[Q_SW + tw] = ds;
                         }
                     }
+                    g.sync();
+                    PROF_ADD(1, tj0);
                 }
-                const bool saw_nan = !no_sum && (s_t != s_t);
-                if (__any_sync(0xffffffffu, saw_nan) && lane == 0) atomicOr(&sl->cnt, 0x80000000u);
-                const float wm = warp_max(m_t);
-                float we = e_t;
-                if (m_t == -INFINITY) we = -INFINITY;
-                we = warp_max(we);
-                double ds = (m_t == -INFINITY) ? 0.0 : double(s_t) * double(ex2_approx(e_t - we));
-                ds = warp_sum(ds);
-                if (lane == 0) sl->red_m[P_SW + tw] = wm, sl->red_e[P_SW + tw] = we, sl->red_s[P_SW + tw] = ds;
+                PROF_T0(ts0);
+                const float inv_t = cfg.inv_t;
+                const uint32_t total_raw = sl->cnt;  // bit 31: a NaN logit met a sum
+                const bool nan_row = (total_raw & 0x80000000u) != 0;
+                const uint32_t total = total_raw & 0x7fffffffu;
+                overflow = total > uint32_t(Q_L) || nan_row || (pen_on && !lazy && sl->side_cnt > uint32_t(kMaxHist));
+                const uint32_t nlog = total > uint32_t(Q_L) ? uint32_t(Q_L) : total;
+                // row max and normaliser: combine the warps' partials, one per lane (not needed when the row is normalised
+                // over its candidates)
+                if (!no_sum) {
+                    const int n_red = Q_SW + ((pen_on && !lazy) ? Q_TW : 0);
+                    static_assert(Q_RED <= 32, "one partial per lane");
+                    const float mw = lane < n_red ? sl->red_m[lane] : -INFINITY;
+                    M = warp_max(mw);
+                    const double cexp = double(inv_t * kLog2e);
+                    const double term = (lane < n_red && mw != -INFINITY) ? sl->red_s[lane] * exp2(double(sl->red_e[lane]) - double(M) * cexp) : 0.0;
+                    sum = float(warp_sum(term));
+                }
+                if (!overflow) {
+                    // Most of the log was appended under an earlier, looser threshold: only entries at or above the current one
+                    // can be among the K best (at least K of them are).  Few survive, so rank them against each other: the
+                    // rank is the position in the sorted order.
+                    unsigned long long* list = reinterpret_cast<unsigned long long*>(hist);  // up to SEL_BINS / 2 entries
+                    write_survivors<Q_TT>(g, log, nlog, sl->tau, list, SEL_BINS / 2, &sh->sel);
+                    const uint32_t m = sh->sel.wcnt;
+                    if (m <= 2u * Q_TT) {
+#pragma unroll 1
+                        for (uint32_t t = g.tid; t < m; t += Q_TT) {
+                            const unsigned long long mine = list[t];
+                            uint32_t rank = 0;
+#pragma unroll 4
+                            for (uint32_t j = 0; j < m; ++j) rank += list[j] > mine;
+                            if (rank < K) hand[rank] = mine;
+                        }
+                        kept = m < K ? m : K;
+                        presorted = true;
+                    } else if (nlog > K) {
+                        const unsigned long long kth = select_kth<Q_TT>(g, log, nlog, K, hist, &sh->sel);
+                        write_survivors<Q_TT>(g, log, nlog, kth, hand, uint32_t(max_k), &sh->sel);
+                        kept = sh->sel.wcnt < uint32_t(max_k) ? sh->sel.wcnt : uint32_t(max_k);
+                    } else {
+                        for (uint32_t i = g.tid; i < nlog; i += Q_TT) hand[i] = log[i];
+                        kept = nlog;
+                    }
+                }
+                while (cap < kept) cap <<= 1;
                 g.sync();
+                for (uint32_t i = kept + g.tid; i < cap; i += Q_TT) hand[i] = 0ull;
+                // the slot is free for the row after the next once its log and its word map are zero again
+                for (uint32_t i = g.tid; i < nlog; i += Q_TT) log[i] = 0ull;
+                if (pen_on) {
+                    uint32_t* gbm = gbms + size_t(p) * gbm_words;
+                    for (int i = g.tid; i < gbm_words / 4; i += Q_TT) reinterpret_cast<uint4*>(gbm)[i] = make_uint4(0, 0, 0, 0);
+                }
+                g.sync();
+                PROF_ADD(2, ts0);
             }
-            const uint32_t total_raw = sl->cnt;  // bit 31: a NaN logit met a sum
-            const bool nan_row = (total_raw & 0x80000000u) != 0;
-            const uint32_t total = total_raw & 0x7fffffffu;
-            const bool overflow = total > uint32_t(P_L) || nan_row;
-            const uint32_t nlog = total > uint32_t(P_L) ? uint32_t(P_L) : total;
-            // row max and normaliser: combine the warps' partials, one per lane (not needed when the row is normalised
-            // over its candidates)
-            float M = -INFINITY, sum = 0.f;
-            if (!no_sum) {
-                const int n_red = P_SW + (pen_on ? P_TW : 0);
-                static_assert(P_RED <= 32, "one partial per lane");
-                const float mw = lane < n_red ? sl->red_m[lane] : -INFINITY;
-                M = warp_max(mw);
-                const double cexp = double(inv_t * kLog2e);
-                const double term = (lane < n_red && mw != -INFINITY) ? sl->red_s[lane] * exp2(double(sl->red_e[lane]) - double(M) * cexp) : 0.0;
-                sum = float(warp_sum(term));
-            }
-            uint32_t kept = 0;
-            bool presorted = false;
-            if (!overflow) {
-                // Most of the log was appended under an earlier, looser threshold: only entries at or above the current one
-                // can be among the K best (at least K of them are).  Few survive, so rank them against each other: the
-                // rank is the position in the sorted order.
-                unsigned long long* list = reinterpret_cast<unsigned long long*>(hist);  // up to SEL_BINS / 2 entries
-                write_survivors<P_TT>(g, log, nlog, sl->tau, list, SEL_BINS / 2, &sh->sel);
-                const uint32_t m = sh->sel.wcnt;
-                if (m <= 2u * P_TT) {
-                    for (uint32_t t = g.tid; t < m; t += P_TT) {
-                        const unsigned long long mine = list[t];
-                        uint32_t rank = 0;
-                        for (uint32_t j = 0; j < m; ++j) rank += list[j] > mine;
-                        if (rank < K) hand[rank] = mine;
+            if (tw > 0) {
+                // ---- the freed slot goes to the row after the next (at the start: both slots go out), then the table of the
+                // row that streams now
+                PROF_T0(tp0);
+                if (ord < 0) {
+                    slot_boot(0, rlist[0]);
+                    if (n_list > 1) slot_boot(1, rlist[1]);
+                } else if (ord + 2 < n_list) {
+                    slot_boot(p, rlist[ord + 2]);
+                }
+                if (ord + 1 < n_list) build_table(p ^ 1);
+#ifdef WB_PROF
+                if (g.tid == 32) atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 16) + 4, (unsigned long long)(clock64() - tp0));
+#endif
+            } else if (ord >= 0) {
+                // ---- the first tail warp: the row's outputs
+                PROF_T0(td0);
+                const bool greedy = (cfg.flags & QF_GREEDY) != 0;
+                const float inv_t = cfg.inv_t;
+                const bool no_sum = (cfg.flags & QF_NO_SUM) != 0;
+                const int row = cfg.row;
+                const Group<32> gw{lane, 0};
+                if (overflow) {
+                    // more candidates than the log holds (rows in adversarial order), or a NaN in a sum: the multi-pass
+                    // kernel takes the row
+                    if (lane == 0) a.out.status[row] = ROW_RETRY;
+                } else if (!sample) {
+                    if (lane == 0) a.out.status[row] = ROW_DONE;
+                    if (!presorted) sort_desc<32>(gw, reinterpret_cast<uint64_t*>(hand), cap);
+                    const T* xr = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
+#pragma unroll 1
+                    for (uint32_t j = lane; j < kept; j += 32) {
+                        const uint32_t id = cand_id(hand[j]);
+                        a.ids[size_t(row) * a.K + j] = int32_t(id) + a.id_offset;
+                        a.vals[size_t(row) * a.K + j] = sizeof(T) == 4 ? reinterpret_cast<const float*>(xr)[id] : bf16_to_f32(reinterpret_cast<const uint16_t*>(xr)[id]);
                     }
-                    kept = m < K ? m : K;
-                    presorted = true;
-                } else if (nlog > K) {
-                    const unsigned long long kth = select_kth<P_TT>(g, log, nlog, K, hist, &sh->sel);
-                    write_survivors<P_TT>(g, log, nlog, kth, hand, uint32_t(max_k), &sh->sel);
-                    kept = sh->sel.wcnt < uint32_t(max_k) ? sh->sel.wcnt : uint32_t(max_k);
+                    if (lane == 0) a.stats[2 * row] = M, a.stats[2 * row + 1] = sum;
+                } else if (greedy) {
+                    if (lane == 0) {
+                        const uint32_t tok = kept ? cand_id(hand[0]) : 0;
+                        a.out.token[row] = int32_t(tok);
+                        a.out.status[row] = ROW_DONE;
+                        if (a.out.n_kept) a.out.n_kept[row] = 1;
+                        if (a.out.closed) a.out.closed[row] = 1;
+                        if (a.out.stats) a.out.stats[2 * row] = kept ? float_of_key(cand_key(hand[0])) : -INFINITY, a.out.stats[2 * row + 1] = 0.f;
+                        if (a.out.kept_ids && a.out.kept_cap > 0) a.out.kept_ids[size_t(row) * a.out.kept_cap] = int32_t(tok);
+                        if (a.out.kept_p && a.out.kept_cap > 0) a.out.kept_p[size_t(row) * a.out.kept_cap] = 1.0;
+                    }
                 } else {
-                    for (uint32_t i = g.tid; i < nlog; i += P_TT) hand[i] = log[i];
-                    kept = nlog;
-                }
-            }
-            uint32_t cap = 1;
-            while (cap < kept) cap <<= 1;
-            g.sync();
-            for (uint32_t i = kept + g.tid; i < cap; i += P_TT) hand[i] = 0ull;
-            // the log is free for row k + 2 once it is zero again
-            for (uint32_t i = g.tid; i < nlog; i += P_TT) log[i] = 0ull;
-            g.sync();
-            if (kn < my_rows) maybe_refine(p ^ 1, K_next);
-            if (overflow) {
-                // more candidates than the log holds (rows in adversarial order), or a NaN in a sum: the multi-pass kernel
-                // takes the row
-                if (g.tid == 0) a.out.status[row] = ROW_RETRY;
-            } else if (!sample) {
-                if (g.tid == 0) a.out.status[row] = ROW_DONE;
-                if (!presorted) sort_desc<P_TT>(g, reinterpret_cast<uint64_t*>(hand), cap);
-                const T* xr = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
-                for (uint32_t j = g.tid; j < kept; j += P_TT) {
-                    const uint32_t id = cand_id(hand[j]);
-                    a.ids[size_t(row) * a.K + j] = int32_t(id) + a.id_offset;
-                    a.vals[size_t(row) * a.K + j] = sizeof(T) == 4 ? reinterpret_cast<const float*>(xr)[id] : bf16_to_f32(reinterpret_cast<const uint16_t*>(xr)[id]);
-                }
-                if (g.tid == 0) a.stats[2 * row] = M, a.stats[2 * row + 1] = sum;
-            } else if (greedy) {
-                if (g.tid == 0) {
-                    const uint32_t tok = kept ? cand_id(hand[0]) : 0;
-                    a.out.token[row] = int32_t(tok);
-                    a.out.status[row] = ROW_DONE;
-                    if (a.out.n_kept) a.out.n_kept[row] = 1;
-                    if (a.out.closed) a.out.closed[row] = 1;
-                    if (a.out.stats) a.out.stats[2 * row] = kept ? float_of_key(cand_key(hand[0])) : -INFINITY, a.out.stats[2 * row + 1] = 0.f;
-                    if (a.out.kept_ids && a.out.kept_cap > 0) a.out.kept_ids[size_t(row) * a.out.kept_cap] = int32_t(tok);
-                    if (a.out.kept_p && a.out.kept_cap > 0) a.out.kept_p[size_t(row) * a.out.kept_cap] = 1.0;
-                }
-            } else {
-                // probabilities, the top-k / top-p / min-p cuts, the draw and the row's outputs
-                TailIn in;
-                in.inv_t = inv_t;
-                in.top_k = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
-                in.top_p = P.top_p ? P.top_p[row] : 1.0, in.min_p = P.min_p ? P.min_p[row] : 0.0, in.u = P.u ? P.u[row] : 0.0;
-                if (no_sum) {
-                    // normalise over the candidates themselves (sorted or not, hand[] holds exactly the kept ones)
-                    if (g.tid < 32) {
+                    // probabilities, the top-k / top-p / min-p cuts, the draw
+                    TailIn in;
+                    in.inv_t = inv_t;
+                    in.top_k = cfg.top_k;
+                    in.top_p = cfg.top_p, in.min_p = cfg.min_p, in.u = cfg.u;
+                    if (no_sum) {
+                        // normalise over the candidates themselves (sorted or not, hand[] holds exactly the kept ones)
                         unsigned long long top = 0ull;
+#pragma unroll 1
                         for (uint32_t i = lane; i < kept; i += 32) top = hand[i] > top ? hand[i] : top;
                         top = warp_max(uint64_t(top));
-                        const float Mc = float_of_key(cand_key(top));
-                        for (uint32_t i = lane; i < kept; i += 32) tail_q[i] = exp(double(__fsub_rn(float_of_key(cand_key(hand[i])), Mc)) * double(inv_t));
+                        M = float_of_key(cand_key(top));
+#pragma unroll 1
+                        for (uint32_t i = lane; i < kept; i += 32) tail_q[i] = f64_exp(double(__fsub_rn(float_of_key(cand_key(hand[i])), M)) * double(inv_t));
                         __syncwarp();
-                        const float sc = float(warp_total(tail_q, kept));
-                        if (lane == 0) sh->res.cum = double(sc), sh->res.token = __float_as_uint(Mc);
+                        sum = float(warp_total(tail_q, kept));
+                        __syncwarp();
                     }
-                    g.sync();
-                    M = __uint_as_float(sh->res.token), sum = float(sh->res.cum);
-                    g.sync();
-                }
-                in.m = M, in.sum = sum, in.cnt = kept, in.cap = cap, in.V = n;
-                in.race = P.race_key != nullptr, in.race_key = P.race_key ? P.race_key[row] : 0;
-                in.presorted = presorted;
-                sample_tail<P_TT>(g, in, reinterpret_cast<uint64_t*>(hand), tail_p, tail_q, &sh->res);
-                const TailOut r = sh->res;
-                if (g.tid == 0) {
-                    a.out.token[row] = int32_t(r.token);
-                    a.out.status[row] = r.status;
-                    if (a.out.n_kept) a.out.n_kept[row] = int32_t(r.n);
-                    if (a.out.closed) a.out.closed[row] = r.closed;
-                    if (a.out.stats) a.out.stats[2 * row] = M, a.out.stats[2 * row + 1] = sum;
-                    if (a.out.counters && r.status == ROW_ESCALATE) atomicAdd(&a.out.counters[0], 1u);
-                    if (a.out.counters && r.status == ROW_OPEN_TAIL) atomicAdd(&a.out.counters[1], 1u);
-                }
-                if (r.status != ROW_ESCALATE) {
-                    const uint32_t nk = min(r.n, uint32_t(max(a.out.kept_cap, 0)));
-                    for (uint32_t j = g.tid; j < nk; j += P_TT) {
-                        if (a.out.kept_ids) a.out.kept_ids[size_t(row) * a.out.kept_cap + j] = int32_t(cand_id(hand[j]));
-                        if (a.out.kept_p) a.out.kept_p[size_t(row) * a.out.kept_cap + j] = tail_p[j];
+                    in.m = M, in.sum = sum, in.cnt = kept, in.cap = cap, in.V = n;
+                    in.race = P.race_key != nullptr, in.race_key = cfg.race_key;
+                    in.presorted = presorted;
+                    sample_tail<32>(gw, in, reinterpret_cast<uint64_t*>(hand), tail_p, tail_q, &sh->res);
+                    const TailOut r = sh->res;
+                    if (lane == 0) {
+                        a.out.token[row] = int32_t(r.token);
+                        a.out.status[row] = r.status;
+                        if (a.out.n_kept) a.out.n_kept[row] = int32_t(r.n);
+                        if (a.out.closed) a.out.closed[row] = r.closed;
+                        if (a.out.stats) a.out.stats[2 * row] = M, a.out.stats[2 * row + 1] = sum;
+                        if (a.out.counters && r.status == ROW_ESCALATE) atomicAdd(&a.out.counters[0], 1u);
+                        if (a.out.counters && r.status == ROW_OPEN_TAIL) atomicAdd(&a.out.counters[1], 1u);
+                    }
+                    if (r.status != ROW_ESCALATE) {
+                        const uint32_t nk = min(r.n, uint32_t(max(a.out.kept_cap, 0)));
+#pragma unroll 1
+                        for (uint32_t j = lane; j < nk; j += 32) {
+                            if (a.out.kept_ids) a.out.kept_ids[size_t(row) * a.out.kept_cap + j] = int32_t(cand_id(hand[j]));
+                            if (a.out.kept_p) a.out.kept_p[size_t(row) * a.out.kept_cap + j] = tail_p[j];
+                        }
                     }
                 }
-                g.sync();
+                PROF_ADD(3, td0);
             }
-            if (kn < my_rows) maybe_refine(p ^ 1, K_next);
-            // ---- the slot goes to the row after the next
-            if (kn2 < my_rows) boot(kn2, ord + 2);
-            k = kn;
+            g.sync();
+#ifdef WB_PROF
+            if (g.tid == 0 && ord >= 0) prof[6] += 1;
+#endif
         }
+#ifdef WB_PROF
+        if (g.tid == 0) {
+            prof[7] = clock64() - prof_begin;
+            unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 16);
+            for (int i = 0; i < 8; ++i) atomicAdd(&dbg[i], (unsigned long long)prof[i]);
+        }
+#endif
         // Every row of this CTA has its status.
         if (a.fin_list) {
             __threadfence();
@@ -592,247 +830,301 @@ __global__ void __launch_bounds__(P_THREADS, 1) single_pass_kernel(SelectArgs a,
     }
 
     // =========================================================== stream warps
-    const int lane = lane_id(), sw = tid >> 5;
-    const uint4 ninf4 = sizeof(T) == 4 ? make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u)
-                                       : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
-    // ---- the load cursor runs P_PF tiles ahead of the tile being worked on, across row boundaries
-    int k_ld = next_row(-1);
-    uint32_t t_ld = 0;
-    const uint4* row_ld = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.x) + size_t(row_of(k_ld)) * n);
-    auto load_tile = [&](uint4(&b)[4]) {
-        if (k_ld >= my_rows) return;
-        const uint32_t q0 = t_ld * TILE_Q + uint32_t(tid);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t qi = q0 + uint32_t(j) * P_ST;
-            b[j] = qi < row_q ? ld_stream(row_ld + qi) : ninf4;
-        }
-        if (++t_ld == n_tiles) {
-            t_ld = 0;
-            k_ld = next_row(k_ld);
-            if (k_ld < my_rows) row_ld = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.x) + size_t(row_of(k_ld)) * n);
-        }
-    };
-    uint4 buf[P_PF][4];
-#pragma unroll
-    for (int j = 0; j < P_PF; ++j) load_tile(buf[j]);
-
-    // ---- row state
-    int k = next_row(-1), ord = 0;
-    uint32_t t = 0;
-    bool fail = false;
-    PSlot* sl = nullptr;
-    unsigned long long* log = nullptr;
-    const uint32_t* bm = nullptr;
-    bool no_sum = false, pen_on = false, renew_ok = false;
-    float cexp = 0.f, m_t = -INFINITY, e_t = 0.f, s_t = 0.f, tau_f = -INFINITY;
-    unsigned long long tau_seen = 0ull;
-    uint32_t rth = 1, next_renew = 1;
-
-    auto row_begin = [&]() {
+    const int lane = lane_id(), sw = warp - 1, st_tid = tid - 32;
+    const uint32_t nw = sizeof(T) == 4 ? 0xff800000u : 0xff80ff80u;  // -inf
+    const uint4 ninf4 = make_uint4(nw, nw, nw, nw);
+    uint32_t st_slot = 0, st_phase = 0;  // ring position of this warp and the parity it waits for
+#ifdef WB_PROF
+    long long sp_wait = 0, sp_boot = 0, sp_head = 0, sp_total = clock64();
+#endif
+#pragma unroll 1
+    for (int ord = 0; ord < n_list; ++ord) {
         const int p = ord & 1;
-        const int row = row_of(k);
-        sl = &sh->slot[p];
-        log = logs + size_t(p) * P_L;
-        bm = bitmaps + size_t(p) * bm_words;
-        // the slot (log, threshold, bit map) is this row's once the tail group says so
+        QSlot* sl = &sh->slot[p];
+        unsigned long long* log = logs + size_t(p) * Q_L;
+        const uint32_t* gbm = gbms + size_t(p) * gbm_words;
+        // the slot (parameters, log, threshold, word map) is this row's once the tail group says so
+#ifdef WB_PROF
+        const long long tb0 = clock64();
+#endif
         if (!mbar_wait(&boot_done[p], (ord >> 1) & 1)) {
             if (lane == 0) atomicExch(a.err, 4u);
-            fail = true;
             return;
         }
-        no_sum = no_sum_row(row);
-        pen_on = pen_row(row);
-        const float inv_t = P.inv_t ? P.inv_t[row] : P.inv_t_scalar;
-        cexp = inv_t * kLog2e;
-        m_t = -INFINITY, e_t = 0.f, s_t = 0.f;
-        tau_seen = 0ull, tau_f = -INFINITY;
-        rth = (k_of(row) + P_SW - 1) / P_SW;
-        // a warp's own bound from its lane maxima is valid only when those hold no raw logit of a history token
-        renew_ok = rth <= 32 && (!pen_on || !no_sum);
-        next_renew = 1;
-    };
+#ifdef WB_PROF
+        sp_boot += clock64() - tb0;
+#endif
+        const uint32_t row_flags = sl->cfg.flags;
+        const float cexp = sl->cfg.inv_t * kLog2e;
+        const float pen_rep = sl->cfg.rep, pen_pres = sl->cfg.pres, pen_freq = sl->cfg.freq;
+        // running maxima (the two largest iteration maxima of this lane: two distinct logits), reference exponent
+        // ceil(m1 * cexp), sum 2^(x * cexp - e_t)
+        float m1 = -INFINITY, m2 = -INFINITY, e_t = 0.f, s_t = 0.f;
+        unsigned long long tau_seen = 0ull;
+        float tau_f = -INFINITY;
+        const uint32_t rth = (sl->cfg.K + Q_SW - 1) / Q_SW;  // each warp's share of the K candidates
+        bool st_fail = false;
+        (void)pen_rep, (void)pen_pres, (void)pen_freq;
 
-    auto process = [&](const uint4(&cur)[4]) {
-        {
-            const unsigned long long tq = ldv_u64(&sl->tau);
-            if (tq > tau_seen) tau_seen = tq, tau_f = float_of_key(cand_key(tq));
-        }
-        const unsigned long long tau = tau_seen;
-        float xv[4 * VE];
-        uint32_t qid[4];  // first token id of each 128-bit word
+        // this warp's bound: the rth largest of its 64 lane maxima (0: none)
+        auto own_bound = [&]() -> uint32_t {
+            if (rth > 64) return 0u;
+            uint32_t kv[2] = {m1 == -INFINITY ? 0u : key_of(m1), m2 == -INFINITY ? 0u : key_of(m2)};
+            return warp_rth_largest<2>(kv, rth);
+        };
+
+        // one iteration: the stages c .. c + Q_NS - 1 (the row's last iteration may have fewer)
+        auto stage = [&](uint32_t c, uint32_t head_in) {
+            constexpr int NW = 2 * Q_NS;  // 128-bit words per thread
+            // (The row's flags go through an empty asm so that the compiler sees values it cannot hoist: it would make one
+            // copy of this whole body per combination of them, and the kernel's code has to fit the instruction cache.)
+            uint32_t fl = row_flags, head = head_in, nst = min(uint32_t(Q_NS), n_chunks - c);
+            asm volatile("" : "+r"(fl), "+r"(head), "+r"(nst));
+            const bool no_sum = (fl & QF_NO_SUM) != 0, pen_on = (fl & QF_PEN) != 0, lazy = (fl & QF_LAZY) != 0;
+            uint4 w[NW];
+            uint32_t wq[NW];  // the word's place in the row
+            uint32_t st_ring[Q_NS];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            qid[j] = (t * TILE_Q + uint32_t(tid) + uint32_t(j) * P_ST) * VE;
-            const uint32_t w4[4] = {cur[j].x, cur[j].y, cur[j].z, cur[j].w};
-            float* x = xv + j * VE;
-            if (sizeof(T) == 4) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) x[e] = __uint_as_float(w4[e]);
-            } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) x[2 * e] = __uint_as_float(w4[e] << 16), x[2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
-            }
-        }
-        if (pen_on && !no_sum) {
-            // the normaliser must not see the raw logits of history tokens: take them out of every word
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (qid[j] < n) {
-                    const uint32_t bits = (bm[qid[j] >> 5] >> (qid[j] & 31)) & ((1u << VE) - 1);
-                    if (bits) {
-#pragma unroll
-                        for (int e = 0; e < VE; ++e)
-                            if ((bits >> e) & 1u) xv[j * VE + e] = -INFINITY;
+            for (int h = 0; h < Q_NS; ++h) {
+                st_ring[h] = st_slot;
+                if (h == 0 || uint32_t(h) < nst) {
+#ifdef WB_PROF
+                    const long long tw0 = clock64();
+#endif
+                    if (!mbar_wait(&full[st_slot], st_phase)) {
+                        if (lane == 0) atomicExch(a.err, 5u);
+                        st_fail = true;
+                        return;
                     }
+#ifdef WB_PROF
+                    sp_wait += clock64() - tw0;
+#endif
+                }
+                const uint4* vec = reinterpret_cast<const uint4*>(ring + size_t(st_slot) * Q_SB);
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    wq[2 * h + j] = (c + h) * Q_SQ + uint32_t(j) * Q_ST + uint32_t(st_tid);
+                    w[2 * h + j] = wq[2 * h + j] < row_q ? vec[j * Q_ST + st_tid] : ninf4;  // (only the row's last stage can be short)
+                }
+                if (h == 0 || uint32_t(h) < nst) {
+                    if (++st_slot == uint32_t(stages)) st_slot = 0, st_phase ^= 1u;
                 }
             }
-        }
-        // maxima of the words; fmaxf skips NaN, so a NaN logit never raises a maximum
-        float qm[4];
+            // words that hold a history token (the warp's 32 words are 32 consecutive bits of the map)
+            uint32_t marked = 0;  // bit i: word i
+            if (pen_on) {
+                const uint4 mw = *reinterpret_cast<const uint4*>(gbm + (((c / 2) * Q_SW + uint32_t(sw)) << 2));
+                marked = ((mw.x >> lane) & 1u) | (((mw.y >> lane) & 1u) << 1) | (((mw.z >> lane) & 1u) << 2) | (((mw.w >> lane) & 1u) << 3);
+                if (!lazy) {
+                    // they are put aside for the tail group, as they are, and count as -inf here
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            float mx = xv[j * VE];
-#pragma unroll
-            for (int e = 1; e < VE; ++e) mx = fmaxf(mx, xv[j * VE + e]);
-            qm[j] = mx;
-        }
-        const float vm = fmaxf(fmaxf(qm[0], qm[1]), fmaxf(qm[2], qm[3]));
-        if (!no_sum) {
-            if (vm > m_t) {
-                // new reference exponent: an integer at or above m * cexp, so every term is at most 1 and
-                // x * cexp - e is one fused operation with a single rounding
-                const float ne = ceilf(vm * cexp);
-                s_t = (m_t == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
-                e_t = ne, m_t = vm;
-            }
-            if (m_t != -INFINITY) {
-                float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int j = 0; j < 4 * VE; ++j) acc[j & 3] += ex2_approx(fmaf(xv[j], cexp, -e_t));
-                s_t += (acc[0] + acc[1]) + (acc[2] + acc[3]);
-            }
-        } else {
-            m_t = fmaxf(m_t, vm);
-        }
-        if (vm >= tau_f) {
-            // rare: this lane holds an element that may beat the threshold
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (qm[j] >= tau_f) {
-#pragma unroll
-                    for (int e = 0; e < VE; ++e) {
-                        const float x = xv[j * VE + e];
-                        const uint32_t id = qid[j] + e;
-                        if (x >= tau_f && id < n) {
-                            const unsigned long long cnd = make_cand(key_of(x), id);
-                            // (a row that masks its words above has no history token left here)
-                            const bool hist_tok = pen_on && no_sum && ((bm[id >> 5] >> (id & 31)) & 1u);
-                            if (cnd > tau && !hist_tok) {
-                                const uint32_t pos = atomicAdd(&sl->cnt, 1u);
-                                if (pos < uint32_t(P_L)) log[pos] = cnd;
+                    for (int i = 0; i < NW; ++i) {
+                        const bool mk = (marked >> i) & 1u;
+                        const uint32_t bal = __ballot_sync(0xffffffffu, mk);
+                        if (bal) {
+                            uint32_t at = 0;
+                            if (lane == 0) at = atomicAdd(&sl->side_cnt, uint32_t(__popc(bal)));
+                            at = __shfl_sync(0xffffffffu, at, 0) + uint32_t(__popc(bal & ((1u << lane) - 1)));
+                            if (mk && at < uint32_t(kMaxHist)) {
+                                __stcg(side_w(p) + at, w[i]);
+                                __stcg(side_q(p) + at, wq[i]);
                             }
+                            if (mk) w[i] = ninf4;
                         }
                     }
+                    marked = 0;
                 }
             }
-        }
-        // this warp's own bound, renewed each time the part of the row seen has doubled: the rth largest of its lane maxima
-        // (16 * rth >= K distinct logits of the row reach the smallest of the 16 warps' bounds; the other warps' entries
-        // may be older: any of their bounds for this row is valid)
-        if (renew_ok && t + 1 == next_renew && t + 1 < n_tiles) {
-            next_renew *= 2;
-            uint32_t kv[1] = {m_t == -INFINITY ? 0u : key_of(m_t)};
-            const uint32_t kr = warp_rth_largest<1>(kv, rth);
+            float xv[NW * VE];
+#pragma unroll
+            for (int i = 0; i < NW; ++i) {
+                const uint32_t w4[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+                float* x = xv + i * VE;
+                if (sizeof(T) == 4) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) x[e] = __uint_as_float(w4[e]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) x[2 * e] = __uint_as_float(w4[e] << 16), x[2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
+                }
+            }
+            // maxima of the words; fmaxf skips NaN, so a NaN logit never raises a maximum
+            float qm[NW];
+#pragma unroll
+            for (int i = 0; i < NW; ++i) {
+                float mx = xv[i * VE];
+#pragma unroll
+                for (int e = 1; e < VE; ++e) mx = fmaxf(mx, xv[i * VE + e]);
+                qm[i] = mx;
+            }
+            // Every loaded register has been consumed, so the shared-memory reads have completed (instructions issue in
+            // order and the fmaxf had to wait for the data): only now may the producer overwrite the stages.
+            __syncwarp();
+            if (lane == 0) {
+#pragma unroll
+                for (int h = 0; h < Q_NS; ++h)
+                    if (h == 0 || uint32_t(h) < nst) mbar_arrive(&empty[st_ring[h]]);
+            }
+            float vm = qm[0];
+#pragma unroll
+            for (int i = 1; i < NW; ++i) vm = fmaxf(vm, qm[i]);
+            // what counts for this lane's bounds: not the marked words (their raw logits are not the row's)
+            float vb = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < NW; ++i) vb = fmaxf(vb, ((marked >> i) & 1u) ? -INFINITY : qm[i]);
+            if (!no_sum) {
+                if (vm > m1) {
+                    // new reference exponent: an integer at or above m * cexp, so every term is at most 1 and
+                    // x * cexp - e is one fused operation with a single rounding
+                    const float ne = ceilf(vm * cexp);
+                    s_t = (m1 == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
+                    e_t = ne;
+                }
+                if (fmaxf(vm, m1) != -INFINITY) {
+                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int j = 0; j < NW * VE; ++j) acc[j & 3] += ex2_approx(fmaf(xv[j], cexp, -e_t));
+                    s_t += (acc[0] + acc[1]) + (acc[2] + acc[3]);
+                }
+            }
+            m2 = fmaxf(m2, fminf(m1, vb));
+            m1 = fmaxf(m1, vb);
+            if (head) {
+                // The row's first threshold: every warp names its bound from what it has just read and the warps meet (their
+                // one meeting per row); what this lane read is tested against the agreed bound below, from its registers.
+#ifdef WB_PROF
+                const long long th0 = clock64();
+#endif
+                const uint32_t kr = own_bound();
+                if (lane == 0) {
+                    sl->wbound[sw] = kr;
+                    mbar_arrive(&head_done[p]);
+                }
+                if (!mbar_wait(&head_done[p], (ord >> 1) & 1)) {
+                    if (lane == 0) atomicExch(a.err, 11u);
+                    st_fail = true;
+                    return;
+                }
+                const uint32_t kmin = __reduce_min_sync(0xffffffffu, lane < Q_SW ? ldv_u32(&sl->wbound[lane]) : 0xffffffffu);
+                if (kmin) tau_seen = (unsigned long long)kmin << 32, tau_f = float_of_key(kmin);
+                if (sw == 0 && lane == 0 && tau_seen > ldv_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = tau_seen;
+#ifdef WB_PROF
+                sp_head += clock64() - th0;
+#endif
+            } else {
+                const unsigned long long tq = ldv_u64(&sl->tau);
+                if (tq > tau_seen) tau_seen = tq, tau_f = float_of_key(cand_key(tq));
+            }
+            if (vm >= tau_f) {
+                // rare: this lane holds an element that may beat the threshold
+#pragma unroll
+                for (int i = 0; i < NW; ++i) {
+                    if (qm[i] >= tau_f && wq[i] < row_q) {
+                        const bool mk = (marked >> i) & 1u;
+#pragma unroll
+                        for (int e = 0; e < VE; ++e)
+                            if (xv[i * VE + e] >= tau_f) log_append(sl, log, xv[i * VE + e], wq[i] * VE + e, tau_seen, mk);
+                    }
+                }
+            }
+        };
+        // a fresh bound from this warp's maxima; the other warps' entries may be older: any of their bounds for this row is valid
+        auto renew = [&]() {
+            const uint32_t kr = own_bound();
             if (lane == 0) sl->wbound[sw] = kr;
             __syncwarp();
-            const uint32_t kmin = __reduce_min_sync(0xffffffffu, lane < P_SW ? ldv_u32(&sl->wbound[lane]) : 0xffffffffu);
+            const uint32_t kmin = __reduce_min_sync(0xffffffffu, lane < Q_SW ? ldv_u32(&sl->wbound[lane]) : 0xffffffffu);
             // (a plain compare and store: a lost update only leaves the threshold at another valid, lower bound)
             if (lane == 0) {
-                const unsigned long long c = (unsigned long long)kmin << 32;
-                if (c > ldv_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = c;
+                const unsigned long long cnd = (unsigned long long)kmin << 32;
+                if (cnd > ldv_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = cnd;
+            }
+        };
+        const uint32_t n_iter = (n_chunks + Q_NS - 1) / Q_NS;
+        uint32_t next_renew = Q_NS == 2 ? 2 : 1;
+#pragma unroll 1
+        for (uint32_t iter = 0; iter < n_iter && !st_fail; ++iter) {
+            stage(Q_NS * iter, iter == 0 ? 1u : 0u);
+            // a fresh bound each time the part of the row seen has grown by half
+            if (iter + 1 == next_renew && iter + 1 < n_iter && !st_fail) {
+                renew();
+                next_renew += (next_renew + 1) / 2;
             }
         }
-    };
-
-    auto row_end = [&]() {
-        const int p = ord & 1;
-        if (!no_sum) {
+        if (st_fail) return;
+        // ---- the row is through for this warp: partials, then close
+        if (!(row_flags & QF_NO_SUM)) {
             // a NaN logit poisons the f32 sum: such rows are redone by the multi-pass kernel, which counts NaN as -inf
             const bool saw_nan = s_t != s_t;
             if (__any_sync(0xffffffffu, saw_nan) && lane == 0) atomicOr(&sl->cnt, 0x80000000u);
-            const float wm = warp_max(m_t);
+            const float wm = warp_max(m1);
             float we = e_t;
-            if (m_t == -INFINITY) we = -INFINITY;
+            if (m1 == -INFINITY) we = -INFINITY;
             we = warp_max(we);
-            double ds = (m_t == -INFINITY) ? 0.0 : double(s_t) * double(ex2_approx(e_t - we));
+            double ds = (m1 == -INFINITY) ? 0.0 : double(s_t) * double(ex2_approx(e_t - we));
             ds = warp_sum(ds);
             if (lane == 0) sl->red_m[sw] = wm, sl->red_e[sw] = we, sl->red_s[sw] = ds;
         }
+        __threadfence();  // (words put aside in global memory are read by the tail group)
         __syncwarp();
         if (lane == 0) mbar_arrive(&closed[p]);
-    };
-
-    while (k < my_rows && !fail) {
-#pragma unroll
-        for (int j = 0; j < P_PF; ++j) {
-            if (k < my_rows && !fail) {
-                uint4 cur[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) cur[q] = buf[j][q];
-                load_tile(buf[j]);
-                if (t == 0) row_begin();
-                if (!fail) {
-                    process(cur);
-                    if (++t == n_tiles) {
-                        row_end();
-                        t = 0;
-                        k = next_row(k);
-                        ++ord;
-                    }
-                }
-            }
-        }
     }
+#ifdef WB_PROF
+    if (st_tid == 0) {
+        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 16);
+        atomicAdd(&dbg[8], (unsigned long long)sp_wait), atomicAdd(&dbg[9], (unsigned long long)sp_boot);
+        atomicAdd(&dbg[10], (unsigned long long)(clock64() - sp_total)), atomicAdd(&dbg[11], (unsigned long long)sp_head);
+    }
+#endif
 }
 
-static size_t single_pass_smem(int bm_words, int max_k, bool pen) {
-    return size_t(2) * P_L * 8 + SEL_BINS * 4 + size_t(max_k) * 8 + 2 * (size_t(max_k) + 2 * P_TW) * 8 + 4 * 8 + sizeof(PShared) + 16 +
-           size_t(2) * bm_words * 4 + (pen ? size_t(kPenSlots) * 4 : 0) + 128;
-}
-
-static int single_pass_bm_words(const SelectArgs& a) {
+static int single_pass_gbm_words(const SelectArgs& a, int dtype) {
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
-    return pen ? ((a.n + 31) / 32 + 3) & ~3 : 0;
+    const int ve = dtype == 0 ? 4 : 8;
+    // one map word per stream warp, word of the thread and iteration (see gbm_word_of)
+    return pen ? ((a.n / ve + 2 * Q_SQ - 1) / (2 * Q_SQ)) * Q_SW * 4 : 0;
+}
+
+static size_t single_pass_fixed_smem(int gbm_words, int max_k, bool pen) {
+    return size_t(2) * Q_L * 8 + SEL_BINS * 4 + size_t(max_k) * 8 + 2 * (size_t(max_k) + 2 * Q_TW) * 8 + (2 * Q_MAXSTAGES + 6) * 8 +
+           sizeof(QShared) + 16 + size_t(2) * gbm_words * 4 + (pen ? size_t(kPenSlots) * 4 : 0) + 128;
 }
 
 bool single_pass_supported(const SelectArgs& a, int dtype) {
     const size_t es = dtype == 0 ? 4 : 2;
-    if (reinterpret_cast<uintptr_t>(a.x) % 16 != 0 || (size_t(a.n) * es) % 16 != 0) return false;  // 128-bit loads need 16-byte rows
+    if (reinterpret_cast<uintptr_t>(a.x) % 16 != 0 || (size_t(a.n) * es) % 16 != 0) return false;  // bulk copies need 16-byte rows
     if (a.mode == MODE_TOPK && a.K > kSinglePassMaxK) return false;
     if (a.mode == MODE_DRAFT) return false;
+    if (a.rows > Q_MAXR * 100) return false;  // (more rows per CTA than its row list holds: far beyond any batch of logits)
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
-    return single_pass_smem(single_pass_bm_words(a), kSinglePassMaxK, pen) <= 232448;
+    return single_pass_fixed_smem(single_pass_gbm_words(a, dtype), kSinglePassMaxK, pen) + 3 * size_t(Q_SB) <= 232448;
 }
 
 cudaError_t single_pass_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st) {
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
-    const int bm_words = single_pass_bm_words(a);
+    const int gbm_words = single_pass_gbm_words(a, dtype);
     const int max_k = kSinglePassMaxK;
-    const size_t smem = single_pass_smem(bm_words, max_k, pen);
+    const size_t fixed = single_pass_fixed_smem(gbm_words, max_k, pen);
+    int stages = int((232448 - fixed) / Q_SB);
+    if (stages > Q_MAXSTAGES) stages = Q_MAXSTAGES;
+    if (stages < 3) return cudaErrorInvalidConfiguration;
+    const size_t smem = fixed + size_t(stages) * Q_SB;
     const int grid = a.rows < sm_count ? a.rows : sm_count;
+    if ((a.rows + grid - 1) / grid > Q_MAXR) return cudaErrorInvalidConfiguration;
     const cudaError_t em = cudaMemsetAsync(a.err, 0, 64, st);  // the error words, the list count and tickets, the scratch locks
     if (em != cudaSuccess) return em;
     if (dtype == 0) {
         const cudaError_t e = cudaFuncSetAttribute(single_pass_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        single_pass_kernel<float><<<grid, P_THREADS, smem, st>>>(a, bm_words, max_k);
+        single_pass_kernel<float><<<grid, Q_THREADS, smem, st>>>(a, stages, gbm_words, max_k);
     } else {
         const cudaError_t e = cudaFuncSetAttribute(single_pass_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        single_pass_kernel<uint16_t><<<grid, P_THREADS, smem, st>>>(a, bm_words, max_k);
+        single_pass_kernel<uint16_t><<<grid, Q_THREADS, smem, st>>>(a, stages, gbm_words, max_k);
     }
     return cudaGetLastError();
 }
+
+size_t single_pass_side_bytes(int sm_bound) { return size_t(sm_bound < 1 ? 1 : sm_bound) * 2 * kMaxHist * 20; }
 
 }  // namespace wb

@@ -36,23 +36,32 @@ struct TailOut {
     double cum;  // cumulative mass of the walked candidates (ROW_OPEN_TAIL: where the id-order walk continues)
 };
 
+// f64 exp / log / division are long instruction sequences: one copy each, called (the tail runs once per row, and a
+// kernel whose code does not fit the instruction cache pays for every line it has to fetch again).
+static __device__ __noinline__ double f64_exp(double x) { return exp(x); }
+static __device__ __noinline__ double f64_log(double x) { return log(x); }
+static __device__ __noinline__ double f64_div(double a, double b) { return a / b; }
+
 __device__ __forceinline__ uint64_t mix64(uint64_t z) {  // include/whirl/spec_sample.h:53-57
     z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
     z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
     return z ^ (z >> 31);
 }
 // E(v) = -ln(1 - U(base, v)), src/common/spec_sample.cpp:83-87
-__device__ __forceinline__ double race_e(uint64_t base, uint32_t token) {
+static __device__ __noinline__ double race_e(uint64_t base, uint32_t token) {
     const uint64_t z = mix64(base + (uint64_t(token) + 1ull) * 0xE7037ED1A0B428DBull);
     const double u = double(z >> 11) * (1.0 / 9007199254740992.0);
-    return -log(1.0 - u);
+    return -f64_log(1.0 - u);
 }
 
 // Bitonic sort of cand[0..cap) in descending composite order (= logit desc, id asc).
 template <int NT>
-__device__ void sort_desc(const Group<NT>& g, uint64_t* cand, uint32_t cap) {
+__device__ __noinline__ void sort_desc(const Group<NT>& g, uint64_t* cand, uint32_t cap) {
+#pragma unroll 1
     for (uint32_t k = 2; k <= cap; k <<= 1) {
+#pragma unroll 1
         for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+#pragma unroll 1
             for (uint32_t t = g.tid; t < (cap >> 1); t += NT) {
                 // t enumerates the pairs (i, i ^ j) with i's bit j clear
                 const uint32_t i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
@@ -84,9 +93,10 @@ __device__ __forceinline__ double warp_excl_scan(double v, double* total) {
     return incl - v;
 }
 // sum of v[0..n)
-__device__ __forceinline__ double warp_total(const double* v, uint32_t n) {
+static __device__ __noinline__ double warp_total(const double* v, uint32_t n) {
     const uint32_t S = (n + 31) / 32, b = lane_id() * S, e = min(n, b + S);
     double s = 0;
+#pragma unroll 1
     for (uint32_t i = b; i < e; ++i) s += v[i];
     double tot;
     warp_excl_scan(s, &tot);
@@ -94,13 +104,15 @@ __device__ __forceinline__ double warp_total(const double* v, uint32_t n) {
 }
 // smallest j with cum(v[0..j]) >= t (STRICT: > t), n when there is none; *cum_end = the sum of everything walked
 template <bool STRICT>
-__device__ __forceinline__ uint32_t warp_first_reach(const double* v, uint32_t n, double t, double* cum_end) {
+__device__ __noinline__ uint32_t warp_first_reach(const double* v, uint32_t n, double t, double* cum_end) {
     const uint32_t S = (n + 31) / 32, b = min(n, lane_id() * S), e = min(n, b + S);
     double s = 0;
+#pragma unroll 1
     for (uint32_t i = b; i < e; ++i) s += v[i];
     double tot;
     double cum = warp_excl_scan(s, &tot);
     uint32_t first = n;
+#pragma unroll 1
     for (uint32_t i = b; i < e; ++i) {
         cum += v[i];
         if (first == n && (STRICT ? cum > t : cum >= t)) first = i;
@@ -117,12 +129,13 @@ __device__ __forceinline__ uint32_t warp_first_reach(const double* v, uint32_t n
 // The steps are those of the host filter (sampler.cpp:15-78); exponentials, divisions and comparisons run on all
 // threads, the running sums on the group's first warp (see above for their order).
 template <int NT>
-__device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand, double* p, double* q, TailOut* res) {
+__device__ __noinline__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand, double* p, double* q, TailOut* res) {
     if (!in.presorted) sort_desc<NT>(g, cand, in.cap);
     const double inv_t = double(in.inv_t), sum = double(in.sum);
+#pragma unroll 1
     for (uint32_t i = g.tid; i < in.cnt; i += NT) {
         const float l = float_of_key(cand_key(cand[i]));
-        p[i] = exp(double(__fsub_rn(l, in.m)) * inv_t) / sum;
+        p[i] = f64_div(f64_exp(double(__fsub_rn(l, in.m)) * inv_t), sum);
     }
     g.sync();
     // ---- top-k, and the normaliser of the top-p walk (sampler.cpp:35-49)
@@ -145,7 +158,8 @@ __device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand
     if (in.top_p < 1.0) {
         const double z = res->cum;
         const uint32_t n0 = res->n;
-        for (uint32_t i = g.tid; i < n0; i += NT) q[i] = p[i] / z;
+#pragma unroll 1
+        for (uint32_t i = g.tid; i < n0; i += NT) q[i] = f64_div(p[i], z);
         g.sync();
     }
     // ---- top-p cut, min-p cut, the renormaliser (sampler.cpp:50-74)
@@ -161,6 +175,7 @@ __device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand
         if (!esc && in.min_p > 0) {
             const double thr = in.min_p * p[0];
             uint32_t j = n;  // first candidate below the threshold
+#pragma unroll 1
             for (uint32_t i = lane_id(); i < n; i += 32)
                 if (!(p[i] >= thr)) {
                     j = i;
@@ -184,7 +199,8 @@ __device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand
     const bool closed = res->closed != 0;
     if (closed) {
         const double z = res->cum;
-        for (uint32_t i = g.tid; i < n; i += NT) p[i] /= z;
+#pragma unroll 1
+        for (uint32_t i = g.tid; i < n; i += NT) p[i] = f64_div(p[i], z);
     }
     g.sync();
     bool do_race = in.race != 0;
@@ -202,9 +218,10 @@ __device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand
         // argmin over the kept candidates of E(id) / p, the first on ties
         double bk = __longlong_as_double(0x7FF0000000000000ll);
         uint32_t bi = 0xffffffffu;
+#pragma unroll 1
         for (uint32_t i = g.tid; i < n; i += NT) {
             if (!(p[i] > 0)) continue;
-            const double k = race_e(in.race_key, cand_id(cand[i])) / p[i];
+            const double k = f64_div(race_e(in.race_key, cand_id(cand[i])), p[i]);
             if (k < bk) bk = k, bi = i;  // i ascends per thread: strict < keeps the first
         }
         // group argmin through shared scratch above the kept set is not available here; reduce with warp shuffles and
@@ -222,6 +239,7 @@ __device__ void sample_tail(const Group<NT>& g, const TailIn& in, uint64_t* cand
         }
         g.sync();
         if (g.tid == 0) {
+#pragma unroll 1
             for (int w = 1; w < NT / 32; ++w) {
                 const double ok = wk[w * 2];
                 const uint32_t oi = (uint32_t)__double_as_longlong(wk[w * 2 + 1]);
