@@ -118,6 +118,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same, letting the hardware keep the thread suspended for up to `ns` nanoseconds while the phase is not complete
+// (a waiting warp that keeps asking takes issue slots from the warps that work).
+__device__ __forceinline__ bool mbar_try_wait_for(uint64_t* bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok != 0;
+}
 // One look at the barrier, never suspending the thread (for a loop that polls several barriers in turn).
 __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
@@ -128,13 +139,12 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait (about a second at 2 GHz).  false = gave up.
+// Bounded wait (about a second).  false = gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
 #pragma unroll 1
-    for (uint32_t it = 0; it < (1u << 24); ++it) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (it > 64) __nanosleep(64);
-    }
+    for (uint32_t it = 0; it < (1u << 20); ++it)
+        if (mbar_try_wait_for(bar, parity, 1000u)) return true;
     return false;
 }
 // global -> shared bulk copy, 16-byte aligned addresses, size a multiple of 16, completion on an mbarrier

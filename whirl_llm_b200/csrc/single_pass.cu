@@ -34,6 +34,8 @@
 //
 // It replaces the reference's topk_rows kernel (seven passes over the row, kernels/shared/sample_cand_topk_rows.h:11-98),
 // the candidate download, and the host filter and draw (src/sampling/sampler.cpp:15-147).
+#include <type_traits>
+
 #include "kernels.h"
 #include "penalty.cuh"
 #include "select_smem.cuh"
@@ -834,6 +836,8 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
     const uint32_t nw = sizeof(T) == 4 ? 0xff800000u : 0xff80ff80u;  // -inf
     const uint4 ninf4 = make_uint4(nw, nw, nw, nw);
     uint32_t st_slot = 0, st_phase = 0;  // ring position of this warp and the parity it waits for
+    const uint32_t n_iter = (n_chunks + Q_NS - 1) / Q_NS;
+    const uint32_t full_iters = row_q / (Q_NS * Q_SQ);  // iterations whose words all lie inside the row
 #ifdef WB_PROF
     long long sp_wait = 0, sp_boot = 0, sp_head = 0, sp_total = clock64();
 #endif
@@ -856,177 +860,20 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
 #endif
         const uint32_t row_flags = sl->cfg.flags;
         const float cexp = sl->cfg.inv_t * kLog2e;
-        const float pen_rep = sl->cfg.rep, pen_pres = sl->cfg.pres, pen_freq = sl->cfg.freq;
         // running maxima (the two largest iteration maxima of this lane: two distinct logits), reference exponent
         // ceil(m1 * cexp), sum 2^(x * cexp - e_t)
         float m1 = -INFINITY, m2 = -INFINITY, e_t = 0.f, s_t = 0.f;
-        unsigned long long tau_seen = 0ull;
+        uint32_t tau_key = 0u;  // the threshold's ordering key as this warp last saw it (0: none)
         float tau_f = -INFINITY;
         const uint32_t rth = (sl->cfg.K + Q_SW - 1) / Q_SW;  // each warp's share of the K candidates
         bool st_fail = false;
-        (void)pen_rep, (void)pen_pres, (void)pen_freq;
+        const volatile uint32_t* tau_hi = reinterpret_cast<const volatile uint32_t*>(&sl->tau) + 1;
 
         // this warp's bound: the rth largest of its 64 lane maxima (0: none)
         auto own_bound = [&]() -> uint32_t {
             if (rth > 64) return 0u;
             uint32_t kv[2] = {m1 == -INFINITY ? 0u : key_of(m1), m2 == -INFINITY ? 0u : key_of(m2)};
             return warp_rth_largest<2>(kv, rth);
-        };
-
-        // one iteration: the stages c .. c + Q_NS - 1 (the row's last iteration may have fewer)
-        auto stage = [&](uint32_t c, uint32_t head_in) {
-            constexpr int NW = 2 * Q_NS;  // 128-bit words per thread
-            // (The row's flags go through an empty asm so that the compiler sees values it cannot hoist: it would make one
-            // copy of this whole body per combination of them, and the kernel's code has to fit the instruction cache.)
-            uint32_t fl = row_flags, head = head_in, nst = min(uint32_t(Q_NS), n_chunks - c);
-            asm volatile("" : "+r"(fl), "+r"(head), "+r"(nst));
-            const bool no_sum = (fl & QF_NO_SUM) != 0, pen_on = (fl & QF_PEN) != 0, lazy = (fl & QF_LAZY) != 0;
-            uint4 w[NW];
-            uint32_t wq[NW];  // the word's place in the row
-            uint32_t st_ring[Q_NS];
-#pragma unroll
-            for (int h = 0; h < Q_NS; ++h) {
-                st_ring[h] = st_slot;
-                if (h == 0 || uint32_t(h) < nst) {
-#ifdef WB_PROF
-                    const long long tw0 = clock64();
-#endif
-                    if (!mbar_wait(&full[st_slot], st_phase)) {
-                        if (lane == 0) atomicExch(a.err, 5u);
-                        st_fail = true;
-                        return;
-                    }
-#ifdef WB_PROF
-                    sp_wait += clock64() - tw0;
-#endif
-                }
-                const uint4* vec = reinterpret_cast<const uint4*>(ring + size_t(st_slot) * Q_SB);
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    wq[2 * h + j] = (c + h) * Q_SQ + uint32_t(j) * Q_ST + uint32_t(st_tid);
-                    w[2 * h + j] = wq[2 * h + j] < row_q ? vec[j * Q_ST + st_tid] : ninf4;  // (only the row's last stage can be short)
-                }
-                if (h == 0 || uint32_t(h) < nst) {
-                    if (++st_slot == uint32_t(stages)) st_slot = 0, st_phase ^= 1u;
-                }
-            }
-            // words that hold a history token (the warp's 32 words are 32 consecutive bits of the map)
-            uint32_t marked = 0;  // bit i: word i
-            if (pen_on) {
-                const uint4 mw = *reinterpret_cast<const uint4*>(gbm + (((c / 2) * Q_SW + uint32_t(sw)) << 2));
-                marked = ((mw.x >> lane) & 1u) | (((mw.y >> lane) & 1u) << 1) | (((mw.z >> lane) & 1u) << 2) | (((mw.w >> lane) & 1u) << 3);
-                if (!lazy) {
-                    // they are put aside for the tail group, as they are, and count as -inf here
-#pragma unroll
-                    for (int i = 0; i < NW; ++i) {
-                        const bool mk = (marked >> i) & 1u;
-                        const uint32_t bal = __ballot_sync(0xffffffffu, mk);
-                        if (bal) {
-                            uint32_t at = 0;
-                            if (lane == 0) at = atomicAdd(&sl->side_cnt, uint32_t(__popc(bal)));
-                            at = __shfl_sync(0xffffffffu, at, 0) + uint32_t(__popc(bal & ((1u << lane) - 1)));
-                            if (mk && at < uint32_t(kMaxHist)) {
-                                __stcg(side_w(p) + at, w[i]);
-                                __stcg(side_q(p) + at, wq[i]);
-                            }
-                            if (mk) w[i] = ninf4;
-                        }
-                    }
-                    marked = 0;
-                }
-            }
-            float xv[NW * VE];
-#pragma unroll
-            for (int i = 0; i < NW; ++i) {
-                const uint32_t w4[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
-                float* x = xv + i * VE;
-                if (sizeof(T) == 4) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) x[e] = __uint_as_float(w4[e]);
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) x[2 * e] = __uint_as_float(w4[e] << 16), x[2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
-                }
-            }
-            // maxima of the words; fmaxf skips NaN, so a NaN logit never raises a maximum
-            float qm[NW];
-#pragma unroll
-            for (int i = 0; i < NW; ++i) {
-                float mx = xv[i * VE];
-#pragma unroll
-                for (int e = 1; e < VE; ++e) mx = fmaxf(mx, xv[i * VE + e]);
-                qm[i] = mx;
-            }
-            // Every loaded register has been consumed, so the shared-memory reads have completed (instructions issue in
-            // order and the fmaxf had to wait for the data): only now may the producer overwrite the stages.
-            __syncwarp();
-            if (lane == 0) {
-#pragma unroll
-                for (int h = 0; h < Q_NS; ++h)
-                    if (h == 0 || uint32_t(h) < nst) mbar_arrive(&empty[st_ring[h]]);
-            }
-            float vm = qm[0];
-#pragma unroll
-            for (int i = 1; i < NW; ++i) vm = fmaxf(vm, qm[i]);
-            // what counts for this lane's bounds: not the marked words (their raw logits are not the row's)
-            float vb = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < NW; ++i) vb = fmaxf(vb, ((marked >> i) & 1u) ? -INFINITY : qm[i]);
-            if (!no_sum) {
-                if (vm > m1) {
-                    // new reference exponent: an integer at or above m * cexp, so every term is at most 1 and
-                    // x * cexp - e is one fused operation with a single rounding
-                    const float ne = ceilf(vm * cexp);
-                    s_t = (m1 == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
-                    e_t = ne;
-                }
-                if (fmaxf(vm, m1) != -INFINITY) {
-                    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                    for (int j = 0; j < NW * VE; ++j) acc[j & 3] += ex2_approx(fmaf(xv[j], cexp, -e_t));
-                    s_t += (acc[0] + acc[1]) + (acc[2] + acc[3]);
-                }
-            }
-            m2 = fmaxf(m2, fminf(m1, vb));
-            m1 = fmaxf(m1, vb);
-            if (head) {
-                // The row's first threshold: every warp names its bound from what it has just read and the warps meet (their
-                // one meeting per row); what this lane read is tested against the agreed bound below, from its registers.
-#ifdef WB_PROF
-                const long long th0 = clock64();
-#endif
-                const uint32_t kr = own_bound();
-                if (lane == 0) {
-                    sl->wbound[sw] = kr;
-                    mbar_arrive(&head_done[p]);
-                }
-                if (!mbar_wait(&head_done[p], (ord >> 1) & 1)) {
-                    if (lane == 0) atomicExch(a.err, 11u);
-                    st_fail = true;
-                    return;
-                }
-                const uint32_t kmin = __reduce_min_sync(0xffffffffu, lane < Q_SW ? ldv_u32(&sl->wbound[lane]) : 0xffffffffu);
-                if (kmin) tau_seen = (unsigned long long)kmin << 32, tau_f = float_of_key(kmin);
-                if (sw == 0 && lane == 0 && tau_seen > ldv_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = tau_seen;
-#ifdef WB_PROF
-                sp_head += clock64() - th0;
-#endif
-            } else {
-                const unsigned long long tq = ldv_u64(&sl->tau);
-                if (tq > tau_seen) tau_seen = tq, tau_f = float_of_key(cand_key(tq));
-            }
-            if (vm >= tau_f) {
-                // rare: this lane holds an element that may beat the threshold
-#pragma unroll
-                for (int i = 0; i < NW; ++i) {
-                    if (qm[i] >= tau_f && wq[i] < row_q) {
-                        const bool mk = (marked >> i) & 1u;
-#pragma unroll
-                        for (int e = 0; e < VE; ++e)
-                            if (xv[i * VE + e] >= tau_f) log_append(sl, log, xv[i * VE + e], wq[i] * VE + e, tau_seen, mk);
-                    }
-                }
-            }
         };
         // a fresh bound from this warp's maxima; the other warps' entries may be older: any of their bounds for this row is valid
         auto renew = [&]() {
@@ -1040,17 +887,193 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 if (cnd > ldv_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = cnd;
             }
         };
-        const uint32_t n_iter = (n_chunks + Q_NS - 1) / Q_NS;
-        uint32_t next_renew = Q_NS == 2 ? 2 : 1;
+
+        // The row's iterations, in one of three forms so that the common rows run a short loop: PLAIN (no normaliser, no
+        // penalties), LAZY (no normaliser, penalties that only lower a logit), GENERAL (the rest).
+        constexpr int SM_PLAIN = 0, SM_LAZY = 1, SM_GENERAL = 2;
+        auto run_row = [&](auto mode_tag) {
+            constexpr int MODE = decltype(mode_tag)::value;
+            constexpr int NW = 2 * Q_NS;  // 128-bit words per thread and iteration
+            uint32_t next_renew = 2;
 #pragma unroll 1
-        for (uint32_t iter = 0; iter < n_iter && !st_fail; ++iter) {
-            stage(Q_NS * iter, iter == 0 ? 1u : 0u);
-            // a fresh bound each time the part of the row seen has grown by half
-            if (iter + 1 == next_renew && iter + 1 < n_iter && !st_fail) {
-                renew();
-                next_renew += (next_renew + 1) / 2;
+            for (uint32_t iter = 0; iter < n_iter; ++iter) {
+                const uint32_t c = Q_NS * iter;
+                // (In the GENERAL form the row's flags go through an empty asm so that the compiler sees values it cannot hoist:
+                // it would make one copy of this whole body per combination of them, and the kernel's code has to fit the
+                // instruction cache.)
+                uint32_t fl = row_flags;
+                if (MODE == SM_GENERAL) asm volatile("" : "+r"(fl));
+                const bool no_sum = MODE != SM_GENERAL || (fl & QF_NO_SUM) != 0;
+                const bool pen_on = MODE == SM_LAZY || (MODE == SM_GENERAL && (fl & QF_PEN) != 0);
+                const bool lazy = MODE == SM_LAZY;
+                const bool whole = iter < full_iters;  // (only the row's last iteration can be short)
+                uint4 w[NW];
+                uint32_t st_ring[Q_NS];
+#pragma unroll
+                for (int h = 0; h < Q_NS; ++h) {
+                    st_ring[h] = st_slot;
+                    if (whole || c + uint32_t(h) < n_chunks) {
+#ifdef WB_PROF
+                        const long long tw0 = clock64();
+#endif
+                        if (!mbar_wait(&full[st_slot], st_phase)) {
+                            if (lane == 0) atomicExch(a.err, 5u);
+                            st_fail = true;
+                            return;
+                        }
+#ifdef WB_PROF
+                        sp_wait += clock64() - tw0;
+#endif
+                    }
+                    const uint4* vec = reinterpret_cast<const uint4*>(ring + size_t(st_slot) * Q_SB);
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) w[2 * h + j] = vec[j * Q_ST + st_tid];  // (a stage that is not the row's reads as
+                                                                                        // whatever the ring holds: masked below)
+                    if (whole || c + uint32_t(h) < n_chunks) {
+                        if (++st_slot == uint32_t(stages)) st_slot = 0, st_phase ^= 1u;
+                    }
+                }
+                const uint32_t wq0 = c * Q_SQ + uint32_t(st_tid);  // word i of this thread is at wq0 + i * Q_ST in the row
+                if (!whole) {
+#pragma unroll
+                    for (int i = 0; i < NW; ++i)
+                        if (wq0 + uint32_t(i) * Q_ST >= row_q) w[i] = ninf4;
+                }
+                // words that hold a history token (one 128-bit load gives the thread its four bits)
+                uint32_t marked = 0;  // bit i: word i
+                if (pen_on) {
+                    const uint4 mw = *reinterpret_cast<const uint4*>(gbm + ((iter * Q_SW + uint32_t(sw)) << 2));
+                    marked = ((mw.x >> lane) & 1u) | (((mw.y >> lane) & 1u) << 1) | (((mw.z >> lane) & 1u) << 2) | (((mw.w >> lane) & 1u) << 3);
+                    if (!lazy) {
+                        // they are put aside for the tail group, as they are, and count as -inf here
+#pragma unroll
+                        for (int i = 0; i < NW; ++i) {
+                            const bool mk = (marked >> i) & 1u;
+                            const uint32_t bal = __ballot_sync(0xffffffffu, mk);
+                            if (bal) {
+                                uint32_t at = 0;
+                                if (lane == 0) at = atomicAdd(&sl->side_cnt, uint32_t(__popc(bal)));
+                                at = __shfl_sync(0xffffffffu, at, 0) + uint32_t(__popc(bal & ((1u << lane) - 1)));
+                                if (mk && at < uint32_t(kMaxHist)) {
+                                    __stcg(side_w(p) + at, w[i]);
+                                    __stcg(side_q(p) + at, wq0 + uint32_t(i) * Q_ST);
+                                }
+                                if (mk) w[i] = ninf4;
+                            }
+                        }
+                        marked = 0;
+                    }
+                }
+                float xv[NW * VE];
+#pragma unroll
+                for (int i = 0; i < NW; ++i) {
+                    const uint32_t w4[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+                    float* x = xv + i * VE;
+                    if (sizeof(T) == 4) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) x[e] = __uint_as_float(w4[e]);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) x[2 * e] = __uint_as_float(w4[e] << 16), x[2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
+                    }
+                }
+                // maxima of the words; fmaxf skips NaN, so a NaN logit never raises a maximum
+                float qm[NW];
+#pragma unroll
+                for (int i = 0; i < NW; ++i) {
+                    float mx = xv[i * VE];
+#pragma unroll
+                    for (int e = 1; e < VE; ++e) mx = fmaxf(mx, xv[i * VE + e]);
+                    qm[i] = mx;
+                }
+                // Every loaded register has been consumed, so the shared-memory reads have completed (instructions issue in
+                // order and the fmaxf had to wait for the data): only now may the producer overwrite the stages.
+                __syncwarp();
+                if (lane == 0) {
+#pragma unroll
+                    for (int h = 0; h < Q_NS; ++h)
+                        if (whole || c + uint32_t(h) < n_chunks) mbar_arrive(&empty[st_ring[h]]);
+                }
+                float vm = qm[0];
+#pragma unroll
+                for (int i = 1; i < NW; ++i) vm = fmaxf(vm, qm[i]);
+                // what counts for this lane's bounds: not the marked words (their raw logits are not the row's)
+                float vb = vm;
+                if (lazy) {
+                    vb = -INFINITY;
+#pragma unroll
+                    for (int i = 0; i < NW; ++i) vb = fmaxf(vb, ((marked >> i) & 1u) ? -INFINITY : qm[i]);
+                }
+                if (!no_sum) {
+                    if (vm > m1) {
+                        // new reference exponent: an integer at or above m * cexp, so every term is at most 1 and
+                        // x * cexp - e is one fused operation with a single rounding
+                        const float ne = ceilf(vm * cexp);
+                        s_t = (m1 == -INFINITY) ? 0.f : s_t * ex2_approx(e_t - ne);
+                        e_t = ne;
+                    }
+                    if (fmaxf(vm, m1) != -INFINITY) {
+                        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int j = 0; j < NW * VE; ++j) acc[j & 3] += ex2_approx(fmaf(xv[j], cexp, -e_t));
+                        s_t += (acc[0] + acc[1]) + (acc[2] + acc[3]);
+                    }
+                }
+                m2 = fmaxf(m2, fminf(m1, vb));
+                m1 = fmaxf(m1, vb);
+                if (iter == 0) {
+                    // The row's first threshold: every warp names its bound from what it has just read and the warps meet (their
+                    // one meeting per row); what this lane read is tested against the agreed bound below, from its registers.
+#ifdef WB_PROF
+                    const long long th0 = clock64();
+#endif
+                    const uint32_t kr = own_bound();
+                    if (lane == 0) {
+                        sl->wbound[sw] = kr;
+                        mbar_arrive(&head_done[p]);
+                    }
+                    if (!mbar_wait(&head_done[p], (ord >> 1) & 1)) {
+                        if (lane == 0) atomicExch(a.err, 11u);
+                        st_fail = true;
+                        return;
+                    }
+                    const uint32_t kmin = __reduce_min_sync(0xffffffffu, lane < Q_SW ? ldv_u32(&sl->wbound[lane]) : 0xffffffffu);
+                    if (kmin) tau_key = kmin, tau_f = float_of_key(kmin);
+                    if (sw == 0 && lane == 0) {
+                        const unsigned long long t0 = (unsigned long long)kmin << 32;
+                        if (t0 > ldv_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = t0;
+                    }
+#ifdef WB_PROF
+                    sp_head += clock64() - th0;
+#endif
+                } else {
+                    const uint32_t tk = *tau_hi;
+                    if (tk > tau_key) tau_key = tk, tau_f = float_of_key(tk);
+                }
+                if (vm >= tau_f) {
+                    // rare: this lane holds an element that may beat the threshold
+                    const unsigned long long tau = (unsigned long long)tau_key << 32;
+#pragma unroll
+                    for (int i = 0; i < NW; ++i) {
+                        if (qm[i] >= tau_f) {
+                            const bool mk = (marked >> i) & 1u;
+                            const uint32_t id0 = (wq0 + uint32_t(i) * Q_ST) * VE;
+#pragma unroll
+                            for (int e = 0; e < VE; ++e)
+                                if (xv[i * VE + e] >= tau_f) log_append(sl, log, xv[i * VE + e], id0 + e, tau, mk);
+                        }
+                    }
+                }
+                // a fresh bound each time the part of the row seen has grown by half
+                if (iter + 1 == next_renew && iter + 1 < n_iter) {
+                    renew();
+                    next_renew += (next_renew + 1) / 2;
+                }
             }
-        }
+        };
+        if ((row_flags & (QF_NO_SUM | QF_PEN)) == QF_NO_SUM) run_row(std::integral_constant<int, SM_PLAIN>{});
+        else if (row_flags & QF_LAZY) run_row(std::integral_constant<int, SM_LAZY>{});
+        else run_row(std::integral_constant<int, SM_GENERAL>{});
         if (st_fail) return;
         // ---- the row is through for this warp: partials, then close
         if (!(row_flags & QF_NO_SUM)) {
@@ -1065,7 +1088,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             ds = warp_sum(ds);
             if (lane == 0) sl->red_m[sw] = wm, sl->red_e[sw] = we, sl->red_s[sw] = ds;
         }
-        __threadfence();  // (words put aside in global memory are read by the tail group)
+        if ((row_flags & (QF_PEN | QF_LAZY)) == QF_PEN) __threadfence();  // (words put aside in global memory are read by the tail group)
         __syncwarp();
         if (lane == 0) mbar_arrive(&closed[p]);
     }
