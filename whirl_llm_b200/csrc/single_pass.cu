@@ -58,6 +58,9 @@ constexpr int Q_MAXSTAGES = 8;
 #define WB_NS 2
 #endif
 constexpr int Q_NS = WB_NS;              // ring stages per iteration of a stream warp
+#ifndef WB_RENEW_STEP
+#define WB_RENEW_STEP (next_renew + 1) / 2
+#endif
 #ifndef WB_QL
 #define WB_QL 3072
 #endif
@@ -491,7 +494,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
         // half are all on their way at once and the inserts are one rolled loop.
         auto build_table = [&](int p) {
             const QRow cfg = sh->slot[p].cfg;
-            if (!(cfg.flags & QF_PEN)) return;
+            if ((cfg.flags & (QF_PEN | QF_LAZY)) != QF_PEN) return;  // (only rows that put words aside need it)
             constexpr int HALF = kMaxHist / 2;
             constexpr int HP = (HALF + Q_PT - 1) / Q_PT;
             static_assert(HALF <= SEL_BINS, "half a history fits the scratch");
@@ -563,6 +566,14 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 cfg = sl->cfg;
                 const uint32_t K = cfg.K;
                 const bool no_sum = (cfg.flags & QF_NO_SUM) != 0, pen_on = (cfg.flags & QF_PEN) != 0, lazy = (cfg.flags & QF_LAZY) != 0;
+                // (a row with marked log entries will want its history when it is through: the loads go out now)
+                constexpr int HB = kMaxHist / Q_TT;
+                int32_t hv[HB];
+                if (lazy) {
+                    const int32_t* h = P.hist + size_t(cfg.row) * P.hist_stride;
+#pragma unroll
+                    for (int u = 0; u < HB; ++u) hv[u] = (u * Q_TT + g.tid) < cfg.hist_len ? h[u * Q_TT + g.tid] : -1;
+                }
                 // ---- while the row streams
                 PROF_T0(tw0);
                 // (one thread watches the row; the others wait at the group's barrier, where they take no issue slot from the
@@ -606,18 +617,45 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     const unsigned long long tau = sl->tau;
                     const float tau_f = cand_key(tau) ? float_of_key(cand_key(tau)) : -INFINITY;
                     if (lazy) {
-                        // the marked entries of the log: logged raw from a word that holds a history token; a history token
-                        // gets its penalty now (another logit of such a word stays as it is)
+                        // The marked entries of the log: logged raw from a word that holds a history token.  A history token
+                        // among them gets its penalty now (another logit of such a word stays as it is).  They are few, so
+                        // their counts come from a scan of the history, not from a table: every thread holds its share of the
+                        // history in registers and all of them count one marked token after the other.
+                        uint32_t* mlist = hist;                 // places in the log of the marked entries
+                        uint32_t* mcnt = hist + SEL_BINS / 2;   // their counts
                         const uint32_t nl = min(sl->cnt & 0x7fffffffu, uint32_t(Q_L));
+                        if (g.tid == 0) sh->flag[3] = 0u;
+                        g.sync();
 #pragma unroll 1
                         for (uint32_t i = g.tid; i < nl; i += Q_TT) {
-                            unsigned long long c = log[i];
+                            const unsigned long long c = log[i];
                             if (c != 0ull && !(c & 0x80000000ull)) {
+                                const uint32_t at = atomicAdd(&sh->flag[3], 1u);
+                                if (at < uint32_t(SEL_BINS / 2)) mlist[at] = i, mcnt[at] = 0u;
+                            }
+                        }
+                        g.sync();
+                        const uint32_t nm = sh->flag[3];
+                        if (nm > uint32_t(SEL_BINS / 2)) {
+                            if (g.tid == 0) atomicOr(&sl->cnt, 0x80000000u);  // (more than the scratch holds: the multi-pass kernel takes the row)
+                        } else if (nm > 0) {
+#pragma unroll 1
+                            for (uint32_t m = 0; m < nm; ++m) {
+                                const int32_t id = int32_t(~uint32_t(log[mlist[m]]) & 0x7fffffffu);
+                                uint32_t c = 0;
+#pragma unroll
+                                for (int u = 0; u < HB; ++u) c += hv[u] == id;
+                                c = warp_sum(c);
+                                if (lane == 0 && c) atomicAdd(&mcnt[m], c);
+                            }
+                            g.sync();
+#pragma unroll 1
+                            for (uint32_t m = g.tid; m < nm; m += Q_TT) {
+                                const unsigned long long c = log[mlist[m]];
                                 const uint32_t id = ~uint32_t(c) & 0x7fffffffu;
-                                const uint32_t cnt = pen_table_count(pslots, id);
                                 float x = float_of_key(cand_key(c));
-                                if (cnt) x = penalised(x, cnt, cfg.rep, cfg.pres, cfg.freq);
-                                log[i] = make_cand(key_of(x), id);
+                                if (mcnt[m]) x = penalised(x, mcnt[m], cfg.rep, cfg.pres, cfg.freq);
+                                log[mlist[m]] = make_cand(key_of(x), id);
                             }
                         }
                     } else {
@@ -1067,7 +1105,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 // a fresh bound each time the part of the row seen has grown by half
                 if (iter + 1 == next_renew && iter + 1 < n_iter) {
                     renew();
-                    next_renew += (next_renew + 1) / 2;
+                    next_renew += WB_RENEW_STEP;
                 }
             }
         };
