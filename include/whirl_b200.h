@@ -46,6 +46,11 @@ enum {
     WHIRL_CNT_ESCALATED = 0, /* rows that needed the second candidate level (the reference's Sampler::big_used) */
     WHIRL_CNT_OPEN_TAIL = 1, /* rows whose draw walked the row in id order (Sampler::full_used) */
     WHIRL_CNT_UNRESOLVED = 2,/* rows left with a status other than WHIRL_ROW_DONE */
+    WHIRL_CNT_TIMEOUT = 3,   /* calls in which a bounded device-side wait ran out (whirl_check names the wait) */
+    WHIRL_CNT_REDO = 4,      /* rows the single-pass kernel handed to the multi-pass kernel to do again: more candidates
+                                than its log holds, a NaN in a sum, an open-set walk, or a row a wait that ran out left
+                                unanswered */
+    WHIRL_CNT_NAN_ROWS = 5,  /* rows of those in which a NaN logit met the normaliser */
     WHIRL_CNT_WORDS = 8
 };
 
@@ -235,10 +240,25 @@ int whirl_spec_accept_residual(const void* target, const void* draft, int dtype,
                                const float* inv_t, const double* u_acc, const double* u_res, int* n_acc, int* next_tok, void* ws,
                                size_t ws_bytes, void* stream);
 
+/* Reads the device error word that the last whirl_sample_rows / whirl_topk_rows call on this workspace left (the call
+ * synchronises `stream`).  WHIRL_OK, or WHIRL_ERR_TIMEOUT when a bounded wait inside the single-pass kernel ran out;
+ * *where (may be null) then gets which wait: 1 producer / ring stage free, 3 tail group / row streamed, 4 stream warps /
+ * slot ready, 5 stream warps / ring stage full, 11 stream warps / threshold meeting.  The rows such a wait left
+ * unanswered were handed to the multi-pass kernel, so the outputs stand unless counters[WHIRL_CNT_UNRESOLVED] is
+ * non-zero; the code still tells the caller that the device did not behave. */
+int whirl_check(const void* ws, size_t ws_bytes, int rows, void* stream, uint32_t* where);
+
+/* Testing aid, per calling thread: the following whirl_sample_rows / whirl_topk_rows calls give every wait of the
+ * single-pass kernel a budget of about wait_us microseconds (0 = the default, about a second), and with lose_copy != 0
+ * the first CTA leaves one bulk copy of its first row out, so that the waits on it run out and the error path above
+ * can be exercised without a fault.  whirl_test_waits(0, 0) restores the defaults. */
+void whirl_test_waits(uint32_t wait_us, int lose_copy);
+
 /* The same call on HOST buffers: logits, parameters and outputs are host pointers; the call copies them to the device
  * (workspace + staging it allocates on first use and keeps), runs whirl_sample_rows in row chunks that overlap the
  * copies, copies the outputs back and synchronises.  For callers that hold logits in host memory and for end-to-end
- * measurement; a serving engine whose logits are already on the device calls whirl_sample_rows. */
+ * measurement; a serving engine whose logits are already on the device calls whirl_sample_rows.  Returns
+ * WHIRL_ERR_TIMEOUT (outputs written all the same) when a device-side wait ran out in one of the chunks. */
 int whirl_sample_rows_host(const void* x_host, int dtype, int rows, int n, const whirl_sample_params* params_host,
                            const whirl_sample_out* out_host, int device);
 /* Releases what whirl_sample_rows_host keeps. */

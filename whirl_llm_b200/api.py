@@ -15,7 +15,8 @@ LIB_PATH = os.environ.get("WHIRL_B200_LIB") or os.path.join(_HERE, "libwhirl_b20
 
 F32, BF16 = 0, 1
 ROW_DONE, ROW_ESCALATE, ROW_OPEN_TAIL = 0, 1, 2
-CNT_ESCALATED, CNT_OPEN_TAIL, CNT_UNRESOLVED, CNT_WORDS = 0, 1, 2, 8
+CNT_ESCALATED, CNT_OPEN_TAIL, CNT_UNRESOLVED, CNT_TIMEOUT, CNT_REDO, CNT_NAN_ROWS, CNT_WORDS = 0, 1, 2, 3, 4, 5, 8
+ERR_TIMEOUT = 5
 MAX_K, STREAM_MAX_K, MAX_HIST, Q_WORDS, Q_MAX, CTL_WORDS = 16384, 1024, 4096, 72, 32, 64
 STATIC_MAX_ROWS = 256
 
@@ -74,6 +75,8 @@ def _load() -> C.CDLL:
         "whirl_host_release": (None, []),
         "whirl_host_last_error": (C.c_char_p, []),
         "whirl_launch_counts": (None, [vp, i]),
+        "whirl_check": (i, [vp, sz, i, vp, vp]),
+        "whirl_test_waits": (None, [C.c_uint32, i]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -86,7 +89,7 @@ DECLARED = ["whirl_status_string", "whirl_last_error", "whirl_version", "whirl_w
             "whirl_argmax_rows", "whirl_argmax_rows_static", "whirl_argmax_rows_to", "whirl_argmax_prob", "whirl_draft_pick", "whirl_draft_pick_rows", "whirl_draft_sample_rows", "whirl_accept_tokens", "whirl_spec_workspace_bytes",
             "whirl_spec_accept_residual",
             "whirl_topk_rows", "whirl_topk_rows_shard", "whirl_merge_sample_rows", "whirl_sample_rows", "whirl_sample_rows_host", "whirl_host_release", "whirl_host_last_error",
-            "whirl_launch_counts"]
+            "whirl_launch_counts", "whirl_check", "whirl_test_waits"]
 
 
 def _check(status: int):
@@ -302,6 +305,21 @@ def sample_rows(x, params: RowParams, kept_cap: int = 0, ws=None, result: Option
     ps = params.struct(rows)
     _check(lib.whirl_sample_rows(x.data_ptr(), _dtype(x), rows, n, C.byref(ps), C.byref(o), ws.data_ptr(), ws.numel(), _stream(x)))
     return result
+
+
+def check(ws: torch.Tensor, rows: int) -> int:
+    """whirl_check: reads the device error word of the last sample_rows / topk_rows call on `ws` (synchronises the
+    stream).  Returns the code of the wait that ran out (0: none)."""
+    where = C.c_uint32(0)
+    st = lib.whirl_check(ws.data_ptr(), ws.numel(), rows, torch.cuda.current_stream(ws.device).cuda_stream, C.byref(where))
+    if st not in (0, ERR_TIMEOUT):
+        _check(st)
+    return int(where.value)
+
+
+def test_waits(wait_us: int = 0, lose_copy: bool = False) -> None:
+    """whirl_test_waits: a testing aid; see include/whirl_b200.h."""
+    lib.whirl_test_waits(wait_us, int(lose_copy))
 
 
 def launch_counts() -> dict:

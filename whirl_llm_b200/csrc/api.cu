@@ -17,6 +17,9 @@
 namespace {
 
 thread_local std::string g_err;
+// testing aid (whirl_test_waits): wait budget and lost copy of this thread's single-pass launches
+thread_local uint32_t g_wait_limit = 0;
+thread_local uint32_t g_lose_copy = 0;
 
 // host-side launch counters per kernel family (whirl_launch_counts)
 std::atomic<uint64_t> g_launch[4];
@@ -87,7 +90,7 @@ __global__ void gather_rows_kernel(const int32_t* status, int rows, int want, in
     __syncthreads();
     for (int base = 0; base < rows; base += blockDim.x) {
         const int r = base + threadIdx.x;
-        const bool f = r < rows && status[r] == want;
+        const bool f = r < rows && (status[r] == want || status[r] == wb::ROW_PENDING);
         // order inside the list does not matter: rows are independent
         if (f) list[atomicAdd(&s_n, 1)] = r;
     }
@@ -225,6 +228,7 @@ int whirl_topk_rows_shard(const void* x, int dtype, int rows, int n, int K, int 
     wb::SelectArgs a{};
     a.x = x, a.rows = rows, a.n = n, a.mode = wb::MODE_TOPK, a.K = K, a.ids = ids, a.vals = vals, a.stats = stats;
     a.id_offset = id_offset;
+    a.wait_limit = g_wait_limit, a.lose_copy = g_lose_copy;
     a.prm.inv_t = inv_t_rows, a.prm.inv_t_scalar = inv_t;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     cudaError_t e;
@@ -284,6 +288,7 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
     a.ws = base + w.off_p;
     a.err = reinterpret_cast<uint32_t*>(base + w.off_err);
     a.side_ws = base + w.off_side;
+    a.wait_limit = g_wait_limit, a.lose_copy = g_lose_copy;
     // level 1: top_k candidates (the set closes there), or 256 of them as the reference's first launch does
     // (k_small, src/server/engine_sampling.h:20)
     a.level_k = wb::kFirstLevelK;
@@ -302,7 +307,7 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
         wb::SelectArgs b = a;
         b.level_k = wb::kGenericMaxK, b.row_list = list_b, b.row_count = counts + 1;
         b.out.counters = nullptr;  // (counters[0] and [1] were counted by the first kernel)
-        b.unresolved = out->counters ? out->counters + WHIRL_CNT_UNRESOLVED : nullptr;
+        b.batch_counters = out->counters;
         if (wb::select_full_ws_bytes(n) != 0) {
             b.full_ws = base + w.off_full, b.full_locks = reinterpret_cast<uint32_t*>(base + w.off_locks);
             b.full_slots = wb::kFullSlots, b.full_npad = wb::select_full_npad(n);
@@ -337,6 +342,23 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
     e = cudaGetLastError();
     return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "sample_rows");
 }
+
+int whirl_check(const void* ws, size_t ws_bytes, int rows, void* stream, uint32_t* where) {
+    if (!ws || rows < 0) return fail(WHIRL_ERR_INVALID, "check: ws is null or rows < 0");
+    const Ws w = ws_layout(rows < 1 ? 1 : rows);
+    if (ws_bytes < w.off_err + 64) return fail(WHIRL_ERR_WORKSPACE, "check: workspace too small for this row count");
+    uint32_t word = 0;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(&word, static_cast<const uint8_t*>(ws) + w.off_err, 4, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail_cuda(e, "check");
+    if (where) *where = word;
+    if (word == 0) return WHIRL_OK;
+    g_err = "a bounded wait of the single-pass kernel ran out (wait " + std::to_string(word) + ")";
+    return WHIRL_ERR_TIMEOUT;
+}
+
+void whirl_test_waits(uint32_t wait_us, int lose_copy) { g_wait_limit = wait_us, g_lose_copy = lose_copy ? 1u : 0u; }
 
 #ifdef WB_PROF
 size_t whirl_debug_err_offset(int rows, int n) { return ws_layout(rows, n).off_err; }

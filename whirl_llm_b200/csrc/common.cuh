@@ -139,11 +139,12 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait (about a second).  false = gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// Bounded wait: up to `limit` suspensions of about a microsecond each (the default is about a second).  false = gave up.
+constexpr uint32_t kWaitLimit = 1u << 20;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = kWaitLimit) {
     if (mbar_try_wait(bar, parity)) return true;
 #pragma unroll 1
-    for (uint32_t it = 0; it < (1u << 20); ++it)
+    for (uint32_t it = 0; it < limit; ++it)
         if (mbar_try_wait_for(bar, parity, 1000u)) return true;
     return false;
 }

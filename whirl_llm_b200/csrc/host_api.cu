@@ -151,7 +151,7 @@ int whirl_sample_rows_host(const void* x, int dtype, int rows, int n, const whir
         dout.n_kept = static_cast<int32_t*>(at(out[2])), dout.closed = static_cast<int32_t*>(at(out[3]));
         dout.stats = static_cast<float*>(at(out[4])), dout.kept_ids = static_cast<int32_t*>(at(out[5]));
         dout.kept_p = static_cast<double*>(at(out[6])), dout.kept_cap = o->kept_cap;
-        dout.counters = o->counters ? reinterpret_cast<uint32_t*>(base + cnt_off) : nullptr;
+        dout.counters = reinterpret_cast<uint32_t*>(base + cnt_off);  // (always: the error report comes through them)
         const int rc = whirl_sample_rows(g_s.logits[s], dtype, nr, n, &dp, &dout, g_s.ws[s], g_s.ws_bytes, g_s.st[s]);
         if (rc != WHIRL_OK) {
             g_herr = whirl_last_error();
@@ -165,10 +165,14 @@ int whirl_sample_rows_host(const void* x, int dtype, int rows, int n, const whir
     }
     CK(cudaStreamSynchronize(g_s.st[0]));
     CK(cudaStreamSynchronize(g_s.st[1]));
-    if (o->counters) {
-        uint32_t c[WHIRL_CNT_WORDS];
-        CK(cudaMemcpy(c, base + cnt_off, sizeof c, cudaMemcpyDeviceToHost));
+    uint32_t c[WHIRL_CNT_WORDS];
+    CK(cudaMemcpy(c, base + cnt_off, sizeof c, cudaMemcpyDeviceToHost));
+    if (o->counters)
         for (int i = 0; i < WHIRL_CNT_WORDS; ++i) o->counters[i] += c[i];
+    if (c[WHIRL_CNT_TIMEOUT]) {
+        g_herr = "sample_rows_host: a bounded device-side wait ran out in " + std::to_string(c[WHIRL_CNT_TIMEOUT]) + " chunk(s); " +
+                 std::to_string(c[WHIRL_CNT_UNRESOLVED]) + " row(s) without an answer";
+        return WHIRL_ERR_TIMEOUT;
     }
     return WHIRL_OK;
 }

@@ -3,6 +3,8 @@
 #pragma once
 
 #include <cuda_runtime.h>
+
+#include "../../include/whirl_b200.h"
 #include <stddef.h>
 #include <stdint.h>
 
@@ -114,13 +116,16 @@ struct SelectArgs {
     DraftArgs draft;          // MODE_DRAFT
     int32_t id_offset;        // MODE_TOPK: added to every id written (a vocabulary slice's first token id)
     uint32_t* err;            // device error word (bounded waits that ran out)
+    uint32_t wait_limit;      // single-pass sampler: budget of every wait, in suspensions of about a microsecond (0 = the default)
+    uint32_t lose_copy;       // single-pass sampler, tests only: the producer of CTA 0 leaves out one bulk copy, so that waits run out
     // single-pass sampler, MODE_SAMPLE: its last CTA lists the rows it left to the multi-pass kernel in fin_list (rows with
     // top_k above its limit, and rows whose kept set may reach past 256 candidates; with bit 30: rows to redo at the first
     // level) and their number in fin_counts[1].  fin_counts[2] and [3] are the two kernels' tickets (zero before a launch).
     int32_t* fin_list;
     int32_t* fin_counts;
     void* side_ws;            // single-pass sampler: side buffers for the words kept out of the stream (single_pass_side_bytes)
-    uint32_t* unresolved;     // multi-pass kernel: its last CTA adds the batch's rows still without an answer here (or null)
+    uint32_t* batch_counters; // multi-pass kernel: its last CTA adds the batch's rows still without an answer, and a wait of
+                              // the kernel before it that ran out, to these WHIRL_CNT_* words (or null)
     // multi-pass kernel, third level (the whole row: the reference's last escalation step, src/server/engine_sampling.cpp:79-83):
     // full_slots scratch areas of 16 * full_npad bytes each in global memory, handed out through full_locks (zero = free)
     void* full_ws;

@@ -11,6 +11,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "kernels.h"
 
 namespace wb {
 
@@ -18,6 +19,16 @@ constexpr int kMaxHist = 4096;
 constexpr int kPenSlots = 8192;  // table slots (power of two, at least 2 * kMaxHist)
 constexpr uint32_t kPenIdBits = 19;
 constexpr uint32_t kPenMaxV = (1u << kPenIdBits) - 1;
+
+// The number of history ids a row's penalties read: hist_len clamped to the row of the history array and to kMaxHist
+// (the one clamp every kernel uses).
+__device__ __forceinline__ int hist_len_of(const RowParams& P, int row) {
+    if (!P.hist || !P.hist_len) return 0;
+    int hl = P.hist_len[row];
+    hl = hl < 0 ? 0 : hl;
+    hl = int64_t(hl) > P.hist_stride ? int(P.hist_stride) : hl;
+    return hl > kMaxHist ? kMaxHist : hl;
+}
 
 struct PenaltyTable {
     uint32_t* bitmap;  // ceil(V / 32) words

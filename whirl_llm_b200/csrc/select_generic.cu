@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(GT) select_generic_kernel(SelectArgs a, int ca
         }
     }
     // the CTA that finishes last counts the rows of the whole batch that are still without an answer
-    if (a.unresolved && a.fin_counts) {
+    if (a.batch_counters && a.fin_counts) {
         __shared__ uint32_t s_last;
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -225,8 +225,12 @@ __global__ void __launch_bounds__(GT) select_generic_kernel(SelectArgs a, int ca
             uint32_t c = 0;
             for (int r = threadIdx.x; r < a.rows; r += blockDim.x) c += __ldcg(a.out.status + r) != ROW_DONE;
             c = warp_sum(c);
-            if ((threadIdx.x & 31) == 0 && c) atomicAdd(a.unresolved, c);
-            if (threadIdx.x == 0) a.fin_counts[3] = 0;
+            if ((threadIdx.x & 31) == 0 && c) atomicAdd(&a.batch_counters[WHIRL_CNT_UNRESOLVED], c);
+            if (threadIdx.x == 0) {
+                a.fin_counts[3] = 0;
+                // a bounded wait of the kernel before this one ran out (the error word says which)
+                if (a.err && __ldcg(a.err) != 0u) atomicAdd(&a.batch_counters[WHIRL_CNT_TIMEOUT], 1u);
+            }
         }
     }
 }
@@ -253,7 +257,7 @@ __device__ int select_row(const SelectArgs& a, int row, int level_k, int cap_max
     // ---- penalties table
     PenaltyTable pt;
     pt.on = false;
-    if (sample && P.hist && P.hist_len && P.hist_len[row] > 0) {
+    if (sample && P.hist && hist_len_of(P, row) > 0) {
         pt.rep = P.rep ? P.rep[row] : 1.f, pt.pres = P.pres ? P.pres[row] : 0.f, pt.freq = P.freq ? P.freq[row] : 0.f;
         pt.on = pt.rep != 1.f || pt.pres != 0.f || pt.freq != 0.f;
     }
@@ -263,7 +267,7 @@ __device__ int select_row(const SelectArgs& a, int row, int level_k, int cap_max
         pt.clear(tid, GT, n);
         __syncthreads();
         const int32_t* h = P.hist + size_t(row) * P.hist_stride;
-        const int hl = min(P.hist_len[row], kMaxHist);
+        const int hl = hist_len_of(P, row);
         for (int i = tid; i < hl; i += GT) pt.insert(h[i], n);
     }
     for (int i = tid; i < GBINS; i += GT) hist[i] = 0;
@@ -421,21 +425,29 @@ __device__ int select_row(const SelectArgs& a, int row, int level_k, int cap_max
         // (src/sampling/sampler.cpp:132-146).  Here: every thread sums a contiguous block of ids, a scan places the blocks,
         // and the thread whose block the draw falls into walks it again.
         __syncthreads();
-        uint32_t* set = hist;  // GBINS slots: the candidates' ids, open addressing (0 = empty, id + 1 stored)
-        for (uint32_t i = tid; i < r.n; i += GT) {
+        // GBINS slots: the candidates' ids, open addressing (0 = empty, id + 1 stored).  An open set has at most
+        // kFirstLevelK candidates, so the table stays at most an eighth full; every probe sequence is bounded by the
+        // table size all the same (a full table would end the insert without a slot and the lookup without a match).
+        static_assert(GBINS >= 4 * kFirstLevelK && (GBINS & (GBINS - 1)) == 0, "candidate id set of the open-set walk");
+        uint32_t* set = hist;
+        for (uint32_t i = tid; i < r.n && i < uint32_t(GBINS / 2); i += GT) {
             const uint32_t id = cand_id(cand[i]);
             uint32_t h = (id * 2654435761u) >> 21;
-            while (atomicCAS(&set[h], 0u, id + 1) != 0u) h = (h + 1) & (GBINS - 1);
+            for (int probe = 0; probe < GBINS; ++probe) {
+                if (atomicCAS(&set[h], 0u, id + 1) == 0u) break;
+                h = (h + 1) & (GBINS - 1);
+            }
         }
         __syncthreads();
         auto member = [&](uint32_t id) -> bool {
             uint32_t h = (id * 2654435761u) >> 21;
-            for (;;) {
+            for (int probe = 0; probe < GBINS; ++probe) {
                 const uint32_t v = set[h];
                 if (v == 0) return false;
                 if (v == id + 1) return true;
                 h = (h + 1) & (GBINS - 1);
             }
+            return false;
         };
         const double it = double(inv_t), zs = double(sh->sum);
         const uint32_t S = (n + GT - 1) / GT, b0 = min(n, uint32_t(tid) * S), b1 = min(n, b0 + S);
@@ -575,7 +587,7 @@ __device__ void full_row(const SelectArgs& a, int row, int cap_max, int pen_word
     // the penalty table built for the row by select_row is still in shared memory
     PenaltyTable pt;
     pt.on = false;
-    if (P.hist && P.hist_len && P.hist_len[row] > 0) {
+    if (P.hist && hist_len_of(P, row) > 0) {
         pt.rep = P.rep ? P.rep[row] : 1.f, pt.pres = P.pres ? P.pres[row] : 0.f, pt.freq = P.freq ? P.freq[row] : 0.f;
         pt.on = pt.rep != 1.f || pt.pres != 0.f || pt.freq != 0.f;
     }

@@ -135,7 +135,7 @@ __device__ void list_leftovers(const SelectArgs& a) {
     if (!last) return;
     __threadfence();
     const int32_t* status = a.out.status;
-    int cnt = 0;
+    int cnt = 0, n_redo = 0;
     for (int base = 0; base < a.rows; base += 256) {
         int st8[8];  // (eight loads on their way at once: this is the last thing the kernel does)
 #pragma unroll
@@ -147,14 +147,18 @@ __device__ void list_leftovers(const SelectArgs& a) {
         for (int j = 0; j < 8; ++j) {
             const int r = base + 32 * j + lane;
             const int st = st8[j];
-            const bool redo = st == ROW_RETRY || st == ROW_OPEN_TAIL;
+            const bool redo = st == ROW_RETRY || st == ROW_OPEN_TAIL || st == ROW_PENDING;
             const bool take = redo || st == ROW_LARGE_K || st == ROW_ESCALATE;
             const uint32_t bal = __ballot_sync(0xffffffffu, take);
             if (take) a.fin_list[cnt + __popc(bal & ((1u << lane) - 1))] = r | (redo ? (1 << 30) : 0);
             cnt += __popc(bal);
+            n_redo += __popc(__ballot_sync(0xffffffffu, redo));
         }
     }
-    if (lane == 0) a.fin_counts[1] = cnt, a.fin_counts[2] = 0;
+    if (lane == 0) {
+        a.fin_counts[1] = cnt, a.fin_counts[2] = 0;
+        if (a.out.counters && n_redo) atomicAdd(&a.out.counters[WHIRL_CNT_REDO], uint32_t(n_redo));
+    }
 }
 
 // The r-th largest of the warp's 32 * G keys (kv[0..G) per lane; 0 = none), by taking the largest away r - 1 times.
@@ -299,6 +303,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
     const size_t row_bytes = size_t(n) * sizeof(T);
     const bool sample = a.mode == MODE_SAMPLE;
     const RowParams& P = a.prm;
+    const uint32_t wlim = a.wait_limit ? a.wait_limit : kWaitLimit;  // budget of every wait
     // the CTA's side buffers (one per slot): kMaxHist words and their places in the row
     uint8_t* const side_base = static_cast<uint8_t*>(a.side_ws) + size_t(blockIdx.x) * 2 * kMaxHist * 20;
     auto side_w = [&](int p) { return reinterpret_cast<uint4*>(side_base + size_t(p) * kMaxHist * 20); };
@@ -321,10 +326,10 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             const int li = int(blockIdx.x) + k * int(gridDim.x);
             row = a.row_list ? a.row_list[li] : li;
             keep = true;
-            if (sample && P.top_k && !(P.greedy && P.greedy[row]) && P.top_k[row] > max_k) {
-                keep = false;
-                if (a.out.status) a.out.status[row] = ROW_LARGE_K;
-            }
+            if (sample && P.top_k && !(P.greedy && P.greedy[row]) && P.top_k[row] > max_k) keep = false;
+            // (a listed row stays "pending" until it has its answer: a role that gives up leaves it so, and the multi-pass
+            // kernel takes it)
+            if (a.out.status) a.out.status[row] = keep ? ROW_PENDING : ROW_LARGE_K;
         }
         const uint32_t bal = __ballot_sync(0xffffffffu, keep);
         if ((tid & 31) == 0 && warp < 32) sh->lcount[warp] = uint32_t(__popc(bal));
@@ -354,13 +359,15 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
     if (warp == 0) {
         if (lane_id() != 0) return;
         uint32_t s = 0, par = 1;  // ring stage and the parity of its "empty" barrier to wait for
+        uint32_t issued = 0;      // copies issued so far
         const uint64_t once = l2_evict_first_policy();
+        bool gave_up = false;
 #ifdef WB_PROF
         long long pw = 0;
         const long long pt0 = clock64();
 #endif
 #pragma unroll 1
-        for (int i = 0; i < n_list; ++i) {
+        for (int i = 0; i < n_list && !gave_up; ++i) {
             const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x) + size_t(rlist[i]) * row_bytes;
             uint32_t left = uint32_t(row_bytes);  // (a row is below 4 GiB: n < 2^30 elements of at most 4 bytes)
 #pragma unroll 1
@@ -368,18 +375,37 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
 #ifdef WB_PROF
                 const long long pw0 = clock64();
 #endif
-                if (!mbar_wait(&empty[s], par)) {
+                if (!mbar_wait(&empty[s], par, wlim)) {
                     atomicExch(a.err, 1u);
-                    return;
+                    gave_up = true;
+                    break;
                 }
 #ifdef WB_PROF
                 pw += clock64() - pw0;
 #endif
                 const uint32_t bytes = left < uint32_t(Q_SB) ? left : uint32_t(Q_SB);
-                mbar_expect_tx(&full[s], bytes);
-                bulk_g2s_once(ring + size_t(s) * Q_SB, src, bytes, &full[s], once);
+                // (tests only: one copy of CTA 0 is left out, so that the waits for it run out)
+                const bool lose = a.lose_copy && blockIdx.x == 0 && i == 0 && c == 3;
+                if (!lose) {
+                    mbar_expect_tx(&full[s], bytes);
+                    bulk_g2s_once(ring + size_t(s) * Q_SB, src, bytes, &full[s], once);
+                    ++issued;
+                }
                 src += Q_SB, left -= bytes;
                 if (++s == uint32_t(stages)) s = 0, par ^= 1u;
+            }
+        }
+        // This thread's last copies may still be on their way into the ring when the other roles have given up: the CTA's
+        // shared memory must outlive them, so each one's "full" phase is awaited (bounded; at once in a run without
+        // faults, where the stream warps have consumed them).  A stage armed in ring round r completes phase r of its
+        // barrier, and this thread waited for parity (r & 1) ^ 1 of the stage's "empty" barrier before it.
+        {
+            uint32_t bs = s, bpar = par;
+#pragma unroll 1
+            for (uint32_t k = 0; k < uint32_t(stages) && k < issued; ++k) {
+                if (bs == 0) bs = uint32_t(stages), bpar ^= 1u;
+                --bs;
+                mbar_wait(&full[bs], bpar ^ 1u, wlim);
             }
         }
 #ifdef WB_PROF
@@ -414,12 +440,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 if (lane == 4) v = (unsigned long long)__double_as_longlong(P.min_p ? P.min_p[row] : 0.0);
                 if (lane == 5) v = (unsigned long long)__double_as_longlong(P.u ? P.u[row] : 0.0);
                 if (lane == 6) v = P.race_key ? P.race_key[row] : 0ull;
-                if (lane == 7 && P.hist && gbm_words) {
-                    int hl = P.hist_len[row];
-                    hl = hl < 0 ? 0 : hl;
-                    hl = int64_t(hl) > P.hist_stride ? int(P.hist_stride) : hl;
-                    v = uint32_t(hl > kMaxHist ? kMaxHist : hl);
-                }
+                if (lane == 7 && gbm_words) v = uint32_t(hist_len_of(P, row));
                 if (lane == 8) v = __float_as_uint(P.rep ? P.rep[row] : 1.f);
                 if (lane == 9) v = __float_as_uint(P.pres ? P.pres[row] : 0.f);
                 if (lane == 10) v = __float_as_uint(P.freq ? P.freq[row] : 0.f);
@@ -560,7 +581,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             unsigned long long* log = logs + size_t(p) * Q_L;
             QRow cfg;
             uint32_t kept = 0, cap = 1;
-            bool presorted = false, overflow = false;
+            bool presorted = false, overflow = false, nan_seen = false;
             float M = -INFINITY, sum = 0.f;
             if (ord >= 0) {
                 cfg = sl->cfg;
@@ -584,7 +605,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         uint32_t what = 2u;  // 0: the row is through, 1: the log wants a refinement, 2: gave up
                         const uint32_t step = 2 * K > uint32_t(Q_L) / 4 ? 2 * K : uint32_t(Q_L) / 4;
 #pragma unroll 1
-                        for (uint32_t spin = 0; spin < (1u << 21); ++spin) {
+                        for (uint32_t spin = 0; spin < 4 * wlim; ++spin) {
                             if (mbar_try_wait(&closed[p], (ord >> 1) & 1)) {
                                 what = 0u;
                                 break;
@@ -603,12 +624,13 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     g.sync();
                     if (what == 0u) break;
                     if (what == 2u) {
+                        // (the rows not answered keep their "pending" status; the CTA still hands in its ticket)
                         if (g.tid == 0) atomicExch(a.err, 3u);
-                        return;
+                        goto tail_done;
                     }
                     maybe_refine(p, K, true);
                 }
-                mbar_wait(&closed[p], (ord >> 1) & 1);  // acquire the stream warps' writes
+                mbar_wait(&closed[p], (ord >> 1) & 1, wlim);  // acquire the stream warps' writes
                 PROF_ADD(0, tw0);
                 rf_last[p] = 0;
                 // ---- the row is through
@@ -704,6 +726,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 const uint32_t total_raw = sl->cnt;  // bit 31: a NaN logit met a sum
                 const bool nan_row = (total_raw & 0x80000000u) != 0;
                 const uint32_t total = total_raw & 0x7fffffffu;
+                nan_seen = nan_row;
                 overflow = total > uint32_t(Q_L) || nan_row || (pen_on && !lazy && sl->side_cnt > uint32_t(kMaxHist));
                 const uint32_t nlog = total > uint32_t(Q_L) ? uint32_t(Q_L) : total;
                 // row max and normaliser: combine the warps' partials, one per lane (not needed when the row is normalised
@@ -781,7 +804,10 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 if (overflow) {
                     // more candidates than the log holds (rows in adversarial order), or a NaN in a sum: the multi-pass
                     // kernel takes the row
-                    if (lane == 0) a.out.status[row] = ROW_RETRY;
+                    if (lane == 0) {
+                        a.out.status[row] = ROW_RETRY;
+                        if (nan_seen && a.out.counters) atomicAdd(&a.out.counters[WHIRL_CNT_NAN_ROWS], 1u);
+                    }
                 } else if (!sample) {
                     if (lane == 0) a.out.status[row] = ROW_DONE;
                     if (!presorted) sort_desc<32>(gw, reinterpret_cast<uint64_t*>(hand), cap);
@@ -853,6 +879,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             if (g.tid == 0 && ord >= 0) prof[6] += 1;
 #endif
         }
+    tail_done:
 #ifdef WB_PROF
         if (g.tid == 0) {
             prof[7] = clock64() - prof_begin;
@@ -889,7 +916,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
 #ifdef WB_PROF
         const long long tb0 = clock64();
 #endif
-        if (!mbar_wait(&boot_done[p], (ord >> 1) & 1)) {
+        if (!mbar_wait(&boot_done[p], (ord >> 1) & 1, wlim)) {
             if (lane == 0) atomicExch(a.err, 4u);
             return;
         }
@@ -954,7 +981,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
 #ifdef WB_PROF
                         const long long tw0 = clock64();
 #endif
-                        if (!mbar_wait(&full[st_slot], st_phase)) {
+                        if (!mbar_wait(&full[st_slot], st_phase, wlim)) {
                             if (lane == 0) atomicExch(a.err, 5u);
                             st_fail = true;
                             return;
@@ -1070,7 +1097,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         sl->wbound[sw] = kr;
                         mbar_arrive(&head_done[p]);
                     }
-                    if (!mbar_wait(&head_done[p], (ord >> 1) & 1)) {
+                    if (!mbar_wait(&head_done[p], (ord >> 1) & 1, wlim)) {
                         if (lane == 0) atomicExch(a.err, 11u);
                         st_fail = true;
                         return;

@@ -15,6 +15,7 @@ enum RowStatus : int32_t {
     ROW_OPEN_TAIL = 2,  // open set and the draw fell past the candidates: needs the id-order walk of the row
     ROW_RETRY = 3,      // internal: the single-pass kernel's candidate log overflowed; the multi-pass kernel redoes the row
     ROW_LARGE_K = 4,    // internal: top_k above the single-pass kernel's limit; the multi-pass kernel takes the row
+    ROW_PENDING = 5,    // internal: listed by the single-pass kernel and not answered yet (what a row keeps when a role gave up)
 };
 
 struct TailIn {
