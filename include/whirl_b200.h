@@ -228,6 +228,73 @@ int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sam
 int whirl_accept_tokens(const int* tokens, const int* drafts, int draft_stride, const int* nd, const int* row0, int seqs, int* acc,
                         int* chosen, void* stream);
 
+/* The whole accept step of sampling::Acceptor (src/sampling/acceptor.cpp:30-100) on the device, relaxed rules
+ * included, so that an engine running relaxed acceptance needs no per-cycle readCtl synchronisation and candidate
+ * download either (src/server/engine_decode.cpp:399-405).  One call decides `seqs` sequences; sequence s checks
+ * drafts[s * draft_stride + 0 .. nd[s]) against the verify rows row0[s] + 0 .. row0[s] + nd[s] of the batch.
+ *
+ *   greedy[s] != 0   Acceptor::greedy: draft j is kept iff it is tokens[row0 + j] (the row's argmax,
+ *                    whirl_argmax_rows / a greedy row of whirl_sample_rows); with relax_on[s], a draft that is not is
+ *                    still kept when relax::acceptGreedy passes on the row's rk best logits (rk_ids / rk_vals /
+ *                    rk_stats = the outputs of whirl_topk_rows with K = rk >= the rule's k: rank below k and
+ *                    exp(l_draft - l_max) >= alpha, include/whirl/relax_accept.h:55-73) and the kept tokens would not
+ *                    extend a repeated 6-gram of the sequence's last 4096 tokens (relax::extendsRepeat, :78-90, over
+ *                    hist[s] followed by next[s] and the drafts up to j, as Engine::relaxRepeats builds it);
+ *                    relax_gap[s] += l_max - l_draft for every draft kept that way.
+ *   greedy[s] == 0   Acceptor::sample: draft j is kept iff it is tokens[row0 + j] (the sampler's draw at output index
+ *                    n_gen + j, whirl_sample_rows with u / race_key made for those indices: that is the reference's
+ *                    RNG contract, src/sampling/acceptor.h:10-12); with relax_on[s], before that comparison, a draft is
+ *                    kept when p(draft) >= min(eps, delta * exp(-H)) on the row's filtered distribution
+ *                    (relax::acceptTypical, :93-96) and it would not extend a repeat.  p(draft) is the reference's
+ *                    probOf (src/sampling/sampler.cpp:108-116): the draft's entry of the kept set, else 0 on a closed
+ *                    row and exp((x[draft] - max) * inv_t) / sum on an open one (x, dtype, n, inv_t: the verify logits,
+ *                    read for that one element; raw logits, so rows with penalties need closed sets); H is the entropy
+ *                    of the kept set (kept_ids / kept_p / n_kept / closed / stats = the outputs of whirl_sample_rows
+ *                    with that kept_cap).  A row that kept more than kept_cap candidates cannot be judged: the draft
+ *                    then takes the exact comparison and flags[s] gets WHIRL_ACCEPT_TRUNCATED.
+ *
+ * acc[s] = drafts kept, chosen[s] = tokens[row0[s] + acc[s]] (the target's own pick after them), relaxed[s] += drafts
+ * kept by a relaxed rule, relax_gap[s] as above, flags[s] written.  relaxed / relax_gap / flags may be null.  Arrays
+ * that a rule in use needs and that are null make the call fail with WHIRL_ERR_INVALID.
+ * Sums that the reference forms in index order (H) are formed in another order here: a decision can differ only when
+ * p(draft) meets its threshold to the last bits. */
+enum { WHIRL_ACCEPT_TRUNCATED = 1 };
+typedef struct whirl_relax_params { /* relax::Params, include/whirl/relax_accept.h:44-50 */
+    uint32_t k;
+    float alpha, eps, delta;
+} whirl_relax_params;
+typedef struct whirl_accept_in {
+    const int32_t* tokens;   /* [rows] */
+    const int32_t* drafts;   /* [seqs][draft_stride] */
+    int64_t draft_stride;
+    const int32_t* nd;       /* [seqs] */
+    const int32_t* row0;     /* [seqs] */
+    const uint8_t* greedy;   /* [seqs] (null = all sampling) */
+    const uint8_t* relax_on; /* [seqs] (null = exact rules everywhere) */
+    /* repeat guard */
+    const int32_t* next;     /* [seqs] the sequence's token before the drafts */
+    const int32_t* hist;     /* [seqs][hist_stride] the sequence's tokens so far, oldest first */
+    int64_t hist_stride;
+    const int32_t* hist_len; /* [seqs] */
+    /* relaxed greedy rule */
+    const int32_t* rk_ids;   /* [rows][rk] */
+    const float* rk_vals;    /* [rows][rk] */
+    const float* rk_stats;   /* [rows][2] (max, sum) */
+    int32_t rk;
+    /* typical rule */
+    int32_t kept_cap;
+    const int32_t* kept_ids; /* [rows][kept_cap] */
+    const double* kept_p;    /* [rows][kept_cap] */
+    const int32_t* n_kept;   /* [rows] */
+    const int32_t* closed;   /* [rows] */
+    const float* stats;      /* [rows][2] (max, sum) */
+    const void* x;           /* [rows][n] verify logits (open rows only; may be null when every row is closed) */
+    int32_t dtype, n;
+    const float* inv_t;      /* [rows] (null = 1) */
+} whirl_accept_in;
+int whirl_accept_rows(const whirl_accept_in* in, const whirl_relax_params* relax, int seqs, int* acc, int* chosen, int* relaxed,
+                      double* relax_gap, int* flags, void* stream);
+
 /* The accept / residual rule (Leviathan et al., Chen et al. 2023) that the reference replaced by the race coupling
  * (include/whirl/spec_sample.h:21-24); its residual helper sampleRow(src, s, ex, p_ex) is still in the reference
  * (src/sampling/sampler.cpp:118-131).  Per sequence: target is [L + 1][n] logits, draft [L][n], full-vocabulary
@@ -239,6 +306,24 @@ size_t whirl_spec_workspace_bytes(int seqs, int L);
 int whirl_spec_accept_residual(const void* target, const void* draft, int dtype, int seqs, int L, int n, const int* draft_tok,
                                const float* inv_t, const double* u_acc, const double* u_res, int* n_acc, int* next_tok, void* ws,
                                size_t ws_bytes, void* stream);
+
+/* ---- draw generators ------------------------------------------------------------------------------------------------
+ * The reference draws one uniform per sampled row on the host, Sampler::uniform(seed, pos) (src/sampling/sampler.h:46-52,
+ * the stream-0 case of spec::uniform, src/common/spec_sample.cpp:13-21), and keys the race draw with
+ * spec::raceBase(seed, pos) (include/whirl/spec_sample.h:58-60).  The three host functions below return exactly those
+ * values (no device needed); whirl_fill_draws computes them on the device for `rows` (seed, pos) pairs held there, into
+ * the u / race_key arrays whirl_sample_rows takes.  Philox4x32-10 is offered beside them for callers that want a
+ * counter-based generator per (seed, pos, row, stream): key = seed (lo, hi), counter = (pos lo, pos hi, row, stream),
+ * uniform = top 53 bits of out0:out1.  The reference has no Philox; this convention is the library's own. */
+enum { WHIRL_GEN_SPLITMIX = 0, WHIRL_GEN_PHILOX = 1 };
+double whirl_uniform_splitmix(uint64_t seed, uint64_t pos_idx, uint32_t stream_id);
+uint64_t whirl_race_base(uint64_t seed, uint64_t pos_idx);
+void whirl_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]);
+double whirl_uniform_philox4x32(uint64_t seed, uint64_t pos_idx, uint32_t row, uint32_t stream_id);
+/* seed, pos_idx [rows] u64 on the device -> u [rows] f64 (may be null), race_key [rows] u64 (may be null).  With
+ * WHIRL_GEN_PHILOX the row index is the counter's third word. */
+int whirl_fill_draws(const uint64_t* seed, const uint64_t* pos_idx, int rows, int generator, uint32_t stream_id, double* u,
+                     uint64_t* race_key, void* stream);
 
 /* Reads the device error word that the last whirl_sample_rows / whirl_topk_rows call on this workspace left (the call
  * synchronises `stream`).  WHIRL_OK, or WHIRL_ERR_TIMEOUT when a bounded wait inside the single-pass kernel ran out;

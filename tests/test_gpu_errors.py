@@ -108,3 +108,21 @@ def test_history_length_is_clamped_to_the_history_row(api, oracle):
     want = oracle.sample_rows(x, kept_cap=8, u=u, threads=4, hist_len=np.minimum(hist_len, H).astype(np.uint32), **prm, **pen)
     res = api.sample_rows(dev(x), row_params(prm, u=u, hist_len=hist_len, **pen), kept_cap=8)
     compare_rows(res, want, u=u)
+
+
+def test_rows_redone_by_the_multi_pass_kernel_still_reach_the_second_level(api, oracle):
+    """A rising row overflows the single-pass kernel's candidate log and is redone by the multi-pass kernel at the first
+    level; with flat logits and a top-p close to one its kept set reaches past 256 candidates, so the redo has to go on
+    to the second level (16384 candidates) instead of leaving the row unanswered."""
+    R, V = 24, 36868
+    x = synth.normalish(421, (R, V), 0.3)
+    x[::2] = np.sort(x[::2], axis=1)
+    f = lambda v, dt=np.float32: np.full(R, v, dtype=dt)
+    prm = dict(inv_t=f(1.0), top_k=f(0, np.uint32), top_p=f(0.5, np.float64), min_p=f(0.0, np.float64))
+    u = synth.hash_u01(422, R, 0)
+    want = oracle.sample_rows(x, kept_cap=8, u=u, threads=4, **prm)
+    assert (want["n"] > 256).all() and (want["n"] <= 16384).all()
+    res = api.sample_rows(dev(x), row_params(prm, u=u), kept_cap=8)
+    compare_rows(res, want, u=u)
+    cnt = res.counters.cpu().numpy()
+    assert cnt[api.CNT_REDO] >= R // 2 and cnt[api.CNT_ESCALATED] == R and cnt[api.CNT_UNRESOLVED] == 0

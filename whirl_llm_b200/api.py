@@ -39,6 +39,19 @@ class DSampArgs(C.Structure):
                 ("min_p", C.c_void_p), ("key_lo", C.c_void_p), ("key_hi", C.c_void_p)]
 
 
+class RelaxParams(C.Structure):
+    _fields_ = [("k", C.c_uint32), ("alpha", C.c_float), ("eps", C.c_float), ("delta", C.c_float)]
+
+
+class AcceptIn(C.Structure):
+    _fields_ = [("tokens", C.c_void_p), ("drafts", C.c_void_p), ("draft_stride", C.c_int64), ("nd", C.c_void_p), ("row0", C.c_void_p),
+                ("greedy", C.c_void_p), ("relax_on", C.c_void_p), ("next", C.c_void_p), ("hist", C.c_void_p),
+                ("hist_stride", C.c_int64), ("hist_len", C.c_void_p), ("rk_ids", C.c_void_p), ("rk_vals", C.c_void_p),
+                ("rk_stats", C.c_void_p), ("rk", C.c_int32), ("kept_cap", C.c_int32), ("kept_ids", C.c_void_p),
+                ("kept_p", C.c_void_p), ("n_kept", C.c_void_p), ("closed", C.c_void_p), ("stats", C.c_void_p), ("x", C.c_void_p),
+                ("dtype", C.c_int32), ("n", C.c_int32), ("inv_t", C.c_void_p)]
+
+
 class SampleOut(C.Structure):
     _fields_ = [("token", C.c_void_p), ("status", C.c_void_p), ("n_kept", C.c_void_p), ("closed", C.c_void_p),
                 ("stats", C.c_void_p), ("kept_ids", C.c_void_p), ("kept_p", C.c_void_p), ("kept_cap", C.c_int32),
@@ -76,6 +89,12 @@ def _load() -> C.CDLL:
         "whirl_host_last_error": (C.c_char_p, []),
         "whirl_launch_counts": (None, [vp, i]),
         "whirl_check": (i, [vp, sz, i, vp, vp]),
+        "whirl_accept_rows": (i, [C.POINTER(AcceptIn), C.POINTER(RelaxParams), i, vp, vp, vp, vp, vp, vp]),
+        "whirl_uniform_splitmix": (C.c_double, [C.c_uint64, C.c_uint64, C.c_uint32]),
+        "whirl_race_base": (C.c_uint64, [C.c_uint64, C.c_uint64]),
+        "whirl_philox4x32_10": (None, [C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
+        "whirl_uniform_philox4x32": (C.c_double, [C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32]),
+        "whirl_fill_draws": (i, [vp, vp, i, i, C.c_uint32, vp, vp, vp]),
         "whirl_test_waits": (None, [C.c_uint32, i]),
     }
     for name, (res, args) in sigs.items():
@@ -89,7 +108,8 @@ DECLARED = ["whirl_status_string", "whirl_last_error", "whirl_version", "whirl_w
             "whirl_argmax_rows", "whirl_argmax_rows_static", "whirl_argmax_rows_to", "whirl_argmax_prob", "whirl_draft_pick", "whirl_draft_pick_rows", "whirl_draft_sample_rows", "whirl_accept_tokens", "whirl_spec_workspace_bytes",
             "whirl_spec_accept_residual",
             "whirl_topk_rows", "whirl_topk_rows_shard", "whirl_merge_sample_rows", "whirl_sample_rows", "whirl_sample_rows_host", "whirl_host_release", "whirl_host_last_error",
-            "whirl_launch_counts", "whirl_check", "whirl_test_waits"]
+            "whirl_launch_counts", "whirl_check", "whirl_test_waits", "whirl_accept_rows",
+            "whirl_uniform_splitmix", "whirl_race_base", "whirl_philox4x32_10", "whirl_uniform_philox4x32", "whirl_fill_draws"]
 
 
 def _check(status: int):
@@ -322,6 +342,39 @@ def test_waits(wait_us: int = 0, lose_copy: bool = False) -> None:
     lib.whirl_test_waits(wait_us, int(lose_copy))
 
 
+GEN_SPLITMIX, GEN_PHILOX = 0, 1
+
+
+def uniform_splitmix(seed: int, pos_idx: int, stream_id: int = 0) -> float:
+    """Sampler::uniform / spec::uniform of the reference, on the host."""
+    return lib.whirl_uniform_splitmix(seed, pos_idx, stream_id)
+
+
+def race_base(seed: int, pos_idx: int) -> int:
+    return lib.whirl_race_base(seed, pos_idx)
+
+
+def philox4x32_10(ctr, key):
+    c, k, o = (C.c_uint32 * 4)(*ctr), (C.c_uint32 * 2)(*key), (C.c_uint32 * 4)()
+    lib.whirl_philox4x32_10(c, k, o)
+    return list(o)
+
+
+def uniform_philox4x32(seed: int, pos_idx: int, row: int, stream_id: int = 0) -> float:
+    return lib.whirl_uniform_philox4x32(seed, pos_idx, row, stream_id)
+
+
+def fill_draws(seed: torch.Tensor, pos_idx: torch.Tensor, generator: int = GEN_SPLITMIX, stream_id: int = 0, want_u: bool = True,
+               want_race_key: bool = True):
+    """seed, pos_idx: int64 CUDA tensors holding the u64 bit patterns -> (u f64, race_key int64 bit patterns)."""
+    rows = seed.numel()
+    u = torch.empty(rows, dtype=torch.float64, device=seed.device) if want_u else None
+    rk = torch.empty(rows, dtype=torch.int64, device=seed.device) if want_race_key else None
+    _check(lib.whirl_fill_draws(seed.data_ptr(), pos_idx.data_ptr(), rows, generator, stream_id, _p(u), _p(rk),
+                                torch.cuda.current_stream(seed.device).cuda_stream))
+    return u, rk
+
+
 def launch_counts() -> dict:
     """Kernel launches made through the library by this process so far, per family."""
     a = (C.c_uint64 * 4)()
@@ -378,6 +431,35 @@ def accept_tokens(tokens, drafts, nd, row0):
     _check(lib.whirl_accept_tokens(tokens.data_ptr(), drafts.data_ptr(), drafts.shape[1], nd.data_ptr(), row0.data_ptr(), seqs,
                                    acc.data_ptr(), chosen.data_ptr(), torch.cuda.current_stream(tokens.device).cuda_stream))
     return acc, chosen
+
+
+def accept_rows(tokens, drafts, nd, row0, relax: RelaxParams, greedy=None, relax_on=None, next_tok=None, hist=None, hist_len=None,
+                rk_ids=None, rk_vals=None, rk_stats=None, kept: Optional[SampleResult] = None, x=None, inv_t=None):
+    """whirl_accept_rows: the accept step with the relaxed rules.  tokens [rows] i32; drafts [seqs, D] i32; nd / row0 / next_tok
+    [seqs] i32; greedy / relax_on [seqs] u8; hist [seqs, H] i32 + hist_len [seqs] i32; rk_* the outputs of topk_rows with
+    K = rk; kept: a SampleResult with kept_ids / kept_p (the typical rule); x / inv_t the verify logits for open rows.
+    Returns (acc, chosen, relaxed, relax_gap, flags)."""
+    seqs = drafts.shape[0]
+    dev = tokens.device
+    a = AcceptIn(tokens=_p(tokens), drafts=_p(drafts), draft_stride=drafts.shape[1], nd=_p(nd), row0=_p(row0), greedy=_p(greedy),
+                 relax_on=_p(relax_on), next=_p(next_tok), hist=_p(hist), hist_stride=0 if hist is None else hist.shape[1],
+                 hist_len=_p(hist_len), rk_ids=_p(rk_ids), rk_vals=_p(rk_vals), rk_stats=_p(rk_stats),
+                 rk=0 if rk_ids is None else rk_ids.shape[1])
+    if kept is not None:
+        a.kept_cap = 0 if kept.kept_ids is None else kept.kept_ids.shape[1]
+        a.kept_ids, a.kept_p, a.n_kept, a.closed, a.stats = _p(kept.kept_ids), _p(kept.kept_p), _p(kept.n_kept), _p(kept.closed), _p(kept.stats)
+    if x is not None:
+        x, _, n = _rows(x)
+        a.x, a.dtype, a.n = x.data_ptr(), _dtype(x), n
+    a.inv_t = _p(inv_t)
+    acc = torch.empty(seqs, dtype=torch.int32, device=dev)
+    chosen = torch.empty(seqs, dtype=torch.int32, device=dev)
+    relaxed = torch.zeros(seqs, dtype=torch.int32, device=dev)
+    gap = torch.zeros(seqs, dtype=torch.float64, device=dev)
+    flags = torch.zeros(seqs, dtype=torch.int32, device=dev)
+    _check(lib.whirl_accept_rows(C.byref(a), C.byref(relax), seqs, acc.data_ptr(), chosen.data_ptr(), relaxed.data_ptr(), gap.data_ptr(),
+                                 flags.data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
+    return acc, chosen, relaxed, gap, flags
 
 
 def spec_accept_residual(target, draft, draft_tok, inv_t, u_acc, u_res):

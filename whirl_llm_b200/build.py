@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libwhirl_b200.so")
 OBJ = os.path.join(HERE, "build")
-SOURCES = ["api.cu", "host_api.cu", "rowscan.cu", "select_generic.cu", "single_pass.cu", "merge.cu", "spec_accept.cu"]
+SOURCES = ["api.cu", "host_api.cu", "rowscan.cu", "select_generic.cu", "single_pass.cu", "merge.cu", "spec_accept.cu", "rng.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=hidden", "-cudart", "shared"]
 

@@ -392,6 +392,28 @@ int whirl_accept_tokens(const int* tokens, const int* drafts, int draft_stride, 
     return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "accept_tokens launch");
 }
 
+int whirl_accept_rows(const whirl_accept_in* in, const whirl_relax_params* relax, int seqs, int* acc, int* chosen, int* relaxed,
+                      double* relax_gap, int* flags, void* stream) {
+    if (!in || !relax || !acc || !chosen || seqs < 0 || !in->tokens || !in->drafts || !in->nd || !in->row0 || in->draft_stride < 0)
+        return fail(WHIRL_ERR_INVALID, "accept_rows: bad pointer / seqs / draft_stride");
+    if (in->relax_on) {
+        // (which rule a sequence takes is known on the device only: every array a relaxed rule may read has to be there)
+        if (!in->next || (in->hist && (!in->hist_len || in->hist_stride < 0)))
+            return fail(WHIRL_ERR_INVALID, "accept_rows: relaxed rules need next (and hist_len with hist)");
+        const bool have_greedy = in->rk_ids && in->rk_vals && in->rk_stats && in->rk >= 1 && in->rk <= 32;
+        const bool have_typical = in->kept_ids && in->kept_p && in->n_kept && in->closed && in->stats && in->kept_cap >= 1;
+        if (in->greedy && !have_greedy) return fail(WHIRL_ERR_INVALID, "accept_rows: the relaxed greedy rule needs rk_ids / rk_vals / rk_stats, 1 <= rk <= 32");
+        if (!have_typical && !(in->greedy && have_greedy)) return fail(WHIRL_ERR_INVALID, "accept_rows: the typical rule needs kept_ids / kept_p / n_kept / closed / stats");
+        if (have_greedy && uint32_t(in->rk) < (relax->k < 1 ? 1u : (relax->k > 16 ? 16u : relax->k)))
+            return fail(WHIRL_ERR_INVALID, "accept_rows: rk below the rule's k");
+        if (in->x && (bad_dtype(in->dtype) || in->n <= 0)) return fail(WHIRL_ERR_INVALID, "accept_rows: x with a bad dtype / n");
+    }
+    if (seqs == 0) return WHIRL_OK;
+    const cudaError_t e = wb::accept_rows_launch(*in, *relax, seqs, acc, chosen, relaxed, relax_gap, flags, static_cast<cudaStream_t>(stream));
+    bump(LC_AUX);
+    return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "accept_rows launch");
+}
+
 size_t whirl_spec_workspace_bytes(int seqs, int L) { return wb::spec_stats_bytes(seqs < 0 ? 0 : seqs, L < 0 ? 0 : L) + 256; }
 
 int whirl_spec_accept_residual(const void* target, const void* draft, int dtype, int seqs, int L, int n, const int* draft_tok,

@@ -153,6 +153,8 @@ bool single_pass_supported(const SelectArgs& a, int dtype);
 size_t spec_stats_bytes(int seqs, int L);
 cudaError_t accept_tokens_launch(const int32_t* tokens, const int32_t* dr, int dr_stride, const int32_t* nd, const int32_t* row0,
                                  int seqs, int32_t* acc, int32_t* chosen, cudaStream_t st);
+cudaError_t accept_rows_launch(const whirl_accept_in& in, const whirl_relax_params& rp, int seqs, int32_t* acc, int32_t* chosen,
+                               int32_t* relaxed, double* gap, int32_t* flags, cudaStream_t st);
 cudaError_t accept_residual_launch(const void* target, const void* draft, int dtype, int seqs, int L, int n, const int32_t* draft_tok,
                                    const float* inv_t, const double* u_acc, const double* u_res, void* stats_ws, int32_t* n_acc,
                                    int32_t* next_tok, cudaStream_t st);

@@ -88,76 +88,99 @@ template <typename T>
 __device__ void full_row(const SelectArgs& a, int row, int cap_max, int pen_words, uint64_t* tile, GShared* sh,
                          uint32_t* pen_mem, uint64_t* fc, double* fp);
 
-// The serial tail of draft_sample_rows (kernels/spec_sample.hip:132-205), by one thread on at most 32 candidates: map the
-// ids, sort by (logit desc, id asc), q = softmax at the request temperature over the candidates in f32 (same operation
-// order as spec::draftDist, src/common/spec_sample.cpp:33-81), top-k / top-p / min-p, renormalise, then the race draw
-// argmin E(id) / q in f64; writes the token to the control area and q to qbuf.
+// The tail of draft_sample_rows (kernels/spec_sample.hip:132-205) on at most 32 candidates, by one warp with one
+// candidate per lane: map the ids, order by (logit desc, id asc) by counting ranks, q = softmax at the request
+// temperature in f32 (the operations and their order as in spec::draftDist, src/common/spec_sample.cpp:33-81: the
+// sums run over the lanes in rank order, every lane adding the same broadcast terms), top-k / top-p / min-p,
+// renormalise, then the race draw argmin E(id) / q in f64; writes the token to the control area and q to qbuf.
+// Call with all 32 lanes of one warp.
 __device__ void draft_tail(const SelectArgs& a, int row, const unsigned long long* cand, uint32_t K, float m, float sum, float inv_t) {
+    constexpr uint32_t FULL = 0xffffffffu;
     const DraftArgs& d = a.draft;
-    int id[32];
-    float lg[32], p[32];
-    for (uint32_t i = 0; i < K; ++i) {
-        const uint32_t raw = cand_id(cand[i]);
-        id[i] = d.map ? d.map[raw] : int(raw);
-        const uint32_t k = cand_key(cand[i]);
-        lg[i] = k ? float_of_key(k) : -INFINITY;  // a NaN logit only fills a slot past the numbers, with p = 0
+    const int lane = lane_id();
+    // ---- this lane's candidate
+    const bool have = uint32_t(lane) < K;
+    int my_id = 0x7fffffff;
+    float my_lg = -INFINITY;  // (a NaN logit only fills a slot past the numbers, with p = 0)
+    if (have) {
+        const unsigned long long c = cand[lane];
+        const uint32_t raw = cand_id(c), k = cand_key(c);
+        my_id = d.map ? d.map[raw] : int(raw);
+        my_lg = k ? float_of_key(k) : -INFINITY;
     }
-    for (uint32_t i = 1; i < K; ++i) {
-        uint32_t j = i;
-        while (j > 0 && (lg[j - 1] < lg[j] || (lg[j - 1] == lg[j] && id[j - 1] > id[j]))) {
-            const float tl = lg[j - 1];
-            lg[j - 1] = lg[j], lg[j] = tl;
-            const int ti = id[j - 1];
-            id[j - 1] = id[j], id[j] = ti;
-            --j;
-        }
+    // ---- rank = the candidates ahead of this one; then lane r takes the candidate of rank r
+    int rank = 0;
+#pragma unroll 1
+    for (int j = 0; j < 32; ++j) {
+        const float lj = __shfl_sync(FULL, my_lg, j);
+        const int ij = __shfl_sync(FULL, my_id, j);
+        const bool hj = uint32_t(j) < K;
+        const bool ahead = have ? (hj && (lj > my_lg || (lj == my_lg && (ij < my_id || (ij == my_id && j < lane))))) : (hj || j < lane);
+        rank += ahead ? 1 : 0;
     }
-    for (uint32_t i = 0; i < K; ++i) p[i] = __fdiv_rn(expf(__fmul_rn(__fsub_rn(lg[i], m), inv_t)), sum);
+    int src = 0;
+#pragma unroll 1
+    for (int j = 0; j < 32; ++j) src = __shfl_sync(FULL, rank, j) == lane ? j : src;
+    const int id = __shfl_sync(FULL, my_id, src);
+    const float lg = __shfl_sync(FULL, my_lg, src);
+    float p = uint32_t(lane) < K ? __fdiv_rn(expf(__fmul_rn(__fsub_rn(lg, m), inv_t)), sum) : 0.f;
+    // the sum of the first `cnt` probabilities, added in rank order
+    auto serial_sum = [&](uint32_t cnt) {
+        float z = 0.f;
+#pragma unroll 1
+        for (uint32_t i = 0; i < cnt; ++i) z = __fadd_rn(z, __shfl_sync(FULL, p, int(i)));
+        return z;
+    };
+    // ---- the cuts
     const int tk = d.top_k[row];
     uint32_t nk = K;
     const bool closed = tk > 0 && uint32_t(tk) <= K;
     if (closed) nk = uint32_t(tk);
     const float top_p = d.top_p[row];
     if (top_p < 1.f) {
-        float z = 1.f;
-        if (closed) {
-            z = 0.f;
-            for (uint32_t i = 0; i < nk; ++i) z = __fadd_rn(z, p[i]);
-        }
+        const float z = closed ? serial_sum(nk) : 1.f;
         float cum = 0.f;
+        uint32_t cut = nk;
+#pragma unroll 1
         for (uint32_t j = 0; j < nk; ++j) {
-            cum = __fadd_rn(cum, __fdiv_rn(p[j], z));
+            cum = __fadd_rn(cum, __fdiv_rn(__shfl_sync(FULL, p, int(j)), z));
             if (cum >= top_p) {
-                nk = j + 1;
+                cut = j + 1;
                 break;
             }
         }
+        nk = cut;
     }
     const float min_p = d.min_p[row];
     if (min_p > 0.f && nk > 0) {
-        const float th = __fmul_rn(min_p, p[0]);
-        uint32_t j = 0;
-        while (j < nk && p[j] >= th) ++j;
+        const float th = __fmul_rn(min_p, __shfl_sync(FULL, p, 0));
+        const uint32_t ok = __ballot_sync(FULL, uint32_t(lane) < nk && p >= th);
+        const uint32_t j = ok == FULL ? 32u : uint32_t(__ffs(int(~ok))) - 1u;  // the leading run of lanes at or above th
         nk = j > 1 ? j : 1;
     }
-    float z = 0.f;
-    for (uint32_t i = 0; i < nk; ++i) z = __fadd_rn(z, p[i]);
-    for (uint32_t i = 0; i < nk; ++i) p[i] = __fdiv_rn(p[i], z);
+    const float z = serial_sum(nk);
+    p = __fdiv_rn(p, z);
+    // ---- the race: the smallest E(id) / q, the lower rank on a tie
     const unsigned long long rkey = ((unsigned long long)d.key_hi[row] << 32) | d.key_lo[row];
-    uint32_t pick = 0;
-    double bk = __longlong_as_double(0x7FF0000000000000ll);
-    for (uint32_t i = 0; i < nk; ++i) {
-        if (!(p[i] > 0.f)) continue;
-        const double k = race_e(rkey, uint32_t(id[i])) / double(p[i]);
-        if (k < bk) bk = k, pick = i;
+    double key = __longlong_as_double(0x7FF0000000000000ll);
+    if (uint32_t(lane) < nk && p > 0.f) key = race_e(rkey, uint32_t(id)) / double(p);
+    int pick = key < __longlong_as_double(0x7FF0000000000000ll) ? lane : 32;  // (32: this lane does not take part)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const double ok = __shfl_xor_sync(FULL, key, o);
+        const int op = __shfl_xor_sync(FULL, pick, o);
+        if (op < 32 && (pick == 32 || ok < key || (ok == key && op < pick))) key = ok, pick = op;
     }
-    int32_t* c = d.ctl_all + d.area[row];
-    c[16 + d.r] = id[pick];
+    pick = pick == 32 ? 0 : pick;
+    const int tok = __shfl_sync(FULL, id, pick);
     int32_t* q = d.qbuf + d.qoff[row];
-    q[0] = int32_t(nk);
-    for (uint32_t i = 0; i < nk; ++i) {
-        q[1 + i] = id[i];
-        q[1 + 32 + i] = __float_as_int(p[i]);
+    if (lane == 0) {
+        d.ctl_all[d.area[row] + 16 + d.r] = tok;
+        q[0] = int32_t(nk);
+    }
+    if (uint32_t(lane) < nk) {
+        q[1 + lane] = id;
+        q[1 + 32 + lane] = __float_as_int(p);
     }
 }
 
@@ -176,8 +199,16 @@ __global__ void __launch_bounds__(GT) select_generic_kernel(SelectArgs a, int ca
         const int entry = a.row_list ? a.row_list[li] : li;
         // bit 30 of a list entry: redo the row at the first candidate level (the single-pass kernel gave it up)
         const int row = entry & 0x3fffffff;
-        const int level = (entry >> 30) & 1 ? min(a.level_k, kFirstLevelK) : a.level_k;
-        const int st = select_row<T>(a, row, level, cap_max, pen_words, cand, hist, sh, pen_mem);
+        int level = (entry >> 30) & 1 ? min(a.level_k, kFirstLevelK) : a.level_k;
+        int st = select_row<T>(a, row, level, cap_max, pen_words, cand, hist, sh, pen_mem);
+        if (st == ROW_ESCALATE && level < a.level_k) {
+            // a row redone at the first level whose kept set may reach past it: on to this launch's level, as a row that the
+            // single-pass kernel had escalated itself
+            if (threadIdx.x == 0 && a.batch_counters) atomicAdd(&a.batch_counters[WHIRL_CNT_ESCALATED], 1u);
+            __syncthreads();
+            level = a.level_k;
+            st = select_row<T>(a, row, level, cap_max, pen_words, cand, hist, sh, pen_mem);
+        }
         // Third level: the kept set may reach past 16384 candidates, so the whole row is sorted (the reference's last
         // escalation step, src/server/engine_sampling.cpp:79-83, filterCands with complete = true).  That needs 16 bytes
         // per logit of global scratch: a few areas are shared by the CTAs through locks, and the wait for one is bounded
@@ -392,7 +423,7 @@ __device__ int select_row(const SelectArgs& a, int row, int level_k, int cap_max
     __syncthreads();
     const Group<GT> g{tid, 0};
     if (draft) {
-        if (tid == 0) draft_tail(a, row, reinterpret_cast<const unsigned long long*>(cand), K, sh->m, sh->sum, inv_t);
+        if (tid < 32) draft_tail(a, row, reinterpret_cast<const unsigned long long*>(cand), K, sh->m, sh->sum, inv_t);
         return ROW_DONE;
     }
     if (!sample) {

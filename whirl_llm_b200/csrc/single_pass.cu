@@ -1181,6 +1181,10 @@ static size_t single_pass_fixed_smem(int gbm_words, int max_k, bool pen) {
 bool single_pass_supported(const SelectArgs& a, int dtype) {
     const size_t es = dtype == 0 ? 4 : 2;
     if (reinterpret_cast<uintptr_t>(a.x) % 16 != 0 || (size_t(a.n) * es) % 16 != 0) return false;  // bulk copies need 16-byte rows
+    // Rows shorter than one iteration of the stream warps (two ring stages) leave most warps without logits, so no bound
+    // on the K-th largest comes out of the first meeting and the candidate log would take the whole row: the multi-pass
+    // kernel serves such rows (vocabularies below 8192 / 16384 tokens).
+    if (size_t(a.n) * es < size_t(Q_NS) * Q_SB) return false;
     if (a.mode == MODE_TOPK && a.K > kSinglePassMaxK) return false;
     if (a.mode == MODE_DRAFT) return false;
     if (a.rows > Q_MAXR * 100) return false;  // (more rows per CTA than its row list holds: far beyond any batch of logits)

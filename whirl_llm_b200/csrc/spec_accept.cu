@@ -26,6 +26,131 @@ __global__ void accept_tokens_kernel(const int32_t* tokens, const int32_t* dr, i
     chosen[s] = tokens[r0 + a];
 }
 
+// ---------------------------------------------------------------- (1b)
+// The accept loops of sampling::Acceptor with the relaxed rules (src/sampling/acceptor.cpp:30-100,
+// include/whirl/relax_accept.h:44-96): one warp per sequence walks the drafts in order; the rules' inner loops (the
+// search and rank over a row's best logits, the kept set's entropy, the 6-gram search over the last 4096 tokens) run
+// across the lanes.
+
+// relax::extendsRepeat over hist[0..hist_n) followed by tail = (next, drafts[0..n_dr)): true when the last 6 tokens of
+// that sequence occur earlier in its last (min(hist_n, 4096) + tail) tokens.
+__device__ bool extends_repeat(const int32_t* hist, uint32_t hist_n, int32_t next, const int32_t* drafts, uint32_t n_dr) {
+    constexpr uint32_t NG = 6, WINDOW = 4096;
+    const int lane = lane_id();
+    const uint32_t hn = hist_n < WINDOW ? hist_n : WINDOW;
+    const uint32_t tail_n = n_dr + 1, s = hn + tail_n;
+    if (s < NG + 1) return false;
+    const int32_t* h = hist + (hist_n - hn);
+    auto at = [&](uint32_t i) -> int32_t { return i < hn ? h[i] : (i == hn ? next : drafts[i - hn - 1]); };
+    int32_t last[NG];
+#pragma unroll
+    for (uint32_t j = 0; j < NG; ++j) last[j] = at(s - NG + j);
+    bool hit = false;
+#pragma unroll 1
+    for (uint32_t base = 0; base + NG < s && !hit; base += 32) {
+        const uint32_t i = base + uint32_t(lane);
+        bool m = i + NG < s;
+#pragma unroll
+        for (uint32_t j = 0; j < NG; ++j) m = m && at(i + j) == last[j];
+        hit = __any_sync(0xffffffffu, m);
+    }
+    return hit;
+}
+
+__global__ void __launch_bounds__(128) accept_rows_kernel(whirl_accept_in in, whirl_relax_params rp, int seqs, int32_t* acc_out,
+                                                          int32_t* chosen, int32_t* relaxed_out, double* gap_out, int32_t* flags_out) {
+    constexpr uint32_t FULL = 0xffffffffu;
+    const int s = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (s >= seqs) return;
+    const int lane = lane_id();
+    const uint32_t nd = uint32_t(in.nd[s]);
+    const int r0 = in.row0[s];
+    const int32_t* dr = in.drafts + size_t(s) * in.draft_stride;
+    const bool greedy = in.greedy && in.greedy[s];
+    const bool relax = in.relax_on && in.relax_on[s];
+    const uint32_t topk = rp.k < 1 ? 1u : (rp.k > 16 ? 16u : rp.k);  // relax::Params::topk
+    const int32_t* hist = in.hist ? in.hist + size_t(s) * in.hist_stride : nullptr;
+    const uint32_t hist_n = in.hist && in.hist_len ? uint32_t(max(in.hist_len[s], 0)) : 0u;
+    const int32_t next = in.next ? in.next[s] : 0;
+    uint32_t acc = 0, n_relaxed = 0;
+    int flags = 0;
+    double gap = 0.0;
+#pragma unroll 1
+    while (acc < nd) {
+        const int row = r0 + int(acc);
+        const int32_t d = dr[acc];
+        const bool exact = in.tokens[row] == d;
+        if (greedy) {
+            if (exact) {
+                ++acc;
+                continue;
+            }
+            if (!relax || !in.rk_ids) break;
+            // relax::acceptGreedy on the row's rk best logits, one per lane
+            const bool have = lane < in.rk;
+            const int32_t id = have ? in.rk_ids[size_t(row) * in.rk + lane] : -1;
+            const float lg = have ? in.rk_vals[size_t(row) * in.rk + lane] : 0.f;
+            const uint32_t found = __ballot_sync(FULL, have && id == d);
+            if (!found) break;
+            const int at = __ffs(int(found)) - 1;
+            const float ld = __shfl_sync(FULL, lg, at);
+            const uint32_t ahead = __ballot_sync(FULL, have && lane != at && (lg > ld || (lg == ld && uint32_t(id) < uint32_t(d))));
+            const float m = in.rk_stats[2 * size_t(row)];
+            if (uint32_t(__popc(ahead)) >= topk || !(exp(double(ld) - double(m)) >= double(rp.alpha))) break;
+            if (extends_repeat(hist, hist_n, next, dr, acc + 1)) break;
+            // (every entry equal to the draft counts, as in the reference's loop: ids of a top-k are distinct)
+            gap += double(__popc(found)) * double(__fsub_rn(m, ld));
+            ++acc, ++n_relaxed;
+            continue;
+        }
+        if (relax && in.kept_ids) {
+            // typical acceptance on the row's kept set: p(draft) (the reference's probOf) and the entropy
+            const uint32_t nk = uint32_t(in.n_kept[row]);
+            if (nk > uint32_t(in.kept_cap)) {
+                flags |= WHIRL_ACCEPT_TRUNCATED;
+            } else {
+                const int32_t* kid = in.kept_ids + size_t(row) * in.kept_cap;
+                const double* kp = in.kept_p + size_t(row) * in.kept_cap;
+                double h = 0.0, pd = -1.0;
+                uint32_t first = 0xffffffffu;  // the first entry that is the draft
+#pragma unroll 1
+                for (uint32_t i = lane; i < nk; i += 32) {
+                    const double p = kp[i];
+                    if (p > 0) h -= p * log(p);
+                    if (kid[i] == d && i < first) first = i, pd = p;
+                }
+                h = warp_sum(h);
+                const uint32_t fmin_i = __reduce_min_sync(FULL, first);
+                const uint32_t owner = __ballot_sync(FULL, first == fmin_i);  // (all lanes when no entry is the draft)
+                pd = __shfl_sync(FULL, pd, __ffs(int(owner)) - 1);
+                if (fmin_i == 0xffffffffu) {
+                    pd = 0.0;
+                    if (!in.closed[row] && in.x && d >= 0 && d < in.n) {
+                        const float xv = in.dtype == WHIRL_F32 ? reinterpret_cast<const float*>(in.x)[size_t(row) * in.n + d]
+                                                               : bf16_to_f32(reinterpret_cast<const uint16_t*>(in.x)[size_t(row) * in.n + d]);
+                        const float it = in.inv_t ? in.inv_t[row] : 1.f;
+                        pd = exp(double(__fsub_rn(xv, in.stats[2 * size_t(row)])) * double(it)) / double(in.stats[2 * size_t(row) + 1]);
+                    }
+                }
+                const double thr = fmin(double(rp.eps), double(rp.delta) * exp(-h));
+                if (pd >= thr && !extends_repeat(hist, hist_n, next, dr, acc + 1)) {
+                    ++acc, ++n_relaxed;
+                    continue;
+                }
+            }
+        }
+        if (!exact) break;
+        ++acc;
+    }
+    if (lane == 0) {
+        acc_out[s] = int32_t(acc);
+        chosen[s] = in.tokens[r0 + int(acc)];
+        if (relaxed_out) relaxed_out[s] += int32_t(n_relaxed);
+        if (gap_out) gap_out[s] += gap;
+        if (flags_out) flags_out[s] = flags;
+    }
+}
+
 // ---------------------------------------------------------------- (2)
 constexpr int RT = 1024;
 
@@ -180,6 +305,12 @@ __global__ void __launch_bounds__(RT) accept_residual_kernel(const T* target, co
 }
 
 size_t spec_stats_bytes(int seqs, int L) { return size_t(seqs) * (2 * L + 1) * sizeof(RowStat); }
+
+cudaError_t accept_rows_launch(const whirl_accept_in& in, const whirl_relax_params& rp, int seqs, int32_t* acc, int32_t* chosen,
+                               int32_t* relaxed, double* gap, int32_t* flags, cudaStream_t st) {
+    accept_rows_kernel<<<(seqs + 3) / 4, 128, 0, st>>>(in, rp, seqs, acc, chosen, relaxed, gap, flags);
+    return cudaGetLastError();
+}
 
 cudaError_t accept_tokens_launch(const int32_t* tokens, const int32_t* dr, int dr_stride, const int32_t* nd, const int32_t* row0,
                                  int seqs, int32_t* acc, int32_t* chosen, cudaStream_t st) {
