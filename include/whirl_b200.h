@@ -174,6 +174,15 @@ int whirl_topk_rows_shard(const void* x, int dtype, int rows, int n, int K, int 
 int whirl_merge_sample_rows(const int* ids, const float* vals, const float* stats, int shards, int rows, int K_s, int n_total,
                             const whirl_sample_params* params, const whirl_sample_out* out, void* stream);
 
+/* The same merge on PACKED blocks.  One rank's block is whirl_shard_block_words(rows, K_s) 4-byte words:
+ *     ids [rows][K_s] i32 | vals [rows][K_s] f32 | stats [rows][2] f32
+ * A rank points whirl_topk_rows_shard's three outputs into its own block and all-gathers the blocks with one collective
+ * (ncclAllGather / all_gather_into_tensor) into `blocks` = [shards] blocks, which this call reads in place: no
+ * repacking copy on either side of the exchange. */
+size_t whirl_shard_block_words(int rows, int K_s);
+int whirl_merge_sample_rows_packed(const void* blocks, int shards, int rows, int K_s, int n_total, const whirl_sample_params* params,
+                                   const whirl_sample_out* out, void* stream);
+
 /* ------------------------------------------------------------------------------------------------------------------
  * The fused sampler: penalties -> candidates -> top-k / top-p / min-p -> draw, one token per row, all on the device.
  * It replaces the round trip topk_rows -> download -> sampling::filterCands -> sampling::sampleRow

@@ -43,6 +43,30 @@ def test_merge_single_gpu(oracle):
     compare_rows(res, want, u=u, sum_rtol=2e-5)
 
 
+def test_packed_blocks_at_full_size(oracle):
+    """256 rows x 262,144 tokens in 8 slices, 1024 candidates per slice, global top-p 0.9: every slice's selection writes
+    straight into its packed block of the gathered buffer (the layout one all-gather leaves), and the merge reads the
+    blocks in place."""
+    from whirl_llm_b200 import api
+    rows, n_total, shards, ks = 256, 262144, 8, 1024
+    x = synth.normalish(57, (rows, n_total), 3.0)
+    x[1] = synth.grid_logits(58, (n_total,), 3.0)
+    f = lambda v, dt=np.float32: np.full(rows, v, dtype=dt)
+    prm = dict(inv_t=f(1.0), top_k=f(ks, np.uint32), top_p=f(0.9, np.float64))
+    prm["top_k"][2::5] = 50
+    u = synth.hash_u01(59, rows, 0)
+    want = oracle.sample_rows(x, kept_cap=ks, u=u, threads=8, kb=16384, **prm)
+    w = n_total // shards
+    words = api.lib.whirl_shard_block_words(rows, ks)
+    assert words == rows * (2 * ks + 2)
+    gathered = torch.empty(shards * words, dtype=torch.int32, device="cuda")
+    for s in range(shards):
+        views = api.shard_block_views(gathered[s * words:(s + 1) * words], rows, ks)
+        api.topk_rows_shard(dev(np.ascontiguousarray(x[:, s * w:(s + 1) * w])), ks, s * w, inv_t=1.0, out=views)
+    res = api.merge_sample_rows_packed(gathered, shards, rows, ks, n_total, row_params(prm, u=u), kept_cap=ks)
+    compare_rows(res, want, u=u, sum_rtol=2e-5)
+
+
 def _nccl_worker(rank, world, port, q):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -61,6 +85,18 @@ def _nccl_worker(rank, world, port, q):
         b, e = sharded.slice_bounds(n_total, world, rank)
         res = sharded.sample_vocab_sharded(dev(np.ascontiguousarray(x[:, b:e])), n_total, row_params(prm, u=u), k_s=ks, inv_t=1.25,
                                            kept_cap=ks)
+        compare_rows(res, want, u=u, sum_rtol=2e-5)
+        # the stated size: 256 rows x 262,144 tokens, 1024 candidates per slice, top-p 0.9; buffers kept across steps
+        rows, n_total, ks = 256, 262144, 1024
+        x = synth.normalish(57, (rows, n_total), 3.0)
+        f = lambda v, dt=np.float32: np.full(rows, v, dtype=dt)
+        prm = dict(inv_t=f(1.0), top_k=f(ks, np.uint32), top_p=f(0.9, np.float64))
+        u = synth.hash_u01(59, rows, 0)
+        want = o.sample_rows(x, kept_cap=8, u=u, threads=8, kb=16384, **prm)
+        vs = sharded.VocabShardedSampler(rows, n_total, ks, torch.device("cuda", rank))
+        xl = dev(np.ascontiguousarray(x[:, vs.begin:vs.end]))
+        for _ in range(2):
+            res = vs.sample(xl, row_params(prm, u=u), kept_cap=8)
         compare_rows(res, want, u=u, sum_rtol=2e-5)
         q.put((rank, "ok"))
     except Exception as ex:

@@ -41,6 +41,16 @@ def _worker(rank, world, port, q):
         assert g_ids.shape == (world, rows, ks) and g_stats.shape == (world, rows, 2)
         # the gathered block of this rank is what it sent
         assert torch.equal(g_ids[rank], torch.from_numpy(ids)) and torch.equal(g_vals[rank], torch.from_numpy(vals))
+        # the packed form: the block of every rank arrives whole and in rank order, and its views alias it
+        block = torch.empty(sharded.block_words(rows, ks), dtype=torch.int32)
+        b_ids, b_vals, b_stats = sharded.block_views(block, rows, ks)
+        b_ids.copy_(torch.from_numpy(ids)), b_vals.copy_(torch.from_numpy(vals)), b_stats.copy_(torch.from_numpy(stats))
+        assert b_ids.data_ptr() == block.data_ptr() and b_stats.data_ptr() == block.data_ptr() + 8 * rows * ks
+        flat = sharded.exchange_blocks(block)
+        assert flat.numel() == world * block.numel() and torch.equal(flat[rank * block.numel():(rank + 1) * block.numel()], block)
+        for r in range(world):
+            gi, gv, gs = sharded.block_views(flat[r * block.numel():(r + 1) * block.numel()], rows, ks)
+            assert torch.equal(gi, g_ids[r]) and torch.equal(gv, g_vals[r]) and torch.equal(gs, g_stats[r])
         # merged candidates == the unsharded row's candidates
         wi, wv, ws = o.topk_rows(x, ks, inv_t)
         for r in range(rows):

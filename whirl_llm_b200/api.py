@@ -89,6 +89,8 @@ def _load() -> C.CDLL:
         "whirl_host_last_error": (C.c_char_p, []),
         "whirl_launch_counts": (None, [vp, i]),
         "whirl_check": (i, [vp, sz, i, vp, vp]),
+        "whirl_shard_block_words": (sz, [i, i]),
+        "whirl_merge_sample_rows_packed": (i, [vp, i, i, i, i, C.POINTER(SampleParams), C.POINTER(SampleOut), vp]),
         "whirl_accept_rows": (i, [C.POINTER(AcceptIn), C.POINTER(RelaxParams), i, vp, vp, vp, vp, vp, vp]),
         "whirl_uniform_splitmix": (C.c_double, [C.c_uint64, C.c_uint64, C.c_uint32]),
         "whirl_race_base": (C.c_uint64, [C.c_uint64, C.c_uint64]),
@@ -108,7 +110,7 @@ DECLARED = ["whirl_status_string", "whirl_last_error", "whirl_version", "whirl_w
             "whirl_argmax_rows", "whirl_argmax_rows_static", "whirl_argmax_rows_to", "whirl_argmax_prob", "whirl_draft_pick", "whirl_draft_pick_rows", "whirl_draft_sample_rows", "whirl_accept_tokens", "whirl_spec_workspace_bytes",
             "whirl_spec_accept_residual",
             "whirl_topk_rows", "whirl_topk_rows_shard", "whirl_merge_sample_rows", "whirl_sample_rows", "whirl_sample_rows_host", "whirl_host_release", "whirl_host_last_error",
-            "whirl_launch_counts", "whirl_check", "whirl_test_waits", "whirl_accept_rows",
+            "whirl_launch_counts", "whirl_check", "whirl_shard_block_words", "whirl_merge_sample_rows_packed", "whirl_test_waits", "whirl_accept_rows",
             "whirl_uniform_splitmix", "whirl_race_base", "whirl_philox4x32_10", "whirl_uniform_philox4x32", "whirl_fill_draws"]
 
 
@@ -245,12 +247,27 @@ def topk_rows(x, K, inv_t=1.0, inv_t_rows=None, ws=None):
     return ids, vals, stats
 
 
-def topk_rows_shard(x, K, id_offset, inv_t=1.0, inv_t_rows=None, ws=None):
-    """topk_rows of one vocabulary slice with global token ids (ids pre-filled with -1)."""
+def shard_block_views(block: torch.Tensor, rows: int, K: int):
+    """The ids / vals / stats views of one rank's packed block (int32 tensor of whirl_shard_block_words words)."""
+    assert block.dtype == torch.int32 and block.is_contiguous() and block.numel() == lib.whirl_shard_block_words(rows, K)
+    ids = block[: rows * K].view(rows, K)
+    vals = block[rows * K: 2 * rows * K].view(torch.float32).view(rows, K)
+    stats = block[2 * rows * K:].view(torch.float32).view(rows, 2)
+    return ids, vals, stats
+
+
+def topk_rows_shard(x, K, id_offset, inv_t=1.0, inv_t_rows=None, ws=None, out=None):
+    """topk_rows of one vocabulary slice with global token ids (ids pre-filled with -1).  out: (ids, vals, stats) to
+    write into, e.g. the views of a packed block."""
     x, rows, n = _rows(x)
-    ids = torch.full((rows, K), -1, dtype=torch.int32, device=x.device)
-    vals = torch.zeros((rows, K), dtype=torch.float32, device=x.device)
-    stats = torch.zeros((rows, 2), dtype=torch.float32, device=x.device)
+    if out is None:
+        ids = torch.full((rows, K), -1, dtype=torch.int32, device=x.device)
+        vals = torch.zeros((rows, K), dtype=torch.float32, device=x.device)
+        stats = torch.zeros((rows, 2), dtype=torch.float32, device=x.device)
+    else:
+        ids, vals, stats = out
+        if K > n:
+            ids.fill_(-1)
     ws = workspace(rows, n, x.device) if ws is None else ws
     _check(lib.whirl_topk_rows_shard(x.data_ptr(), _dtype(x), rows, n, K, int(id_offset), float(inv_t), _p(inv_t_rows),
                                      ids.data_ptr(), vals.data_ptr(), stats.data_ptr(), ws.data_ptr(), ws.numel(), _stream(x)))
@@ -420,6 +437,26 @@ def merge_sample_rows(ids, vals, stats, n_total: int, params: RowParams, kept_ca
     assert ids.is_contiguous() and vals.is_contiguous() and stats.is_contiguous()
     _check(lib.whirl_merge_sample_rows(ids.data_ptr(), vals.data_ptr(), stats.data_ptr(), shards, rows, ks, n_total, C.byref(ps),
                                        C.byref(o), torch.cuda.current_stream(dev).cuda_stream))
+    return res
+
+
+def merge_sample_rows_packed(blocks: torch.Tensor, shards: int, rows: int, ks: int, n_total: int, params: RowParams,
+                             kept_cap: int = 0) -> SampleResult:
+    """blocks: int32 tensor of `shards` packed blocks (the all-gather of every rank's block) -> one token per row."""
+    dev = blocks.device
+    assert blocks.is_contiguous() and blocks.numel() == shards * lib.whirl_shard_block_words(rows, ks)
+    res = SampleResult(
+        token=torch.empty(rows, dtype=torch.int32, device=dev), status=torch.empty(rows, dtype=torch.int32, device=dev),
+        n_kept=torch.empty(rows, dtype=torch.int32, device=dev), closed=torch.empty(rows, dtype=torch.int32, device=dev),
+        stats=torch.empty((rows, 2), dtype=torch.float32, device=dev),
+        kept_ids=torch.full((rows, kept_cap), -1, dtype=torch.int32, device=dev) if kept_cap else None,
+        kept_p=torch.zeros((rows, kept_cap), dtype=torch.float64, device=dev) if kept_cap else None,
+        counters=torch.zeros(CNT_WORDS, dtype=torch.int32, device=dev))
+    o = SampleOut(token=_p(res.token), status=_p(res.status), n_kept=_p(res.n_kept), closed=_p(res.closed), stats=_p(res.stats),
+                  kept_ids=_p(res.kept_ids), kept_p=_p(res.kept_p), kept_cap=kept_cap, counters=_p(res.counters))
+    ps = params.struct(rows)
+    _check(lib.whirl_merge_sample_rows_packed(blocks.data_ptr(), shards, rows, ks, n_total, C.byref(ps), C.byref(o),
+                                              torch.cuda.current_stream(dev).cuda_stream))
     return res
 
 

@@ -431,8 +431,9 @@ int whirl_spec_accept_residual(const void* target, const void* draft, int dtype,
     return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "spec_accept_residual launch");
 }
 
-int whirl_merge_sample_rows(const int* ids, const float* vals, const float* stats, int shards, int rows, int K_s, int n_total,
-                            const whirl_sample_params* prm, const whirl_sample_out* out, void* stream) {
+namespace {
+int merge_call(const int* ids, const float* vals, const float* stats, int shards, size_t cand_stride, size_t stat_stride, int rows, int K_s,
+               int n_total, const whirl_sample_params* prm, const whirl_sample_out* out, void* stream) {
     if (!ids || !vals || !stats || !prm || !out || !out->token || shards < 1 || rows < 0 || K_s < 1 || n_total < 1)
         return fail(WHIRL_ERR_INVALID, "merge_sample_rows: bad pointer / shards / rows / K_s / n_total");
     if (K_s > WHIRL_STREAM_MAX_K || size_t(shards) * K_s > 16384) return fail(WHIRL_ERR_UNSUPPORTED, "merge_sample_rows: K_s above 1024 or shards * K_s above 16384");
@@ -444,9 +445,28 @@ int whirl_merge_sample_rows(const int* ids, const float* vals, const float* stat
     wb::RowOutputs O{};
     O.token = out->token, O.status = out->status, O.n_kept = out->n_kept, O.closed = out->closed, O.stats = out->stats;
     O.kept_ids = out->kept_ids, O.kept_p = out->kept_p, O.kept_cap = out->kept_cap, O.counters = out->counters;
-    const cudaError_t e = wb::merge_sample_launch(ids, vals, stats, shards, rows, K_s, n_total, P, O, sm_count(), static_cast<cudaStream_t>(stream));
+    const cudaError_t e = wb::merge_sample_launch(ids, vals, stats, shards, cand_stride, stat_stride, rows, K_s, n_total, P, O, sm_count(),
+                                                  static_cast<cudaStream_t>(stream));
     bump(LC_AUX);
     return e == cudaSuccess ? WHIRL_OK : fail_cuda(e, "merge_sample_rows launch");
+}
+}  // namespace
+
+int whirl_merge_sample_rows(const int* ids, const float* vals, const float* stats, int shards, int rows, int K_s, int n_total,
+                            const whirl_sample_params* prm, const whirl_sample_out* out, void* stream) {
+    return merge_call(ids, vals, stats, shards, size_t(rows < 0 ? 0 : rows) * size_t(K_s < 0 ? 0 : K_s), size_t(rows < 0 ? 0 : rows) * 2, rows, K_s,
+                      n_total, prm, out, stream);
+}
+
+size_t whirl_shard_block_words(int rows, int K_s) { return rows < 0 || K_s < 0 ? 0 : size_t(rows) * (2 * size_t(K_s) + 2); }
+
+int whirl_merge_sample_rows_packed(const void* blocks, int shards, int rows, int K_s, int n_total, const whirl_sample_params* prm,
+                                   const whirl_sample_out* out, void* stream) {
+    if (!blocks || rows < 0 || K_s < 1) return fail(WHIRL_ERR_INVALID, "merge_sample_rows_packed: bad pointer / rows / K_s");
+    const size_t words = whirl_shard_block_words(rows, K_s);
+    const int32_t* base = static_cast<const int32_t*>(blocks);
+    return merge_call(base, reinterpret_cast<const float*>(base + size_t(rows) * K_s), reinterpret_cast<const float*>(base + 2 * size_t(rows) * K_s),
+                      shards, words, words, rows, K_s, n_total, prm, out, stream);
 }
 
 void whirl_launch_counts(uint64_t* out, int n) {

@@ -160,7 +160,8 @@ cudaError_t accept_residual_launch(const void* target, const void* draft, int dt
                                    int32_t* next_tok, cudaStream_t st);
 
 // ---- vocab-sharded candidates (merge.cu)
-cudaError_t merge_sample_launch(const int32_t* ids, const float* vals, const float* stats, int shards, int rows, int Ks,
+cudaError_t merge_sample_launch(const int32_t* ids, const float* vals, const float* stats, int shards, size_t cand_stride,
+                                size_t stat_stride, int rows, int Ks,
                                 int n_total, const RowParams& P, const RowOutputs& out, int sm_count, cudaStream_t st);
 
 }  // namespace wb

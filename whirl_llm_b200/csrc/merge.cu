@@ -19,9 +19,13 @@ struct MShared {
     float m, sum;
 };
 
-// ids / vals: [shards][rows][Ks]; stats: [shards][rows][2].  One CTA per row (grid-strided).
+// ids / vals: [shards][rows][Ks] with cand_stride words from one shard's block to the next; stats: [shards][rows][2] with
+// stat_stride words between blocks (rows * Ks and rows * 2 for three dense arrays; rows * (2 Ks + 2) for both when every
+// shard's ids, vals and stats lie in one packed block, as an all-gather of such blocks leaves them).  One CTA per row
+// (grid-strided).
 __global__ void __launch_bounds__(MT) merge_sample_kernel(const int32_t* ids, const float* vals, const float* stats, int shards,
-                                                           int rows, int Ks, int n_total, RowParams P, RowOutputs out, int cap_all) {
+                                                           size_t cand_stride, size_t stat_stride, int rows, int Ks, int n_total,
+                                                           RowParams P, RowOutputs out, int cap_all) {
     extern __shared__ __align__(16) uint8_t smem[];
     unsigned long long* all = reinterpret_cast<unsigned long long*>(smem);            // cap_all
     uint32_t* hist = reinterpret_cast<uint32_t*>(all + cap_all);                      // SEL_BINS
@@ -40,19 +44,19 @@ __global__ void __launch_bounds__(MT) merge_sample_kernel(const int32_t* ids, co
         // ---- candidates of all slices (entries a slice left empty carry id < 0)
         for (uint32_t i = g.tid; i < total; i += MT) {
             const uint32_t s = i / uint32_t(Ks), j = i % uint32_t(Ks);
-            const size_t at = (size_t(s) * rows + row) * Ks + j;
+            const size_t at = size_t(s) * cand_stride + size_t(row) * Ks + j;
             const int32_t id = ids[at];
             all[i] = id >= 0 ? make_cand(key_of(fmaxf(vals[at], -INFINITY)), uint32_t(id)) : 0ull;
         }
         // ---- merged row statistics
         if (g.tid < 32) {
             float m = -INFINITY;
-            for (int s = g.tid; s < shards; s += 32) m = fmaxf(m, stats[(size_t(s) * rows + row) * 2]);
+            for (int s = g.tid; s < shards; s += 32) m = fmaxf(m, stats[size_t(s) * stat_stride + size_t(row) * 2]);
             m = warp_max(m);
             double z = 0;
             for (int s = g.tid; s < shards; s += 32) {
-                const float ms = stats[(size_t(s) * rows + row) * 2];
-                if (ms != -INFINITY) z += double(stats[(size_t(s) * rows + row) * 2 + 1]) * exp(double(__fsub_rn(ms, m)) * double(inv_t));
+                const float ms = stats[size_t(s) * stat_stride + size_t(row) * 2];
+                if (ms != -INFINITY) z += double(stats[size_t(s) * stat_stride + size_t(row) * 2 + 1]) * exp(double(__fsub_rn(ms, m)) * double(inv_t));
             }
             z = warp_sum(z);
             if (g.tid == 0) sh->m = m, sh->sum = float(z);
@@ -107,8 +111,8 @@ __global__ void __launch_bounds__(MT) merge_sample_kernel(const int32_t* ids, co
     }
 }
 
-cudaError_t merge_sample_launch(const int32_t* ids, const float* vals, const float* stats, int shards, int rows, int Ks,
-                                int n_total, const RowParams& P, const RowOutputs& out, int sm_count, cudaStream_t st) {
+cudaError_t merge_sample_launch(const int32_t* ids, const float* vals, const float* stats, int shards, size_t cand_stride,
+                                size_t stat_stride, int rows, int Ks, int n_total, const RowParams& P, const RowOutputs& out, int sm_count, cudaStream_t st) {
     const int cap_all = shards * Ks;
     int cap_hand = 1;
     while (cap_hand < Ks) cap_hand <<= 1;
@@ -118,7 +122,7 @@ cudaError_t merge_sample_launch(const int32_t* ids, const float* vals, const flo
     if (e != cudaSuccess) return e;
     const int per_sm = smem > 110000 ? 1 : 2;
     const int grid = rows < per_sm * sm_count ? rows : per_sm * sm_count;
-    merge_sample_kernel<<<grid, MT, smem, st>>>(ids, vals, stats, shards, rows, Ks, n_total, P, out, cap_all);
+    merge_sample_kernel<<<grid, MT, smem, st>>>(ids, vals, stats, shards, cand_stride, stat_stride, rows, Ks, n_total, P, out, cap_all);
     return cudaGetLastError();
 }
 

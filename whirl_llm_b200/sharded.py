@@ -43,32 +43,80 @@ def slice_bounds(n_total: int, world: int, rank: int) -> Tuple[int, int]:
     return rank * w, (rank + 1) * w
 
 
-def exchange_candidates(ids: torch.Tensor, vals: torch.Tensor, stats: torch.Tensor, group=None):
-    """One all-gather of every rank's [rows, K_s] ids / vals and [rows, 2] stats -> [world, rows, K_s] / [world, rows, 2].
+def block_words(rows: int, ks: int) -> int:
+    """4-byte words of one rank's packed block: ids [rows][ks] | vals [rows][ks] | stats [rows][2]
+    (whirl_shard_block_words)."""
+    return rows * (2 * ks + 2)
 
-    The three arrays travel as one buffer (ids and vals are 4-byte words; 2 * K_s + 2 words per row), so the exchange
-    is a single collective: 2 MiB per rank at 256 rows x 1024 candidates."""
+
+def block_views(block: torch.Tensor, rows: int, ks: int):
+    """ids (int32), vals (float32), stats (float32) views of one packed block; no copy."""
+    assert block.dtype == torch.int32 and block.is_contiguous() and block.numel() == block_words(rows, ks)
+    ids = block[: rows * ks].view(rows, ks)
+    vals = block[rows * ks: 2 * rows * ks].view(torch.float32).view(rows, ks)
+    stats = block[2 * rows * ks:].view(torch.float32).view(rows, 2)
+    return ids, vals, stats
+
+
+def exchange_blocks(block: torch.Tensor, out: Optional[torch.Tensor] = None, group=None) -> torch.Tensor:
+    """ONE all-gather of every rank's packed block -> [world * block_words] int32 (rank r's block at r * block_words).
+    Nothing is repacked on either side: the selection kernel wrote into `block`, the merge kernel reads `out` in
+    place.  2 MiB per rank at 256 rows x 1024 candidates."""
+    world = dist.get_world_size(group)
+    if out is None:
+        out = torch.empty(world * block.numel(), dtype=torch.int32, device=block.device)
+    dist.all_gather_into_tensor(out, block, group=group)
+    return out
+
+
+def exchange_candidates(ids: torch.Tensor, vals: torch.Tensor, stats: torch.Tensor, group=None):
+    """Three separate arrays -> [world, rows, K_s] ids / vals and [world, rows, 2] stats (views of the gathered blocks).
+    For callers that hold the arrays apart; it packs them first (one copy), which sample_vocab_sharded avoids by
+    letting the kernel write into the block."""
     world = dist.get_world_size(group)
     rows, ks = ids.shape
-    packed = torch.cat([ids.view(torch.int32), vals.view(torch.int32), stats.view(torch.int32)], dim=1).contiguous()
-    flat = torch.empty((world * rows, 2 * ks + 2), dtype=torch.int32, device=ids.device)
-    dist.all_gather_into_tensor(flat, packed, group=group)
-    out = flat.view(world, rows, 2 * ks + 2)
-    g_ids = out[:, :, :ks].contiguous()
-    g_vals = out[:, :, ks: 2 * ks].contiguous().view(torch.float32)
-    g_stats = out[:, :, 2 * ks:].contiguous().view(torch.float32)
+    block = torch.empty(block_words(rows, ks), dtype=torch.int32, device=ids.device)
+    b_ids, b_vals, b_stats = block_views(block, rows, ks)
+    b_ids.copy_(ids), b_vals.copy_(vals), b_stats.copy_(stats)
+    flat = exchange_blocks(block, group=group).view(world, block_words(rows, ks))
+    g_ids = flat[:, : rows * ks].view(world, rows, ks)
+    g_vals = flat[:, rows * ks: 2 * rows * ks].view(torch.float32).view(world, rows, ks)
+    g_stats = flat[:, 2 * rows * ks:].view(torch.float32).view(world, rows, 2)
     return g_ids, g_vals, g_stats
+
+
+class VocabShardedSampler:
+    """Vocab-sharded sampling with its buffers kept across steps: this rank's packed block and the gathered blocks."""
+
+    def __init__(self, rows: int, n_total: int, k_s: int = 1024, device=None, group=None):
+        self.rows, self.n_total, self.k_s, self.group = rows, n_total, k_s, group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.begin, self.end = slice_bounds(n_total, self.world, self.rank)
+        self.block = torch.empty(block_words(rows, k_s), dtype=torch.int32, device=device)
+        self.gathered = torch.empty(self.world * self.block.numel(), dtype=torch.int32, device=device)
+        self.views = block_views(self.block, rows, k_s)
+
+    def select(self, x_local: torch.Tensor, inv_t: float = 1.0, inv_t_rows: Optional[torch.Tensor] = None):
+        from . import api
+        assert x_local.shape == (self.rows, self.end - self.begin)
+        api.topk_rows_shard(x_local, self.k_s, self.begin, inv_t=inv_t, inv_t_rows=inv_t_rows, out=self.views)
+
+    def exchange(self):
+        exchange_blocks(self.block, self.gathered, self.group)
+
+    def merge(self, params, kept_cap: int = 0):
+        from . import api
+        return api.merge_sample_rows_packed(self.gathered, self.world, self.rows, self.k_s, self.n_total, params, kept_cap=kept_cap)
+
+    def sample(self, x_local: torch.Tensor, params, inv_t: float = 1.0, inv_t_rows: Optional[torch.Tensor] = None, kept_cap: int = 0):
+        self.select(x_local, inv_t, inv_t_rows)
+        self.exchange()
+        return self.merge(params, kept_cap)
 
 
 def sample_vocab_sharded(x_local: torch.Tensor, n_total: int, params, k_s: int = 1024, inv_t: float = 1.0,
                          inv_t_rows: Optional[torch.Tensor] = None, kept_cap: int = 0, group=None):
     """x_local: this rank's [rows, n_total / world] slice of the logits on its GPU.  Returns the SampleResult (the same
     on every rank).  inv_t / inv_t_rows: the temperature the slice statistics are taken at (must match params.inv_t)."""
-    from . import api
-    rank = dist.get_rank(group)
-    world = dist.get_world_size(group)
-    begin, end = slice_bounds(n_total, world, rank)
-    assert x_local.shape[1] == end - begin
-    ids, vals, stats = api.topk_rows_shard(x_local, k_s, begin, inv_t=inv_t, inv_t_rows=inv_t_rows)
-    g_ids, g_vals, g_stats = exchange_candidates(ids, vals, stats, group)
-    return api.merge_sample_rows(g_ids, g_vals, g_stats, n_total, params, kept_cap=kept_cap)
+    s = VocabShardedSampler(x_local.shape[0], n_total, k_s, x_local.device, group)
+    return s.sample(x_local, params, inv_t, inv_t_rows, kept_cap)
