@@ -50,7 +50,7 @@ constexpr int Q_ST = Q_SW * 32;
 #endif
 constexpr int Q_TW = WB_TW;              // tail warps
 constexpr int Q_TT = Q_TW * 32;
-constexpr int Q_THREADS = 32 + Q_ST + Q_TT;  // producer warp, stream warps, tail group
+constexpr int Q_THREADS = 32 + Q_ST + Q_TT + 32;  // producer warp, stream warps, tail group, threshold keeper
 constexpr int Q_SB = 16384;              // bytes per ring stage
 constexpr int Q_SQ = Q_SB / 16;          // 128-bit words per stage
 constexpr int Q_MAXSTAGES = 8;
@@ -90,6 +90,7 @@ struct QSlot {
     unsigned long long tau;  // current threshold candidate; elements must beat it to be logged
     uint32_t cnt;            // log entries reserved so far (may exceed Q_L: overflow); bit 31: a NaN poisoned a sum
     uint32_t side_cnt;       // words put aside in the side buffer (penalised rows that need their normaliser)
+    uint32_t done_warps;     // stream warps that are through the row (the threshold keeper watches this, then closes the row too)
     QRow cfg;
     float red_m[Q_RED];
     float red_e[Q_RED];
@@ -268,6 +269,78 @@ __device__ __forceinline__ void join_word(JoinCtx& c, uint32_t wq, uint4 w) {
     }
 }
 
+// ---- the small-K threshold keeper (a warp of its own, while a row streams)
+// 32 ordering keys, one per lane, into descending order over the lanes (a bitonic network of shuffles).
+__device__ __forceinline__ uint32_t warp_sort_desc(uint32_t x, int lane) {
+#pragma unroll
+    for (int k = 2; k <= 32; k <<= 1) {
+#pragma unroll
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            const uint32_t o = __shfl_xor_sync(0xffffffffu, x, j);
+            const bool take_max = ((lane & j) == 0) == ((lane & k) == 0);
+            x = take_max ? max(x, o) : min(x, o);
+        }
+    }
+    return x;
+}
+// a bitonic sequence over the lanes into descending order
+__device__ __forceinline__ uint32_t warp_merge_desc(uint32_t x, int lane) {
+#pragma unroll
+    for (int j = 16; j > 0; j >>= 1) {
+        const uint32_t o = __shfl_xor_sync(0xffffffffu, x, j);
+        x = (lane & j) == 0 ? max(x, o) : min(x, o);
+    }
+    return x;
+}
+
+// Rows that want at most 64 candidates: one warp follows the row's log while the stream warps fill it, keeps the 64
+// largest keys it has seen in sorted order (two per lane) and raises the row's threshold to the K-th of them.  That is
+// the K-th largest logit of the part of the row streamed so far, short of entries it skips - not written yet when it
+// came by, or logged raw from a word that holds a history token - and the K-th largest of any subset of a row is a valid
+// lower bound.  Returns 0 when every stream warp is through the row, 2 when the wait ran out.
+static __device__ __noinline__ uint32_t keep_threshold_small_k(QSlot* sl, const unsigned long long* log, uint32_t K, uint32_t limit) {
+    const int lane = lane_id();
+    uint32_t top_a = 0u, top_b = 0u;  // ranks lane and 32 + lane
+    uint32_t done = 0, tau_key = 0;
+#pragma unroll 1
+    for (uint32_t spin = 0; spin < 4 * limit; ++spin) {
+        uint32_t through = 0, c = 0;
+        if (lane == 0) {
+            through = ldv_u32(&sl->done_warps) == uint32_t(Q_SW) ? 1u : 0u;
+            c = ldv_u32(&sl->cnt) & 0x7fffffffu;
+        }
+        through = __shfl_sync(0xffffffffu, through, 0);
+        c = __shfl_sync(0xffffffffu, c, 0);
+        if (through) return 0u;  // (a threshold is of no use any more)
+        c = c < uint32_t(Q_L) ? c : uint32_t(Q_L);
+        const uint32_t pending = c - done;
+        if (pending >= 8u) {
+            const uint32_t nb = pending < 32u ? pending : 32u;
+            const unsigned long long e = uint32_t(lane) < nb ? ldv_u64(&log[done + lane]) : 0ull;
+            uint32_t v = (e & 0x80000000ull) ? cand_key(e) : 0u;  // (0: not written yet, or logged raw)
+            done += nb;
+            if (!__any_sync(0xffffffffu, v > __shfl_sync(0xffffffffu, top_b, 31))) continue;  // nothing enters the 64
+            v = warp_sort_desc(v, lane);
+            // the 32 largest of (ranks 32..63, the batch), then the two halves of (ranks 0..31, those)
+            const uint32_t d = warp_merge_desc(max(top_b, __shfl_sync(0xffffffffu, v, 31 - lane)), lane);
+            const uint32_t dr = __shfl_sync(0xffffffffu, d, 31 - lane);
+            const uint32_t hi = max(top_a, dr), lo = min(top_a, dr);
+            top_a = warp_merge_desc(hi, lane);
+            top_b = warp_merge_desc(lo, lane);
+            const uint32_t kk = K <= 32u ? __shfl_sync(0xffffffffu, top_a, int(K) - 1) : __shfl_sync(0xffffffffu, top_b, int(K) - 33);
+            if (kk > tau_key) {
+                tau_key = kk;
+                // (a plain compare and store, as the stream warps do: a lost update leaves another valid bound)
+                if (lane == 0 && ((unsigned long long)kk << 32) > ldv_u64(&sl->tau))
+                    *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = (unsigned long long)kk << 32;
+            }
+            continue;
+        }
+        __nanosleep(100);
+    }
+    return 2u;
+}
+
 #ifdef WB_PROF
 #define PROF_T0(v) const long long v = clock64()
 #define PROF_ADD(i, v) do { if (g.tid == 0) prof[i] += clock64() - (v); } while (0)
@@ -303,7 +376,6 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
     const size_t row_bytes = size_t(n) * sizeof(T);
     const bool sample = a.mode == MODE_SAMPLE;
     const RowParams& P = a.prm;
-    const uint32_t wlim = a.wait_limit ? a.wait_limit : kWaitLimit;  // budget of every wait
     // the CTA's side buffers (one per slot): kMaxHist words and their places in the row
     uint8_t* const side_base = static_cast<uint8_t*>(a.side_ws) + size_t(blockIdx.x) * 2 * kMaxHist * 20;
     auto side_w = [&](int p) { return reinterpret_cast<uint4*>(side_base + size_t(p) * kMaxHist * 20); };
@@ -311,7 +383,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
 
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], Q_SW);
-        for (int p = 0; p < 2; ++p) mbar_init(&boot_done[p], 1), mbar_init(&closed[p], Q_SW), mbar_init(&head_done[p], Q_SW);
+        for (int p = 0; p < 2; ++p) mbar_init(&boot_done[p], 1), mbar_init(&closed[p], Q_SW + 1), mbar_init(&head_done[p], Q_SW);
         mbar_fence_init();
     }
     for (int i = tid; i < 2 * Q_L; i += Q_THREADS) logs[i] = 0ull;
@@ -375,7 +447,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
 #ifdef WB_PROF
                 const long long pw0 = clock64();
 #endif
-                if (!mbar_wait(&empty[s], par, wlim)) {
+                if (!mbar_wait(&empty[s], par, a.wait_limit)) {
                     atomicExch(a.err, 1u);
                     gave_up = true;
                     break;
@@ -405,7 +477,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             for (uint32_t k = 0; k < uint32_t(stages) && k < issued; ++k) {
                 if (bs == 0) bs = uint32_t(stages), bpar ^= 1u;
                 --bs;
-                mbar_wait(&full[bs], bpar ^ 1u, wlim);
+                mbar_wait(&full[bs], bpar ^ 1u, a.wait_limit);
             }
         }
 #ifdef WB_PROF
@@ -414,6 +486,42 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             atomicAdd(&dbg[12], (unsigned long long)pw), atomicAdd(&dbg[13], (unsigned long long)(clock64() - pt0));
         }
 #endif
+        return;
+    }
+
+    // =========================================================== threshold keeper
+    // One warp follows every row from the moment its slot is handed out until the last stream warp is through it: for
+    // rows that want at most 64 candidates it keeps the threshold at the K-th largest of the log (see
+    // keep_threshold_small_k); then it adds its arrival to the row's "closed" barrier, so that the slot is not given to
+    // another row while this warp could still write a threshold into it.
+    if (warp == 1 + Q_SW + Q_TW) {
+        const int lane = lane_id();
+#pragma unroll 1
+        for (int ord = 0; ord < n_list; ++ord) {
+            const int p = ord & 1;
+            QSlot* sl = &sh->slot[p];
+            if (!mbar_wait(&boot_done[p], (ord >> 1) & 1, a.wait_limit)) {
+                if (lane == 0) atomicExch(a.err, 6u);
+                return;
+            }
+            const uint32_t K = sl->cfg.K;
+            uint32_t what = 2u;
+            if (K <= 64u) {
+                what = keep_threshold_small_k(sl, logs + size_t(p) * Q_L, K, a.wait_limit);
+            } else {
+#pragma unroll 1
+                for (uint32_t spin = 0; spin < 4 * a.wait_limit && what != 0u; ++spin) {
+                    if (ldv_u32(&sl->done_warps) == uint32_t(Q_SW)) what = 0u;
+                    else __nanosleep(500);
+                }
+            }
+            if (what != 0u) {
+                if (lane == 0) atomicExch(a.err, 6u);
+                return;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&closed[p]);
+        }
         return;
     }
 
@@ -503,6 +611,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 sl->tau = 0ull;
                 sl->cnt = 0;
                 sl->side_cnt = 0;
+                sl->done_warps = 0;
                 for (int w = 0; w < Q_SW; ++w) sl->wbound[w] = 0u;
                 for (int w = Q_SW; w < Q_RED; ++w) sl->red_m[w] = -INFINITY, sl->red_e[w] = -INFINITY, sl->red_s[w] = 0.0;
                 mbar_arrive(&boot_done[p]);
@@ -605,7 +714,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         uint32_t what = 2u;  // 0: the row is through, 1: the log wants a refinement, 2: gave up
                         const uint32_t step = 2 * K > uint32_t(Q_L) / 4 ? 2 * K : uint32_t(Q_L) / 4;
 #pragma unroll 1
-                        for (uint32_t spin = 0; spin < 4 * wlim; ++spin) {
+                        for (uint32_t spin = 0; spin < 4 * a.wait_limit; ++spin) {
                             if (mbar_try_wait(&closed[p], (ord >> 1) & 1)) {
                                 what = 0u;
                                 break;
@@ -630,7 +739,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     }
                     maybe_refine(p, K, true);
                 }
-                mbar_wait(&closed[p], (ord >> 1) & 1, wlim);  // acquire the stream warps' writes
+                mbar_wait(&closed[p], (ord >> 1) & 1, a.wait_limit);  // acquire the stream warps' writes
                 PROF_ADD(0, tw0);
                 rf_last[p] = 0;
                 // ---- the row is through
@@ -726,6 +835,9 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 const uint32_t total_raw = sl->cnt;  // bit 31: a NaN logit met a sum
                 const bool nan_row = (total_raw & 0x80000000u) != 0;
                 const uint32_t total = total_raw & 0x7fffffffu;
+#ifdef WB_PROF
+                if (g.tid == 0) atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 16) + 14, (unsigned long long)total);
+#endif
                 nan_seen = nan_row;
                 overflow = total > uint32_t(Q_L) || nan_row || (pen_on && !lazy && sl->side_cnt > uint32_t(kMaxHist));
                 const uint32_t nlog = total > uint32_t(Q_L) ? uint32_t(Q_L) : total;
@@ -904,7 +1016,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
     const uint32_t n_iter = (n_chunks + Q_NS - 1) / Q_NS;
     const uint32_t full_iters = row_q / (Q_NS * Q_SQ);  // iterations whose words all lie inside the row
 #ifdef WB_PROF
-    long long sp_wait = 0, sp_boot = 0, sp_head = 0, sp_total = clock64();
+    long long sp_wait = 0, sp_boot = 0, sp_head = 0, sp_total = clock64(), sp_visits = 0;
 #endif
 #pragma unroll 1
     for (int ord = 0; ord < n_list; ++ord) {
@@ -916,7 +1028,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
 #ifdef WB_PROF
         const long long tb0 = clock64();
 #endif
-        if (!mbar_wait(&boot_done[p], (ord >> 1) & 1, wlim)) {
+        if (!mbar_wait(&boot_done[p], (ord >> 1) & 1, a.wait_limit)) {
             if (lane == 0) atomicExch(a.err, 4u);
             return;
         }
@@ -981,7 +1093,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
 #ifdef WB_PROF
                         const long long tw0 = clock64();
 #endif
-                        if (!mbar_wait(&full[st_slot], st_phase, wlim)) {
+                        if (!mbar_wait(&full[st_slot], st_phase, a.wait_limit)) {
                             if (lane == 0) atomicExch(a.err, 5u);
                             st_fail = true;
                             return;
@@ -1097,7 +1209,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         sl->wbound[sw] = kr;
                         mbar_arrive(&head_done[p]);
                     }
-                    if (!mbar_wait(&head_done[p], (ord >> 1) & 1, wlim)) {
+                    if (!mbar_wait(&head_done[p], (ord >> 1) & 1, a.wait_limit)) {
                         if (lane == 0) atomicExch(a.err, 11u);
                         st_fail = true;
                         return;
@@ -1115,18 +1227,40 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     const uint32_t tk = *tau_hi;
                     if (tk > tau_key) tau_key = tk, tau_f = float_of_key(tk);
                 }
-                if (vm >= tau_f) {
-                    // rare: this lane holds an element that may beat the threshold
-                    const unsigned long long tau = (unsigned long long)tau_key << 32;
+                if (__any_sync(0xffffffffu, vm >= tau_f)) {
+#ifdef WB_PROF
+                    ++sp_visits;
+#endif
+                    // Some lane holds logits that may beat the threshold.
+                    uint32_t hm = 0;  // bit j: this lane's logit j is at or above the threshold
 #pragma unroll
-                    for (int i = 0; i < NW; ++i) {
-                        if (qm[i] >= tau_f) {
-                            const bool mk = (marked >> i) & 1u;
-                            const uint32_t id0 = (wq0 + uint32_t(i) * Q_ST) * VE;
+                    for (int j = 0; j < NW * VE; ++j) hm |= (xv[j] >= tau_f ? 1u : 0u) << j;
+                    // (each lane with logits to log reserves its places itself: few lanes have any, and a scan over the warp
+                    // would put its latency in front of every one of them)
+                    uint32_t pos = 0;
+                    if (hm) pos = atomicAdd(&sl->cnt, uint32_t(__popc(hm))) & 0x7fffffffu;
+#pragma unroll 1
+                    while (hm) {
+                        const int j = __ffs(int(hm)) - 1;
+                        hm &= hm - 1;
+                        // logit j out of the registers: a tree of selects on the bits of j
+                        float t[NW * VE];
 #pragma unroll
-                            for (int e = 0; e < VE; ++e)
-                                if (xv[i * VE + e] >= tau_f) log_append(sl, log, xv[i * VE + e], id0 + e, tau, mk);
+                        for (int q = 0; q < NW * VE; ++q) t[q] = xv[q];
+#pragma unroll
+                        for (int lvl = 0; (1 << lvl) < NW * VE; ++lvl) {
+                            const bool odd = (j >> lvl) & 1;
+#pragma unroll
+                            for (int q = 0; q < (NW * VE) >> (lvl + 1); ++q) t[q] = odd ? t[2 * q + 1] : t[2 * q];
                         }
+                        const int wi = j / VE;  // (VE is a power of two)
+                        const uint32_t id = (wq0 + uint32_t(wi) * Q_ST) * VE + uint32_t(j % VE);
+                        const uint32_t u = __float_as_uint(t[0] + 0.0f);  // -0 + +0 = +0: the two zeros share a key
+                        const uint32_t key = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+                        unsigned long long cnd = make_cand(key, id);
+                        if ((marked >> wi) & 1u) cnd &= ~0x80000000ull;  // logged raw from a word that holds a history token
+                        if (pos < uint32_t(Q_L)) log[pos] = cnd;
+                        ++pos;
                     }
                 }
                 // a fresh bound each time the part of the row seen has grown by half
@@ -1155,7 +1289,10 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
         }
         if ((row_flags & (QF_PEN | QF_LAZY)) == QF_PEN) __threadfence();  // (words put aside in global memory are read by the tail group)
         __syncwarp();
-        if (lane == 0) mbar_arrive(&closed[p]);
+        if (lane == 0) {
+            atomicAdd(&sl->done_warps, 1u);
+            mbar_arrive(&closed[p]);
+        }
     }
 #ifdef WB_PROF
     if (st_tid == 0) {
@@ -1163,6 +1300,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
         atomicAdd(&dbg[8], (unsigned long long)sp_wait), atomicAdd(&dbg[9], (unsigned long long)sp_boot);
         atomicAdd(&dbg[10], (unsigned long long)(clock64() - sp_total)), atomicAdd(&dbg[11], (unsigned long long)sp_head);
     }
+    if (lane == 0) atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 16) + 15, (unsigned long long)sp_visits);
 #endif
 }
 
@@ -1192,7 +1330,9 @@ bool single_pass_supported(const SelectArgs& a, int dtype) {
     return single_pass_fixed_smem(single_pass_gbm_words(a, dtype), kSinglePassMaxK, pen) + 3 * size_t(Q_SB) <= 232448;
 }
 
-cudaError_t single_pass_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st) {
+cudaError_t single_pass_launch(const SelectArgs& args, int dtype, int sm_count, cudaStream_t st) {
+    SelectArgs a = args;
+    if (a.wait_limit == 0) a.wait_limit = kWaitLimit;  // the budget of every wait inside the kernel
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
     const int gbm_words = single_pass_gbm_words(a, dtype);
     const int max_k = kSinglePassMaxK;
