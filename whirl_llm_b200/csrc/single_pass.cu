@@ -86,6 +86,9 @@ struct QRow {
 // frequency >= 0): a history token then matters only if its RAW logit passes the threshold, which the stream sees.
 enum : uint32_t { QF_NO_SUM = 1u, QF_PEN = 2u, QF_GREEDY = 4u, QF_LAZY = 8u };
 
+constexpr int Q_TOP = 8;  // lane maxima per stream warp that go into a small-K row's first threshold
+static_assert(Q_SW * Q_TOP == 128, "four published keys per lane");
+
 struct QSlot {
     unsigned long long tau;  // current threshold candidate; elements must beat it to be logged
     uint32_t cnt;            // log entries reserved so far (may exceed Q_L: overflow); bit 31: a NaN poisoned a sum
@@ -96,6 +99,7 @@ struct QSlot {
     float red_e[Q_RED];
     double red_s[Q_RED];
     uint32_t wbound[Q_SW];   // per stream warp: its own lower bound (an ordering key)
+    alignas(16) uint32_t wtop[Q_SW * Q_TOP];  // per stream warp: its Q_TOP largest lane maxima of the row's first iteration, descending
 };
 
 constexpr int Q_MAXR = 512;  // rows per CTA and launch
@@ -1071,7 +1075,8 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
         auto run_row = [&](auto mode_tag) {
             constexpr int MODE = decltype(mode_tag)::value;
             constexpr int NW = 2 * Q_NS;  // 128-bit words per thread and iteration
-            uint32_t next_renew = 2;
+            // (a small-K row's threshold is kept by the keeper warp: the stream warps name no further bounds for it)
+            uint32_t next_renew = sl->cfg.K <= 64u ? 0xffffffffu : 2u;
 #pragma unroll 1
             for (uint32_t iter = 0; iter < n_iter; ++iter) {
                 const uint32_t c = Q_NS * iter;
@@ -1204,7 +1209,33 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
 #ifdef WB_PROF
                     const long long th0 = clock64();
 #endif
-                    const uint32_t kr = own_bound();
+                    const bool merged = sl->cfg.K <= 64u;
+                    uint32_t kr;
+                    if (merged) {
+                        // Small K: the warp publishes its Q_TOP largest lane maxima.  The K-th largest of all warps'
+                        // published keys is a valid bound (that many logits of the row lie at or above it), and close to the
+                        // K-th largest logit read so far; the warp's own rth largest, taken on the way, keeps the plain bound
+                        // (the smallest of the warps' rth largest) at hand as well.
+                        uint32_t kv[2] = {m1 == -INFINITY ? 0u : key_of(m1), m2 == -INFINITY ? 0u : key_of(m2)};
+                        uint32_t mine = 0u;
+                        kr = 0u;
+#pragma unroll
+                        for (int t = 0; t < Q_TOP; ++t) {
+                            const uint32_t mx = kv[0] > kv[1] ? kv[0] : kv[1];
+                            const uint32_t top = __reduce_max_sync(0xffffffffu, mx);
+                            if (lane == t) mine = top;
+                            if (uint32_t(t) + 1u == rth) kr = top;
+                            const uint32_t holders = __ballot_sync(0xffffffffu, mx == top && top != 0u);
+                            if (lane == __ffs(int(holders)) - 1) {
+                                if (kv[0] == top) kv[0] = 0u;
+                                else kv[1] = 0u;
+                            }
+                        }
+                        if (lane < Q_TOP) sl->wtop[sw * Q_TOP + lane] = mine;
+                        __syncwarp();
+                    } else {
+                        kr = own_bound();
+                    }
                     if (lane == 0) {
                         sl->wbound[sw] = kr;
                         mbar_arrive(&head_done[p]);
@@ -1214,7 +1245,20 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         st_fail = true;
                         return;
                     }
-                    const uint32_t kmin = __reduce_min_sync(0xffffffffu, lane < Q_SW ? ldv_u32(&sl->wbound[lane]) : 0xffffffffu);
+                    uint32_t kmin = __reduce_min_sync(0xffffffffu, lane < Q_SW ? ldv_u32(&sl->wbound[lane]) : 0xffffffffu);
+                    if (merged) {
+                        // the largest key prefix (20 bits) that at least K of the published keys reach
+                        const uint4 q = *reinterpret_cast<const uint4*>(&sl->wtop[4 * lane]);  // (written before the meeting's barrier)
+                        const uint32_t K = sl->cfg.K;
+                        uint32_t t = 0u;
+#pragma unroll 1
+                        for (int b = 31; b >= 12; --b) {
+                            const uint32_t cand = t | (1u << b);
+                            const uint32_t c = (q.x >= cand ? 1u : 0u) + (q.y >= cand ? 1u : 0u) + (q.z >= cand ? 1u : 0u) + (q.w >= cand ? 1u : 0u);
+                            if (__reduce_add_sync(0xffffffffu, c) >= K) t = cand;
+                        }
+                        kmin = t > kmin ? t : kmin;
+                    }
                     if (kmin) tau_key = kmin, tau_f = float_of_key(kmin);
                     if (sw == 0 && lane == 0) {
                         const unsigned long long t0 = (unsigned long long)kmin << 32;
