@@ -278,7 +278,8 @@ def run_ours(args):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
 
     rows, vocab, esize = args.rows, args.vocab, (4 if args.dtype == "f32" else 2)
     xs, params, us, base, what = make_workload(torch, api, args, dev, rank)
@@ -310,6 +311,10 @@ def run_ours(args):
     e1.record()
     sync_all()
     est = max(e0.elapsed_time(e1), 1e-3)
+    if dist is not None:  # every rank must run the same number of regions: take the slowest rank's estimate
+        te = torch.tensor([est], dtype=torch.float64, device=dev)
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        est = float(te.item())
     n_regions = args.regions if args.regions > 0 else int(min(400, max(10, 1000.0 / est)))
     clocks = ClockSampler(local)
     lc0 = api.launch_counts()
