@@ -73,6 +73,7 @@ __device__ __forceinline__ uint32_t warp_scan_incl(uint32_t v) {
 // id 0 is __syncthreads' barrier; groups that are not the whole CTA use ids 1..15.
 template <int NT>
 struct Group {
+    static constexpr int size = NT;
     int tid;  // 0..NT-1 within the group
     int bar;  // hardware barrier id
     __device__ __forceinline__ void sync() const {

@@ -144,7 +144,8 @@ cudaError_t select_generic_launch(const SelectArgs& a, int dtype, int sm_count, 
 // single-pass kernel (single_pass.cu): rows keeping at most kSinglePassMaxK candidates, 16-byte aligned rows
 constexpr int kFirstLevelK = 256;     // candidates of a row without a usable top_k at the first level (the reference's k_small,
                                       // src/server/engine_sampling.h:20)
-constexpr int kSinglePassMaxK = 256;
+constexpr int kSinglePassMaxK = 1024;  // candidates a row may keep in the single-pass kernel
+constexpr int kSinglePassHandK = 256;  // ... of which rows up to this many are finished by one warp from dedicated shared memory
 cudaError_t single_pass_launch(const SelectArgs& a, int dtype, int sm_count, cudaStream_t st);
 size_t single_pass_side_bytes(int sm_bound);  // bytes of SelectArgs::side_ws for a GPU of up to sm_bound SMs
 bool single_pass_supported(const SelectArgs& a, int dtype);

@@ -58,9 +58,6 @@ constexpr int Q_MAXSTAGES = 8;
 #define WB_NS 2
 #endif
 constexpr int Q_NS = WB_NS;              // ring stages per iteration of a stream warp
-#ifndef WB_RENEW_STEP
-#define WB_RENEW_STEP (next_renew + 1) / 2
-#endif
 #ifndef WB_QL
 #define WB_QL 3072
 #endif
@@ -72,6 +69,7 @@ static_assert(Q_SQ == 2 * Q_ST, "two 128-bit words per stream thread and stage")
 // What the roles need to know about a row, fetched once (by one tail warp, a row ahead) into shared memory: while the rows
 // stream a load from global memory takes microseconds, so nobody on the path of a row reads parameters from there.
 struct QRow {
+    uint32_t rank0;          // first_rank of the row
     int32_t row;             // index in the batch
     uint32_t K;              // candidates wanted
     uint32_t top_k;
@@ -86,8 +84,21 @@ struct QRow {
 // frequency >= 0): a history token then matters only if its RAW logit passes the threshold, which the stream sees.
 enum : uint32_t { QF_NO_SUM = 1u, QF_PEN = 2u, QF_GREEDY = 4u, QF_LAZY = 8u };
 
-constexpr int Q_TOP = 8;  // lane maxima per stream warp that go into a small-K row's first threshold
-static_assert(Q_SW * Q_TOP == 128, "four published keys per lane");
+constexpr int Q_TOP = 16;       // lane maxima a stream warp publishes for a row's first threshold (the first 8 for a small-K row)
+constexpr int Q_SMALL_K = 64;   // rows keeping at most this many candidates: exact first threshold, threshold kept by the keeper warp
+constexpr int Q_RANK_MAX = 192; // largest rank among the published maxima a first threshold may be taken at
+static_assert(Q_SW * Q_TOP == 256, "eight published keys per lane");
+
+// The rank, among the logits of a row's first iteration, that the row's first threshold is taken at.  Small K: K itself
+// (the K-th largest of a part of the row is a valid bound).  Larger K: a guess - the rank that, scaled from the first
+// iteration (it0 logits) to the whole row (n logits), leaves K candidates 3.5 standard deviations below the expected
+// count.  A row that ends with fewer than K logged candidates is redone by the multi-pass kernel.
+__device__ __forceinline__ uint32_t first_rank(uint32_t K, uint32_t n, uint32_t it0) {
+    if (K <= uint32_t(Q_SMALL_K)) return K;
+    const float x = float(K) * float(it0 < n ? it0 : n) / float(n);
+    const float r = 0.5f * (3.5f + sqrtf(12.25f + 4.f * x));
+    return uint32_t(ceilf(r * r));
+}
 
 struct QSlot {
     unsigned long long tau;  // current threshold candidate; elements must beat it to be logged
@@ -98,7 +109,6 @@ struct QSlot {
     float red_m[Q_RED];
     float red_e[Q_RED];
     double red_s[Q_RED];
-    uint32_t wbound[Q_SW];   // per stream warp: its own lower bound (an ordering key)
     alignas(16) uint32_t wtop[Q_SW * Q_TOP];  // per stream warp: its Q_TOP largest lane maxima of the row's first iteration, descending
 };
 
@@ -354,16 +364,17 @@ static __device__ __noinline__ uint32_t keep_threshold_small_k(QSlot* sl, const 
 #endif
 
 template <typename T>
-__global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a, int stages, int gbm_words, int max_k) {
+__global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a, int stages, int gbm_words, int max_k, int hand_k) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int VE = 16 / int(sizeof(T));      // logits per 128-bit word
     uint8_t* ring = smem;                                                                // stages * Q_SB
     unsigned long long* logs = reinterpret_cast<unsigned long long*>(ring + size_t(stages) * Q_SB);  // 2 * Q_L
     uint32_t* hist = reinterpret_cast<uint32_t*>(logs + 2 * Q_L);                        // SEL_BINS
-    unsigned long long* hand = reinterpret_cast<unsigned long long*>(hist + SEL_BINS);   // max_k: a row's candidates
-    double* tail_p = reinterpret_cast<double*>(hand + max_k);                            // max_k + 2 * Q_TW
-    double* tail_q = tail_p + max_k + 2 * Q_TW;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(tail_q + max_k + 2 * Q_TW);             // 2 * Q_MAXSTAGES + 6
+    // (hand, tail_p, tail_q serve rows of up to hand_k candidates; a row of more finds the room in its own log, see below)
+    unsigned long long* hand = reinterpret_cast<unsigned long long*>(hist + SEL_BINS);   // hand_k: a row's candidates
+    double* tail_p = reinterpret_cast<double*>(hand + hand_k);                           // hand_k + 2 * Q_TW
+    double* tail_q = tail_p + hand_k + 2 * Q_TW;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tail_q + hand_k + 2 * Q_TW);            // 2 * Q_MAXSTAGES + 6
     QShared* sh = reinterpret_cast<QShared*>(bars + 2 * Q_MAXSTAGES + 6);
     uint32_t* gbms = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));  // 2 * gbm_words
     uint32_t* pslots = gbms + 2 * size_t(gbm_words);                                     // kPenSlots (only with penalties)
@@ -402,7 +413,17 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             const int li = int(blockIdx.x) + k * int(gridDim.x);
             row = a.row_list ? a.row_list[li] : li;
             keep = true;
-            if (sample && P.top_k && !(P.greedy && P.greedy[row]) && P.top_k[row] > max_k) keep = false;
+            // rows whose top_k is above this launch's limit, and rows whose first threshold would have to be taken deeper
+            // among the first iteration's maxima than the stream warps publish (a large K on a short row)
+            uint32_t K = uint32_t(a.K);
+            if (sample) {
+                const int tk = P.top_k ? P.top_k[row] : 0;
+                const bool greedy = P.greedy && P.greedy[row];
+                if (!greedy && tk > max_k) keep = false;
+                K = greedy ? 1u : ((tk > 0 && tk <= max_k) ? uint32_t(tk) : uint32_t(min(a.level_k, max_k)));
+            }
+            K = K > n ? n : K;
+            if (first_rank(K, n, uint32_t(Q_NS * Q_SQ * VE)) > uint32_t(Q_RANK_MAX)) keep = false;
             // (a listed row stays "pending" until it has its answer: a role that gives up leaves it so, and the multi-pass
             // kernel takes it)
             if (a.out.status) a.out.status[row] = keep ? ROW_PENDING : ROW_LARGE_K;
@@ -510,7 +531,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             }
             const uint32_t K = sl->cfg.K;
             uint32_t what = 2u;
-            if (K <= 64u) {
+            if (K <= uint32_t(Q_SMALL_K)) {
                 what = keep_threshold_small_k(sl, logs + size_t(p) * Q_L, K, a.wait_limit);
             } else {
 #pragma unroll 1
@@ -572,6 +593,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 // candidates wanted: the row's own top_k when it fits, else the first level's
                 uint32_t K = sample ? (greedy ? 1u : ((top_k > 0 && top_k <= uint32_t(max_k)) ? top_k : uint32_t(min(a.level_k, max_k)))) : uint32_t(a.K);
                 c.K = K > n ? n : K;
+                c.rank0 = first_rank(c.K, n, uint32_t(Q_NS * Q_SQ * VE));
                 // Rows whose kept set is closed by their own top_k need no softmax normaliser: every probability the filter
                 // compares is a ratio inside the candidate set, so the row sum cancels.  When the caller does not ask for the
                 // row statistics either, the stream warps skip the exponentials and the tail normalises over the candidates.
@@ -616,7 +638,6 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 sl->cnt = 0;
                 sl->side_cnt = 0;
                 sl->done_warps = 0;
-                for (int w = 0; w < Q_SW; ++w) sl->wbound[w] = 0u;
                 for (int w = Q_SW; w < Q_RED; ++w) sl->red_m[w] = -INFINITY, sl->red_e[w] = -INFINITY, sl->red_s[w] = 0.0;
                 mbar_arrive(&boot_done[p]);
             }
@@ -686,6 +707,92 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             return true;
         };
 
+        // ---- a row's outputs from its candidates (cand[0..kept), padded with zeros up to cap, a power of two; bp, bq:
+        // cap + 2 * NT / 32 doubles each), by a group of NT threads: the first tail warp for rows of up to hand_k
+        // candidates, the whole tail group for larger ones.
+        auto finish_row = [&](auto grp, const QRow& cfg, uint64_t* cand, double* bp, double* bq, uint32_t kept, uint32_t cap, bool presorted,
+                              bool overflow, bool nan_seen, float M, float sum) {
+            constexpr int NT = decltype(grp)::size;
+            const bool greedy = (cfg.flags & QF_GREEDY) != 0;
+            const float inv_t = cfg.inv_t;
+            const bool no_sum = (cfg.flags & QF_NO_SUM) != 0;
+            const int row = cfg.row;
+            const bool first = grp.tid == 0;
+            if (overflow) {
+                // more candidates than the log holds (rows in adversarial order), fewer than K (a guessed first threshold that
+                // was too high), or a NaN in a sum: the multi-pass kernel takes the row
+                if (first) {
+                    a.out.status[row] = ROW_RETRY;
+                    if (nan_seen && a.out.counters) atomicAdd(&a.out.counters[WHIRL_CNT_NAN_ROWS], 1u);
+                }
+            } else if (!sample) {
+                if (first) a.out.status[row] = ROW_DONE;
+                if (!presorted) sort_desc<NT>(grp, cand, cap);
+                const T* xr = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
+#pragma unroll 1
+                for (uint32_t j = grp.tid; j < kept; j += NT) {
+                    const uint32_t id = cand_id(cand[j]);
+                    a.ids[size_t(row) * a.K + j] = int32_t(id) + a.id_offset;
+                    a.vals[size_t(row) * a.K + j] = sizeof(T) == 4 ? reinterpret_cast<const float*>(xr)[id] : bf16_to_f32(reinterpret_cast<const uint16_t*>(xr)[id]);
+                }
+                if (first) a.stats[2 * row] = M, a.stats[2 * row + 1] = sum;
+            } else if (greedy) {
+                if (first) {
+                    const uint32_t tok = kept ? cand_id(cand[0]) : 0;
+                    a.out.token[row] = int32_t(tok);
+                    a.out.status[row] = ROW_DONE;
+                    if (a.out.n_kept) a.out.n_kept[row] = 1;
+                    if (a.out.closed) a.out.closed[row] = 1;
+                    if (a.out.stats) a.out.stats[2 * row] = kept ? float_of_key(cand_key(cand[0])) : -INFINITY, a.out.stats[2 * row + 1] = 0.f;
+                    if (a.out.kept_ids && a.out.kept_cap > 0) a.out.kept_ids[size_t(row) * a.out.kept_cap] = int32_t(tok);
+                    if (a.out.kept_p && a.out.kept_cap > 0) a.out.kept_p[size_t(row) * a.out.kept_cap] = 1.0;
+                }
+            } else {
+                // probabilities, the top-k / top-p / min-p cuts, the draw
+                TailIn in;
+                in.inv_t = inv_t;
+                in.top_k = cfg.top_k;
+                in.top_p = cfg.top_p, in.min_p = cfg.min_p, in.u = cfg.u;
+                if (no_sum) {
+                    // normalise over the candidates themselves: cand[] holds exactly the kept ones, the largest first once sorted
+                    if (!presorted) sort_desc<NT>(grp, cand, cap), presorted = true;
+                    M = float_of_key(cand_key(cand[0]));
+#pragma unroll 1
+                    for (uint32_t i = grp.tid; i < kept; i += NT) bq[i] = f64_exp(double(__fsub_rn(float_of_key(cand_key(cand[i])), M)) * double(inv_t));
+                    grp.sync();
+                    if (grp.tid < 32) {
+                        const double tot = warp_total(bq, kept);
+                        if (first) sh->res.cum = tot;
+                    }
+                    grp.sync();
+                    sum = float(sh->res.cum);
+                    grp.sync();
+                }
+                in.m = M, in.sum = sum, in.cnt = kept, in.cap = cap, in.V = n;
+                in.race = P.race_key != nullptr, in.race_key = cfg.race_key;
+                in.presorted = presorted;
+                sample_tail<NT>(grp, in, cand, bp, bq, &sh->res);
+                const TailOut r = sh->res;
+                if (first) {
+                    a.out.token[row] = int32_t(r.token);
+                    a.out.status[row] = r.status;
+                    if (a.out.n_kept) a.out.n_kept[row] = int32_t(r.n);
+                    if (a.out.closed) a.out.closed[row] = r.closed;
+                    if (a.out.stats) a.out.stats[2 * row] = M, a.out.stats[2 * row + 1] = sum;
+                    if (a.out.counters && r.status == ROW_ESCALATE) atomicAdd(&a.out.counters[0], 1u);
+                    if (a.out.counters && r.status == ROW_OPEN_TAIL) atomicAdd(&a.out.counters[1], 1u);
+                }
+                if (r.status != ROW_ESCALATE) {
+                    const uint32_t nk = min(r.n, uint32_t(max(a.out.kept_cap, 0)));
+#pragma unroll 1
+                    for (uint32_t j = grp.tid; j < nk; j += NT) {
+                        if (a.out.kept_ids) a.out.kept_ids[size_t(row) * a.out.kept_cap + j] = int32_t(cand_id(cand[j]));
+                        if (a.out.kept_p) a.out.kept_p[size_t(row) * a.out.kept_cap + j] = bp[j];
+                    }
+                }
+            }
+        };
+
         // order -1 is the start: nothing to finish, the first two rows' slots to hand out, the first row's table
 #pragma unroll 1
         for (int ord = -1; ord < n_list; ++ord) {
@@ -694,7 +801,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             unsigned long long* log = logs + size_t(p) * Q_L;
             QRow cfg;
             uint32_t kept = 0, cap = 1;
-            bool presorted = false, overflow = false, nan_seen = false;
+            bool presorted = false, overflow = false, nan_seen = false, big_done = false;
             float M = -INFINITY, sum = 0.f;
             if (ord >= 0) {
                 cfg = sl->cfg;
@@ -724,7 +831,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                                 break;
                             }
                             const uint32_t c = ldv_u32(&sl->cnt) & 0x7fffffffu;
-                            if (!lazy && c >= K && c >= rf_last[p] + step && c <= uint32_t(Q_L)) {
+                            if (!lazy && K > uint32_t(Q_SMALL_K) && c >= K && c >= rf_last[p] + step && c <= uint32_t(Q_L)) {
                                 what = 1u;
                                 break;
                             }
@@ -856,7 +963,28 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     const double term = (lane < n_red && mw != -INFINITY) ? sl->red_s[lane] * exp2(double(sl->red_e[lane]) - double(M) * cexp) : 0.0;
                     sum = float(warp_sum(term));
                 }
-                if (!overflow) {
+                // (a guessed first threshold that left fewer than K candidates: the row is done again)
+                if (K > uint32_t(Q_SMALL_K) && total < K && total < n) overflow = true;
+                big_done = K > uint32_t(hand_k) && !overflow;
+                if (big_done) {
+                    // More candidates than the hand holds: the K best of the log go to the select scratch, the whole group
+                    // sorts them and draws, with the probabilities in the row's log (which nobody reads any more).
+                    unsigned long long* list = reinterpret_cast<unsigned long long*>(hist);  // SEL_BINS / 2 entries
+                    static_assert(SEL_BINS / 2 >= kSinglePassMaxK && size_t(Q_L) * 8 >= 2 * size_t(kSinglePassMaxK + 2 * Q_TW) * 8, "room for a large-K row");
+                    const unsigned long long kth = nlog > K ? select_kth<Q_TT>(g, log, nlog, K, hist, &sh->sel) : 0ull;
+                    g.sync();
+                    write_survivors<Q_TT>(g, log, nlog, kth, list, uint32_t(SEL_BINS / 2), &sh->sel);
+                    uint32_t bk = sh->sel.wcnt < uint32_t(SEL_BINS / 2) ? sh->sel.wcnt : uint32_t(SEL_BINS / 2);
+                    uint32_t bcap = 1;
+                    while (bcap < bk) bcap <<= 1;
+                    g.sync();
+                    for (uint32_t i = bk + g.tid; i < bcap; i += Q_TT) list[i] = 0ull;
+                    g.sync();
+                    double* bp = reinterpret_cast<double*>(log);
+                    finish_row(g, cfg, reinterpret_cast<uint64_t*>(list), bp, bp + bcap + 2 * Q_TW, bk, bcap, false, false, false, M, sum);
+                    g.sync();
+                    for (uint32_t i = g.tid; i < uint32_t(Q_L); i += Q_TT) log[i] = 0ull;
+                } else if (!overflow) {
                     // Most of the log was appended under an earlier, looser threshold: only entries at or above the current one
                     // can be among the K best (at least K of them are).  Few survive, so rank them against each other: the
                     // rank is the position in the sorted order.
@@ -876,8 +1004,8 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         presorted = true;
                     } else if (nlog > K) {
                         const unsigned long long kth = select_kth<Q_TT>(g, log, nlog, K, hist, &sh->sel);
-                        write_survivors<Q_TT>(g, log, nlog, kth, hand, uint32_t(max_k), &sh->sel);
-                        kept = sh->sel.wcnt < uint32_t(max_k) ? sh->sel.wcnt : uint32_t(max_k);
+                        write_survivors<Q_TT>(g, log, nlog, kth, hand, uint32_t(hand_k), &sh->sel);
+                        kept = sh->sel.wcnt < uint32_t(hand_k) ? sh->sel.wcnt : uint32_t(hand_k);
                     } else {
                         for (uint32_t i = g.tid; i < nlog; i += Q_TT) hand[i] = log[i];
                         kept = nlog;
@@ -909,85 +1037,10 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
 #ifdef WB_PROF
                 if (g.tid == 32) atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 16) + 4, (unsigned long long)(clock64() - tp0));
 #endif
-            } else if (ord >= 0) {
+            } else if (ord >= 0 && !big_done) {
                 // ---- the first tail warp: the row's outputs
                 PROF_T0(td0);
-                const bool greedy = (cfg.flags & QF_GREEDY) != 0;
-                const float inv_t = cfg.inv_t;
-                const bool no_sum = (cfg.flags & QF_NO_SUM) != 0;
-                const int row = cfg.row;
-                const Group<32> gw{lane, 0};
-                if (overflow) {
-                    // more candidates than the log holds (rows in adversarial order), or a NaN in a sum: the multi-pass
-                    // kernel takes the row
-                    if (lane == 0) {
-                        a.out.status[row] = ROW_RETRY;
-                        if (nan_seen && a.out.counters) atomicAdd(&a.out.counters[WHIRL_CNT_NAN_ROWS], 1u);
-                    }
-                } else if (!sample) {
-                    if (lane == 0) a.out.status[row] = ROW_DONE;
-                    if (!presorted) sort_desc<32>(gw, reinterpret_cast<uint64_t*>(hand), cap);
-                    const T* xr = reinterpret_cast<const T*>(a.x) + size_t(row) * n;
-#pragma unroll 1
-                    for (uint32_t j = lane; j < kept; j += 32) {
-                        const uint32_t id = cand_id(hand[j]);
-                        a.ids[size_t(row) * a.K + j] = int32_t(id) + a.id_offset;
-                        a.vals[size_t(row) * a.K + j] = sizeof(T) == 4 ? reinterpret_cast<const float*>(xr)[id] : bf16_to_f32(reinterpret_cast<const uint16_t*>(xr)[id]);
-                    }
-                    if (lane == 0) a.stats[2 * row] = M, a.stats[2 * row + 1] = sum;
-                } else if (greedy) {
-                    if (lane == 0) {
-                        const uint32_t tok = kept ? cand_id(hand[0]) : 0;
-                        a.out.token[row] = int32_t(tok);
-                        a.out.status[row] = ROW_DONE;
-                        if (a.out.n_kept) a.out.n_kept[row] = 1;
-                        if (a.out.closed) a.out.closed[row] = 1;
-                        if (a.out.stats) a.out.stats[2 * row] = kept ? float_of_key(cand_key(hand[0])) : -INFINITY, a.out.stats[2 * row + 1] = 0.f;
-                        if (a.out.kept_ids && a.out.kept_cap > 0) a.out.kept_ids[size_t(row) * a.out.kept_cap] = int32_t(tok);
-                        if (a.out.kept_p && a.out.kept_cap > 0) a.out.kept_p[size_t(row) * a.out.kept_cap] = 1.0;
-                    }
-                } else {
-                    // probabilities, the top-k / top-p / min-p cuts, the draw
-                    TailIn in;
-                    in.inv_t = inv_t;
-                    in.top_k = cfg.top_k;
-                    in.top_p = cfg.top_p, in.min_p = cfg.min_p, in.u = cfg.u;
-                    if (no_sum) {
-                        // normalise over the candidates themselves (sorted or not, hand[] holds exactly the kept ones)
-                        unsigned long long top = 0ull;
-#pragma unroll 1
-                        for (uint32_t i = lane; i < kept; i += 32) top = hand[i] > top ? hand[i] : top;
-                        top = warp_max(uint64_t(top));
-                        M = float_of_key(cand_key(top));
-#pragma unroll 1
-                        for (uint32_t i = lane; i < kept; i += 32) tail_q[i] = f64_exp(double(__fsub_rn(float_of_key(cand_key(hand[i])), M)) * double(inv_t));
-                        __syncwarp();
-                        sum = float(warp_total(tail_q, kept));
-                        __syncwarp();
-                    }
-                    in.m = M, in.sum = sum, in.cnt = kept, in.cap = cap, in.V = n;
-                    in.race = P.race_key != nullptr, in.race_key = cfg.race_key;
-                    in.presorted = presorted;
-                    sample_tail<32>(gw, in, reinterpret_cast<uint64_t*>(hand), tail_p, tail_q, &sh->res);
-                    const TailOut r = sh->res;
-                    if (lane == 0) {
-                        a.out.token[row] = int32_t(r.token);
-                        a.out.status[row] = r.status;
-                        if (a.out.n_kept) a.out.n_kept[row] = int32_t(r.n);
-                        if (a.out.closed) a.out.closed[row] = r.closed;
-                        if (a.out.stats) a.out.stats[2 * row] = M, a.out.stats[2 * row + 1] = sum;
-                        if (a.out.counters && r.status == ROW_ESCALATE) atomicAdd(&a.out.counters[0], 1u);
-                        if (a.out.counters && r.status == ROW_OPEN_TAIL) atomicAdd(&a.out.counters[1], 1u);
-                    }
-                    if (r.status != ROW_ESCALATE) {
-                        const uint32_t nk = min(r.n, uint32_t(max(a.out.kept_cap, 0)));
-#pragma unroll 1
-                        for (uint32_t j = lane; j < nk; j += 32) {
-                            if (a.out.kept_ids) a.out.kept_ids[size_t(row) * a.out.kept_cap + j] = int32_t(cand_id(hand[j]));
-                            if (a.out.kept_p) a.out.kept_p[size_t(row) * a.out.kept_cap + j] = tail_p[j];
-                        }
-                    }
-                }
+                finish_row(Group<32>{lane, 0}, cfg, reinterpret_cast<uint64_t*>(hand), tail_p, tail_q, kept, cap, presorted, overflow, nan_seen, M, sum);
                 PROF_ADD(3, td0);
             }
             g.sync();
@@ -1046,28 +1099,8 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
         float m1 = -INFINITY, m2 = -INFINITY, e_t = 0.f, s_t = 0.f;
         uint32_t tau_key = 0u;  // the threshold's ordering key as this warp last saw it (0: none)
         float tau_f = -INFINITY;
-        const uint32_t rth = (sl->cfg.K + Q_SW - 1) / Q_SW;  // each warp's share of the K candidates
         bool st_fail = false;
         const volatile uint32_t* tau_hi = reinterpret_cast<const volatile uint32_t*>(&sl->tau) + 1;
-
-        // this warp's bound: the rth largest of its 64 lane maxima (0: none)
-        auto own_bound = [&]() -> uint32_t {
-            if (rth > 64) return 0u;
-            uint32_t kv[2] = {m1 == -INFINITY ? 0u : key_of(m1), m2 == -INFINITY ? 0u : key_of(m2)};
-            return warp_rth_largest<2>(kv, rth);
-        };
-        // a fresh bound from this warp's maxima; the other warps' entries may be older: any of their bounds for this row is valid
-        auto renew = [&]() {
-            const uint32_t kr = own_bound();
-            if (lane == 0) sl->wbound[sw] = kr;
-            __syncwarp();
-            const uint32_t kmin = __reduce_min_sync(0xffffffffu, lane < Q_SW ? ldv_u32(&sl->wbound[lane]) : 0xffffffffu);
-            // (a plain compare and store: a lost update only leaves the threshold at another valid, lower bound)
-            if (lane == 0) {
-                const unsigned long long cnd = (unsigned long long)kmin << 32;
-                if (cnd > ldv_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = cnd;
-            }
-        };
 
         // The row's iterations, in one of three forms so that the common rows run a short loop: PLAIN (no normaliser, no
         // penalties), LAZY (no normaliser, penalties that only lower a logit), GENERAL (the rest).
@@ -1075,8 +1108,6 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
         auto run_row = [&](auto mode_tag) {
             constexpr int MODE = decltype(mode_tag)::value;
             constexpr int NW = 2 * Q_NS;  // 128-bit words per thread and iteration
-            // (a small-K row's threshold is kept by the keeper warp: the stream warps name no further bounds for it)
-            uint32_t next_renew = sl->cfg.K <= 64u ? 0xffffffffu : 2u;
 #pragma unroll 1
             for (uint32_t iter = 0; iter < n_iter; ++iter) {
                 const uint32_t c = Q_NS * iter;
@@ -1209,55 +1240,47 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
 #ifdef WB_PROF
                     const long long th0 = clock64();
 #endif
-                    const bool merged = sl->cfg.K <= 64u;
-                    uint32_t kr;
-                    if (merged) {
-                        // Small K: the warp publishes its Q_TOP largest lane maxima.  The K-th largest of all warps'
-                        // published keys is a valid bound (that many logits of the row lie at or above it), and close to the
-                        // K-th largest logit read so far; the warp's own rth largest, taken on the way, keeps the plain bound
-                        // (the smallest of the warps' rth largest) at hand as well.
-                        uint32_t kv[2] = {m1 == -INFINITY ? 0u : key_of(m1), m2 == -INFINITY ? 0u : key_of(m2)};
+                    // The warp publishes its largest lane maxima, in descending order: 8 for a small-K row, Q_TOP otherwise.
+                    const uint32_t rank0 = sl->cfg.rank0;
+                    {
+                        const int ntop = sl->cfg.K <= uint32_t(Q_SMALL_K) ? 8 : Q_TOP;
+                        uint32_t kv0 = m1 == -INFINITY ? 0u : key_of(m1), kv1 = m2 == -INFINITY ? 0u : key_of(m2);
                         uint32_t mine = 0u;
-                        kr = 0u;
-#pragma unroll
-                        for (int t = 0; t < Q_TOP; ++t) {
-                            const uint32_t mx = kv[0] > kv[1] ? kv[0] : kv[1];
+#pragma unroll 1
+                        for (int t = 0; t < ntop; ++t) {
+                            const uint32_t mx = kv0 > kv1 ? kv0 : kv1;
                             const uint32_t top = __reduce_max_sync(0xffffffffu, mx);
                             if (lane == t) mine = top;
-                            if (uint32_t(t) + 1u == rth) kr = top;
                             const uint32_t holders = __ballot_sync(0xffffffffu, mx == top && top != 0u);
                             if (lane == __ffs(int(holders)) - 1) {
-                                if (kv[0] == top) kv[0] = 0u;
-                                else kv[1] = 0u;
+                                if (kv0 == top) kv0 = 0u;
+                                else kv1 = 0u;
                             }
                         }
                         if (lane < Q_TOP) sl->wtop[sw * Q_TOP + lane] = mine;
                         __syncwarp();
-                    } else {
-                        kr = own_bound();
                     }
-                    if (lane == 0) {
-                        sl->wbound[sw] = kr;
-                        mbar_arrive(&head_done[p]);
-                    }
+                    if (lane == 0) mbar_arrive(&head_done[p]);
                     if (!mbar_wait(&head_done[p], (ord >> 1) & 1, a.wait_limit)) {
                         if (lane == 0) atomicExch(a.err, 11u);
                         st_fail = true;
                         return;
                     }
-                    uint32_t kmin = __reduce_min_sync(0xffffffffu, lane < Q_SW ? ldv_u32(&sl->wbound[lane]) : 0xffffffffu);
-                    if (merged) {
-                        // the largest key prefix (20 bits) that at least K of the published keys reach
-                        const uint4 q = *reinterpret_cast<const uint4*>(&sl->wtop[4 * lane]);  // (written before the meeting's barrier)
-                        const uint32_t K = sl->cfg.K;
-                        uint32_t t = 0u;
+                    // The row's first threshold: the largest key prefix (20 bits) that at least rank0 of the published keys
+                    // reach.  That many logits of the row lie at or above it.  For a small-K row rank0 is K and this is a bound
+                    // on the K-th largest logit of the row, close to the K-th largest read so far; for a larger K rank0 is
+                    // first_rank's guess.
+                    uint32_t kmin = 0u;
+                    {
+                        const uint4 qa = *reinterpret_cast<const uint4*>(&sl->wtop[8 * lane]);  // (written before the meeting's barrier)
+                        const uint4 qb = *reinterpret_cast<const uint4*>(&sl->wtop[8 * lane + 4]);
 #pragma unroll 1
                         for (int b = 31; b >= 12; --b) {
-                            const uint32_t cand = t | (1u << b);
-                            const uint32_t c = (q.x >= cand ? 1u : 0u) + (q.y >= cand ? 1u : 0u) + (q.z >= cand ? 1u : 0u) + (q.w >= cand ? 1u : 0u);
-                            if (__reduce_add_sync(0xffffffffu, c) >= K) t = cand;
+                            const uint32_t cand = kmin | (1u << b);
+                            const uint32_t c = (qa.x >= cand ? 1u : 0u) + (qa.y >= cand ? 1u : 0u) + (qa.z >= cand ? 1u : 0u) + (qa.w >= cand ? 1u : 0u) +
+                                               (qb.x >= cand ? 1u : 0u) + (qb.y >= cand ? 1u : 0u) + (qb.z >= cand ? 1u : 0u) + (qb.w >= cand ? 1u : 0u);
+                            if (__reduce_add_sync(0xffffffffu, c) >= rank0) kmin = cand;
                         }
-                        kmin = t > kmin ? t : kmin;
                     }
                     if (kmin) tau_key = kmin, tau_f = float_of_key(kmin);
                     if (sw == 0 && lane == 0) {
@@ -1307,11 +1330,6 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         ++pos;
                     }
                 }
-                // a fresh bound each time the part of the row seen has grown by half
-                if (iter + 1 == next_renew && iter + 1 < n_iter) {
-                    renew();
-                    next_renew += WB_RENEW_STEP;
-                }
             }
         };
         if ((row_flags & (QF_NO_SUM | QF_PEN)) == QF_NO_SUM) run_row(std::integral_constant<int, SM_PLAIN>{});
@@ -1355,8 +1373,8 @@ static int single_pass_gbm_words(const SelectArgs& a, int dtype) {
     return pen ? ((a.n / ve + 2 * Q_SQ - 1) / (2 * Q_SQ)) * Q_SW * 4 : 0;
 }
 
-static size_t single_pass_fixed_smem(int gbm_words, int max_k, bool pen) {
-    return size_t(2) * Q_L * 8 + SEL_BINS * 4 + size_t(max_k) * 8 + 2 * (size_t(max_k) + 2 * Q_TW) * 8 + (2 * Q_MAXSTAGES + 6) * 8 +
+static size_t single_pass_fixed_smem(int gbm_words, int hand_k, bool pen) {
+    return size_t(2) * Q_L * 8 + SEL_BINS * 4 + size_t(hand_k) * 8 + 2 * (size_t(hand_k) + 2 * Q_TW) * 8 + (2 * Q_MAXSTAGES + 6) * 8 +
            sizeof(QShared) + 16 + size_t(2) * gbm_words * 4 + (pen ? size_t(kPenSlots) * 4 : 0) + 128;
 }
 
@@ -1367,11 +1385,21 @@ bool single_pass_supported(const SelectArgs& a, int dtype) {
     // on the K-th largest comes out of the first meeting and the candidate log would take the whole row: the multi-pass
     // kernel serves such rows (vocabularies below 8192 / 16384 tokens).
     if (size_t(a.n) * es < size_t(Q_NS) * Q_SB) return false;
-    if (a.mode == MODE_TOPK && a.K > kSinglePassMaxK) return false;
+    if (a.mode == MODE_TOPK) {
+        // (the rule of first_rank: a large K on a short row would need a first threshold deeper than the stream warps publish)
+        if (a.K > kSinglePassMaxK) return false;
+        const uint32_t K = uint32_t(a.K) > uint32_t(a.n) ? uint32_t(a.n) : uint32_t(a.K);
+        if (K > uint32_t(Q_SMALL_K)) {
+            const uint32_t it0 = uint32_t(Q_NS) * Q_SB / uint32_t(es);
+            const float x = float(K) * float(it0 < uint32_t(a.n) ? it0 : uint32_t(a.n)) / float(a.n);
+            const float r = 0.5f * (3.5f + sqrtf(12.25f + 4.f * x));
+            if (uint32_t(ceilf(r * r)) > uint32_t(Q_RANK_MAX)) return false;
+        }
+    }
     if (a.mode == MODE_DRAFT) return false;
     if (a.rows > Q_MAXR * 100) return false;  // (more rows per CTA than its row list holds: far beyond any batch of logits)
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
-    return single_pass_fixed_smem(single_pass_gbm_words(a, dtype), kSinglePassMaxK, pen) + 3 * size_t(Q_SB) <= 232448;
+    return single_pass_fixed_smem(single_pass_gbm_words(a, dtype), kSinglePassHandK, pen) + 3 * size_t(Q_SB) <= 232448;
 }
 
 cudaError_t single_pass_launch(const SelectArgs& args, int dtype, int sm_count, cudaStream_t st) {
@@ -1379,8 +1407,8 @@ cudaError_t single_pass_launch(const SelectArgs& args, int dtype, int sm_count, 
     if (a.wait_limit == 0) a.wait_limit = kWaitLimit;  // the budget of every wait inside the kernel
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
     const int gbm_words = single_pass_gbm_words(a, dtype);
-    const int max_k = kSinglePassMaxK;
-    const size_t fixed = single_pass_fixed_smem(gbm_words, max_k, pen);
+    const int max_k = kSinglePassMaxK, hand_k = kSinglePassHandK;
+    const size_t fixed = single_pass_fixed_smem(gbm_words, hand_k, pen);
     int stages = int((232448 - fixed) / Q_SB);
     if (stages > Q_MAXSTAGES) stages = Q_MAXSTAGES;
     if (stages < 3) return cudaErrorInvalidConfiguration;
@@ -1392,11 +1420,11 @@ cudaError_t single_pass_launch(const SelectArgs& args, int dtype, int sm_count, 
     if (dtype == 0) {
         const cudaError_t e = cudaFuncSetAttribute(single_pass_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        single_pass_kernel<float><<<grid, Q_THREADS, smem, st>>>(a, stages, gbm_words, max_k);
+        single_pass_kernel<float><<<grid, Q_THREADS, smem, st>>>(a, stages, gbm_words, max_k, hand_k);
     } else {
         const cudaError_t e = cudaFuncSetAttribute(single_pass_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        single_pass_kernel<uint16_t><<<grid, Q_THREADS, smem, st>>>(a, stages, gbm_words, max_k);
+        single_pass_kernel<uint16_t><<<grid, Q_THREADS, smem, st>>>(a, stages, gbm_words, max_k, hand_k);
     }
     return cudaGetLastError();
 }
