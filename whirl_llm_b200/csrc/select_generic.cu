@@ -448,6 +448,7 @@ __device__ int select_row(const SelectArgs& a, int row, int level_k, int cap_max
     double* q = p + size_t(cap_max) + 2 * GT / 32;
     // the tail's race scratch sits at p + in.cap; keep it inside this row's slice
     in.presorted = 0;
+    in.want_p = a.out.kept_p != nullptr && a.out.kept_cap > 0;
     sample_tail<GT>(g, in, cand, p, q, &sh->res);
     TailOut r = sh->res;
     if (r.status == ROW_OPEN_TAIL) {

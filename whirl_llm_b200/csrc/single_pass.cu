@@ -771,6 +771,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 in.m = M, in.sum = sum, in.cnt = kept, in.cap = cap, in.V = n;
                 in.race = P.race_key != nullptr, in.race_key = cfg.race_key;
                 in.presorted = presorted;
+                in.want_p = a.out.kept_p != nullptr && a.out.kept_cap > 0;
                 sample_tail<NT>(grp, in, cand, bp, bq, &sh->res);
                 const TailOut r = sh->res;
                 if (first) {

@@ -29,6 +29,7 @@ struct TailIn {
     uint64_t race_key;  // spec::raceBase(seed, pos) when race != 0
     int32_t race;
     int32_t presorted;  // cand[0..cnt) is already in descending order
+    int32_t want_p;     // the caller reads p[] afterwards: leave the kept probabilities renormalised there
 };
 struct TailOut {
     int32_t status;
@@ -156,20 +157,16 @@ __device__ __noinline__ void sample_tail(const Group<NT>& g, const TailIn& in, u
     }
     g.sync();
     if (res->status == ROW_ESCALATE) return;
-    if (in.top_p < 1.0) {
-        const double z = res->cum;
-        const uint32_t n0 = res->n;
-#pragma unroll 1
-        for (uint32_t i = g.tid; i < n0; i += NT) q[i] = f64_div(p[i], z);
-        g.sync();
-    }
+    // (The host filter divides every probability by z and walks until the running sum reaches top_p; here the walk runs over
+    // the probabilities as they are, up to top_p * z: one multiplication instead of a division per candidate.)
+    const double z_top = res->cum;
     // ---- top-p cut, min-p cut, the renormaliser (sampler.cpp:50-74)
     if (g.tid < 32) {
         uint32_t n = res->n;
         bool closed = res->closed != 0, esc = false;
         if (in.top_p < 1.0) {
             double walked;
-            const uint32_t j = warp_first_reach<false>(q, n, in.top_p, &walked);
+            const uint32_t j = warp_first_reach<false>(p, n, in.top_p * z_top, &walked);
             if (j < n) n = j + 1, closed = true;
             else if (!closed) esc = true;
         }
@@ -198,7 +195,10 @@ __device__ __noinline__ void sample_tail(const Group<NT>& g, const TailIn& in, u
     if (res->status == ROW_ESCALATE) return;
     const uint32_t n = res->n;
     const bool closed = res->closed != 0;
-    if (closed) {
+    // A closed set is renormalised by z.  Only a caller that reads the probabilities needs them divided; the draw itself
+    // compares against u * z (and the race's argmin of E / p does not change when every p is scaled alike).
+    const double z_draw = (closed && !in.want_p) ? res->cum : 1.0;
+    if (closed && in.want_p) {
         const double z = res->cum;
 #pragma unroll 1
         for (uint32_t i = g.tid; i < n; i += NT) p[i] = f64_div(p[i], z);
@@ -255,7 +255,7 @@ __device__ __noinline__ void sample_tail(const Group<NT>& g, const TailIn& in, u
     if (g.tid < 32) {
         // inverse CDF over the kept candidates (sampleRow with no excluded token): the first i with cum > u
         double walked;
-        const uint32_t i = warp_first_reach<true>(p, n, in.u, &walked);
+        const uint32_t i = warp_first_reach<true>(p, n, in.u * z_draw, &walked);
         if (g.tid == 0) {
             const bool hit = i < n;
             res->token = cand_id(cand[hit ? i : (n ? n - 1 : 0)]);  // closed and not hit: the last candidate is the fallback
