@@ -283,6 +283,34 @@ __device__ __forceinline__ void join_word(JoinCtx& c, uint32_t wq, uint4 w) {
     }
 }
 
+// The largest of N floats by three-input maxima (max.f32 with three operands, sm_100: comparisons and maxima share the
+// half-rate ALU pipe, which is what the stream loop runs out of first).  Like fmaxf, it skips NaN.
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+template <int N>
+__device__ __forceinline__ float max_of(const float* v) {
+    float t[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) t[i] = v[i];
+    int n = N;
+#pragma unroll
+    for (int lvl = 0; lvl < 4; ++lvl) {  // (3^4 >= 32)
+        const int m = (n + 2) / 3;
+#pragma unroll
+        for (int i = 0; i < (N + 2) / 3; ++i) {
+            if (i < m) {
+                const int b = 3 * i;
+                t[i] = b + 2 < n ? fmax3(t[b], t[b + 1], t[b + 2]) : (b + 1 < n ? fmaxf(t[b], t[b + 1]) : t[b]);
+            }
+        }
+        n = m;
+    }
+    return t[0];
+}
+
 // ---- the small-K threshold keeper (a warp of its own, while a row streams)
 // 32 ordering keys, one per lane, into descending order over the lanes (a bitonic network of shuffles).
 __device__ __forceinline__ uint32_t warp_sort_desc(uint32_t x, int lane) {
@@ -1191,32 +1219,15 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         for (int e = 0; e < 4; ++e) x[2 * e] = __uint_as_float(w4[e] << 16), x[2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
                     }
                 }
-                // maxima of the words; fmaxf skips NaN, so a NaN logit never raises a maximum
-                float qm[NW];
-#pragma unroll
-                for (int i = 0; i < NW; ++i) {
-                    float mx = xv[i * VE];
-#pragma unroll
-                    for (int e = 1; e < VE; ++e) mx = fmaxf(mx, xv[i * VE + e]);
-                    qm[i] = mx;
-                }
+                // the iteration's largest logit (a NaN logit never raises a maximum)
+                const float vm = max_of<NW * VE>(xv);
                 // Every loaded register has been consumed, so the shared-memory reads have completed (instructions issue in
-                // order and the fmaxf had to wait for the data): only now may the producer overwrite the stages.
+                // order and the maximum had to wait for the data): only now may the producer overwrite the stages.
                 __syncwarp();
                 if (lane == 0) {
 #pragma unroll
                     for (int h = 0; h < Q_NS; ++h)
                         if (whole || c + uint32_t(h) < n_chunks) mbar_arrive(&empty[st_ring[h]]);
-                }
-                float vm = qm[0];
-#pragma unroll
-                for (int i = 1; i < NW; ++i) vm = fmaxf(vm, qm[i]);
-                // what counts for this lane's bounds: not the marked words (their raw logits are not the row's)
-                float vb = vm;
-                if (lazy) {
-                    vb = -INFINITY;
-#pragma unroll
-                    for (int i = 0; i < NW; ++i) vb = fmaxf(vb, ((marked >> i) & 1u) ? -INFINITY : qm[i]);
                 }
                 if (!no_sum) {
                     if (vm > m1) {
@@ -1233,8 +1244,20 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         s_t += (acc[0] + acc[1]) + (acc[2] + acc[3]);
                     }
                 }
-                m2 = fmaxf(m2, fminf(m1, vb));
-                m1 = fmaxf(m1, vb);
+                // The lane's two largest iteration maxima: what the first threshold is made of (iteration 0), and the running
+                // maximum of the sum (the GENERAL form).  For the bounds the marked words do not count: their raw logits are
+                // not the row's.
+                if (MODE == SM_GENERAL || iter == 0) {
+                    float vb = vm;
+                    if (lazy) {
+                        vb = -INFINITY;
+#pragma unroll
+                        for (int i = 0; i < NW; ++i)
+                            if (!((marked >> i) & 1u)) vb = fmaxf(vb, max_of<VE>(xv + i * VE));
+                    }
+                    m2 = fmaxf(m2, fminf(m1, vb));
+                    m1 = fmaxf(m1, vb);
+                }
                 if (iter == 0) {
                     // The row's first threshold: every warp names its bound from what it has just read and the warps meet (their
                     // one meeting per row); what this lane read is tested against the agreed bound below, from its registers.
