@@ -1183,7 +1183,9 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 }
                 // words that hold a history token (one 128-bit load gives the thread its four bits)
                 uint32_t marked = 0;  // bit i: word i
-                if (pen_on) {
+                // (a row that only marks log entries needs the bits for its bounds in iteration 0; later it looks them up when
+                // it has something to log)
+                if (pen_on && (!lazy || iter == 0)) {
                     const uint4 mw = *reinterpret_cast<const uint4*>(gbm + ((iter * Q_SW + uint32_t(sw)) << 2));
                     marked = ((mw.x >> lane) & 1u) | (((mw.y >> lane) & 1u) << 1) | (((mw.z >> lane) & 1u) << 2) | (((mw.w >> lane) & 1u) << 3);
                     if (!lazy) {
@@ -1323,6 +1325,10 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     ++sp_visits;
 #endif
                     // Some lane holds logits that may beat the threshold.
+                    if (lazy && iter != 0) {
+                        const uint4 mw = *reinterpret_cast<const uint4*>(gbm + ((iter * Q_SW + uint32_t(sw)) << 2));
+                        marked = ((mw.x >> lane) & 1u) | (((mw.y >> lane) & 1u) << 1) | (((mw.z >> lane) & 1u) << 2) | (((mw.w >> lane) & 1u) << 3);
+                    }
                     uint32_t hm = 0;  // bit j: this lane's logit j is at or above the threshold
 #pragma unroll
                     for (int j = 0; j < NW * VE; ++j) hm |= (xv[j] >= tau_f ? 1u : 0u) << j;
