@@ -360,9 +360,6 @@ int whirl_check(const void* ws, size_t ws_bytes, int rows, void* stream, uint32_
 
 void whirl_test_waits(uint32_t wait_us, int lose_copy) { g_wait_limit = wait_us, g_lose_copy = lose_copy ? 1u : 0u; }
 
-#ifdef WB_PROF
-size_t whirl_debug_err_offset(int rows, int n) { return ws_layout(rows, n).off_err; }
-#endif
 
 int whirl_draft_sample_rows(const void* x, int dtype, int rows, int n, int* ctl_all, const int* area, int r, const int* map,
                             const whirl_dsamp_args* da, int* qbuf, void* stream) {

@@ -1,36 +1,47 @@
 // The single-pass fused sampler: every logits row is read from HBM once, through a ring of shared-memory stages
 // filled by bulk async copies (TMA, cp.async.bulk + mbarrier).
 //
-// One persistent CTA per SM, three roles that never meet at a CTA-wide barrier while rows stream:
-//   producer (1 thread)  bulk copies of 16 KiB stages of the CTA's rows into the ring, running ahead across row boundaries.
-//   stream warps (16)    consume the stages, two per iteration: per-lane running maxima (the two largest iteration maxima;
-//                        and, where the row needs its softmax normaliser, a running sum of exponentials) and a threshold
-//                        test on the maximum of what the lane just read.  The few logits at or above the threshold are
-//                        appended to the row's candidate log.  The threshold comes from the warps themselves: each names
-//                        the r-th largest of its 64 lane maxima, r = ceil(K / 16), and the smallest of the 16 warps' values
-//                        is reached by at least K logits of the row.  The warps agree on the first one after their first
-//                        iteration (its logits are still in registers and are tested afterwards: the one meeting per row)
-//                        and renew it, without meeting, each time the part of the row seen has grown by half.
-//   tail group (8 warps) when a row is through: its exact K best, ranked; then one warp does top-k / top-p / min-p in f64,
-//                        the draw and the row's outputs, while the others fetch the parameters of the row after the next
-//                        and prepare the penalties of the rows to come.
+// One persistent CTA per SM, four roles that never meet at a CTA-wide barrier while rows stream:
+//   producer (1 thread)   bulk copies of 16 KiB stages of the CTA's rows into the ring, running ahead across row
+//                         boundaries.
+//   stream warps (16)     consume the stages, two per iteration: the largest logit of what the lane just read (and, where
+//                         the row needs its softmax normaliser, a running sum of exponentials), and a threshold test on
+//                         it.  The few logits at or above the threshold are appended to the row's candidate log.
+//   threshold keeper      (1 warp) for rows that keep at most 64 candidates: follows the log while it fills, holds the 64
+//                         largest keys seen in sorted order (bitonic merges of 32-key batches) and raises the threshold to
+//                         the K-th of them.
+//   tail group (8 warps)  when a row is through: its exact K best, ranked; top-k / top-p / min-p in f64, the draw and the
+//                         row's outputs (one warp for rows of up to 256 candidates, while the others fetch the parameters
+//                         of the row after the next and prepare its penalties; the whole group for larger rows).
 // The roles work on alternating row slots (two logs, two word maps), so the tail of one row overlaps the streaming of the
 // next.
 //
-// Why a threshold from partial data is exact: an element is dropped only when it is below a value that at least K
-// elements of the same row reach, so the K best are always in the log; the final select over the log is exact.
+// Thresholds.  An element is dropped only when it is below a value that at least K elements of the same row reach, so
+// the K best are always in the log and the final select over the log is exact.
+//   * First threshold (the stream warps' one meeting per row, after their first iteration, whose logits are still in
+//     registers and are tested afterwards): every warp publishes its largest lane maxima in descending order, and every
+//     warp finds the largest 20-bit key prefix that rank0 of the published keys reach.  For K <= 64, rank0 = K: a valid
+//     bound, close to the K-th largest logit read so far.  For larger K, rank0 is a guess (first_rank): the rank that,
+//     scaled from the first iteration to the whole row, leaves K candidates 3.5 standard deviations below the expected
+//     count.  A row whose guess leaves fewer than K logged candidates is done again by the multi-pass kernel; a row
+//     whose K on its length would need a rank beyond what the warps publish goes there from the start.
+//   * Later thresholds: the keeper warp (K <= 64); for larger K the tail group, which selects the exact K-th largest of
+//     the log when the log has grown enough (rows without marked entries).
 //
 // Penalties.  A raw logit of a history token must count nowhere.  The tail group builds, a row ahead, a bit map of the
-// 16-byte words (4 f32 / 8 bf16 logits) that hold a history token, and, while the row streams, the table of the row's
-// distinct history tokens with their counts (open addressing, warp-aggregated inserts).  The stream warps test one bit per
-// word (one broadcast shared-memory load per warp and word).  Nothing of a row is ever fetched a second time from global
-// memory: random 16-byte reads at that rate are more than the memory can serve while it streams.
+// 16-byte words (4 f32 / 8 bf16 logits) that hold a history token.  Nothing of a row is ever fetched a second time from
+// global memory: random 16-byte reads at that rate are more than the memory can serve while it streams.
 //   * A row that needs no normaliser and whose penalties can only lower a logit (the usual case): a word with a history
 //     token counts for no bound, and one of its logits is looked at only when it passes the threshold raw; it is then
-//     logged with a mark, and the tail group applies the penalty to the few marked entries before it ranks the log.
+//     logged with a mark, and the tail group applies the penalty to the few marked entries (their counts come from a
+//     scan of the history) before it ranks the log.
 //   * Any other penalised row: the stream warps put the marked words aside (from their registers into a side buffer in
-//     global memory that stays in L2) and see -inf instead; the tail group brings them in at the end of the row, history
-//     tokens with their penalty, the others as they are.
+//     global memory that stays in L2) and see -inf instead; the tail group, which has built the table of the row's
+//     distinct history tokens with their counts meanwhile, brings them in at the end of the row, history tokens with
+//     their penalty, the others as they are.
+//
+// Every wait has a budget (SelectArgs::wait_limit).  A role whose wait runs out records which in the error word and
+// returns; the rows it leaves without an answer keep the status "pending" and are done by the multi-pass kernel.
 //
 // It replaces the reference's topk_rows kernel (seven passes over the row, kernels/shared/sample_cand_topk_rows.h:11-98),
 // the candidate download, and the host filter and draw (src/sampling/sampler.cpp:15-147).
@@ -383,13 +394,6 @@ static __device__ __noinline__ uint32_t keep_threshold_small_k(QSlot* sl, const 
     return 2u;
 }
 
-#ifdef WB_PROF
-#define PROF_T0(v) const long long v = clock64()
-#define PROF_ADD(i, v) do { if (g.tid == 0) prof[i] += clock64() - (v); } while (0)
-#else
-#define PROF_T0(v)
-#define PROF_ADD(i, v)
-#endif
 
 template <typename T>
 __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a, int stages, int gbm_words, int max_k, int hand_k) {
@@ -487,27 +491,17 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
         uint32_t issued = 0;      // copies issued so far
         const uint64_t once = l2_evict_first_policy();
         bool gave_up = false;
-#ifdef WB_PROF
-        long long pw = 0;
-        const long long pt0 = clock64();
-#endif
 #pragma unroll 1
         for (int i = 0; i < n_list && !gave_up; ++i) {
             const uint8_t* src = reinterpret_cast<const uint8_t*>(a.x) + size_t(rlist[i]) * row_bytes;
             uint32_t left = uint32_t(row_bytes);  // (a row is below 4 GiB: n < 2^30 elements of at most 4 bytes)
 #pragma unroll 1
             for (uint32_t c = 0; c < n_chunks; ++c) {
-#ifdef WB_PROF
-                const long long pw0 = clock64();
-#endif
                 if (!mbar_wait(&empty[s], par, a.wait_limit)) {
                     atomicExch(a.err, 1u);
                     gave_up = true;
                     break;
                 }
-#ifdef WB_PROF
-                pw += clock64() - pw0;
-#endif
                 const uint32_t bytes = left < uint32_t(Q_SB) ? left : uint32_t(Q_SB);
                 // (tests only: one copy of CTA 0 is left out, so that the waits for it run out)
                 const bool lose = a.lose_copy && blockIdx.x == 0 && i == 0 && c == 3;
@@ -533,12 +527,6 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 mbar_wait(&full[bs], bpar ^ 1u, a.wait_limit);
             }
         }
-#ifdef WB_PROF
-        {
-            unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 16);
-            atomicAdd(&dbg[12], (unsigned long long)pw), atomicAdd(&dbg[13], (unsigned long long)(clock64() - pt0));
-        }
-#endif
         return;
     }
 
@@ -583,10 +571,6 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
         const Group<Q_TT> g{tid - 32 - Q_ST, 1};
         const Group<Q_PT> gp{g.tid - 32, 2};  // the tail warps but the first
         const int lane = lane_id(), tw = g.tid >> 5;
-#ifdef WB_PROF
-        long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // wait, join, select, draw, prepare, refine, rows, total
-        const long long prof_begin = clock64();
-#endif
 
         // ---- a row's parameters come into the slot it will stream through (one warp, every lane fetching one of them)
         auto fetch_params = [&](int p, int row) {
@@ -725,13 +709,11 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             g.sync();
             const uint32_t step = 2 * K > uint32_t(Q_L) / 4 ? 2 * K : uint32_t(Q_L) / 4;
             if (!allowed || !(nlog >= K && nlog >= rf_last[p] + step)) return false;
-            PROF_T0(tr0);
             // (entries reserved but not written yet read as zero and rank last: the bound stays valid)
             const unsigned long long kth = select_kth<Q_TT>(g, logs + size_t(p) * Q_L, nlog, K, hist, &sh->sel);
             if (g.tid == 0 && kth > ldv_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = kth;
             rf_last[p] = nlog;
             g.sync();
-            PROF_ADD(5, tr0);
             return true;
         };
 
@@ -845,7 +827,6 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     for (int u = 0; u < HB; ++u) hv[u] = (u * Q_TT + g.tid) < cfg.hist_len ? h[u * Q_TT + g.tid] : -1;
                 }
                 // ---- while the row streams
-                PROF_T0(tw0);
                 // (one thread watches the row; the others wait at the group's barrier, where they take no issue slot from the
                 // stream warps)
 #pragma unroll 1
@@ -880,11 +861,9 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     maybe_refine(p, K, true);
                 }
                 mbar_wait(&closed[p], (ord >> 1) & 1, a.wait_limit);  // acquire the stream warps' writes
-                PROF_ADD(0, tw0);
                 rf_last[p] = 0;
                 // ---- the row is through
                 if (pen_on) {
-                    PROF_T0(tj0);
                     const unsigned long long tau = sl->tau;
                     const float tau_f = cand_key(tau) ? float_of_key(cand_key(tau)) : -INFINITY;
                     if (lazy) {
@@ -968,16 +947,11 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         }
                     }
                     g.sync();
-                    PROF_ADD(1, tj0);
                 }
-                PROF_T0(ts0);
                 const float inv_t = cfg.inv_t;
                 const uint32_t total_raw = sl->cnt;  // bit 31: a NaN logit met a sum
                 const bool nan_row = (total_raw & 0x80000000u) != 0;
                 const uint32_t total = total_raw & 0x7fffffffu;
-#ifdef WB_PROF
-                if (g.tid == 0) atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 16) + 14, (unsigned long long)total);
-#endif
                 nan_seen = nan_row;
                 overflow = total > uint32_t(Q_L) || nan_row || (pen_on && !lazy && sl->side_cnt > uint32_t(kMaxHist));
                 const uint32_t nlog = total > uint32_t(Q_L) ? uint32_t(Q_L) : total;
@@ -1050,12 +1024,10 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     for (int i = g.tid; i < gbm_words / 4; i += Q_TT) reinterpret_cast<uint4*>(gbm)[i] = make_uint4(0, 0, 0, 0);
                 }
                 g.sync();
-                PROF_ADD(2, ts0);
             }
             if (tw > 0) {
                 // ---- the freed slot goes to the row after the next (at the start: both slots go out), then the table of the
                 // row that streams now
-                PROF_T0(tp0);
                 if (ord < 0) {
                     slot_boot(0, rlist[0]);
                     if (n_list > 1) slot_boot(1, rlist[1]);
@@ -1063,28 +1035,13 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     slot_boot(p, rlist[ord + 2]);
                 }
                 if (ord + 1 < n_list) build_table(p ^ 1);
-#ifdef WB_PROF
-                if (g.tid == 32) atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 16) + 4, (unsigned long long)(clock64() - tp0));
-#endif
             } else if (ord >= 0 && !big_done) {
                 // ---- the first tail warp: the row's outputs
-                PROF_T0(td0);
                 finish_row(Group<32>{lane, 0}, cfg, reinterpret_cast<uint64_t*>(hand), tail_p, tail_q, kept, cap, presorted, overflow, nan_seen, M, sum);
-                PROF_ADD(3, td0);
             }
             g.sync();
-#ifdef WB_PROF
-            if (g.tid == 0 && ord >= 0) prof[6] += 1;
-#endif
         }
     tail_done:
-#ifdef WB_PROF
-        if (g.tid == 0) {
-            prof[7] = clock64() - prof_begin;
-            unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 16);
-            for (int i = 0; i < 8; ++i) atomicAdd(&dbg[i], (unsigned long long)prof[i]);
-        }
-#endif
         // Every row of this CTA has its status.
         if (a.fin_list) {
             __threadfence();
@@ -1101,9 +1058,6 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
     uint32_t st_slot = 0, st_phase = 0;  // ring position of this warp and the parity it waits for
     const uint32_t n_iter = (n_chunks + Q_NS - 1) / Q_NS;
     const uint32_t full_iters = row_q / (Q_NS * Q_SQ);  // iterations whose words all lie inside the row
-#ifdef WB_PROF
-    long long sp_wait = 0, sp_boot = 0, sp_head = 0, sp_total = clock64(), sp_visits = 0;
-#endif
 #pragma unroll 1
     for (int ord = 0; ord < n_list; ++ord) {
         const int p = ord & 1;
@@ -1111,16 +1065,10 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
         unsigned long long* log = logs + size_t(p) * Q_L;
         const uint32_t* gbm = gbms + size_t(p) * gbm_words;
         // the slot (parameters, log, threshold, word map) is this row's once the tail group says so
-#ifdef WB_PROF
-        const long long tb0 = clock64();
-#endif
         if (!mbar_wait(&boot_done[p], (ord >> 1) & 1, a.wait_limit)) {
             if (lane == 0) atomicExch(a.err, 4u);
             return;
         }
-#ifdef WB_PROF
-        sp_boot += clock64() - tb0;
-#endif
         const uint32_t row_flags = sl->cfg.flags;
         const float cexp = sl->cfg.inv_t * kLog2e;
         // running maxima (the two largest iteration maxima of this lane: two distinct logits), reference exponent
@@ -1155,17 +1103,11 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 for (int h = 0; h < Q_NS; ++h) {
                     st_ring[h] = st_slot;
                     if (whole || c + uint32_t(h) < n_chunks) {
-#ifdef WB_PROF
-                        const long long tw0 = clock64();
-#endif
                         if (!mbar_wait(&full[st_slot], st_phase, a.wait_limit)) {
                             if (lane == 0) atomicExch(a.err, 5u);
                             st_fail = true;
                             return;
                         }
-#ifdef WB_PROF
-                        sp_wait += clock64() - tw0;
-#endif
                     }
                     const uint4* vec = reinterpret_cast<const uint4*>(ring + size_t(st_slot) * Q_SB);
 #pragma unroll
@@ -1263,9 +1205,6 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 if (iter == 0) {
                     // The row's first threshold: every warp names its bound from what it has just read and the warps meet (their
                     // one meeting per row); what this lane read is tested against the agreed bound below, from its registers.
-#ifdef WB_PROF
-                    const long long th0 = clock64();
-#endif
                     // The warp publishes its largest lane maxima, in descending order: 8 for a small-K row, Q_TOP otherwise.
                     const uint32_t rank0 = sl->cfg.rank0;
                     {
@@ -1313,17 +1252,11 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         const unsigned long long t0 = (unsigned long long)kmin << 32;
                         if (t0 > ldv_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = t0;
                     }
-#ifdef WB_PROF
-                    sp_head += clock64() - th0;
-#endif
                 } else {
                     const uint32_t tk = *tau_hi;
                     if (tk > tau_key) tau_key = tk, tau_f = float_of_key(tk);
                 }
                 if (__any_sync(0xffffffffu, vm >= tau_f)) {
-#ifdef WB_PROF
-                    ++sp_visits;
-#endif
                     // Some lane holds logits that may beat the threshold.
                     if (lazy && iter != 0) {
                         const uint4 mw = *reinterpret_cast<const uint4*>(gbm + ((iter * Q_SW + uint32_t(sw)) << 2));
@@ -1386,14 +1319,6 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             mbar_arrive(&closed[p]);
         }
     }
-#ifdef WB_PROF
-    if (st_tid == 0) {
-        unsigned long long* dbg = reinterpret_cast<unsigned long long*>(a.err + 16);
-        atomicAdd(&dbg[8], (unsigned long long)sp_wait), atomicAdd(&dbg[9], (unsigned long long)sp_boot);
-        atomicAdd(&dbg[10], (unsigned long long)(clock64() - sp_total)), atomicAdd(&dbg[11], (unsigned long long)sp_head);
-    }
-    if (lane == 0) atomicAdd(reinterpret_cast<unsigned long long*>(a.err + 16) + 15, (unsigned long long)sp_visits);
-#endif
 }
 
 static int single_pass_gbm_words(const SelectArgs& a, int dtype) {

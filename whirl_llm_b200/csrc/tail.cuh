@@ -1,8 +1,13 @@
 // The per-row tail of the sampling path: sort the selected candidates, probabilities in f64, top-k / top-p / min-p on
 // the sorted prefix, then the draw.  It restates, for a group of GPU threads, what the reference does on the host in
 // sampling::filterCands (src/sampling/sampler.cpp:15-78), sampleRow (:118-131, the candidate part) and sampleRace
-// (:82-106, the race part).  Sums that the host accumulates sequentially are accumulated sequentially here too (one
-// thread walks them in candidate order), so the kept set and the cumulative sums follow the same order of operations.
+// (:82-106, the race part).
+// Running sums: the host adds the probabilities one after the other in candidate order.  Here the group's first warp
+// adds them in blocks - every lane a contiguous block of candidates in order, then a scan of the lanes' block sums in
+// lane order - so the cumulative sum at a candidate is made of the same terms in the same order up to how they are
+// grouped; results agree with the host's to the last bits of a double, and a cut or a draw can differ only when a
+// cumulative sum meets its bound that closely (the parity tests count draws within 1e-6 of a boundary).  The top-p walk
+// and the draw compare against top_p * z and u * z instead of dividing every probability by z first.
 #pragma once
 
 #include "common.cuh"
@@ -13,8 +18,10 @@ enum RowStatus : int32_t {
     ROW_DONE = 0,       // token drawn from a closed (or reached) candidate set
     ROW_ESCALATE = 1,   // the kept set may reach past the candidates: needs a larger candidate set
     ROW_OPEN_TAIL = 2,  // open set and the draw fell past the candidates: needs the id-order walk of the row
-    ROW_RETRY = 3,      // internal: the single-pass kernel's candidate log overflowed; the multi-pass kernel redoes the row
-    ROW_LARGE_K = 4,    // internal: top_k above the single-pass kernel's limit; the multi-pass kernel takes the row
+    ROW_RETRY = 3,      // internal: the single-pass kernel could not finish the row (its candidate log overflowed, a guessed
+                        // threshold left too few candidates, a NaN met a sum); the multi-pass kernel redoes the row
+    ROW_LARGE_K = 4,    // internal: top_k above the single-pass kernel's limit (or too large for the row's length); the
+                        // multi-pass kernel takes the row
     ROW_PENDING = 5,    // internal: listed by the single-pass kernel and not answered yet (what a row keeps when a role gave up)
 };
 
