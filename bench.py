@@ -279,6 +279,7 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist
         import datetime
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # (stdout carries the one JSON line only)
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
 
     rows, vocab, esize = args.rows, args.vocab, (4 if args.dtype == "f32" else 2)
