@@ -91,6 +91,7 @@ __global__ void __launch_bounds__(MT) merge_sample_kernel(const int32_t* ids, co
         in.u = P.u ? P.u[row] : 0.0, in.m = sh->m, in.sum = sh->sum, in.cnt = kept, in.cap = cap, in.V = uint32_t(n_total);
         in.race = P.race_key != nullptr, in.race_key = P.race_key ? P.race_key[row] : 0, in.presorted = 0;
         in.want_p = out.kept_p != nullptr && out.kept_cap > 0;
+        in.have_e = 0;
         sample_tail<MT>(g, in, reinterpret_cast<uint64_t*>(hand), tp, tq, &sh->res);
         const TailOut r = sh->res;
         if (g.tid == 0) {

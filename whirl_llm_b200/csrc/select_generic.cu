@@ -194,6 +194,12 @@ __global__ void __launch_bounds__(GT) select_generic_kernel(SelectArgs a, int ca
     uint32_t* pen_mem = reinterpret_cast<uint32_t*>((reinterpret_cast<uintptr_t>(sh + 1) + 15) & ~uintptr_t(15));
 
     const int n_rows = a.row_count ? min(*a.row_count, a.rows) : a.rows;
+    if (a.row_list && n_rows == 0 && a.batch_counters && a.fin_counts) {
+        // An empty list of leftover rows (the usual case after the single-pass kernel: every row has its answer, so there
+        // is nothing to count either).  Only a wait that ran out without costing a row its answer is still to report.
+        if (blockIdx.x == 0 && threadIdx.x == 0 && a.err && __ldcg(a.err) != 0u) atomicAdd(&a.batch_counters[WHIRL_CNT_TIMEOUT], 1u);
+        return;
+    }
     for (int li = blockIdx.x; li < n_rows; li += gridDim.x) {
         __syncthreads();  // the previous row's shared state is dead
         const int entry = a.row_list ? a.row_list[li] : li;
@@ -449,6 +455,7 @@ __device__ int select_row(const SelectArgs& a, int row, int level_k, int cap_max
     // the tail's race scratch sits at p + in.cap; keep it inside this row's slice
     in.presorted = 0;
     in.want_p = a.out.kept_p != nullptr && a.out.kept_cap > 0;
+    in.have_e = 0;
     sample_tail<GT>(g, in, cand, p, q, &sh->res);
     TailOut r = sh->res;
     if (r.status == ROW_OPEN_TAIL) {

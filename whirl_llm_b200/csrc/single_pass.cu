@@ -782,6 +782,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 in.race = P.race_key != nullptr, in.race_key = cfg.race_key;
                 in.presorted = presorted;
                 in.want_p = a.out.kept_p != nullptr && a.out.kept_cap > 0;
+                in.have_e = no_sum;  // (the normaliser over the candidates has just left them in bq)
                 sample_tail<NT>(grp, in, cand, bp, bq, &sh->res);
                 const TailOut r = sh->res;
                 if (first) {
@@ -895,7 +896,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                                 uint32_t c = 0;
 #pragma unroll
                                 for (int u = 0; u < HB; ++u) c += hv[u] == id;
-                                c = warp_sum(c);
+                                c = __reduce_add_sync(0xffffffffu, c);
                                 if (lane == 0 && c) atomicAdd(&mcnt[m], c);
                             }
                             g.sync();

@@ -37,6 +37,7 @@ struct TailIn {
     int32_t race;
     int32_t presorted;  // cand[0..cnt) is already in descending order
     int32_t want_p;     // the caller reads p[] afterwards: leave the kept probabilities renormalised there
+    int32_t have_e;     // q[0..cnt) already holds exp((l - m) * inv_t) of the candidates in cand[]'s order (which is sorted)
 };
 struct TailOut {
     int32_t status;
@@ -144,7 +145,8 @@ __device__ __noinline__ void sample_tail(const Group<NT>& g, const TailIn& in, u
 #pragma unroll 1
     for (uint32_t i = g.tid; i < in.cnt; i += NT) {
         const float l = float_of_key(cand_key(cand[i]));
-        p[i] = f64_div(f64_exp(double(__fsub_rn(l, in.m)) * inv_t), sum);
+        const double e = in.have_e ? q[i] : f64_exp(double(__fsub_rn(l, in.m)) * inv_t);
+        p[i] = f64_div(e, sum);
     }
     g.sync();
     // ---- top-k, and the normaliser of the top-p walk (sampler.cpp:35-49)
