@@ -205,7 +205,16 @@ __global__ void __launch_bounds__(GT) select_generic_kernel(SelectArgs a, int ca
         const int entry = a.row_list ? a.row_list[li] : li;
         // bit 30 of a list entry: redo the row at the first candidate level (the single-pass kernel gave it up)
         const int row = entry & 0x3fffffff;
-        int level = (entry >> 30) & 1 ? min(a.level_k, kFirstLevelK) : a.level_k;
+        int level = a.level_k;
+        if ((entry >> 30) & 1) {
+            // (the first level as the single-pass kernel takes it: the row's own top_k when it is at most kSinglePassMaxK,
+            // else kFirstLevelK candidates)
+            level = min(a.level_k, kFirstLevelK);
+            if (a.mode == MODE_SAMPLE && a.prm.top_k) {
+                const int tk = a.prm.top_k[row];
+                if (tk > kFirstLevelK && tk <= kSinglePassMaxK) level = min(a.level_k, kSinglePassMaxK);
+            }
+        }
         int st = select_row<T>(a, row, level, cap_max, pen_words, cand, hist, sh, pen_mem);
         if (st == ROW_ESCALATE && level < a.level_k) {
             // a row redone at the first level whose kept set may reach past it: on to this launch's level, as a row that the

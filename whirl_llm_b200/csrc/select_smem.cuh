@@ -63,16 +63,21 @@ __device__ __noinline__ void find_bin_desc(const Group<NT>& g, const uint32_t* h
 // The K-th largest of buf[0..cnt) (1 <= K <= cnt; entries distinct; zeros allowed as "empty", they rank last).
 // hist: SEL_BINS words of shared scratch (also used as a list of up to SEL_LIST candidates).  Every thread of the
 // group calls it and gets the same answer.
-template <int NT>
+// MASKED: entries whose bit 31 is clear (log entries that still carry a raw logit) count as empty.
+template <int NT, bool MASKED = false>
 __device__ __noinline__ unsigned long long select_kth(const Group<NT>& g, const unsigned long long* buf, uint32_t cnt, uint32_t K,
                                          uint32_t* hist, SelScratch* sc) {
+    auto entry = [&](uint32_t i) -> unsigned long long {
+        const unsigned long long c = buf[i];
+        return (MASKED && !(c & 0x80000000ull)) ? 0ull : c;
+    };
     if (g.tid == 0) sc->lo = ~0ull, sc->hi = 0ull;
     g.sync();
     {
         unsigned long long lo = ~0ull, hi = 0ull;
 #pragma unroll 1
         for (uint32_t i = g.tid; i < cnt; i += NT) {
-            const unsigned long long c = buf[i];
+            const unsigned long long c = entry(i);
             lo = c < lo ? c : lo, hi = c > hi ? c : hi;
         }
 #pragma unroll
@@ -96,7 +101,7 @@ __device__ __noinline__ unsigned long long select_kth(const Group<NT>& g, const 
         g.sync();
 #pragma unroll 1
         for (uint32_t i = g.tid; i < cnt; i += NT) {
-            const unsigned long long c = buf[i];
+            const unsigned long long c = entry(i);
             if (c >= lo && c <= hi) atomicAdd(&hist[uint32_t((c - lo) >> sa)], 1u);
         }
         g.sync();
@@ -113,7 +118,7 @@ __device__ __noinline__ unsigned long long select_kth(const Group<NT>& g, const 
             unsigned long long* list = reinterpret_cast<unsigned long long*>(hist);
 #pragma unroll 1
             for (uint32_t i = g.tid; i < cnt; i += NT) {
-                const unsigned long long c = buf[i];
+                const unsigned long long c = entry(i);
                 if (c >= nlo && c <= nhi) list[atomicAdd(&sc->lcnt, 1u)] = c;
             }
             g.sync();

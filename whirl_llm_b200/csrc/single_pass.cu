@@ -26,7 +26,7 @@
 //     count.  A row whose guess leaves fewer than K logged candidates is done again by the multi-pass kernel; a row
 //     whose K on its length would need a rank beyond what the warps publish goes there from the start.
 //   * Later thresholds: the keeper warp (K <= 64); for larger K the tail group, which selects the exact K-th largest of
-//     the log when the log has grown enough (rows without marked entries).
+//     the log when the log has grown enough (marked entries, which carry raw logits, count as absent there).
 //
 // Penalties.  A raw logit of a history token must count nowhere.  The tail group builds, a row ahead, a bit map of the
 // 16-byte words (4 f32 / 8 bf16 logits) that hold a history token.  Nothing of a row is ever fetched a second time from
@@ -70,7 +70,7 @@ constexpr int Q_MAXSTAGES = 8;
 #endif
 constexpr int Q_NS = WB_NS;              // ring stages per iteration of a stream warp
 #ifndef WB_QL
-#define WB_QL 3072
+#define WB_QL 2944
 #endif
 constexpr int Q_L = WB_QL;               // candidate log entries per row slot
 constexpr int Q_RED = Q_SW + Q_TW;       // partial (max, exponent, sum) triples per row: stream warps, then tail warps
@@ -97,18 +97,33 @@ enum : uint32_t { QF_NO_SUM = 1u, QF_PEN = 2u, QF_GREEDY = 4u, QF_LAZY = 8u };
 
 constexpr int Q_TOP = 16;       // lane maxima a stream warp publishes for a row's first threshold (the first 8 for a small-K row)
 constexpr int Q_SMALL_K = 64;   // rows keeping at most this many candidates: exact first threshold, threshold kept by the keeper warp
+#ifndef WB_Z
+#define WB_Z 3.5f
+#endif
+constexpr float Q_GUESS_Z = WB_Z;  // standard deviations between a guessed first threshold's expected count and K
 constexpr int Q_RANK_MAX = 192; // largest rank among the published maxima a first threshold may be taken at
 static_assert(Q_SW * Q_TOP == 256, "eight published keys per lane");
 
 // The rank, among the logits of a row's first iteration, that the row's first threshold is taken at.  Small K: K itself
 // (the K-th largest of a part of the row is a valid bound).  Larger K: a guess - the rank that, scaled from the first
 // iteration (it0 logits) to the whole row (n logits), leaves K candidates 3.5 standard deviations below the expected
-// count.  A row that ends with fewer than K logged candidates is redone by the multi-pass kernel.
+// count (for K = 1024 on 262,144 f32 logits: rank 59, about 2000 candidates expected, between the K wanted and the log's
+// 2944 places with 3.5 deviations to spare on either side; the stream warps publish one maximum per lane, so a lane
+// holding two of the first-ranked logits makes the count a few per cent larger).  A row that ends with fewer than K logged candidates is redone by the multi-pass kernel.
 __device__ __forceinline__ uint32_t first_rank(uint32_t K, uint32_t n, uint32_t it0) {
     if (K <= uint32_t(Q_SMALL_K)) return K;
     const float x = float(K) * float(it0 < n ? it0 : n) / float(n);
-    const float r = 0.5f * (3.5f + sqrtf(12.25f + 4.f * x));
+    const float r = 0.5f * (Q_GUESS_Z + sqrtf(Q_GUESS_Z * Q_GUESS_Z + 4.f * x));
     return uint32_t(ceilf(r * r));
+}
+
+// How far the log has to grow past its size at the last refinement (0: none yet) before the tail group refines the
+// threshold again.  The first refinement waits for twice the candidates wanted (a quarter of the log at least): until then
+// the log is no burden.  Once the log has needed one, the next ones follow closely, so that a row whose first threshold
+// was guessed low is cut back several times before its log is full.
+__device__ __forceinline__ uint32_t refine_step(uint32_t K, uint32_t last) {
+    if (last == 0) return 2 * K > uint32_t(Q_L) / 4 ? 2 * K : uint32_t(Q_L) / 4;
+    return K / 4 > 128u ? K / 4 : 128u;
 }
 
 struct QSlot {
@@ -694,11 +709,11 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             }
         };
 
-        // ---- raise a streaming row's threshold to the exact K-th largest of its log so far.  The stream warps keep the
-        // threshold close to that by themselves; this is for a log that fills up all the same.  (Not for a row whose log
-        // holds marked entries: their raw logits would count.)
+        // ---- raise a streaming row's threshold to the exact K-th largest of its log so far (rows of more than 64
+        // candidates: the keeper warp does it for the others).  This is what keeps the log of a row whose first threshold
+        // was a guess from filling up.  Marked entries carry raw logits and count as absent.
         uint32_t rf_last[2] = {0, 0};
-        auto maybe_refine = [&](int p, uint32_t K, bool allowed) {
+        auto maybe_refine = [&](int p, uint32_t K, bool allowed, bool masked) {
             QSlot* sl = &sh->slot[p];
             if (g.tid == 0) {
                 const uint32_t c = ldv_u32(&sl->cnt) & 0x7fffffffu;
@@ -707,10 +722,25 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             g.sync();
             const uint32_t nlog = sh->flag[2];
             g.sync();
-            const uint32_t step = 2 * K > uint32_t(Q_L) / 4 ? 2 * K : uint32_t(Q_L) / 4;
+            const uint32_t step = refine_step(K, rf_last[p]);
             if (!allowed || !(nlog >= K && nlog >= rf_last[p] + step)) return false;
-            // (entries reserved but not written yet read as zero and rank last: the bound stays valid)
-            const unsigned long long kth = select_kth<Q_TT>(g, logs + size_t(p) * Q_L, nlog, K, hist, &sh->sel);
+            // The select makes several passes over the log's first nlog places and needs them to read the same every time.
+            // A place is reserved before it is written, so a place that still reads zero is waited for (every entry is
+            // non-zero; the writer is a few instructions away); what the stream warps append meanwhile lies behind nlog.
+            {
+                const unsigned long long* lg = logs + size_t(p) * Q_L;
+#pragma unroll 1
+                for (uint32_t i = g.tid; i < nlog; i += Q_TT) {
+#pragma unroll 1
+                    for (uint32_t spin = 0; spin < 100000u && ldv_u64(&lg[i]) == 0ull; ++spin) {
+                    }
+                }
+                g.sync();
+            }
+            // (a row with marked entries: they carry raw logits and count as absent; the K-th largest of the others is a
+            // valid bound all the same)
+            const unsigned long long kth = masked ? select_kth<Q_TT, true>(g, logs + size_t(p) * Q_L, nlog, K, hist, &sh->sel)
+                                                  : select_kth<Q_TT, false>(g, logs + size_t(p) * Q_L, nlog, K, hist, &sh->sel);
             if (g.tid == 0 && kth > ldv_u64(&sl->tau)) *reinterpret_cast<volatile unsigned long long*>(&sl->tau) = kth;
             rf_last[p] = nlog;
             g.sync();
@@ -834,7 +864,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 for (;;) {
                     if (g.tid == 0) {
                         uint32_t what = 2u;  // 0: the row is through, 1: the log wants a refinement, 2: gave up
-                        const uint32_t step = 2 * K > uint32_t(Q_L) / 4 ? 2 * K : uint32_t(Q_L) / 4;
+                        const uint32_t step = refine_step(K, rf_last[p]);
 #pragma unroll 1
                         for (uint32_t spin = 0; spin < 4 * a.wait_limit; ++spin) {
                             if (mbar_try_wait(&closed[p], (ord >> 1) & 1)) {
@@ -842,7 +872,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                                 break;
                             }
                             const uint32_t c = ldv_u32(&sl->cnt) & 0x7fffffffu;
-                            if (!lazy && K > uint32_t(Q_SMALL_K) && c >= K && c >= rf_last[p] + step && c <= uint32_t(Q_L)) {
+                            if (K > uint32_t(Q_SMALL_K) && c >= K && c >= rf_last[p] + step && c <= uint32_t(Q_L)) {
                                 what = 1u;
                                 break;
                             }
@@ -859,7 +889,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         if (g.tid == 0) atomicExch(a.err, 3u);
                         goto tail_done;
                     }
-                    maybe_refine(p, K, true);
+                    maybe_refine(p, K, true, lazy);
                 }
                 mbar_wait(&closed[p], (ord >> 1) & 1, a.wait_limit);  // acquire the stream warps' writes
                 rf_last[p] = 0;
@@ -1348,7 +1378,7 @@ bool single_pass_supported(const SelectArgs& a, int dtype) {
         if (K > uint32_t(Q_SMALL_K)) {
             const uint32_t it0 = uint32_t(Q_NS) * Q_SB / uint32_t(es);
             const float x = float(K) * float(it0 < uint32_t(a.n) ? it0 : uint32_t(a.n)) / float(a.n);
-            const float r = 0.5f * (3.5f + sqrtf(12.25f + 4.f * x));
+            const float r = 0.5f * (Q_GUESS_Z + sqrtf(Q_GUESS_Z * Q_GUESS_Z + 4.f * x));
             if (uint32_t(ceilf(r * r)) > uint32_t(Q_RANK_MAX)) return false;
         }
     }
