@@ -126,3 +126,33 @@ def test_rows_redone_by_the_multi_pass_kernel_still_reach_the_second_level(api, 
     compare_rows(res, want, u=u)
     cnt = res.counters.cpu().numpy()
     assert cnt[api.CNT_REDO] >= R // 2 and cnt[api.CNT_ESCALATED] == R and cnt[api.CNT_UNRESOLVED] == 0
+
+
+def test_large_top_k_on_adversarial_rows(api, oracle):
+    """Rows keeping more than 64 candidates take their first threshold from a guess made on the first 8192 logits.
+    Falling rows (the guess is far too high: fewer than top_k candidates get logged), rising rows (every logit beats the
+    threshold so far: the log overflows), constant rows and rows with few distinct values must all come back right: the
+    single-pass kernel hands what it cannot finish to the multi-pass kernel."""
+    R, V = 64, 65536
+    x = synth.normalish(431, (R, V), 2.0)
+    x[0::8] = np.sort(x[0::8], axis=1)
+    x[1::8] = -np.sort(-x[1::8], axis=1)
+    x[2::8] = 0.75
+    x[3::8] = np.round(x[3::8])
+    x[4::8, :8192] -= 6.0                                  # a first iteration that says nothing about the rest
+    x[5::8, :8192] += 6.0
+    f = lambda v, dt=np.float32: np.full(R, v, dtype=dt)
+    prm = dict(inv_t=f(1.0), top_k=f(300, np.uint32), top_p=f(0.95, np.float64), min_p=f(0.0, np.float64))
+    prm["top_k"][R // 2:] = 1000
+    u = synth.hash_u01(432, R, 0)
+    want = oracle.sample_rows(x, kept_cap=1024, u=u, threads=4, **prm)
+    res = api.sample_rows(dev(x), row_params(prm, u=u), kept_cap=1024)
+    compare_rows(res, want, u=u)
+    cnt = res.counters.cpu().numpy()
+    assert cnt[api.CNT_REDO] >= R // 4 and cnt[api.CNT_UNRESOLVED] == 0
+    # the candidates entry point on the same rows
+    ids, vals, stats = api.topk_rows(dev(x), 1000, inv_t=1.0)
+    wi, wv, ws = oracle.topk_rows(x, 1000, 1.0)
+    assert np.array_equal(ids.cpu().numpy(), wi) and np.array_equal(vals.cpu().numpy(), wv)
+    assert np.array_equal(stats.cpu().numpy()[:, 0], ws[:, 0])
+    np.testing.assert_allclose(stats.cpu().numpy()[:, 1], ws[:, 1], rtol=1e-5)

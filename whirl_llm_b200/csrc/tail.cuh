@@ -6,8 +6,8 @@
 // adds them in blocks - every lane a contiguous block of candidates in order, then a scan of the lanes' block sums in
 // lane order - so the cumulative sum at a candidate is made of the same terms in the same order up to how they are
 // grouped; results agree with the host's to the last bits of a double, and a cut or a draw can differ only when a
-// cumulative sum meets its bound that closely (the parity tests count draws within 1e-6 of a boundary).  The top-p walk
-// and the draw compare against top_p * z and u * z instead of dividing every probability by z first.
+// cumulative sum meets its bound that closely (the parity tests count draws within 1e-6 of a boundary).  The draw compares
+// against u * z instead of dividing every kept probability by z first (unless the caller reads the probabilities).
 #pragma once
 
 #include "common.cuh"
@@ -166,16 +166,21 @@ __device__ __noinline__ void sample_tail(const Group<NT>& g, const TailIn& in, u
     }
     g.sync();
     if (res->status == ROW_ESCALATE) return;
-    // (The host filter divides every probability by z and walks until the running sum reaches top_p; here the walk runs over
-    // the probabilities as they are, up to top_p * z: one multiplication instead of a division per candidate.)
-    const double z_top = res->cum;
+    if (in.top_p < 1.0) {
+        // (as the host filter: every probability divided by z, then the walk until the running sum reaches top_p)
+        const double z = res->cum;
+        const uint32_t n0 = res->n;
+#pragma unroll 1
+        for (uint32_t i = g.tid; i < n0; i += NT) q[i] = f64_div(p[i], z);
+        g.sync();
+    }
     // ---- top-p cut, min-p cut, the renormaliser (sampler.cpp:50-74)
     if (g.tid < 32) {
         uint32_t n = res->n;
         bool closed = res->closed != 0, esc = false;
         if (in.top_p < 1.0) {
             double walked;
-            const uint32_t j = warp_first_reach<false>(p, n, in.top_p * z_top, &walked);
+            const uint32_t j = warp_first_reach<false>(q, n, in.top_p, &walked);
             if (j < n) n = j + 1, closed = true;
             else if (!closed) esc = true;
         }
