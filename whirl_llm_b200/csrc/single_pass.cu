@@ -56,23 +56,15 @@ namespace wb {
 
 constexpr int Q_SW = 16;                 // stream warps
 constexpr int Q_ST = Q_SW * 32;
-#ifndef WB_TW
-#define WB_TW 8
-#endif
-constexpr int Q_TW = WB_TW;              // tail warps
+constexpr int Q_TW = 8;                  // tail warps
 constexpr int Q_TT = Q_TW * 32;
 constexpr int Q_THREADS = 32 + Q_ST + Q_TT + 32;  // producer warp, stream warps, tail group, threshold keeper
 constexpr int Q_SB = 16384;              // bytes per ring stage
 constexpr int Q_SQ = Q_SB / 16;          // 128-bit words per stage
 constexpr int Q_MAXSTAGES = 8;
-#ifndef WB_NS
-#define WB_NS 2
-#endif
-constexpr int Q_NS = WB_NS;              // ring stages per iteration of a stream warp
-#ifndef WB_QL
-#define WB_QL 2944
-#endif
-constexpr int Q_L = WB_QL;               // candidate log entries per row slot
+constexpr int Q_NS = 2;                  // ring stages per iteration of a stream warp
+constexpr int Q_L = 2944;                // candidate log entries per row slot (sized so that penalised f32 rows of 262,144
+                                         // logits leave room for seven ring stages)
 constexpr int Q_RED = Q_SW + Q_TW;       // partial (max, exponent, sum) triples per row: stream warps, then tail warps
 constexpr int Q_PT = Q_TT - 32;          // tail threads that prepare penalties (all tail warps but the first)
 static_assert(Q_SQ == 2 * Q_ST, "two 128-bit words per stream thread and stage");
@@ -97,10 +89,7 @@ enum : uint32_t { QF_NO_SUM = 1u, QF_PEN = 2u, QF_GREEDY = 4u, QF_LAZY = 8u };
 
 constexpr int Q_TOP = 16;       // lane maxima a stream warp publishes for a row's first threshold (the first 8 for a small-K row)
 constexpr int Q_SMALL_K = 64;   // rows keeping at most this many candidates: exact first threshold, threshold kept by the keeper warp
-#ifndef WB_Z
-#define WB_Z 3.5f
-#endif
-constexpr float Q_GUESS_Z = WB_Z;  // standard deviations between a guessed first threshold's expected count and K
+constexpr float Q_GUESS_Z = 3.5f;  // standard deviations between a guessed first threshold's expected count and K
 constexpr int Q_RANK_MAX = 192; // largest rank among the published maxima a first threshold may be taken at
 static_assert(Q_SW * Q_TOP == 256, "eight published keys per lane");
 
@@ -200,29 +189,6 @@ __device__ void list_leftovers(const SelectArgs& a) {
         a.fin_counts[1] = cnt, a.fin_counts[2] = 0;
         if (a.out.counters && n_redo) atomicAdd(&a.out.counters[WHIRL_CNT_REDO], uint32_t(n_redo));
     }
-}
-
-// The r-th largest of the warp's 32 * G keys (kv[0..G) per lane; 0 = none), by taking the largest away r - 1 times.
-// Equal keys of distinct elements count separately.  0 when the warp holds fewer than r keys.
-template <int G>
-__device__ __forceinline__ uint32_t warp_rth_largest(uint32_t (&kv)[G], uint32_t r) {
-    const int lane = lane_id();
-    uint32_t kr = 0;
-    for (uint32_t i = 0; i < r; ++i) {
-        uint32_t mx = kv[0];
-#pragma unroll
-        for (int j = 1; j < G; ++j) mx = kv[j] > mx ? kv[j] : mx;
-        kr = __reduce_max_sync(0xffffffffu, mx);
-        if (kr == 0) break;
-        const uint32_t holders = __ballot_sync(0xffffffffu, mx == kr);
-        if (lane == __ffs(holders) - 1) {
-            bool gone = false;
-#pragma unroll
-            for (int j = 0; j < G; ++j)
-                if (!gone && kv[j] == kr) kv[j] = 0, gone = true;
-        }
-    }
-    return kr;
 }
 
 // ---- the table of a row's distinct history tokens: (token + 1) | count << 19, open addressing, kPenSlots words
