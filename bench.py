@@ -279,8 +279,19 @@ def run_ours(args):
     if world > 1:
         import torch.distributed as dist
         import datetime
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # (stdout carries the one JSON line only)
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+        # stdout carries the one JSON line only: what NCCL prints when its communicator comes up (its version line) goes to
+        # stderr, by pointing file descriptor 1 there until the first collective has run
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
 
     rows, vocab, esize = args.rows, args.vocab, (4 if args.dtype == "f32" else 2)
     xs, params, us, base, what = make_workload(torch, api, args, dev, rank)
