@@ -1068,9 +1068,8 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
         }
         const uint32_t row_flags = sl->cfg.flags;
         const float cexp = sl->cfg.inv_t * kLog2e;
-        // running maxima (the two largest iteration maxima of this lane: two distinct logits), reference exponent
-        // ceil(m1 * cexp), sum 2^(x * cexp - e_t)
-        float m1 = -INFINITY, m2 = -INFINITY, e_t = 0.f, s_t = 0.f;
+        // the lane's running maximum, reference exponent ceil(m1 * cexp), sum 2^(x * cexp - e_t)
+        float m1 = -INFINITY, e_t = 0.f, s_t = 0.f;
         uint32_t tau_key = 0u;  // the threshold's ordering key as this warp last saw it (0: none)
         float tau_f = -INFINITY;
         bool st_fail = false;
@@ -1185,9 +1184,9 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         s_t += (acc[0] + acc[1]) + (acc[2] + acc[3]);
                     }
                 }
-                // The lane's two largest iteration maxima: what the first threshold is made of (iteration 0), and the running
-                // maximum of the sum (the GENERAL form).  For the bounds the marked words do not count: their raw logits are
-                // not the row's.
+                // The lane's maximum: what the first threshold is made of (iteration 0: the largest of the logits the lane has
+                // just read), and the running maximum of the sum (the GENERAL form).  For the threshold the marked words do not
+                // count: their raw logits are not the row's.
                 if (MODE == SM_GENERAL || iter == 0) {
                     float vb = vm;
                     if (lazy) {
@@ -1196,28 +1195,23 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         for (int i = 0; i < NW; ++i)
                             if (!((marked >> i) & 1u)) vb = fmaxf(vb, max_of<VE>(xv + i * VE));
                     }
-                    m2 = fmaxf(m2, fminf(m1, vb));
                     m1 = fmaxf(m1, vb);
                 }
                 if (iter == 0) {
-                    // The row's first threshold: every warp names its bound from what it has just read and the warps meet (their
-                    // one meeting per row); what this lane read is tested against the agreed bound below, from its registers.
+                    // The row's first threshold: the warps meet (their one meeting per row); what this lane read is tested against
+                    // the agreed threshold below, from its registers.
                     // The warp publishes its largest lane maxima, in descending order: 8 for a small-K row, Q_TOP otherwise.
                     const uint32_t rank0 = sl->cfg.rank0;
                     {
                         const int ntop = sl->cfg.K <= uint32_t(Q_SMALL_K) ? 8 : Q_TOP;
-                        uint32_t kv0 = m1 == -INFINITY ? 0u : key_of(m1), kv1 = m2 == -INFINITY ? 0u : key_of(m2);
+                        uint32_t kv = m1 == -INFINITY ? 0u : key_of(m1);  // (0: none, or taken already)
                         uint32_t mine = 0u;
 #pragma unroll 1
                         for (int t = 0; t < ntop; ++t) {
-                            const uint32_t mx = kv0 > kv1 ? kv0 : kv1;
-                            const uint32_t top = __reduce_max_sync(0xffffffffu, mx);
+                            const uint32_t top = __reduce_max_sync(0xffffffffu, kv);
                             if (lane == t) mine = top;
-                            const uint32_t holders = __ballot_sync(0xffffffffu, mx == top && top != 0u);
-                            if (lane == __ffs(int(holders)) - 1) {
-                                if (kv0 == top) kv0 = 0u;
-                                else kv1 = 0u;
-                            }
+                            const uint32_t holders = __ballot_sync(0xffffffffu, kv == top && top != 0u);
+                            if (lane == __ffs(int(holders)) - 1) kv = 0u;
                         }
                         if (lane < Q_TOP) sl->wtop[sw * Q_TOP + lane] = mine;
                         __syncwarp();
