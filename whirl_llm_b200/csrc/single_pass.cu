@@ -1203,7 +1203,8 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     // The warp publishes its largest lane maxima, in descending order: 8 for a small-K row, Q_TOP otherwise.
                     const uint32_t rank0 = sl->cfg.rank0;
                     {
-                        const int ntop = sl->cfg.K <= uint32_t(Q_SMALL_K) ? 8 : Q_TOP;
+                        const bool small_k = sl->cfg.K <= uint32_t(Q_SMALL_K);
+                        const int ntop = small_k ? 8 : Q_TOP;
                         uint32_t kv = m1 == -INFINITY ? 0u : key_of(m1);  // (0: none, or taken already)
                         uint32_t mine = 0u;
 #pragma unroll 1
@@ -1213,7 +1214,8 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                             const uint32_t holders = __ballot_sync(0xffffffffu, kv == top && top != 0u);
                             if (lane == __ffs(int(holders)) - 1) kv = 0u;
                         }
-                        if (lane < Q_TOP) sl->wtop[sw * Q_TOP + lane] = mine;
+                        // (a small-K row's 128 keys lie packed at the front: four per lane to read back instead of eight)
+                        if (lane < ntop) sl->wtop[sw * ntop + lane] = mine;
                         __syncwarp();
                     }
                     if (lane == 0) mbar_arrive(&head_done[p]);
@@ -1228,13 +1230,15 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     // first_rank's guess.
                     uint32_t kmin = 0u;
                     {
-                        const uint4 qa = *reinterpret_cast<const uint4*>(&sl->wtop[8 * lane]);  // (written before the meeting's barrier)
-                        const uint4 qb = *reinterpret_cast<const uint4*>(&sl->wtop[8 * lane + 4]);
+                        const bool small_k = sl->cfg.K <= uint32_t(Q_SMALL_K);
+                        // (written before the meeting's barrier)
+                        const uint4 qa = *reinterpret_cast<const uint4*>(&sl->wtop[small_k ? 4 * lane : 8 * lane]);
+                        const uint4 qb = small_k ? make_uint4(0u, 0u, 0u, 0u) : *reinterpret_cast<const uint4*>(&sl->wtop[8 * lane + 4]);
 #pragma unroll 1
                         for (int b = 31; b >= 12; --b) {
                             const uint32_t cand = kmin | (1u << b);
-                            const uint32_t c = (qa.x >= cand ? 1u : 0u) + (qa.y >= cand ? 1u : 0u) + (qa.z >= cand ? 1u : 0u) + (qa.w >= cand ? 1u : 0u) +
-                                               (qb.x >= cand ? 1u : 0u) + (qb.y >= cand ? 1u : 0u) + (qb.z >= cand ? 1u : 0u) + (qb.w >= cand ? 1u : 0u);
+                            uint32_t c = (qa.x >= cand ? 1u : 0u) + (qa.y >= cand ? 1u : 0u) + (qa.z >= cand ? 1u : 0u) + (qa.w >= cand ? 1u : 0u);
+                            if (!small_k) c += (qb.x >= cand ? 1u : 0u) + (qb.y >= cand ? 1u : 0u) + (qb.z >= cand ? 1u : 0u) + (qb.w >= cand ? 1u : 0u);
                             if (__reduce_add_sync(0xffffffffu, c) >= rank0) kmin = cand;
                         }
                     }
