@@ -1234,8 +1234,32 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         // (written before the meeting's barrier)
                         const uint4 qa = *reinterpret_cast<const uint4*>(&sl->wtop[small_k ? 4 * lane : 8 * lane]);
                         const uint4 qb = small_k ? make_uint4(0u, 0u, 0u, 0u) : *reinterpret_cast<const uint4*>(&sl->wtop[8 * lane + 4]);
+                        // (All published keys share their leading bits - sign, exponent, often some of the mantissa - and the
+                        // answer shares them too: the search starts below the common prefix of the largest and the smallest.)
+                        uint32_t hi = max(max(qa.x, qa.y), max(qa.z, qa.w)), lo = 0xffffffffu, nz = 0;
+                        if (!small_k) hi = max(hi, max(max(qb.x, qb.y), max(qb.z, qb.w)));
+                        {
+                            const uint32_t v8[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                if (v8[i] != 0u) lo = min(lo, v8[i]), ++nz;
+                        }
+                        hi = __reduce_max_sync(0xffffffffu, hi);
+                        lo = __reduce_min_sync(0xffffffffu, lo);
+                        nz = __reduce_add_sync(0xffffffffu, nz);
+                        int b_start = -1;
+                        if (nz >= rank0 && hi != 0u) {  // (else: fewer keys than rank0, no threshold)
+                            const uint32_t diff = hi ^ lo;
+                            if (diff == 0u) {
+                                kmin = hi & 0xfffff000u;  // (all keys equal)
+                            } else {
+                                b_start = 31 - __clz(int(diff));
+                                kmin = b_start >= 31 ? 0u : (hi & ~((2u << b_start) - 1u));
+                                if (b_start < 12) kmin &= 0xfffff000u;
+                            }
+                        }
 #pragma unroll 1
-                        for (int b = 31; b >= 12; --b) {
+                        for (int b = b_start; b >= 12; --b) {
                             const uint32_t cand = kmin | (1u << b);
                             uint32_t c = (qa.x >= cand ? 1u : 0u) + (qa.y >= cand ? 1u : 0u) + (qa.z >= cand ? 1u : 0u) + (qa.w >= cand ? 1u : 0u);
                             if (!small_k) c += (qb.x >= cand ? 1u : 0u) + (qb.y >= cand ? 1u : 0u) + (qb.z >= cand ? 1u : 0u) + (qb.w >= cand ? 1u : 0u);
