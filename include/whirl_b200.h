@@ -222,6 +222,13 @@ struct whirl_sample_out {
     uint32_t* counters; /* [WHIRL_CNT_WORDS] added to, never cleared */
 };
 
+/* ws: whirl_workspace_bytes(rows, n) bytes of device memory, contents arbitrary; a workspace serves one call at a time
+ * (calls on different streams need their own).  Rows of 16-byte aligned logits, at least 32 KiB long, that keep at most
+ * WHIRL_STREAM_MAX_K candidates at the first level (their top_k, or 256 without one) are read from memory once; other
+ * rows, and rows that need the second (16384 candidates) or third (whole row) level, take several passes.  When stats is
+ * null, rows whose top_k closes their kept set skip the softmax normaliser altogether.  Every row comes back
+ * WHIRL_ROW_DONE but for the corner cases named at WHIRL_ROW_ESCALATE; counters and whirl_check report what the device
+ * met on the way. */
 int whirl_sample_rows(const void* x, int dtype, int rows, int n, const whirl_sample_params* params,
                       const whirl_sample_out* out, void* ws, size_t ws_bytes, void* stream);
 
