@@ -30,6 +30,63 @@ __device__ __forceinline__ float elem(const T* row, uint32_t i, const PenaltyTab
     return x;
 }
 
+// BODY (a statement that reads the float V_ and the index I_) for every logit of the row that this thread owns, each
+// thread's indices in ascending order.  The loads go out in batches before the first of them is used (with one load in
+// flight per thread a CTA reads a row at a few GB/s): four 128-bit words per batch when the row is 16-byte aligned and a
+// whole number of words long (the thread then owns words tid, tid + GT, ...), else eight single logits (tid, tid + GT, ...).
+template <typename T>
+__device__ __forceinline__ float word_elem(const uint4& w, int e) {
+    const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+    if (sizeof(T) == 4) return __uint_as_float(u[e]);
+    return __uint_as_float((e & 1) ? (u[e >> 1] & 0xffff0000u) : (u[e >> 1] << 16));
+}
+#define WB_ELEM_STEP_(PT, V_, I_, RAW, BODY)                      \
+    {                                                             \
+        float V_ = (RAW);                                         \
+        if ((PT).on && (PT).hit(I_)) V_ = (PT).apply(V_, I_);     \
+        BODY                                                      \
+    }
+#define WB_FOR_EACH_ELEM(TY, ROW, N, TID, PT, V_, I_, BODY)                                                        \
+    do {                                                                                                           \
+        constexpr uint32_t ve_ = 16 / sizeof(TY);                                                                  \
+        if ((reinterpret_cast<uintptr_t>(ROW) & 15) == 0 && (N) % ve_ == 0) {                                      \
+            const uint4* rq_ = reinterpret_cast<const uint4*>(ROW);                                                \
+            const uint32_t nq_ = (N) / ve_;                                                                        \
+            uint32_t q0_ = uint32_t(TID);                                                                          \
+            _Pragma("unroll 1") for (; q0_ + 3u * GT < nq_; q0_ += 4u * GT) {                                      \
+                uint4 w_[4];                                                                                       \
+                _Pragma("unroll") for (int j_ = 0; j_ < 4; ++j_) w_[j_] = rq_[q0_ + uint32_t(j_) * GT];            \
+                _Pragma("unroll") for (int j_ = 0; j_ < 4; ++j_) {                                                 \
+                    _Pragma("unroll") for (int e_ = 0; e_ < int(ve_); ++e_) {                                      \
+                        const uint32_t I_ = (q0_ + uint32_t(j_) * GT) * ve_ + uint32_t(e_);                        \
+                        WB_ELEM_STEP_(PT, V_, I_, word_elem<TY>(w_[j_], e_), BODY)                                 \
+                    }                                                                                              \
+                }                                                                                                  \
+            }                                                                                                      \
+            _Pragma("unroll 1") for (; q0_ < nq_; q0_ += GT) {                                                     \
+                const uint4 w1_ = rq_[q0_];                                                                        \
+                _Pragma("unroll") for (int e_ = 0; e_ < int(ve_); ++e_) {                                          \
+                    const uint32_t I_ = q0_ * ve_ + uint32_t(e_);                                                  \
+                    WB_ELEM_STEP_(PT, V_, I_, word_elem<TY>(w1_, e_), BODY)                                        \
+                }                                                                                                  \
+            }                                                                                                      \
+        } else {                                                                                                   \
+            uint32_t i0_ = uint32_t(TID);                                                                          \
+            _Pragma("unroll 1") for (; i0_ + 7u * GT < (N); i0_ += 8u * GT) {                                      \
+                float raw_[8];                                                                                     \
+                _Pragma("unroll") for (int j_ = 0; j_ < 8; ++j_) raw_[j_] = raw_elem((ROW), i0_ + uint32_t(j_) * GT); \
+                _Pragma("unroll") for (int j_ = 0; j_ < 8; ++j_) {                                                 \
+                    const uint32_t I_ = i0_ + uint32_t(j_) * GT;                                                   \
+                    WB_ELEM_STEP_(PT, V_, I_, raw_[j_], BODY)                                                      \
+                }                                                                                                  \
+            }                                                                                                      \
+            _Pragma("unroll 1") for (; i0_ < (N); i0_ += GT) {                                                     \
+                const uint32_t I_ = i0_;                                                                           \
+                WB_ELEM_STEP_(PT, V_, I_, raw_elem((ROW), I_), BODY)                                               \
+            }                                                                                                      \
+        }                                                                                                          \
+    } while (0)
+
 struct GShared {
     uint32_t prefix, remain, cnt, eq;
     float m;
@@ -186,7 +243,7 @@ __device__ void draft_tail(const SelectArgs& a, int row, const unsigned long lon
 
 // grid-strided over the rows (or over the entries of row_list); one row at a time per CTA
 template <typename T>
-__global__ void __launch_bounds__(GT) select_generic_kernel(SelectArgs a, int cap_max, int pen_words) {
+__global__ void __launch_bounds__(GT, 1) select_generic_kernel(SelectArgs a, int cap_max, int pen_words) {
     extern __shared__ __align__(16) uint8_t smem[];
     uint64_t* cand = reinterpret_cast<uint64_t*>(smem);
     uint32_t* hist = reinterpret_cast<uint32_t*>(smem + size_t(cap_max) * 8);
@@ -323,13 +380,12 @@ __device__ int select_row(const SelectArgs& a, int row, int level_k, int cap_max
     // ---- greedy rows: the first maximum
     if (sample && P.greedy && P.greedy[row]) {
         uint64_t best = 0;  // composite of the best element; 0 = none
-        for (uint32_t i = tid; i < n; i += GT) {
-            const float v = elem(x, i, pt);
+        WB_FOR_EACH_ELEM(T, x, n, tid, pt, v, i, {
             if (v == v) {
                 const uint64_t c = make_cand(key_of(v), i);
                 best = c > best ? c : best;
             }
-        }
+        });
         best = warp_max(best);
         if (lane_id() == 0) sh->red_c[tid >> 5] = best;
         __syncthreads();
@@ -367,14 +423,13 @@ __device__ int select_row(const SelectArgs& a, int row, int level_k, int cap_max
     {
         const float c = inv_t * kLog2e;
         float m = -INFINITY, s = 0.f;
-        for (uint32_t i = tid; i < n; i += GT) {
-            const float v = elem(x, i, pt);
+        WB_FOR_EACH_ELEM(T, x, n, tid, pt, v, i, {
             if (v > m) {
                 s = (m == -INFINITY) ? 0.f : s * ex2_approx((m - v) * c);
                 m = v;
             }
             if (v == v && m != -INFINITY) s += ex2_approx((v - m) * c);
-        }
+        });
         const float wm = warp_max(m);
         double ds = (m == -INFINITY) ? 0.0 : double(s) * double(ex2_approx((m - wm) * c));
         ds = warp_sum(ds);
@@ -397,10 +452,11 @@ __device__ int select_row(const SelectArgs& a, int row, int level_k, int cap_max
     for (int ps = 0; ps < 3 && K > 0; ++ps) {
         const uint32_t prefix = sh->prefix;
         const uint32_t bm = (1u << widths[ps]) - 1;
-        for (uint32_t i = tid; i < n; i += GT) {
-            const uint32_t k = key_of(elem(x, i, pt));
-            if ((k & mask) == prefix) atomicAdd(&hist[(k >> shifts[ps]) & bm], 1u);
-        }
+        const int sh_ps = shifts[ps];
+        WB_FOR_EACH_ELEM(T, x, n, tid, pt, v, i, {
+            const uint32_t k = key_of(v);
+            if ((k & mask) == prefix) atomicAdd(&hist[(k >> sh_ps) & bm], 1u);
+        });
         pick_bin<true>(hist, sh, shifts[ps], widths[ps]);
         mask |= bm << shifts[ps];
     }
@@ -427,12 +483,14 @@ __device__ int select_row(const SelectArgs& a, int row, int level_k, int cap_max
     // ---- collect
     uint32_t cap = 1;
     while (cap < K) cap <<= 1;
-    for (uint32_t i = tid; i < n && K > 0; i += GT) {
-        const uint32_t k = key_of(elem(x, i, pt));
-        if (k > thr || (k == thr && i <= id_thr)) {
-            const uint32_t pos = atomicAdd(&sh->cnt, 1u);
-            if (pos < cap) cand[pos] = make_cand(k, i);
-        }
+    if (K > 0) {
+        WB_FOR_EACH_ELEM(T, x, n, tid, pt, v, i, {
+            const uint32_t k = key_of(v);
+            if (k > thr || (k == thr && i <= id_thr)) {
+                const uint32_t pos = atomicAdd(&sh->cnt, 1u);
+                if (pos < cap) cand[pos] = make_cand(k, i);
+            }
+        });
     }
     for (uint32_t i = K + tid; i < cap; i += GT) cand[i] = 0;
     __syncthreads();
