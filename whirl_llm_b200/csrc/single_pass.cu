@@ -975,13 +975,14 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     g.sync();
                     write_survivors<Q_TT>(g, log, nlog, kth, list, uint32_t(SEL_BINS / 2), &sh->sel);
                     uint32_t bk = sh->sel.wcnt < uint32_t(SEL_BINS / 2) ? sh->sel.wcnt : uint32_t(SEL_BINS / 2);
-                    uint32_t bcap = 1;
-                    while (bcap < bk) bcap <<= 1;
+                    constexpr uint32_t bcap = 4 * Q_TT;  // (the sort takes four candidates per thread: the list is padded to that)
+                    static_assert(bcap == SEL_BINS / 2 && bcap >= kSinglePassMaxK, "the select scratch holds the padded candidates");
                     g.sync();
                     for (uint32_t i = bk + g.tid; i < bcap; i += Q_TT) list[i] = 0ull;
                     g.sync();
+                    sort_desc_x4<Q_TT>(g, reinterpret_cast<uint64_t*>(list));
                     double* bp = reinterpret_cast<double*>(log);
-                    finish_row(g, cfg, reinterpret_cast<uint64_t*>(list), bp, bp + bcap + 2 * Q_TW, bk, bcap, false, false, false, M, sum);
+                    finish_row(g, cfg, reinterpret_cast<uint64_t*>(list), bp, bp + bcap + 2 * Q_TW, bk, bcap, true, false, false, M, sum);
                     g.sync();
                     for (uint32_t i = g.tid; i < uint32_t(Q_L); i += Q_TT) log[i] = 0ull;
                 } else if (!overflow) {

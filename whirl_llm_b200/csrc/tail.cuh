@@ -88,6 +88,54 @@ __device__ __noinline__ void sort_desc(const Group<NT>& g, uint64_t* cand, uint3
     }
 }
 
+// Descending order for exactly 4 * NT candidates, four of them in every thread's registers: exchanges at distances below 4
+// run inside a thread, below 128 over warp shuffles, and only the few at 128 and above go through shared memory (with a
+// barrier pair each).  cand[] holds the result.
+template <int NT>
+__device__ __noinline__ void sort_desc_x4(const Group<NT>& g, uint64_t* cand) {
+    constexpr uint32_t CAP = 4 * NT;
+    unsigned long long v0, v1, v2, v3;
+    const uint32_t base = uint32_t(g.tid) * 4;
+    v0 = cand[base], v1 = cand[base + 1], v2 = cand[base + 2], v3 = cand[base + 3];
+    auto cx = [](unsigned long long& a, unsigned long long& b, bool desc) {  // a before b
+        const unsigned long long lo = a < b ? a : b, hi = a < b ? b : a;
+        a = desc ? hi : lo, b = desc ? lo : hi;
+    };
+    auto keep = [](unsigned long long mine, unsigned long long other, bool keep_max) {
+        return keep_max ? (mine > other ? mine : other) : (mine < other ? mine : other);
+    };
+#pragma unroll 1
+    for (uint32_t k = 2; k <= CAP; k <<= 1) {
+#pragma unroll 1
+        for (uint32_t j = k >> 1; j > 0; j >>= 1) {
+            if (j >= 128) {
+                g.sync();  // (the reads of the exchange before this one are over)
+                cand[base] = v0, cand[base + 1] = v1, cand[base + 2] = v2, cand[base + 3] = v3;
+                g.sync();
+                const bool km = ((base & j) == 0) == ((base & k) == 0);  // (the same for the thread's four: j, k >= 4)
+                v0 = keep(v0, cand[base ^ j], km), v1 = keep(v1, cand[(base + 1) ^ j], km);
+                v2 = keep(v2, cand[(base + 2) ^ j], km), v3 = keep(v3, cand[(base + 3) ^ j], km);
+            } else if (j >= 4) {
+                const int lx = int(j >> 2);
+                const bool km = ((base & j) == 0) == ((base & k) == 0);
+                v0 = keep(v0, __shfl_xor_sync(0xffffffffu, v0, lx), km), v1 = keep(v1, __shfl_xor_sync(0xffffffffu, v1, lx), km);
+                v2 = keep(v2, __shfl_xor_sync(0xffffffffu, v2, lx), km), v3 = keep(v3, __shfl_xor_sync(0xffffffffu, v3, lx), km);
+            } else if (j == 2) {
+                // pairs (0, 2) and (1, 3); k >= 4, so the direction is the same for the thread's four
+                const bool desc = (base & k) == 0;
+                cx(v0, v2, desc), cx(v1, v3, desc);
+            } else {
+                // j == 1: pairs (0, 1) and (2, 3); for k == 2 the second pair runs the other way
+                const bool d01 = (base & k) == 0, d23 = ((base + 2) & k) == 0;
+                cx(v0, v1, d01), cx(v2, v3, d23);
+            }
+        }
+    }
+    g.sync();
+    cand[base] = v0, cand[base + 1] = v1, cand[base + 2] = v2, cand[base + 3] = v3;
+    g.sync();
+}
+
 // ---- sums over the sorted candidates, by one warp.  Lane l owns the l-th block of ceil(n / 32) consecutive terms: terms are
 // added in candidate order inside a block and the block sums are combined in block order.  (The host adds all terms in one
 // sequence; the two orders differ by rounding in the last place only, the same size as the difference between the
