@@ -303,6 +303,36 @@ __device__ __forceinline__ float max_of(const float* v) {
     return t[0];
 }
 
+// Two bf16 maxima in one instruction (max.bf16x2 skips NaN like fmaxf): a bf16 row has twice the logits per byte, and
+// widening each of them to f32 before comparing would cost the stream warps three times the ALU work of an f32 row.
+__device__ __forceinline__ uint32_t bmax2(uint32_t a, uint32_t b) {
+    uint32_t d;
+    asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ float bmax2_wide(uint32_t m) { return fmaxf(__uint_as_float(m << 16), __uint_as_float(m & 0xffff0000u)); }
+// The largest logit of NWORDS 128-bit words of a row of T.
+template <typename T, int NWORDS>
+__device__ __forceinline__ float words_max(const uint4* w) {
+    if (sizeof(T) == 4) {
+        float x[NWORDS * 4];
+#pragma unroll
+        for (int i = 0; i < NWORDS; ++i)
+            x[4 * i] = __uint_as_float(w[i].x), x[4 * i + 1] = __uint_as_float(w[i].y), x[4 * i + 2] = __uint_as_float(w[i].z),
+                  x[4 * i + 3] = __uint_as_float(w[i].w);
+        return max_of<NWORDS * 4>(x);
+    } else {
+        uint32_t m[NWORDS];
+#pragma unroll
+        for (int i = 0; i < NWORDS; ++i) m[i] = bmax2(bmax2(w[i].x, w[i].y), bmax2(w[i].z, w[i].w));
+#pragma unroll
+        for (int s = 1; s < NWORDS; s <<= 1)
+#pragma unroll
+            for (int i = 0; i + s < NWORDS; i += 2 * s) m[i] = bmax2(m[i], m[i + s]);
+        return bmax2_wide(m[0]);
+    }
+}
+
 // ---- the small-K threshold keeper (a warp of its own, while a row streams)
 // 32 ordering keys, one per lane, into descending order over the lanes (a bitonic network of shuffles).
 __device__ __forceinline__ uint32_t warp_sort_desc(uint32_t x, int lane) {
@@ -1147,21 +1177,27 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         marked = 0;
                     }
                 }
+                // The logits as f32: free for an f32 row; a bf16 row widens them only where it needs them one by one (the sum of
+                // the GENERAL form, an iteration with something to log).
                 float xv[NW * VE];
+                auto widen = [&]() {
 #pragma unroll
-                for (int i = 0; i < NW; ++i) {
-                    const uint32_t w4[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
-                    float* x = xv + i * VE;
-                    if (sizeof(T) == 4) {
+                    for (int i = 0; i < NW; ++i) {
+                        const uint32_t w4[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+                        float* x = xv + i * VE;
+                        if (sizeof(T) == 4) {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) x[e] = __uint_as_float(w4[e]);
-                    } else {
+                            for (int e = 0; e < 4; ++e) x[e] = __uint_as_float(w4[e]);
+                        } else {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) x[2 * e] = __uint_as_float(w4[e] << 16), x[2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
+                            for (int e = 0; e < 4; ++e) x[2 * e] = __uint_as_float(w4[e] << 16), x[2 * e + 1] = __uint_as_float(w4[e] & 0xffff0000u);
+                        }
                     }
-                }
+                };
+                constexpr bool WIDEN_FIRST = sizeof(T) == 4 || MODE == SM_GENERAL;
+                if (WIDEN_FIRST) widen();
                 // the iteration's largest logit (a NaN logit never raises a maximum)
-                const float vm = max_of<NW * VE>(xv);
+                const float vm = words_max<T, NW>(w);
                 // Every loaded register has been consumed, so the shared-memory reads have completed (instructions issue in
                 // order and the maximum had to wait for the data): only now may the producer overwrite the stages.
                 __syncwarp();
@@ -1194,7 +1230,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         vb = -INFINITY;
 #pragma unroll
                         for (int i = 0; i < NW; ++i)
-                            if (!((marked >> i) & 1u)) vb = fmaxf(vb, max_of<VE>(xv + i * VE));
+                            if (!((marked >> i) & 1u)) vb = fmaxf(vb, words_max<T, 1>(w + i));
                     }
                     m1 = fmaxf(m1, vb);
                 }
@@ -1282,6 +1318,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         const uint4 mw = *reinterpret_cast<const uint4*>(gbm + ((iter * Q_SW + uint32_t(sw)) << 2));
                         marked = ((mw.x >> lane) & 1u) | (((mw.y >> lane) & 1u) << 1) | (((mw.z >> lane) & 1u) << 2) | (((mw.w >> lane) & 1u) << 3);
                     }
+                    if (!WIDEN_FIRST) widen();
                     uint32_t hm = 0;  // bit j: this lane's logit j is at or above the threshold
 #pragma unroll
                     for (int j = 0; j < NW * VE; ++j) hm |= (xv[j] >= tau_f ? 1u : 0u) << j;
