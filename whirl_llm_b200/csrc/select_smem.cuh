@@ -13,6 +13,7 @@ constexpr int SEL_LIST = 256;  // rank directly when the target bin holds at mos
 struct SelScratch {
     unsigned long long lo, hi, kth;
     uint32_t bin, need, eq, lcnt, wcnt;
+    uint32_t klo, khi, maxc;
     uint32_t wsum[32];
 };
 
@@ -161,6 +162,143 @@ __device__ __noinline__ void write_survivors(const Group<NT>& g, const unsigned 
         }
     }
     g.sync();
+}
+
+// The K largest of buf[0..cnt) in descending order, by one histogram instead of a selection followed by a sorting
+// network: the entries' ordering keys are spread over SB_BINS bins between the smallest and the largest key (the bin is
+// monotone in the key, equal keys share a bin), a scan of the bin counts gives every bin its first place in the output,
+// the entries are scattered to their bins' places, and each one then finds its exact place by counting the larger
+// entries of its own bin.  The bin that straddles place K goes through a side list (xlist), where its entries rank
+// themselves and the first of them take the places that are left.  Work per entry is a few instructions plus the size of
+// its bin, against the several hundred compare-exchanges per entry of a network.
+// buf: entries distinct; zero = empty; entries below `floor` count as empty too (the caller knows that at least
+// min(K, what is there) entries are at or above it).  K <= 4 * NT.  bins: SB_BINS words; out: K entries; xlist: SB_X
+// entries.  Returns false, with nothing usable in out, when one bin holds more than SB_X entries (many equal logits): the
+// caller then takes the selection-and-network path.  On success sc->wcnt = entries written, out[0..wcnt) descending.
+constexpr int SB_BINS = 1024;
+constexpr int SB_X = 256;
+template <int NT>
+__device__ __noinline__ bool bucket_sort_top(const Group<NT>& g, const unsigned long long* buf, uint32_t cnt, uint32_t K,
+                                             unsigned long long floor, uint32_t* bins, unsigned long long* out,
+                                             unsigned long long* xlist, SelScratch* sc) {
+    constexpr int PER = SB_BINS / NT;
+    static_assert(PER == 4 && SB_X <= NT, "four bins per thread, one side-list entry per thread");
+    // ---- the keys' range
+    if (g.tid == 0) sc->klo = 0xffffffffu, sc->khi = 0u, sc->maxc = 0u, sc->bin = 0xffffffffu, sc->need = 0u, sc->eq = 0u, sc->wcnt = 0u;
+    reinterpret_cast<uint4*>(bins)[g.tid] = make_uint4(0, 0, 0, 0);
+    g.sync();
+    {
+        uint32_t lo = 0xffffffffu, hi = 0u;
+#pragma unroll 1
+        for (uint32_t i = g.tid; i < cnt; i += NT) {
+            const unsigned long long c = buf[i];
+            if (c != 0ull && c >= floor) {
+                const uint32_t k = cand_key(c);
+                lo = min(lo, k), hi = max(hi, k);
+            }
+        }
+        lo = __reduce_min_sync(0xffffffffu, lo), hi = __reduce_max_sync(0xffffffffu, hi);
+        if ((g.tid & 31) == 0) atomicMin(&sc->klo, lo), atomicMax(&sc->khi, hi);
+    }
+    g.sync();
+    const uint32_t klo = sc->klo, khi = sc->khi;
+    if (klo > khi) {  // (nothing there)
+        g.sync();
+        return true;
+    }
+    // bin 0 holds the largest keys
+    const float inv = float(SB_BINS) / (float(khi - klo) + 1.0f) * 0.99999f;
+    auto bin_of = [&](unsigned long long c) -> uint32_t {
+        const uint32_t b = uint32_t(float(cand_key(c) - klo) * inv);
+        return uint32_t(SB_BINS - 1) - min(b, uint32_t(SB_BINS - 1));
+    };
+#pragma unroll 1
+    for (uint32_t i = g.tid; i < cnt; i += NT) {
+        const unsigned long long c = buf[i];
+        if (c != 0ull && c >= floor) atomicAdd(&bins[bin_of(c)], 1u);
+    }
+    g.sync();
+    // ---- every bin's first place: an exclusive scan of the counts (thread t owns bins 4t .. 4t + 3)
+    {
+        const uint4 v = reinterpret_cast<const uint4*>(bins)[g.tid];
+        const uint32_t c[4] = {v.x, v.y, v.z, v.w};
+        const uint32_t s = c[0] + c[1] + c[2] + c[3];
+        const uint32_t incl_w = warp_scan_incl(s);
+        if ((g.tid & 31) == 31) sc->wsum[g.tid >> 5] = incl_w;
+        g.sync();
+        uint32_t before = 0;
+#pragma unroll 1
+        for (int w = 0; w < (g.tid >> 5); ++w) before += sc->wsum[w];
+        uint32_t st[4];
+        st[0] = before + incl_w - s, st[1] = st[0] + c[0], st[2] = st[1] + c[1], st[3] = st[2] + c[2];
+        reinterpret_cast<uint4*>(bins)[g.tid] = make_uint4(st[0], st[1], st[2], st[3]);
+        uint32_t mc = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (st[j] < K) mc = max(mc, c[j]);
+            if (st[j] < K && st[j] + c[j] > K) sc->bin = uint32_t(4 * g.tid + j), sc->need = K - st[j], sc->eq = c[j];  // (at most one bin)
+        }
+        mc = __reduce_max_sync(0xffffffffu, mc);
+        if ((g.tid & 31) == 0 && mc) atomicMax(&sc->maxc, mc);
+        if (g.tid == NT - 1) sc->lcnt = st[3] + c[3];  // entries in all
+    }
+    g.sync();
+    if (sc->maxc > uint32_t(SB_X)) {
+        g.sync();
+        return false;
+    }
+    const uint32_t xbin = sc->bin, x_need = sc->need, x_cnt = sc->eq, total = sc->lcnt;
+    const uint32_t kept = total < K ? total : K;
+    const uint32_t x_start = xbin != 0xffffffffu ? K - x_need : kept;  // places filled by whole bins
+    // ---- scatter: a bin's counter now hands out its places (and ends as the bin's end); bins past place K drop out
+#pragma unroll 1
+    for (uint32_t i = g.tid; i < cnt; i += NT) {
+        const unsigned long long c = buf[i];
+        if (c != 0ull && c >= floor) {
+            const uint32_t b = bin_of(c);
+            if (b == xbin) {
+                xlist[atomicAdd(&sc->wcnt, 1u)] = c;
+            } else {
+                const uint32_t pos = atomicAdd(&bins[b], 1u);
+                if (pos < K) out[pos] = c;
+            }
+        }
+    }
+    g.sync();
+    // ---- the exact place of every kept entry: its bin's first place plus the larger entries of the bin
+    unsigned long long item[4];
+    uint32_t np[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const uint32_t i = uint32_t(r) * NT + uint32_t(g.tid);
+        np[r] = 0xffffffffu;
+        if (i < x_start) {
+            const unsigned long long mine = out[i];
+            const uint32_t b = bin_of(mine);
+            const uint32_t e = bins[b], s0 = b ? bins[b - 1] : 0u;  // (the bins before a kept one are whole bins: their counters hold their ends)
+            uint32_t rank = 0;
+#pragma unroll 1
+            for (uint32_t j = s0; j < e; ++j) rank += out[j] > mine;
+            item[r] = mine, np[r] = s0 + rank;
+        }
+    }
+    unsigned long long xi = 0ull;
+    uint32_t xp = 0xffffffffu;
+    if (uint32_t(g.tid) < x_cnt) {
+        xi = xlist[g.tid];
+        uint32_t rank = 0;
+#pragma unroll 1
+        for (uint32_t j = 0; j < x_cnt; ++j) rank += xlist[j] > xi;
+        if (rank < x_need) xp = x_start + rank;
+    }
+    g.sync();
+#pragma unroll
+    for (int r = 0; r < 4; ++r)
+        if (np[r] != 0xffffffffu) out[np[r]] = item[r];
+    if (xp != 0xffffffffu) out[xp] = xi;
+    if (g.tid == 0) sc->wcnt = kept;
+    g.sync();
+    return true;
 }
 
 // A lower bound of the K-th largest ordering key among n floats in shared memory (1 <= K <= n): the key's top 22 bits

@@ -789,27 +789,40 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 in.inv_t = inv_t;
                 in.top_k = cfg.top_k;
                 in.top_p = cfg.top_p, in.min_p = cfg.min_p, in.u = cfg.u;
-                if (no_sum) {
-                    // normalise over the candidates themselves: cand[] holds exactly the kept ones, the largest first once sorted
-                    if (!presorted) sort_desc<NT>(grp, cand, cap), presorted = true;
-                    M = float_of_key(cand_key(cand[0]));
+                in.m = M, in.sum = sum, in.cnt = kept, in.cap = cap, in.V = n;
+                in.race = P.race_key != nullptr, in.race_key = cfg.race_key;
+                in.want_p = a.out.kept_p != nullptr && a.out.kept_cap > 0;
+                in.have_e = 0, in.sum_of_e = no_sum;
+                if (!presorted) sort_desc<NT>(grp, cand, cap), presorted = true;
+                in.presorted = 1;
+                bool decided = false;
+                if (kept > 0 && (no_sum || (!in.race && !in.want_p))) {
+                    // the candidates' exponentials (a row normalised over its candidates: cand[] holds exactly the kept ones,
+                    // the largest first)
+                    if (no_sum) M = float_of_key(cand_key(cand[0])), in.m = M;
 #pragma unroll 1
                     for (uint32_t i = grp.tid; i < kept; i += NT) bq[i] = f64_exp(double(__fsub_rn(float_of_key(cand_key(cand[i])), M)) * double(inv_t));
                     grp.sync();
-                    if (grp.tid < 32) {
-                        const double tot = warp_total(bq, kept);
-                        if (first) sh->res.cum = tot;
+                    in.have_e = 1;
+                    if (!in.race && !in.want_p && kept <= 16384u) {
+                        decided = sample_tail_quick<NT>(grp, in, cand, bp, bq, &sh->res);
+                        if (decided && no_sum) sum = sh->res.sum;
+                        grp.sync();
                     }
-                    grp.sync();
-                    sum = float(sh->res.cum);
-                    grp.sync();
                 }
-                in.m = M, in.sum = sum, in.cnt = kept, in.cap = cap, in.V = n;
-                in.race = P.race_key != nullptr, in.race_key = cfg.race_key;
-                in.presorted = presorted;
-                in.want_p = a.out.kept_p != nullptr && a.out.kept_cap > 0;
-                in.have_e = no_sum;  // (the normaliser over the candidates has just left them in bq)
-                sample_tail<NT>(grp, in, cand, bp, bq, &sh->res);
+                if (!decided) {
+                    if (no_sum) {
+                        if (grp.tid < 32) {
+                            const double tot = warp_total(bq, kept);
+                            if (first) sh->res.cum = tot;
+                        }
+                        grp.sync();
+                        sum = float(sh->res.cum);
+                        grp.sync();
+                        in.sum = sum;
+                    }
+                    sample_tail<NT>(grp, in, cand, bp, bq, &sh->res);
+                }
                 const TailOut r = sh->res;
                 if (first) {
                     a.out.token[row] = int32_t(r.token);
@@ -1001,16 +1014,26 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     // sorts them and draws, with the probabilities in the row's log (which nobody reads any more).
                     unsigned long long* list = reinterpret_cast<unsigned long long*>(hist);  // SEL_BINS / 2 entries
                     static_assert(SEL_BINS / 2 >= kSinglePassMaxK && size_t(Q_L) * 8 >= 2 * size_t(kSinglePassMaxK + 2 * Q_TW) * 8, "room for a large-K row");
-                    const unsigned long long kth = nlog > K ? select_kth<Q_TT>(g, log, nlog, K, hist, &sh->sel) : 0ull;
-                    g.sync();
-                    write_survivors<Q_TT>(g, log, nlog, kth, list, uint32_t(SEL_BINS / 2), &sh->sel);
-                    uint32_t bk = sh->sel.wcnt < uint32_t(SEL_BINS / 2) ? sh->sel.wcnt : uint32_t(SEL_BINS / 2);
-                    constexpr uint32_t bcap = 4 * Q_TT;  // (the sort takes four candidates per thread: the list is padded to that)
-                    static_assert(bcap == SEL_BINS / 2 && bcap >= kSinglePassMaxK, "the select scratch holds the padded candidates");
-                    g.sync();
-                    for (uint32_t i = bk + g.tid; i < bcap; i += Q_TT) list[i] = 0ull;
-                    g.sync();
-                    sort_desc_x4<Q_TT>(g, reinterpret_cast<uint64_t*>(list));
+                    // (the hand and the first tail warp's scratch lie idle for such a row: they hold the bins)
+                    uint32_t* bins = reinterpret_cast<uint32_t*>(hand);
+                    constexpr uint32_t bcap = 4 * Q_TT;
+                    static_assert(bcap == SEL_BINS / 2 && bcap >= kSinglePassMaxK, "the select scratch holds the candidates");
+                    static_assert(size_t(kSinglePassHandK) * 8 + 2 * (size_t(kSinglePassHandK) + 2 * Q_TW) * 8 >= size_t(SB_BINS) * 4 + size_t(SB_X) * 8,
+                                  "bins and side list fit the hand and its scratch");
+                    uint32_t bk;
+                    if (bucket_sort_top<Q_TT>(g, log, nlog, K, sl->tau, bins, list, reinterpret_cast<unsigned long long*>(bins + SB_BINS), &sh->sel)) {
+                        bk = sh->sel.wcnt;
+                    } else {
+                        // (many equal logits: the K-th largest of the log, the entries at or above it, a sorting network)
+                        const unsigned long long kth = nlog > K ? select_kth<Q_TT>(g, log, nlog, K, hist, &sh->sel) : 0ull;
+                        g.sync();
+                        write_survivors<Q_TT>(g, log, nlog, kth, list, uint32_t(SEL_BINS / 2), &sh->sel);
+                        bk = sh->sel.wcnt < uint32_t(SEL_BINS / 2) ? sh->sel.wcnt : uint32_t(SEL_BINS / 2);
+                        g.sync();
+                        for (uint32_t i = bk + g.tid; i < bcap; i += Q_TT) list[i] = 0ull;  // (the network takes four per thread)
+                        g.sync();
+                        sort_desc_x4<Q_TT>(g, reinterpret_cast<uint64_t*>(list));
+                    }
                     double* bp = reinterpret_cast<double*>(log);
                     finish_row(g, cfg, reinterpret_cast<uint64_t*>(list), bp, bp + bcap + 2 * Q_TW, bk, bcap, true, false, false, M, sum);
                     g.sync();
@@ -1020,26 +1043,35 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     // can be among the K best (at least K of them are).  Few survive, so rank them against each other: the
                     // rank is the position in the sorted order.
                     unsigned long long* list = reinterpret_cast<unsigned long long*>(hist);  // up to SEL_BINS / 2 entries
-                    write_survivors<Q_TT>(g, log, nlog, sl->tau, list, SEL_BINS / 2, &sh->sel);
-                    const uint32_t m = sh->sel.wcnt;
-                    if (m <= 2u * Q_TT) {
-#pragma unroll 1
-                        for (uint32_t t = g.tid; t < m; t += Q_TT) {
-                            const unsigned long long mine = list[t];
-                            uint32_t rank = 0;
-#pragma unroll 4
-                            for (uint32_t j = 0; j < m; ++j) rank += list[j] > mine;
-                            if (rank < K) hand[rank] = mine;
-                        }
-                        kept = m < K ? m : K;
+                    // (more than 64 candidates: the histogram ranks them; it gives up on rows of many equal logits)
+                    static_assert(SEL_BINS >= SB_BINS + 2 * SB_X, "bins and side list fit the select scratch");
+                    const bool ranked = K > uint32_t(Q_SMALL_K) && bucket_sort_top<Q_TT>(g, log, nlog, K, sl->tau, hist, hand,
+                                                                                         reinterpret_cast<unsigned long long*>(hist + SB_BINS), &sh->sel);
+                    if (ranked) {
+                        kept = sh->sel.wcnt;
                         presorted = true;
-                    } else if (nlog > K) {
-                        const unsigned long long kth = select_kth<Q_TT>(g, log, nlog, K, hist, &sh->sel);
-                        write_survivors<Q_TT>(g, log, nlog, kth, hand, uint32_t(hand_k), &sh->sel);
-                        kept = sh->sel.wcnt < uint32_t(hand_k) ? sh->sel.wcnt : uint32_t(hand_k);
                     } else {
-                        for (uint32_t i = g.tid; i < nlog; i += Q_TT) hand[i] = log[i];
-                        kept = nlog;
+                        write_survivors<Q_TT>(g, log, nlog, sl->tau, list, SEL_BINS / 2, &sh->sel);
+                        const uint32_t m = sh->sel.wcnt;
+                        if (m <= 2u * Q_TT) {
+#pragma unroll 1
+                            for (uint32_t t = g.tid; t < m; t += Q_TT) {
+                                const unsigned long long mine = list[t];
+                                uint32_t rank = 0;
+#pragma unroll 4
+                                for (uint32_t j = 0; j < m; ++j) rank += list[j] > mine;
+                                if (rank < K) hand[rank] = mine;
+                            }
+                            kept = m < K ? m : K;
+                            presorted = true;
+                        } else if (nlog > K) {
+                            const unsigned long long kth = select_kth<Q_TT>(g, log, nlog, K, hist, &sh->sel);
+                            write_survivors<Q_TT>(g, log, nlog, kth, hand, uint32_t(hand_k), &sh->sel);
+                            kept = sh->sel.wcnt < uint32_t(hand_k) ? sh->sel.wcnt : uint32_t(hand_k);
+                        } else {
+                            for (uint32_t i = g.tid; i < nlog; i += Q_TT) hand[i] = log[i];
+                            kept = nlog;
+                        }
                     }
                 }
                 while (cap < kept) cap <<= 1;

@@ -38,12 +38,15 @@ struct TailIn {
     int32_t presorted;  // cand[0..cnt) is already in descending order
     int32_t want_p;     // the caller reads p[] afterwards: leave the kept probabilities renormalised there
     int32_t have_e;     // q[0..cnt) already holds exp((l - m) * inv_t) of the candidates in cand[]'s order (which is sorted)
+    int32_t sum_of_e;   // sample_tail_quick: the normaliser is the sum of those exponentials, rounded to f32 (sum is not read)
 };
 struct TailOut {
     int32_t status;
     uint32_t token, n;
     int32_t closed;
     double cum;  // cumulative mass of the walked candidates (ROW_OPEN_TAIL: where the id-order walk continues)
+    float sum;          // sample_tail_quick with sum_of_e: the normaliser it used
+    int32_t undecided;  // sample_tail_quick: a sum met a bound too closely to call
 };
 
 // f64 exp / log / division are long instruction sequences: one copy each, called (the tail runs once per row, and a
@@ -179,6 +182,111 @@ __device__ __noinline__ uint32_t warp_first_reach(const double* v, uint32_t n, d
     for (int o = 16; o > 0; o >>= 1) first = min(first, __shfl_xor_sync(0xffffffffu, first, o));
     *cum_end = tot;
     return first;
+}
+
+// The first i in [0, n) for which pred(i) holds, n when there is none; pred is false up to some place and true from
+// there on.  One warp, 32 probes per step.
+template <class Pred>
+__device__ __forceinline__ uint32_t warp_first_true(uint32_t n, Pred pred) {
+    const uint32_t lane = uint32_t(lane_id());
+    uint32_t lo = 0, len = n;
+#pragma unroll 1
+    while (len > 32u) {
+        const uint32_t stride = (len + 31u) / 32u;
+        const uint32_t off = min(len, (lane + 1u) * stride);  // the last place of the lane's stretch
+        const uint32_t bal = __ballot_sync(0xffffffffu, pred(lo + off - 1u));
+        if (!bal) return n;
+        const uint32_t f = uint32_t(__ffs(int(bal))) - 1u;
+        lo += f * stride, len = min(stride, len - f * stride);
+    }
+    const uint32_t bal = __ballot_sync(0xffffffffu, lane < len && pred(lo + lane));
+    return bal ? lo + uint32_t(__ffs(int(bal))) - 1u : n;
+}
+
+// The same outcome as sample_tail, decided on the exponentials themselves: with e[i] = exp((l_i - m) * inv_t) and c[i]
+// their running sums, "the probabilities up to i, each divided by z, reach top_p" is c[i] >= top_p * z in the same
+// units, and likewise for the min-p bound and the draw, so no candidate is divided at all, one scan over the whole group
+// gives every partial sum any of the steps asks for, and each cut is a search in a monotone array.  The two ways of
+// computing agree unless a sum meets its bound within rounding; such a row is left undecided (the function returns false
+// and the caller runs sample_tail), so that every decision made here is the one sample_tail makes: a comparison is
+// trusted only when its two sides differ by more than 1e-11 of the normaliser, against at most 2e-12 of accumulated
+// rounding in either form for up to 16384 candidates.
+// cand: sorted; e[0..cnt): the exponentials (kept intact); c: cnt + NT / 32 doubles of scratch.  Not for rows drawn by
+// the race, nor for callers that read the kept probabilities.
+template <int NT>
+__device__ __noinline__ bool sample_tail_quick(const Group<NT>& g, const TailIn& in, const uint64_t* cand, double* c, const double* e, TailOut* res) {
+    const uint32_t cnt = in.cnt;
+    // ---- running sums: thread t adds its stretch in order; the stretches' sums are combined in order
+    {
+        const uint32_t S = (cnt + NT - 1) / NT, b = min(cnt, uint32_t(g.tid) * S), en = min(cnt, b + S);
+        double s = 0;
+#pragma unroll 1
+        for (uint32_t i = b; i < en; ++i) s += e[i];
+        double wtot;
+        double run = warp_excl_scan(s, &wtot);
+        if (NT > 32) {
+            double* wsum = c + cnt;
+            if ((g.tid & 31) == 31) wsum[g.tid >> 5] = wtot;
+            g.sync();
+            double before = 0;
+#pragma unroll 1
+            for (int w = 0; w < (g.tid >> 5); ++w) before += wsum[w];
+            run += before;
+        }
+#pragma unroll 1
+        for (uint32_t i = b; i < en; ++i) run += e[i], c[i] = run;
+    }
+    g.sync();
+    if (g.tid < 32) {
+        const double inf = __longlong_as_double(0x7FF0000000000000ll);
+        const double sum = in.sum_of_e ? double(float(c[cnt - 1])) : double(in.sum);
+        uint32_t n = cnt, token = 0;
+        bool closed = cnt == in.V, esc = false, tight = !(sum > 0.0 && sum < inf);
+        int32_t status = ROW_DONE;
+        double walked = 0.0;
+        auto close_to = [&](const double* v, uint32_t j, uint32_t lim, double t, double tol) {
+            bool r = false;
+            if (j < lim) r = fabs(v[j] - t) <= tol;
+            if (j > 0) r = r || fabs(v[j - 1] - t) <= tol;
+            return r;
+        };
+        if (in.top_k > 0) {
+            if (in.top_k <= cnt) n = in.top_k, closed = true;
+            else if (!closed) esc = true;
+        }
+        if (!esc && !tight && in.top_p < 1.0) {
+            const double z = closed ? c[n - 1] : sum;
+            const double bound = in.top_p * z;
+            const uint32_t j = warp_first_true(n, [&](uint32_t i) { return c[i] >= bound; });
+            tight = close_to(c, j, n, bound, 1e-11 * z);
+            if (j < n) n = j + 1, closed = true;
+            else if (!closed) esc = true;
+        }
+        if (!esc && !tight && in.min_p > 0) {
+            const double thr = in.min_p * e[0];
+            const uint32_t j = warp_first_true(n, [&](uint32_t i) { return !(e[i] >= thr); });
+            tight = close_to(e, j, n, thr, 1e-11 * thr);
+            if (j == n && !closed) esc = true;
+            else n = j > 1 ? j : 1, closed = true;
+        }
+        if (esc) status = ROW_ESCALATE;
+        if (!esc && !tight) {
+            const double z = closed ? c[n - 1] : sum;
+            const double t = in.u * z;
+            const uint32_t i = warp_first_true(n, [&](uint32_t k) { return c[k] > t; });
+            tight = close_to(c, i, n, t, 1e-11 * z);
+            const bool hit = i < n;
+            token = cand_id(cand[hit ? i : n - 1]);  // closed and not hit: the last candidate is the fallback
+            status = (hit || closed) ? ROW_DONE : ROW_OPEN_TAIL;
+            if (status == ROW_OPEN_TAIL) walked = f64_div(c[n - 1], sum);
+        }
+        if (g.tid == 0) {
+            res->status = status, res->token = token, res->n = n, res->closed = closed, res->cum = walked;
+            res->sum = float(sum), res->undecided = tight;
+        }
+    }
+    g.sync();
+    return res->undecided == 0;
 }
 
 // cand: the exact candidate set (any order unless in.presorted, padded with zeros up to cap); p, q: scratch of
