@@ -410,6 +410,7 @@ template <typename T>
 __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a, int stages, int gbm_words, int max_k, int hand_k) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr int VE = 16 / int(sizeof(T));      // logits per 128-bit word
+    constexpr bool LAZY_TABLE = sizeof(T) == 4;  // rows that only mark log entries: the history's table is built while they stream
     uint8_t* ring = smem;                                                                // stages * Q_SB
     unsigned long long* logs = reinterpret_cast<unsigned long long*>(ring + size_t(stages) * Q_SB);  // 2 * Q_L
     uint32_t* hist = reinterpret_cast<uint32_t*>(logs + 2 * Q_L);                        // SEL_BINS
@@ -443,6 +444,32 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
         for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1), mbar_init(&empty[s], Q_SW);
         for (int p = 0; p < 2; ++p) mbar_init(&boot_done[p], 1), mbar_init(&closed[p], Q_SW + 1), mbar_init(&head_done[p], Q_SW);
         mbar_fence_init();
+    }
+    // The first two rows' parameters and histories are asked for now (into L2): the tail group reads them as soon as the
+    // rows are listed, and the stream warps cannot start before it has.
+    if (sample && !a.row_list && tid < 2 * 160) {
+        const int which = tid / 160, t = tid % 160;
+        const int r = int(blockIdx.x) + which * int(gridDim.x);
+        if (which < my_rows) {
+            const void* ptr = nullptr;
+            if (t < 128) {
+                if (P.hist && gbm_words && int64_t(t) * 32 < P.hist_stride) ptr = P.hist + size_t(r) * P.hist_stride + size_t(t) * 32;
+            } else {
+                switch (t - 128) {
+                    case 0: ptr = P.inv_t ? P.inv_t + r : nullptr; break;
+                    case 1: ptr = P.top_p ? P.top_p + r : nullptr; break;
+                    case 2: ptr = P.min_p ? P.min_p + r : nullptr; break;
+                    case 3: ptr = P.u ? P.u + r : nullptr; break;
+                    case 4: ptr = P.race_key ? P.race_key + r : nullptr; break;
+                    case 5: ptr = P.hist_len ? P.hist_len + r : nullptr; break;
+                    case 6: ptr = P.rep ? P.rep + r : nullptr; break;
+                    case 7: ptr = P.pres ? P.pres + r : nullptr; break;
+                    case 8: ptr = P.freq ? P.freq + r : nullptr; break;
+                    default: break;
+                }
+            }
+            if (ptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+        }
     }
     for (int i = tid; i < 2 * Q_L; i += Q_THREADS) logs[i] = 0ull;
     for (int i = tid; i < 2 * gbm_words; i += Q_THREADS) gbms[i] = 0u;
@@ -672,7 +699,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
         // half are all on their way at once and the inserts are one rolled loop.
         auto build_table = [&](int p) {
             const QRow cfg = sh->slot[p].cfg;
-            if ((cfg.flags & (QF_PEN | QF_LAZY)) != QF_PEN) return;  // (only rows that put words aside need it)
+            if (!(cfg.flags & QF_PEN) || ((cfg.flags & QF_LAZY) && !LAZY_TABLE)) return;  // (only rows that will look tokens up)
             constexpr int HALF = kMaxHist / 2;
             constexpr int HP = (HALF + Q_PT - 1) / Q_PT;
             static_assert(HALF <= SEL_BINS, "half a history fits the scratch");
@@ -858,10 +885,10 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 cfg = sl->cfg;
                 const uint32_t K = cfg.K;
                 const bool no_sum = (cfg.flags & QF_NO_SUM) != 0, pen_on = (cfg.flags & QF_PEN) != 0, lazy = (cfg.flags & QF_LAZY) != 0;
-                // (a row with marked log entries will want its history when it is through: the loads go out now)
+                // (a row with marked log entries that has no table will want its history when it is through: the loads go out now)
                 constexpr int HB = kMaxHist / Q_TT;
                 int32_t hv[HB];
-                if (lazy) {
+                if (lazy && !LAZY_TABLE) {
                     const int32_t* h = P.hist + size_t(cfg.row) * P.hist_stride;
 #pragma unroll
                     for (int u = 0; u < HB; ++u) hv[u] = (u * Q_TT + g.tid) < cfg.hist_len ? h[u * Q_TT + g.tid] : -1;
@@ -907,45 +934,66 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     const unsigned long long tau = sl->tau;
                     const float tau_f = cand_key(tau) ? float_of_key(cand_key(tau)) : -INFINITY;
                     if (lazy) {
-                        // The marked entries of the log: logged raw from a word that holds a history token.  A history token
-                        // among them gets its penalty now (another logit of such a word stays as it is).  They are few, so
-                        // their counts come from a scan of the history, not from a table: every thread holds its share of the
-                        // history in registers and all of them count one marked token after the other.
-                        uint32_t* mlist = hist;                 // places in the log of the marked entries
-                        uint32_t* mcnt = hist + SEL_BINS / 2;   // their counts
-                        const uint32_t nl = min(sl->cnt & 0x7fffffffu, uint32_t(Q_L));
-                        if (g.tid == 0) sh->flag[3] = 0u;
-                        g.sync();
+                        // (An f32 row streams long enough for the tail warps to build the table of its history meanwhile; a
+                        // bf16 row is through in half the time, so its few marked tokens are counted against the history
+                        // itself.)
+                        if (LAZY_TABLE) {
+                            // The marked entries of the log: logged raw from a word that holds a history token.  A history token
+                            // among them gets its penalty now (another logit of such a word stays as it is); its count comes from
+                            // the table of the row's history, which the other tail warps built while the row streamed.
+                            const uint32_t nl = min(sl->cnt & 0x7fffffffu, uint32_t(Q_L));
 #pragma unroll 1
-                        for (uint32_t i = g.tid; i < nl; i += Q_TT) {
-                            const unsigned long long c = log[i];
-                            if (c != 0ull && !(c & 0x80000000ull)) {
-                                const uint32_t at = atomicAdd(&sh->flag[3], 1u);
-                                if (at < uint32_t(SEL_BINS / 2)) mlist[at] = i, mcnt[at] = 0u;
+                            for (uint32_t i = g.tid; i < nl; i += Q_TT) {
+                                const unsigned long long c = log[i];
+                                if (c != 0ull && !(c & 0x80000000ull)) {
+                                    const uint32_t id = ~uint32_t(c) & 0x7fffffffu;
+                                    float x = float_of_key(cand_key(c));
+                                    const uint32_t times = pen_table_count(pslots, id);
+                                    if (times) x = penalised(x, times, cfg.rep, cfg.pres, cfg.freq);
+                                    log[i] = make_cand(key_of(x), id);
+                                }
                             }
-                        }
-                        g.sync();
-                        const uint32_t nm = sh->flag[3];
-                        if (nm > uint32_t(SEL_BINS / 2)) {
-                            if (g.tid == 0) atomicOr(&sl->cnt, 0x80000000u);  // (more than the scratch holds: the multi-pass kernel takes the row)
-                        } else if (nm > 0) {
-#pragma unroll 1
-                            for (uint32_t m = 0; m < nm; ++m) {
-                                const int32_t id = int32_t(~uint32_t(log[mlist[m]]) & 0x7fffffffu);
-                                uint32_t c = 0;
-#pragma unroll
-                                for (int u = 0; u < HB; ++u) c += hv[u] == id;
-                                c = __reduce_add_sync(0xffffffffu, c);
-                                if (lane == 0 && c) atomicAdd(&mcnt[m], c);
-                            }
+                        } else {
+                            // The marked entries of the log: logged raw from a word that holds a history token.  A history token
+                            // among them gets its penalty now (another logit of such a word stays as it is).  They are few, so
+                            // their counts come from a scan of the history, not from a table: every thread holds its share of the
+                            // history in registers and all of them count one marked token after the other.
+                            uint32_t* mlist = hist;                 // places in the log of the marked entries
+                            uint32_t* mcnt = hist + SEL_BINS / 2;   // their counts
+                            const uint32_t nl = min(sl->cnt & 0x7fffffffu, uint32_t(Q_L));
+                            if (g.tid == 0) sh->flag[3] = 0u;
                             g.sync();
 #pragma unroll 1
-                            for (uint32_t m = g.tid; m < nm; m += Q_TT) {
-                                const unsigned long long c = log[mlist[m]];
-                                const uint32_t id = ~uint32_t(c) & 0x7fffffffu;
-                                float x = float_of_key(cand_key(c));
-                                if (mcnt[m]) x = penalised(x, mcnt[m], cfg.rep, cfg.pres, cfg.freq);
-                                log[mlist[m]] = make_cand(key_of(x), id);
+                            for (uint32_t i = g.tid; i < nl; i += Q_TT) {
+                                const unsigned long long c = log[i];
+                                if (c != 0ull && !(c & 0x80000000ull)) {
+                                    const uint32_t at = atomicAdd(&sh->flag[3], 1u);
+                                    if (at < uint32_t(SEL_BINS / 2)) mlist[at] = i, mcnt[at] = 0u;
+                                }
+                            }
+                            g.sync();
+                            const uint32_t nm = sh->flag[3];
+                            if (nm > uint32_t(SEL_BINS / 2)) {
+                                if (g.tid == 0) atomicOr(&sl->cnt, 0x80000000u);  // (more than the scratch holds: the multi-pass kernel takes the row)
+                            } else if (nm > 0) {
+#pragma unroll 1
+                                for (uint32_t m = 0; m < nm; ++m) {
+                                    const int32_t id = int32_t(~uint32_t(log[mlist[m]]) & 0x7fffffffu);
+                                    uint32_t c = 0;
+#pragma unroll
+                                    for (int u = 0; u < HB; ++u) c += hv[u] == id;
+                                    c = __reduce_add_sync(0xffffffffu, c);
+                                    if (lane == 0 && c) atomicAdd(&mcnt[m], c);
+                                }
+                                g.sync();
+#pragma unroll 1
+                                for (uint32_t m = g.tid; m < nm; m += Q_TT) {
+                                    const unsigned long long c = log[mlist[m]];
+                                    const uint32_t id = ~uint32_t(c) & 0x7fffffffu;
+                                    float x = float_of_key(cand_key(c));
+                                    if (mcnt[m]) x = penalised(x, mcnt[m], cfg.rep, cfg.pres, cfg.freq);
+                                    log[mlist[m]] = make_cand(key_of(x), id);
+                                }
                             }
                         }
                     } else {
