@@ -244,6 +244,10 @@ __device__ void draft_tail(const SelectArgs& a, int row, const unsigned long lon
 // grid-strided over the rows (or over the entries of row_list); one row at a time per CTA
 template <typename T>
 __global__ void __launch_bounds__(GT, 1) select_generic_kernel(SelectArgs a, int cap_max, int pen_words) {
+    // A launch over the single-pass kernel's leftovers is made a programmatic dependent of it: its CTAs come up as that
+    // kernel's CTAs leave their SMs and wait here until all of it has completed and its writes are visible (with no such
+    // dependency the wait returns at once).
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     extern __shared__ __align__(16) uint8_t smem[];
     uint64_t* cand = reinterpret_cast<uint64_t*>(smem);
     uint32_t* hist = reinterpret_cast<uint32_t*>(smem + size_t(cap_max) * 8);
@@ -851,16 +855,24 @@ cudaError_t select_generic_launch(const SelectArgs& a, int dtype, int sm_count, 
     const bool pen = a.mode == MODE_SAMPLE && a.prm.hist != nullptr;
     const int pen_words = pen ? ((a.n + 31) / 32 + 3) & ~3 : 0;
     const size_t smem = size_t(cap) * 8 + GBINS * 4 + sizeof(GShared) + (pen ? size_t(pen_words) * 4 + kPenSlots * 4 : 0) + 48;
+    // (over a list of leftovers the launch may overlap the end of the kernel before it in the stream: see the kernel's top)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(unsigned(grid)), cfg.blockDim = dim3(GT), cfg.dynamicSmemBytes = smem, cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = a.row_list ? 1 : 0;
     cudaError_t e;
     if (dtype == 0) {
         e = cudaFuncSetAttribute(select_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        select_generic_kernel<float><<<grid, GT, smem, st>>>(a, cap, pen_words);
+        e = cudaLaunchKernelEx(&cfg, select_generic_kernel<float>, a, cap, pen_words);
     } else {
         e = cudaFuncSetAttribute(select_generic_kernel<uint16_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return e;
-        select_generic_kernel<uint16_t><<<grid, GT, smem, st>>>(a, cap, pen_words);
+        e = cudaLaunchKernelEx(&cfg, select_generic_kernel<uint16_t>, a, cap, pen_words);
     }
+    if (e != cudaSuccess) return e;
     return cudaGetLastError();
 }
 

@@ -427,6 +427,9 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
     uint64_t *boot_done = bars + 2 * Q_MAXSTAGES, *closed = boot_done + 2, *head_done = boot_done + 4;
 
     const int tid = threadIdx.x, warp = tid >> 5;
+    // (the kernel after this one in the stream, if it was launched as a programmatic dependent, may bring its CTAs up as
+    // this kernel's CTAs leave; it waits for this whole grid before it reads anything)
+    asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t n = uint32_t(a.n);
     const int n_rows = a.row_count ? min(*a.row_count, a.rows) : a.rows;
     const int my_rows = n_rows > int(blockIdx.x) ? (n_rows - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x) : 0;
@@ -471,8 +474,112 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
             if (ptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
         }
     }
+    // (the tail group's own indices, for the lambdas below; they mean nothing in the other warps)
+    const Group<Q_TT> t_g{tid - 32 - Q_ST, 1};
+    const Group<Q_PT> t_gp{t_g.tid - 32, 2};  // the tail warps but the first
+    const int t_lane = lane_id(), t_tw = t_g.tid >> 5;
+    const bool boot_warp = warp > Q_SW + 1 && warp <= Q_SW + Q_TW;  // tail warps 1 ..
+
+    // ---- a row's parameters come into the slot it will stream through (one warp, every t_lane fetching one of them)
+    auto fetch_params = [&](int p, int row) {
+        QSlot* sl = &sh->slot[p];
+        // t_lane: 0 inv_t, 1 top_k, 2 greedy, 3 top_p, 4 min_p, 5 u, 6 race_key, 7 hist_len, 8 rep, 9 pres, 10 freq
+        unsigned long long v = 0ull;
+        if (t_lane == 0) v = __float_as_uint(P.inv_t ? P.inv_t[row] : P.inv_t_scalar);
+        if (sample) {
+            if (t_lane == 1) v = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
+            if (t_lane == 2) v = (P.greedy && P.greedy[row]) ? 1u : 0u;
+            if (t_lane == 3) v = (unsigned long long)__double_as_longlong(P.top_p ? P.top_p[row] : 1.0);
+            if (t_lane == 4) v = (unsigned long long)__double_as_longlong(P.min_p ? P.min_p[row] : 0.0);
+            if (t_lane == 5) v = (unsigned long long)__double_as_longlong(P.u ? P.u[row] : 0.0);
+            if (t_lane == 6) v = P.race_key ? P.race_key[row] : 0ull;
+            if (t_lane == 7 && gbm_words) v = uint32_t(hist_len_of(P, row));
+            if (t_lane == 8) v = __float_as_uint(P.rep ? P.rep[row] : 1.f);
+            if (t_lane == 9) v = __float_as_uint(P.pres ? P.pres[row] : 0.f);
+            if (t_lane == 10) v = __float_as_uint(P.freq ? P.freq[row] : 0.f);
+        }
+        const float inv_t = __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, v, 0)));
+        const uint32_t top_k = uint32_t(__shfl_sync(0xffffffffu, v, 1));
+        const bool greedy = __shfl_sync(0xffffffffu, v, 2) != 0;
+        const unsigned long long top_p = __shfl_sync(0xffffffffu, v, 3), min_p = __shfl_sync(0xffffffffu, v, 4);
+        const unsigned long long u = __shfl_sync(0xffffffffu, v, 5), race_key = __shfl_sync(0xffffffffu, v, 6);
+        const int hist_len = int(uint32_t(__shfl_sync(0xffffffffu, v, 7)));
+        const float rep = sample ? __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, v, 8))) : 1.f;
+        const float pres = __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, v, 9)));
+        const float freq = __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, v, 10)));
+        if (t_lane == 0) {
+            QRow c;
+            c.row = row, c.top_k = top_k, c.inv_t = inv_t;
+            // candidates wanted: the row's own top_k when it fits, else the first level's
+            uint32_t K = sample ? (greedy ? 1u : ((top_k > 0 && top_k <= uint32_t(max_k)) ? top_k : uint32_t(min(a.level_k, max_k)))) : uint32_t(a.K);
+            c.K = K > n ? n : K;
+            c.rank0 = first_rank(c.K, n, uint32_t(Q_NS * Q_SQ * VE));
+            // Rows whose kept set is closed by their own top_k need no softmax normaliser: every probability the filter
+            // compares is a ratio inside the candidate set, so the row sum cancels.  When the caller does not ask for the
+            // row statistics either, the stream warps skip the exponentials and the tail normalises over the candidates.
+            const bool no_sum = sample && (greedy || (!a.out.stats && P.top_k && top_k >= 1 && top_k <= uint32_t(max_k) && top_k <= n));
+            const bool pen = sample && hist_len > 0 && (rep != 1.f || pres != 0.f || freq != 0.f);
+            const bool lazy = pen && no_sum && rep >= 1.f && pres >= 0.f && freq >= 0.f;
+            c.flags = (no_sum ? QF_NO_SUM : 0u) | (pen ? QF_PEN : 0u) | (greedy ? QF_GREEDY : 0u) | (lazy ? QF_LAZY : 0u);
+            c.rep = rep, c.pres = pres, c.freq = freq, c.hist_len = pen ? hist_len : 0;
+            c.top_p = __longlong_as_double((long long)top_p), c.min_p = __longlong_as_double((long long)min_p);
+            c.u = __longlong_as_double((long long)u), c.race_key = race_key;
+            sl->cfg = c;
+        }
+        __syncwarp();
+    };
+
+    // ---- a slot becomes a row's (the tail warps but the first; the slot's log and word map are zero): parameters and the
+    // map of the words that hold a history token (slot_prepare), then the stream warps are told (slot_release)
+    auto slot_prepare = [&](int p, int row) {
+        QSlot* sl = &sh->slot[p];
+        if (t_tw == 1) fetch_params(p, row);
+        t_gp.sync();
+        const int hl = sl->cfg.hist_len;  // (0 without penalties)
+        if (hl > 0) {
+            uint32_t* gbm = gbms + size_t(p) * gbm_words;
+            const int32_t* h = P.hist + size_t(row) * P.hist_stride;
+            constexpr int HB = (kMaxHist + Q_PT - 1) / Q_PT;
+            int32_t hv[HB];  // (all loads first: one trip to memory)
+#pragma unroll
+            for (int u = 0; u < HB; ++u) hv[u] = (u * Q_PT + t_gp.tid) < hl ? h[u * Q_PT + t_gp.tid] : -1;
+#pragma unroll
+            for (int u = 0; u < HB; ++u) {
+                const uint32_t t = uint32_t(hv[u]);
+                if (t < n) {
+                    const uint32_t wd = gbm_word_of(t / VE), bit = 1u << ((t / VE) & 31);
+                    if (!(ldv_u32(&gbm[wd]) & bit)) atomicOr(&gbm[wd], bit);
+                }
+            }
+            t_gp.sync();
+        }
+    };
+    auto slot_release = [&](int p) {
+        QSlot* sl = &sh->slot[p];
+        if (t_gp.tid == 0) {
+            sl->tau = 0ull;
+            sl->cnt = 0;
+            sl->side_cnt = 0;
+            sl->done_warps = 0;
+            for (int w = Q_SW; w < Q_RED; ++w) sl->red_m[w] = -INFINITY, sl->red_e[w] = -INFINITY, sl->red_s[w] = 0.0;
+            mbar_arrive(&boot_done[p]);
+        }
+    };
+    auto slot_boot = [&](int p, int row) {
+        slot_prepare(p, row);
+        slot_release(p);
+    };
+
     for (int i = tid; i < 2 * Q_L; i += Q_THREADS) logs[i] = 0ull;
     for (int i = tid; i < 2 * gbm_words; i += Q_THREADS) gbms[i] = 0u;
+    __syncthreads();  // (barriers, logs and word maps are ready)
+    // The first slot is prepared while the rows are listed, for the row the list will most likely start with (the CTA's
+    // first): the stream warps cannot start before it is.
+    bool early_boot = false;
+    if (sample && !a.row_list && my_rows > 0 && boot_warp) {
+        slot_prepare(0, int(blockIdx.x));
+        early_boot = true;
+    }
     // ---- the CTA's rows: rows blockIdx.x, + gridDim.x, ...; rows whose top_k is above this launch's limit are left to the
     // multi-pass kernel (marked here, not listed).  my_rows <= Q_MAXR <= Q_THREADS: one row per thread.
     {
@@ -609,89 +716,6 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
         const Group<Q_TT> g{tid - 32 - Q_ST, 1};
         const Group<Q_PT> gp{g.tid - 32, 2};  // the tail warps but the first
         const int lane = lane_id(), tw = g.tid >> 5;
-
-        // ---- a row's parameters come into the slot it will stream through (one warp, every lane fetching one of them)
-        auto fetch_params = [&](int p, int row) {
-            QSlot* sl = &sh->slot[p];
-            // lane: 0 inv_t, 1 top_k, 2 greedy, 3 top_p, 4 min_p, 5 u, 6 race_key, 7 hist_len, 8 rep, 9 pres, 10 freq
-            unsigned long long v = 0ull;
-            if (lane == 0) v = __float_as_uint(P.inv_t ? P.inv_t[row] : P.inv_t_scalar);
-            if (sample) {
-                if (lane == 1) v = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
-                if (lane == 2) v = (P.greedy && P.greedy[row]) ? 1u : 0u;
-                if (lane == 3) v = (unsigned long long)__double_as_longlong(P.top_p ? P.top_p[row] : 1.0);
-                if (lane == 4) v = (unsigned long long)__double_as_longlong(P.min_p ? P.min_p[row] : 0.0);
-                if (lane == 5) v = (unsigned long long)__double_as_longlong(P.u ? P.u[row] : 0.0);
-                if (lane == 6) v = P.race_key ? P.race_key[row] : 0ull;
-                if (lane == 7 && gbm_words) v = uint32_t(hist_len_of(P, row));
-                if (lane == 8) v = __float_as_uint(P.rep ? P.rep[row] : 1.f);
-                if (lane == 9) v = __float_as_uint(P.pres ? P.pres[row] : 0.f);
-                if (lane == 10) v = __float_as_uint(P.freq ? P.freq[row] : 0.f);
-            }
-            const float inv_t = __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, v, 0)));
-            const uint32_t top_k = uint32_t(__shfl_sync(0xffffffffu, v, 1));
-            const bool greedy = __shfl_sync(0xffffffffu, v, 2) != 0;
-            const unsigned long long top_p = __shfl_sync(0xffffffffu, v, 3), min_p = __shfl_sync(0xffffffffu, v, 4);
-            const unsigned long long u = __shfl_sync(0xffffffffu, v, 5), race_key = __shfl_sync(0xffffffffu, v, 6);
-            const int hist_len = int(uint32_t(__shfl_sync(0xffffffffu, v, 7)));
-            const float rep = sample ? __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, v, 8))) : 1.f;
-            const float pres = __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, v, 9)));
-            const float freq = __uint_as_float(uint32_t(__shfl_sync(0xffffffffu, v, 10)));
-            if (lane == 0) {
-                QRow c;
-                c.row = row, c.top_k = top_k, c.inv_t = inv_t;
-                // candidates wanted: the row's own top_k when it fits, else the first level's
-                uint32_t K = sample ? (greedy ? 1u : ((top_k > 0 && top_k <= uint32_t(max_k)) ? top_k : uint32_t(min(a.level_k, max_k)))) : uint32_t(a.K);
-                c.K = K > n ? n : K;
-                c.rank0 = first_rank(c.K, n, uint32_t(Q_NS * Q_SQ * VE));
-                // Rows whose kept set is closed by their own top_k need no softmax normaliser: every probability the filter
-                // compares is a ratio inside the candidate set, so the row sum cancels.  When the caller does not ask for the
-                // row statistics either, the stream warps skip the exponentials and the tail normalises over the candidates.
-                const bool no_sum = sample && (greedy || (!a.out.stats && P.top_k && top_k >= 1 && top_k <= uint32_t(max_k) && top_k <= n));
-                const bool pen = sample && hist_len > 0 && (rep != 1.f || pres != 0.f || freq != 0.f);
-                const bool lazy = pen && no_sum && rep >= 1.f && pres >= 0.f && freq >= 0.f;
-                c.flags = (no_sum ? QF_NO_SUM : 0u) | (pen ? QF_PEN : 0u) | (greedy ? QF_GREEDY : 0u) | (lazy ? QF_LAZY : 0u);
-                c.rep = rep, c.pres = pres, c.freq = freq, c.hist_len = pen ? hist_len : 0;
-                c.top_p = __longlong_as_double((long long)top_p), c.min_p = __longlong_as_double((long long)min_p);
-                c.u = __longlong_as_double((long long)u), c.race_key = race_key;
-                sl->cfg = c;
-            }
-            __syncwarp();
-        };
-
-        // ---- a slot becomes a row's (the tail warps but the first; the slot's log and word map are zero): parameters, the
-        // map of the words that hold a history token, then the stream warps are told
-        auto slot_boot = [&](int p, int row) {
-            QSlot* sl = &sh->slot[p];
-            if (tw == 1) fetch_params(p, row);
-            gp.sync();
-            const int hl = sl->cfg.hist_len;  // (0 without penalties)
-            if (hl > 0) {
-                uint32_t* gbm = gbms + size_t(p) * gbm_words;
-                const int32_t* h = P.hist + size_t(row) * P.hist_stride;
-                constexpr int HB = (kMaxHist + Q_PT - 1) / Q_PT;
-                int32_t hv[HB];  // (all loads first: one trip to memory)
-#pragma unroll
-                for (int u = 0; u < HB; ++u) hv[u] = (u * Q_PT + gp.tid) < hl ? h[u * Q_PT + gp.tid] : -1;
-#pragma unroll
-                for (int u = 0; u < HB; ++u) {
-                    const uint32_t t = uint32_t(hv[u]);
-                    if (t < n) {
-                        const uint32_t wd = gbm_word_of(t / VE), bit = 1u << ((t / VE) & 31);
-                        if (!(ldv_u32(&gbm[wd]) & bit)) atomicOr(&gbm[wd], bit);
-                    }
-                }
-                gp.sync();
-            }
-            if (gp.tid == 0) {
-                sl->tau = 0ull;
-                sl->cnt = 0;
-                sl->side_cnt = 0;
-                sl->done_warps = 0;
-                for (int w = Q_SW; w < Q_RED; ++w) sl->red_m[w] = -INFINITY, sl->red_e[w] = -INFINITY, sl->red_s[w] = 0.0;
-                mbar_arrive(&boot_done[p]);
-            }
-        };
 
         // ---- the table of the distinct history tokens of the row in slot p, with their counts, for when the row is through
         // (the tail warps but the first, while the row streams).  Equal tokens of one warp-wide step go in as one insert;
@@ -1137,7 +1161,14 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                 // ---- the freed slot goes to the row after the next (at the start: both slots go out), then the table of the
                 // row that streams now
                 if (ord < 0) {
-                    slot_boot(0, rlist[0]);
+                    if (!(early_boot && rlist[0] == int(blockIdx.x))) {
+                        if (early_boot) {  // (prepared for a row that is not listed: its marks go)
+                            for (int i = gp.tid; i < gbm_words; i += Q_PT) gbms[i] = 0u;
+                            gp.sync();
+                        }
+                        slot_prepare(0, rlist[0]);
+                    }
+                    slot_release(0);
                     if (n_list > 1) slot_boot(1, rlist[1]);
                 } else if (ord + 2 < n_list) {
                     slot_boot(p, rlist[ord + 2]);
