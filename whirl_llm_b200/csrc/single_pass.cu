@@ -10,7 +10,8 @@
 //   threshold keeper      (1 warp) for rows that keep at most 64 candidates: follows the log while it fills, holds the 64
 //                         largest keys seen in sorted order (bitonic merges of 32-key batches) and raises the threshold to
 //                         the K-th of them.
-//   tail group (8 warps)  when a row is through: its exact K best, ranked; top-k / top-p / min-p in f64, the draw and the
+//   tail group (8 warps)  when a row is through: its exact K best, ranked (by counting for K <= 64, by one histogram over
+//                         the keys' range for larger K: bucket_sort_top); top-k / top-p / min-p in f64, the draw and the
 //                         row's outputs (one warp for rows of up to 256 candidates, while the others fetch the parameters
 //                         of the row after the next and prepare its penalties; the whole group for larger rows).
 // The roles work on alternating row slots (two logs, two word maps), so the tail of one row overlaps the streaming of the
@@ -33,8 +34,9 @@
 // global memory: random 16-byte reads at that rate are more than the memory can serve while it streams.
 //   * A row that needs no normaliser and whose penalties can only lower a logit (the usual case): a word with a history
 //     token counts for no bound, and one of its logits is looked at only when it passes the threshold raw; it is then
-//     logged with a mark, and the tail group applies the penalty to the few marked entries (their counts come from a
-//     scan of the history) before it ranks the log.
+//     logged with a mark, and the tail group applies the penalty to the few marked entries before it ranks the log
+//     (their counts: an f32 row's from the table of its history, built while it streams; a bf16 row's, which streams in
+//     half the time, from a scan of the history).
 //   * Any other penalised row: the stream warps put the marked words aside (from their registers into a side buffer in
 //     global memory that stays in L2) and see -inf instead; the tail group, which has built the table of the row's
 //     distinct history tokens with their counts meanwhile, brings them in at the end of the row, history tokens with
