@@ -66,11 +66,22 @@ __global__ void __launch_bounds__(MT) merge_sample_kernel(const int32_t* ids, co
         uint32_t top_k = P.top_k ? uint32_t(max(P.top_k[row], 0)) : 0u;
         uint32_t K = greedy ? 1u : ((top_k > 0 && top_k <= uint32_t(Ks)) ? top_k : uint32_t(Ks));
         if (K > uint32_t(n_total)) K = uint32_t(n_total);
-        const unsigned long long kth = select_kth<MT>(g, all, total, K, hist, &sh->sel);
-        write_survivors<MT>(g, all, total, kth, hand, uint32_t(cap_hand), &sh->sel);
-        const uint32_t kept = min(sh->sel.wcnt, K);
+        // (ranked by one histogram where that applies - see bucket_sort_top -, else selected here and sorted by the tail)
+        static_assert(SEL_BINS >= SB_BINS + 2 * SB_X, "bins and side list fit the select scratch");
+        uint32_t kept;
+        bool sorted = false;
+        if (K <= 4u * MT && K <= uint32_t(cap_hand) &&
+            bucket_sort_top<MT>(g, all, total, K, 0ull, hist, hand, reinterpret_cast<unsigned long long*>(hist + SB_BINS), &sh->sel)) {
+            kept = sh->sel.wcnt;
+            sorted = true;
+        } else {
+            const unsigned long long kth = select_kth<MT>(g, all, total, K, hist, &sh->sel);
+            write_survivors<MT>(g, all, total, kth, hand, uint32_t(cap_hand), &sh->sel);
+            kept = min(sh->sel.wcnt, K);
+        }
         uint32_t cap = 1;
         while (cap < kept) cap <<= 1;
+        __syncthreads();
         for (uint32_t i = kept + g.tid; i < cap; i += MT) hand[i] = 0ull;
         __syncthreads();
         if (greedy) {
@@ -89,10 +100,19 @@ __global__ void __launch_bounds__(MT) merge_sample_kernel(const int32_t* ids, co
         TailIn in;
         in.inv_t = inv_t, in.top_k = top_k, in.top_p = P.top_p ? P.top_p[row] : 1.0, in.min_p = P.min_p ? P.min_p[row] : 0.0;
         in.u = P.u ? P.u[row] : 0.0, in.m = sh->m, in.sum = sh->sum, in.cnt = kept, in.cap = cap, in.V = uint32_t(n_total);
-        in.race = P.race_key != nullptr, in.race_key = P.race_key ? P.race_key[row] : 0, in.presorted = 0;
+        in.race = P.race_key != nullptr, in.race_key = P.race_key ? P.race_key[row] : 0, in.presorted = sorted;
         in.want_p = out.kept_p != nullptr && out.kept_cap > 0;
-        in.have_e = 0;
-        sample_tail<MT>(g, in, reinterpret_cast<uint64_t*>(hand), tp, tq, &sh->res);
+        in.have_e = 0, in.sum_of_e = 0;
+        bool decided = false;
+        if (!in.race && !in.want_p && kept > 0) {
+            // the division-free form first (sample_tail_quick); it leaves a row undecided when a sum meets a bound too closely
+            if (!sorted) sort_desc<MT>(g, reinterpret_cast<uint64_t*>(hand), cap), in.presorted = 1;
+            for (uint32_t i = g.tid; i < kept; i += MT) tq[i] = f64_exp(double(__fsub_rn(float_of_key(cand_key(hand[i])), in.m)) * double(inv_t));
+            __syncthreads();
+            in.have_e = 1;
+            decided = sample_tail_quick<MT>(g, in, reinterpret_cast<const uint64_t*>(hand), tp, tq, &sh->res);
+        }
+        if (!decided) sample_tail<MT>(g, in, reinterpret_cast<uint64_t*>(hand), tp, tq, &sh->res);
         const TailOut r = sh->res;
         if (g.tid == 0) {
             out.token[row] = int32_t(r.token);

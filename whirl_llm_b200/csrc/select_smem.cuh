@@ -172,7 +172,7 @@ __device__ __noinline__ void write_survivors(const Group<NT>& g, const unsigned 
 // themselves and the first of them take the places that are left.  Work per entry is a few instructions plus the size of
 // its bin, against the several hundred compare-exchanges per entry of a network.
 // buf: entries distinct; zero = empty; entries below `floor` count as empty too (the caller knows that at least
-// min(K, what is there) entries are at or above it).  K <= 4 * NT.  bins: SB_BINS words; out: K entries; xlist: SB_X
+// min(K, what is there) entries are at or above it).  K <= 4 * NT (sc->wsum holds one word per warp: NT <= 1024).  bins: SB_BINS words; out: K entries; xlist: SB_X
 // entries.  Returns false, with nothing usable in out, when one bin holds more than SB_X entries (many equal logits): the
 // caller then takes the selection-and-network path.  On success sc->wcnt = entries written, out[0..wcnt) descending.
 constexpr int SB_BINS = 1024;
@@ -181,11 +181,12 @@ template <int NT>
 __device__ __noinline__ bool bucket_sort_top(const Group<NT>& g, const unsigned long long* buf, uint32_t cnt, uint32_t K,
                                              unsigned long long floor, uint32_t* bins, unsigned long long* out,
                                              unsigned long long* xlist, SelScratch* sc) {
-    constexpr int PER = SB_BINS / NT;
-    static_assert(PER == 4 && SB_X <= NT, "four bins per thread, one side-list entry per thread");
+    constexpr int PER = SB_BINS / NT;  // bins per thread
+    static_assert(PER >= 1 && PER * NT == SB_BINS && SB_X <= NT, "whole bins per thread, one side-list entry per thread");
     // ---- the keys' range
     if (g.tid == 0) sc->klo = 0xffffffffu, sc->khi = 0u, sc->maxc = 0u, sc->bin = 0xffffffffu, sc->need = 0u, sc->eq = 0u, sc->wcnt = 0u;
-    reinterpret_cast<uint4*>(bins)[g.tid] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) bins[PER * g.tid + j] = 0u;
     g.sync();
     {
         uint32_t lo = 0xffffffffu, hi = 0u;
@@ -218,29 +219,29 @@ __device__ __noinline__ bool bucket_sort_top(const Group<NT>& g, const unsigned 
         if (c != 0ull && c >= floor) atomicAdd(&bins[bin_of(c)], 1u);
     }
     g.sync();
-    // ---- every bin's first place: an exclusive scan of the counts (thread t owns bins 4t .. 4t + 3)
+    // ---- every bin's first place: an exclusive scan of the counts (every thread owns PER consecutive bins)
     {
-        const uint4 v = reinterpret_cast<const uint4*>(bins)[g.tid];
-        const uint32_t c[4] = {v.x, v.y, v.z, v.w};
-        const uint32_t s = c[0] + c[1] + c[2] + c[3];
+        uint32_t c[PER], st[PER], s = 0;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) c[j] = bins[PER * g.tid + j], s += c[j];
         const uint32_t incl_w = warp_scan_incl(s);
         if ((g.tid & 31) == 31) sc->wsum[g.tid >> 5] = incl_w;
         g.sync();
         uint32_t before = 0;
 #pragma unroll 1
         for (int w = 0; w < (g.tid >> 5); ++w) before += sc->wsum[w];
-        uint32_t st[4];
-        st[0] = before + incl_w - s, st[1] = st[0] + c[0], st[2] = st[1] + c[1], st[3] = st[2] + c[2];
-        reinterpret_cast<uint4*>(bins)[g.tid] = make_uint4(st[0], st[1], st[2], st[3]);
+        uint32_t run = before + incl_w - s;
         uint32_t mc = 0;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < PER; ++j) {
+            st[j] = run, run += c[j];
+            bins[PER * g.tid + j] = st[j];
             if (st[j] < K) mc = max(mc, c[j]);
-            if (st[j] < K && st[j] + c[j] > K) sc->bin = uint32_t(4 * g.tid + j), sc->need = K - st[j], sc->eq = c[j];  // (at most one bin)
+            if (st[j] < K && st[j] + c[j] > K) sc->bin = uint32_t(PER * g.tid + j), sc->need = K - st[j], sc->eq = c[j];  // (at most one bin)
         }
         mc = __reduce_max_sync(0xffffffffu, mc);
         if ((g.tid & 31) == 0 && mc) atomicMax(&sc->maxc, mc);
-        if (g.tid == NT - 1) sc->lcnt = st[3] + c[3];  // entries in all
+        if (g.tid == NT - 1) sc->lcnt = run;  // entries in all
     }
     g.sync();
     if (sc->maxc > uint32_t(SB_X)) {

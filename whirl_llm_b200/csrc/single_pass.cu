@@ -1095,8 +1095,13 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     static_assert(size_t(kSinglePassHandK) * 8 + 2 * (size_t(kSinglePassHandK) + 2 * Q_TW) * 8 >= size_t(SB_BINS) * 4 + size_t(SB_X) * 8,
                                   "bins and side list fit the hand and its scratch");
                     uint32_t bk;
+                    bool short_of_k = false;
                     if (bucket_sort_top<Q_TT>(g, log, nlog, K, sl->tau, bins, list, reinterpret_cast<unsigned long long*>(bins + SB_BINS), &sh->sel)) {
                         bk = sh->sel.wcnt;
+                        // (A guessed threshold is checked against the number of logged entries, marked ones included; when
+                        // penalties then take so many of them below the threshold that fewer than K stay at or above it, the
+                        // K-th best may be a logit that was never logged: the row is done again.)
+                        short_of_k = bk < K && sl->tau != 0ull;
                     } else {
                         // (many equal logits: the K-th largest of the log, the entries at or above it, a sorting network)
                         const unsigned long long kth = nlog > K ? select_kth<Q_TT>(g, log, nlog, K, hist, &sh->sel) : 0ull;
@@ -1109,7 +1114,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                         sort_desc_x4<Q_TT>(g, reinterpret_cast<uint64_t*>(list));
                     }
                     double* bp = reinterpret_cast<double*>(log);
-                    finish_row(g, cfg, reinterpret_cast<uint64_t*>(list), bp, bp + bcap + 2 * Q_TW, bk, bcap, true, false, false, M, sum);
+                    finish_row(g, cfg, reinterpret_cast<uint64_t*>(list), bp, bp + bcap + 2 * Q_TW, bk, bcap, true, short_of_k, false, M, sum);
                     g.sync();
                     for (uint32_t i = g.tid; i < uint32_t(Q_L); i += Q_TT) log[i] = 0ull;
                 } else if (!overflow) {
@@ -1124,6 +1129,7 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     if (ranked) {
                         kept = sh->sel.wcnt;
                         presorted = true;
+                        if (kept < K && sl->tau != 0ull) overflow = true;  // (penalties left fewer than K at or above a guessed threshold)
                     } else {
                         write_survivors<Q_TT>(g, log, nlog, sl->tau, list, SEL_BINS / 2, &sh->sel);
                         const uint32_t m = sh->sel.wcnt;
@@ -1355,15 +1361,8 @@ __global__ void __launch_bounds__(Q_THREADS, 1) single_pass_kernel(SelectArgs a,
                     {
                         const bool small_k = sl->cfg.K <= uint32_t(Q_SMALL_K);
                         const int ntop = small_k ? 8 : Q_TOP;
-                        uint32_t kv = m1 == -INFINITY ? 0u : key_of(m1);  // (0: none, or taken already)
-                        uint32_t mine = 0u;
-#pragma unroll 1
-                        for (int t = 0; t < ntop; ++t) {
-                            const uint32_t top = __reduce_max_sync(0xffffffffu, kv);
-                            if (lane == t) mine = top;
-                            const uint32_t holders = __ballot_sync(0xffffffffu, kv == top && top != 0u);
-                            if (lane == __ffs(int(holders)) - 1) kv = 0u;
-                        }
+                        // (0: none; the lane maxima in descending order over the lanes: 15 shuffle steps)
+                        const uint32_t mine = warp_sort_desc(m1 == -INFINITY ? 0u : key_of(m1), lane);
                         // (a small-K row's 128 keys lie packed at the front: four per lane to read back instead of eight)
                         if (lane < ntop) sl->wtop[sw * ntop + lane] = mine;
                         __syncwarp();
