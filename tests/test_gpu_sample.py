@@ -210,6 +210,40 @@ def test_config4_bf16_mix(api, oracle):
     compare_rows(res, want, u=u)
 
 
+def test_large_kept_sets_with_ties_and_penalties(api, oracle):
+    """Rows keeping 65 .. 1024 candidates out of logits with few distinct values (many equal keys for the histogram that
+    ranks them), half of the rows penalised with a history that holds their best tokens, one row whose cumulative
+    probabilities meet top_p exactly (285 of 300 equal candidates against 0.95: the division-free cuts must hand it to
+    the dividing form).  Tokens and kept-set sizes only, so that the single-pass kernel takes its quick tail; f32 and
+    bf16."""
+    R, V, H = 48, 65536, 512
+    x = np.round(synth.normalish(611, (R, V), 2.0) * 8.0).astype(np.float32) / 8.0
+    x[5] = -50.0
+    x[5, 1000:1300] = 3.0
+    ks = np.array([65, 128, 256, 257, 300, 300, 512, 1000, 1024, 96, 640, 200], dtype=np.uint32)
+    u8 = synth.hash_u01(612, R * 2, 1).reshape(R, 2)
+    prm = dict(inv_t=np.full(R, 1.0, dtype=np.float32), top_k=np.tile(ks, R // len(ks)),
+               top_p=np.array([0.7, 0.9, 0.95, 1.0])[(u8[:, 0] * 4).astype(int)], min_p=np.where(u8[:, 1] < 0.5, 0.0, 0.01))
+    prm["top_p"][5] = 0.95
+    prm["min_p"][5] = 0.0
+    order = np.argsort(-x, axis=1, kind="stable")[:, :H].astype(np.int32)
+    hist = np.ascontiguousarray(order[:, ::-1])                       # the best 512 tokens of every row, some of them twice
+    hist[:, ::7] = hist[:, 3:4]
+    hist_len = np.where(np.arange(R) % 2 == 0, H, 0).astype(np.int32)  # (odd rows: no penalties)
+    f = lambda v: np.full(R, v, dtype=np.float32)
+    pen = dict(hist=hist, hist_len=hist_len, rep=f(1.2), pres=f(0.3), freq=f(0.1))
+    u = synth.hash_u01(613, R, 2)
+    open_pen = {k: (v.astype(np.uint32) if k == "hist_len" else v) for k, v in pen.items()}
+    want = oracle.sample_rows(x, kept_cap=1024, u=u, threads=4, **prm, **open_pen)
+    res = api.sample_rows(dev(x), row_params(prm, u=u, **pen), kept_cap=0, want_stats=False)
+    compare_rows(res, want, u=u)
+    assert int(want["n"][5]) in (285, 286)
+    bits = synth.to_bf16_bits(x)
+    want = oracle.sample_rows(bits, kept_cap=1024, u=u, threads=4, **prm, **open_pen)
+    res = api.sample_rows(bf16_tensor(bits), row_params(prm, u=u, **pen), kept_cap=0, want_stats=False)
+    compare_rows(res, want, u=u)
+
+
 def test_argument_errors(api):
     x = torch.zeros((2, 64), device="cuda")
     with pytest.raises(api.WhirlError) as e:
