@@ -387,8 +387,12 @@ def run_ours(args):
     d2h = rows * 4 + 32
 
     traffic = None
-    tp = os.path.join(ROOT, "profiles", "single_pass_kernel_traffic.txt")
-    if os.path.exists(tp) and args.config != 4 and args.dtype == "f32":
+    tp = None
+    if args.config != 4 and args.dtype == "f32":
+        tp = os.path.join(ROOT, "profiles", "single_pass_kernel_traffic.txt")
+    elif args.config == 4:
+        tp = os.path.join(ROOT, "profiles", "single_pass_kernel_bf16_mix_traffic.txt")
+    if tp and os.path.exists(tp):
         try:
             traffic = float(json.load(open(tp))["dram_bytes_per_row"]) * rows
         except Exception:
