@@ -190,7 +190,7 @@ __device__ __noinline__ bool bucket_sort_top(const Group<NT>& g, const unsigned 
     g.sync();
     {
         uint32_t lo = 0xffffffffu, hi = 0u;
-#pragma unroll 1
+#pragma unroll 4
         for (uint32_t i = g.tid; i < cnt; i += NT) {
             const unsigned long long c = buf[i];
             if (c != 0ull && c >= floor) {
@@ -213,7 +213,7 @@ __device__ __noinline__ bool bucket_sort_top(const Group<NT>& g, const unsigned 
         const uint32_t b = uint32_t(float(cand_key(c) - klo) * inv);
         return uint32_t(SB_BINS - 1) - min(b, uint32_t(SB_BINS - 1));
     };
-#pragma unroll 1
+#pragma unroll 4
     for (uint32_t i = g.tid; i < cnt; i += NT) {
         const unsigned long long c = buf[i];
         if (c != 0ull && c >= floor) atomicAdd(&bins[bin_of(c)], 1u);
@@ -252,7 +252,7 @@ __device__ __noinline__ bool bucket_sort_top(const Group<NT>& g, const unsigned 
     const uint32_t kept = total < K ? total : K;
     const uint32_t x_start = xbin != 0xffffffffu ? K - x_need : kept;  // places filled by whole bins
     // ---- scatter: a bin's counter now hands out its places (and ends as the bin's end); bins past place K drop out
-#pragma unroll 1
+#pragma unroll 2
     for (uint32_t i = g.tid; i < cnt; i += NT) {
         const unsigned long long c = buf[i];
         if (c != 0ull && c >= floor) {
@@ -278,7 +278,7 @@ __device__ __noinline__ bool bucket_sort_top(const Group<NT>& g, const unsigned 
             const uint32_t b = bin_of(mine);
             const uint32_t e = bins[b], s0 = b ? bins[b - 1] : 0u;  // (the bins before a kept one are whole bins: their counters hold their ends)
             uint32_t rank = 0;
-#pragma unroll 1
+#pragma unroll 4
             for (uint32_t j = s0; j < e; ++j) rank += out[j] > mine;
             item[r] = mine, np[r] = s0 + rank;
         }
@@ -288,7 +288,7 @@ __device__ __noinline__ bool bucket_sort_top(const Group<NT>& g, const unsigned 
     if (uint32_t(g.tid) < x_cnt) {
         xi = xlist[g.tid];
         uint32_t rank = 0;
-#pragma unroll 1
+#pragma unroll 4
         for (uint32_t j = 0; j < x_cnt; ++j) rank += xlist[j] > xi;
         if (rank < x_need) xp = x_start + rank;
     }
